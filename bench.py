@@ -1,0 +1,349 @@
+#!/usr/bin/env python
+"""Benchmark of the NativeBit packed-inference hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch M] [--impl ours|reference]
+
+Workload (one "step"): the FFN decode matvecs of the 2.2B configuration — per layer gate and
+up (6912 x 2560) and down (2560 x 6912), 3-bit indices, block 128, fp16 K=8 codebooks, bf16
+activations at batch M — over 26 layers of distinct synthetic weights (691 MB, larger than L2, so
+every launch streams its weights from HBM).  The 78 launches of a step are replayed from one
+CUDA graph.  Metric: achieved HBM GB/s = algorithmic bytes / time.
+
+With N > 1 ranks (torchrun) the same stack is tensor-parallel: gate/up split by rows, down by
+input blocks, one NCCL all-reduce of the down output per layer; `value` is the whole job's
+algorithmic bytes over the slowest rank's time ("strong" scaling: total work fixed).
+
+`--impl reference` times the reference's CPU PyTorch path (restated in oracle/nb_oracle.py) on
+the host cores over a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, FFN, LAYERS, BITS, BLOCK = 2560, 6912, 26, 3, 128
+METRIC, UNIT = "dequant_matvec_hbm_gbs", "GB/s"
+
+
+def alg_bytes(m, n, k, bits=BITS):
+    return n * k * bits // 8 + (n * k // BLOCK) * (1 << bits) * 2 + m * k * 2 + m * n * 2
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [c.strip() for c in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ----------------------------------------------------------------------------- CPU arms
+def cpu_sample(batch: int, repeats: int):
+    """One layer's gate, up and down matvec through the reference's CPU PyTorch path."""
+    import numpy as np
+    import torch
+    from oracle import nb_oracle as o
+    torch.set_num_threads(os.cpu_count() or 1)
+    mats = []
+    for j, (n, k) in enumerate(((FFN, HIDDEN), (FFN, HIDDEN), (HIDDEN, FFN))):
+        packed, cb, _ = o.make_packed_linear(n, k, BITS, seed=j)
+        x = o.make_activation(batch, k, seed=j)
+        mats.append((torch.from_numpy(x), torch.from_numpy(packed), torch.from_numpy(cb.astype(np.float32)), n, k))
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for x, p, c, n, k in mats:
+            o.torch_reference_forward(x, p, c, n, k)
+        times.append(time.perf_counter() - t0)
+    nbytes = sum(alg_bytes(batch, n, k) for *_, n, k in mats)
+    return nbytes, times, torch.get_num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    nbytes, _, cores = cpu_sample(args.batch, max(1, args.warmup))
+    nbytes, times, cores = cpu_sample(args.batch, args.steps)
+    t = sum(times) / len(times)
+    val = nbytes / t / 1e9
+    sample = "per step: gate+up+down matvec of ONE layer (1/26 of the GPU arm's step), unpack+gather+matmul each call"
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"2.2B FFN decode matvecs 3-bit, batch {args.batch} (configs[1])", "sample": sample},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import nativebit_b200 as nbt
+    from nativebit_b200 import ops, synthetic, tp
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    m = args.batch
+
+    # ---- weights: this rank's shard of every layer
+    ch0, ch_n = tp.ffn_shard_plan(FFN, world, rank)            # hidden channels of this rank
+    shapes = [("gate", ch_n, HIDDEN), ("up", ch_n, HIDDEN), ("down", HIDDEN, ch_n)]
+    layers = []
+    for l in range(LAYERS):
+        mods = {}
+        for j, (name, n, k) in enumerate(shapes):
+            p, c = synthetic.synthetic_packed(n, k, BITS, seed=1000 * rank + 10 * l + j, device=dev)
+            mods[name] = nbt.PackedLinear(p, c, n, k, bits=BITS)
+        layers.append(mods)
+    x = synthetic.synthetic_activation(m, HIDDEN, 1, dev)
+    h = synthetic.synthetic_activation(m, ch_n, 2, dev)
+    y_gate = torch.empty(LAYERS, m, ch_n, dtype=torch.bfloat16, device=dev)
+    y_up = torch.empty_like(y_gate)
+    y_down = torch.empty(LAYERS, m, HIDDEN, dtype=torch.bfloat16, device=dev)
+    ws = ops.workspace(dev, 8 << 20)
+
+    def launch_all(xin, hin):
+        for l, mods in enumerate(layers):
+            for name, src, dst in (("gate", xin, y_gate[l]), ("up", xin, y_up[l]), ("down", hin, y_down[l])):
+                lin = mods[name]
+                ops.gemv(src, lin.packed_indices, lin.codebook, BITS, BLOCK, lin.out_features, lin.in_features,
+                         out=dst, ws=ws)
+            if world > 1:
+                dist.all_reduce(y_down[l])
+
+    stream = torch.cuda.Stream(device=dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        launch_all(x, h)                     # warm the kernels / NCCL before capture
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            launch_all(x, h)
+    launches_per_step = 3 * LAYERS
+    step_bytes_rank = sum(alg_bytes(m, n, k) for _, n, k in shapes) * LAYERS
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t)
+        return ms
+
+    # ---- device-resident throughput (the `value`)
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            graph.replay()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(graph.replay, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    total_bytes = torch.tensor([float(step_bytes_rank)], device=dev)
+    if world > 1:
+        dist.all_reduce(total_bytes)
+    step_bytes = float(total_bytes)
+    ms_per_step = ms / args.steps
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the module API with host buffers
+    x_host = x.cpu().pin_memory()
+    h_host = h.cpu().pin_memory()
+    out_host = torch.empty(LAYERS, m, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    xd, hd = torch.empty_like(x), torch.empty_like(h)
+
+    def e2e_step():
+        xd.copy_(x_host, non_blocking=True)
+        hd.copy_(h_host, non_blocking=True)
+        for l, mods in enumerate(layers):
+            g = mods["gate"](xd)
+            u = mods["up"](xd)
+            y_down[l] = mods["down"](hd)
+            if world > 1:
+                dist.all_reduce(y_down[l])
+            del g, u
+        out_host.copy_(y_down, non_blocking=True)
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(1, args.warmup // 2)):
+            e2e_step()
+    e2e_steps = max(1, min(args.steps, 20))
+    ms_e2e = timed(e2e_step, e2e_steps) / e2e_steps
+    e2e_value = step_bytes / (ms_e2e * 1e-3) / 1e9
+    h2d = x_host.numel() * 2 + h_host.numel() * 2
+    d2h = out_host.numel() * 2
+
+    # ---- roofline of the dominant kernel: the 6912 x 2560 matvec, timed alone (1 GPU only)
+    roofline, extra = None, {}
+    if world == 1:
+        peak, peak_src = measured_peak()
+        gate_up = [(mods[nm]) for mods in layers for nm in ("gate", "up")]          # 52 copies, 461 MB > L2
+        yb = torch.empty(m, FFN, dtype=torch.bfloat16, device=dev)
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(g2, stream=stream):
+                for lin in gate_up:
+                    ops.gemv(x, lin.packed_indices, lin.codebook, BITS, BLOCK, FFN, HIDDEN, out=yb, ws=ws)
+            for _ in range(3):
+                g2.replay()
+        reps = max(5, args.steps)
+        ms_k = timed(g2.replay, reps) / (reps * len(gate_up))
+        kb = alg_bytes(m, FFN, HIDDEN)
+        ach = kb / (ms_k * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                    "kernel": "nb::gemv_kernel<3,%d> 6912x2560 batch %d" % (2 if m > 8 else 1, m),
+                    "us_per_launch": ms_k * 1e3, "algorithmic_bytes": kb, "peak_source": peak_src,
+                    "frac_of_nominal_8TBs": ach / 8000.0}
+        # other batch sizes of configs[1], same kernel, for the record
+        for mb in (1, 4, 16):
+            xb = synthetic.synthetic_activation(mb, HIDDEN, 3, dev)
+            hb = synthetic.synthetic_activation(mb, FFN, 4, dev)
+            ob1 = torch.empty(mb, FFN, dtype=torch.bfloat16, device=dev)
+            ob2 = torch.empty(mb, HIDDEN, dtype=torch.bfloat16, device=dev)
+            for tag, key, src, dst, n, k in (("6912x2560", "gate", xb, ob1, FFN, HIDDEN), ("2560x6912", "down", hb, ob2, HIDDEN, FFN)):
+                gk = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(stream):
+                    lins = [mods[key] for mods in layers] * 2
+                    for lin in lins[:2]:
+                        ops.gemv(src, lin.packed_indices, lin.codebook, BITS, BLOCK, n, k, out=dst, ws=ws)
+                    stream.synchronize()
+                    with torch.cuda.graph(gk, stream=stream):
+                        for lin in lins:
+                            ops.gemv(src, lin.packed_indices, lin.codebook, BITS, BLOCK, n, k, out=dst, ws=ws)
+                    for _ in range(3):
+                        gk.replay()
+                t = timed(gk.replay, 5) / (5 * len(lins))
+                extra[f"{tag}_b{mb}"] = {"us": round(t * 1e3, 3), "GB/s": round(alg_bytes(mb, n, k) / (t * 1e-3) / 1e9, 1)}
+
+    # ---- CPU baseline on the host cores (rank 0, N=1 only)
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        nbytes, times, cores = cpu_sample(m, 4)
+        t = min(times[1:]) if len(times) > 1 else times[0]
+        cpu = {"value": nbytes / t / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": "gate+up+down matvec of one layer (3 of the step's 78 matvecs), best of 3 after 1 warm-up; "
+                         "reference CPU PyTorch path: unpack + gather + matmul per call"}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16xf16->f32",
+                "data": "synthetic",
+                "config": {"workload": f"2.2B FFN decode matvecs (gate/up 6912x2560, down 2560x6912) x {LAYERS} layers, "
+                                       f"3-bit block-128 K=8 fp16 codebooks, bf16 activations batch {m} (configs[1])",
+                           "l2": "weights of one step total 691 MB (> 126 MB L2); each launch reads weights not touched "
+                                 "for 77 launches",
+                           "parallelism": f"tp{world}" if world > 1 else "single",
+                           "launch": "one CUDA graph of 78 kernels per step"},
+                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": ms_e2e, "api": "PackedLinear.forward per matvec, pinned host in/out"},
+                "gpu_launches": launches_per_step * args.steps,
+                "clocks": clocks}
+        if roofline is not None:
+            line["roofline"] = roofline
+            line["per_shape"] = extra
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

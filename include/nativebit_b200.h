@@ -1,0 +1,89 @@
+/* nativebit_b200 — C ABI of the B200 (sm_100a) packed-inference kernels.
+ *
+ * This is the boundary a NativeBit maintainer binds instead of the reference's JIT-built
+ * kernels.  Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (cudaStream_t passed as void*; NULL = the legacy default stream), launches asynchronously on
+ * that stream, never allocates or frees device memory, never synchronises, and returns an
+ * nb_status (0 = ok).  There is no CPU fallback: on a machine without a usable sm_100 device
+ * the compute entry points return NB_ERR_ARCH or NB_ERR_LAUNCH.
+ *
+ * Packed layout: exactly the bytes nativebit/pack.py writes (pack_3bit :21-41, pack_nbits
+ * :97-116, pack_4bit :75-82), weights flat in row-major (out_features, in_features) order, one
+ * codebook of 2^bits entries per `block_size` consecutive weights.
+ */
+#ifndef NATIVEBIT_B200_H_
+#define NATIVEBIT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  NB_OK = 0,
+  NB_ERR_ARG = 1,       /* null pointer, bad enum, non-positive size */
+  NB_ERR_ALIGN = 2,     /* a pointer is not aligned as the kernel needs (16 bytes) */
+  NB_ERR_SHAPE = 3,     /* shape not supported by the fast kernels (see each function) */
+  NB_ERR_ARCH = 4,      /* current device is not compute capability 10.x */
+  NB_ERR_LAUNCH = 5,    /* the CUDA runtime refused the launch; see nb_last_cuda_error() */
+  NB_ERR_TIMEOUT = 6,   /* a bounded device-side wait ran out (tensor-parallel paths only) */
+  NB_ERR_WORKSPACE = 7  /* workspace missing or smaller than nb_*_workspace_bytes() */
+} nb_status;
+
+typedef enum { NB_F32 = 0, NB_F16 = 1, NB_BF16 = 2 } nb_dtype;
+
+/* Library version (major*10000 + minor*100 + patch) and a printable name for a status. */
+int nb_version(void);
+const char* nb_status_string(int status);
+/* Text of the last CUDA runtime error seen by this thread inside the library ("" if none). */
+const char* nb_last_cuda_error(void);
+
+/* CPU-only self check of the in-register unpack tables (no GPU needed): returns NB_OK when the
+ * selector scheme used by the kernels reproduces every index position for random packed
+ * blocks at 2 and 3 bits.  No counterpart in the reference; used by the CPU test-suite. */
+int nb_selftest_tables(void);
+
+/* ---- bit-unpack:  replaces nativebit/pack.py:44-68 (unpack_3bit), :85-90 (unpack_4bit),
+ * :119-138 (unpack_nbits, bits=2) and the per-forward unpack of
+ * inference/triton_kernel.py:262-269 / inference/generate_torch.py:165-173.
+ * packed: ceil(count*bits/8) bytes for bits 2/4, 3*ceil(count/8) bytes for bits 3 (device).
+ * idx_out: count bytes (device), one index per byte.  bits in {2,3,4}. */
+int nb_unpack(const uint8_t* packed, int bits, int64_t count, uint8_t* idx_out, void* stream);
+
+/* ---- bit-pack on device: replaces inference/triton_kernel.py:199-220 (pack_indices_to_3bit)
+ * and nativebit/pack.py:21-41 / :75-82 / :97-116 for bits in {2,3,4}.  `packed_out` must hold
+ * the byte counts given for nb_unpack; padding indices are zero as in the reference. */
+int nb_pack(const uint8_t* idx, int bits, int64_t count, uint8_t* packed_out, void* stream);
+
+/* ---- dequantise a whole weight: replaces nativebit/pack.py:145-169 (reconstruct_weight) and the
+ * gather of nativebit/inference.py:44-45.  W[r][c] = codebook[b][idx[b][t]] with
+ * b*block_size+t = r*n_cols+c; bit-exact (the values are the codebook entries converted to
+ * w_dtype; fp16 -> fp32 and fp16 -> fp16 are exact, -> bf16 rounds to nearest even).
+ * codebook: (ceil(n_rows*n_cols/block_size), 2^bits) of cb_dtype (NB_F16 or NB_F32).
+ * Any block_size >= 1 and bits in {2,3,4}; total weights need not fill the last block. */
+int nb_dequant(const uint8_t* packed, const void* codebook, int cb_dtype, int bits, int block_size,
+               int64_t n_rows, int64_t n_cols, void* w_out, int w_dtype, void* stream);
+
+/* ---- fused decode GEMV / skinny GEMM (M = 1..16 activation rows):
+ * y[m][n] = sum_k W[n][k] * x[m][k].  Replaces inference/cuda_kernel.py:38-104
+ * (dequant_matvec_3bit_kernel + wrapper), inference/triton_kernel.py:144-196 (Triton 3-bit kernel)
+ * and, for 2 <= M <= 16, the unpack+gather+matmul of inference/triton_kernel.py:258-275.
+ * x: (M, K) row-major of x_dtype; y: (M, N) row-major of y_dtype; fp32 accumulation.
+ * bits in {2,3}; block_size 128 (or 64 for tensor-parallel sub-blocks); K % block_size == 0.
+ * packed and codebook must be 16-byte aligned.  Weights enter the tensor-core contraction as
+ * exact fp16 values (an fp32 codebook is rounded to fp16); activations are converted to fp16
+ * (exact for bf16 inputs of magnitude 6.1e-5..65504; larger magnitudes are clamped).
+ * workspace: device scratch of at least nb_gemv_workspace_bytes() bytes, zero-filled once
+ * before its first use and then owned by calls on one stream at a time (the kernel leaves it
+ * zeroed).  It carries the partial sums of split-K launches. */
+size_t nb_gemv_workspace_bytes(int M, int N, int K, int bits, int block_size);
+int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype,
+            int bits, int block_size, int N, int K, void* y, int y_dtype, void* workspace,
+            size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NATIVEBIT_B200_H_ */

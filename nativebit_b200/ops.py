@@ -1,0 +1,112 @@
+"""Thin torch-tensor wrappers over the C ABI (device pointers in, device tensors out).
+
+torch is used for device memory and streams only; all arithmetic happens in the kernels of
+libnativebit_b200.so.  Every function requires CUDA tensors and raises otherwise.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import NB_BF16, NB_F16, NB_F32
+
+_DTYPE = {torch.float32: NB_F32, torch.float16: NB_F16, torch.bfloat16: NB_BF16}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("nativebit_b200 runs on CUDA tensors only (no CPU fallback); got a "
+                               f"{t.device} tensor")
+        if not t.is_contiguous():
+            raise RuntimeError("nativebit_b200 needs contiguous tensors")
+
+
+def packed_nbytes(count: int, bits: int) -> int:
+    """Bytes the reference's packers emit for `count` indices (nativebit/pack.py:21-41, 75-82, 97-116)."""
+    return 3 * ((count + 7) // 8) if bits == 3 else (count * bits + 7) // 8
+
+
+def unpack(packed: torch.Tensor, bits: int, count: int) -> torch.Tensor:
+    """Packed bytes -> uint8 indices, one per byte (nativebit/pack.py:44-68, 85-90, 119-138)."""
+    _need_cuda(packed)
+    if packed.dtype != torch.uint8:
+        raise RuntimeError("packed indices must be uint8")
+    if packed.numel() < packed_nbytes(count, bits):
+        raise RuntimeError(f"packed buffer too small: {packed.numel()} bytes for {count} {bits}-bit indices")
+    out = torch.empty(count, dtype=torch.uint8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        _lib.check(_lib.lib().nb_unpack(packed.data_ptr(), bits, count, out.data_ptr(), _stream()), "nb_unpack")
+    return out
+
+
+def pack(indices: torch.Tensor, bits: int) -> torch.Tensor:
+    """uint8 indices -> packed bytes in the reference layout (nativebit/pack.py:21-41, 75-82, 97-116;
+    inference/triton_kernel.py:199-220)."""
+    _need_cuda(indices)
+    if indices.dtype != torch.uint8:
+        raise RuntimeError("indices must be uint8")
+    flat = indices.reshape(-1)
+    out = torch.empty(packed_nbytes(flat.numel(), bits), dtype=torch.uint8, device=indices.device)
+    with torch.cuda.device(indices.device):
+        _lib.check(_lib.lib().nb_pack(flat.data_ptr(), bits, flat.numel(), out.data_ptr(), _stream()), "nb_pack")
+    return out
+
+
+def dequant(packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size: int, shape,
+            dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Whole-weight gather W[r, c] = codebook[b, idx[b, t]] (nativebit/pack.py:145-169)."""
+    _need_cuda(packed, codebook)
+    n_rows, n_cols = int(shape[0]), int(shape[1])
+    total = n_rows * n_cols
+    n_blocks = (total + block_size - 1) // block_size
+    if codebook.dtype not in (torch.float16, torch.float32) or codebook.numel() != n_blocks * (1 << bits):
+        raise RuntimeError(f"codebook must be fp16/fp32 with {n_blocks} x {1 << bits} entries")
+    if packed.dtype != torch.uint8 or packed.numel() < packed_nbytes(n_blocks * block_size, bits):
+        raise RuntimeError("packed buffer has the wrong dtype or is too small")
+    out = torch.empty(n_rows, n_cols, dtype=dtype, device=packed.device)
+    with torch.cuda.device(packed.device):
+        _lib.check(_lib.lib().nb_dequant(packed.data_ptr(), codebook.data_ptr(), _DTYPE[codebook.dtype], bits, block_size,
+                                         n_rows, n_cols, out.data_ptr(), _DTYPE[dtype], _stream()), "nb_dequant")
+    return out
+
+
+_workspaces: dict = {}
+
+
+def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch for split-K launches, one per (device, stream), grown on demand."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def gemv(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size: int,
+         n: int, k: int, out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
+         ws: torch.Tensor | None = None) -> torch.Tensor:
+    """y (M, n) = x (M, k) @ W.T for M <= 16, fused unpack + codebook gather + contraction."""
+    _need_cuda(x, packed, codebook)
+    if x.dim() != 2 or x.shape[1] != k:
+        raise RuntimeError(f"x must be (M, {k}); got {tuple(x.shape)}")
+    m = x.shape[0]
+    if x.dtype not in _DTYPE:
+        raise RuntimeError(f"unsupported activation dtype {x.dtype}")
+    out_dtype = out_dtype or x.dtype
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=x.device)
+    l = _lib.lib()
+    with torch.cuda.device(x.device):
+        need = l.nb_gemv_workspace_bytes(m, n, k, bits, block_size)
+        if ws is None:
+            ws = workspace(x.device, need)
+        _lib.check(l.nb_gemv(x.data_ptr(), _DTYPE[x.dtype], m, packed.data_ptr(), codebook.data_ptr(),
+                             _DTYPE[codebook.dtype], bits, block_size, n, k, out.data_ptr(), _DTYPE[out.dtype],
+                             ws.data_ptr(), ws.numel(), _stream()), "nb_gemv")
+    return out

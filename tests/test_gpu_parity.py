@@ -1,0 +1,250 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and the reference's golden
+vectors.  Integer/byte/gather work must be bit-exact; GEMV outputs are held to
+max|y - y_ref| / max|y_ref| <= 2e-3 (the tolerance the task states; fp32 accumulation), and in
+practice land near 1e-6 for fp32 outputs."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nb_oracle as o
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+@pytest.fixture(scope="module")
+def dev(built_lib):
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device")
+    return torch.device("cuda:0")
+
+
+def _cu(a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+# ------------------------------------------------------------------ unpack / pack
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("n", [1, 3, 7, 8, 10, 13, 31, 32, 33, 100, 1001, 4096, 100_000])
+def test_unpack_pack_roundtrip_bit_exact(dev, bits, n):
+    from nativebit_b200 import ops
+    idx = np.random.default_rng(n * 10 + bits).integers(0, 1 << bits, n, dtype=np.uint8)
+    packed_ref = o.pack_nbits(idx, bits)
+    packed = ops.pack(_cu(idx, dev), bits)
+    assert np.array_equal(packed.cpu().numpy(), packed_ref)
+    out = ops.unpack(_cu(packed_ref, dev), bits, n)
+    assert np.array_equal(out.cpu().numpy(), idx)
+
+
+def test_unpack_golden_vectors(dev, golden):
+    from nativebit_b200 import ops, pack as nbpack
+    for name in golden["p3_names"]:
+        idx, packed = golden[f"p3_idx_{name}"], golden[f"p3_packed_{name}"]
+        assert np.array_equal(ops.unpack(_cu(packed, dev), 3, idx.size).cpu().numpy(), idx), name
+        assert np.array_equal(nbpack.pack_3bit(_cu(idx, dev)).cpu().numpy(), packed), name
+    assert np.array_equal(nbpack.pack_nbits(_cu(golden["p2_idx"], dev), 2).cpu().numpy(), golden["p2_packed"])
+    assert np.array_equal(nbpack.unpack_nbits(_cu(golden["p2_packed"], dev), 203, 2).cpu().numpy(), golden["p2_idx"])
+    assert np.array_equal(nbpack.pack_4bit(_cu(golden["p4_idx"], dev)).cpu().numpy(), golden["p4_packed"])
+    assert np.array_equal(nbpack.unpack_4bit(_cu(golden["p4_packed"], dev), 101).cpu().numpy(), golden["p4_idx"])
+
+
+def test_unpack_all_zero_all_seven_and_unaligned(dev):
+    from nativebit_b200 import ops
+    for fill in (0, 7):
+        idx = np.full(4099, fill, np.uint8)
+        packed = _cu(o.pack_3bit(idx), dev)
+        assert np.array_equal(ops.unpack(packed, 3, idx.size).cpu().numpy(), idx)
+    # a packed buffer that starts at an odd byte offset takes the byte-wise path
+    idx = np.random.default_rng(5).integers(0, 8, 4099, dtype=np.uint8)
+    buf = torch.zeros(o.pack_3bit(idx).size + 3, dtype=torch.uint8, device=dev)
+    buf[3:] = _cu(o.pack_3bit(idx), dev)
+    assert np.array_equal(ops.unpack(buf[3:], 3, idx.size).cpu().numpy(), idx)
+
+
+# ------------------------------------------------------------------ dequant (bit-exact)
+@pytest.mark.parametrize("bits", [3, 2])
+def test_dequant_golden_bit_exact(dev, golden, bits):
+    from nativebit_b200 import ops
+    tag = f"lin{bits}"
+    n, k = (int(v) for v in golden[f"{tag}_shape"])
+    packed, cb16 = _cu(golden[f"{tag}_packed"], dev), _cu(golden[f"{tag}_cb16"], dev)
+    w32 = ops.dequant(packed, cb16, bits, 128, (n, k), torch.float32)
+    assert np.array_equal(w32.cpu().numpy(), golden[f"{tag}_w"])
+    w16 = ops.dequant(packed, cb16, bits, 128, (n, k), torch.float16)
+    assert np.array_equal(w16.float().cpu().numpy(), golden[f"{tag}_w"])
+    wb = ops.dequant(packed, cb16, bits, 128, (n, k), torch.bfloat16)
+    assert torch.equal(wb.cpu(), torch.from_numpy(golden[f"{tag}_w"]).bfloat16())
+    # fp32 codebook (the .nbpack.npz flavour)
+    w32b = ops.dequant(packed, cb16.float(), bits, 128, (n, k), torch.float32)
+    assert np.array_equal(w32b.cpu().numpy(), golden[f"{tag}_w"])
+
+
+def test_reconstruct_weight_small_blocks_and_padding(dev, golden):
+    from nativebit_b200 import pack as nbpack
+    w = nbpack.reconstruct_weight(_cu(golden["rw_small_idx"], dev), _cu(golden["rw_small_cb"], dev), (4, 8), 8, 32)
+    assert np.array_equal(w.cpu().numpy(), golden["rw_small_w"])
+    wp = nbpack.reconstruct_weight(_cu(golden["rw_pad_idx"], dev), _cu(golden["rw_pad_cb"], dev), (2, 5), 8, 10)
+    assert wp.shape == (2, 5) and np.array_equal(wp.cpu().numpy(), golden["rw_pad_w"])
+
+
+@pytest.mark.parametrize("bits,n,k", [(3, 2560, 2560), (3, 6912, 2560), (2, 2560, 6912)])
+def test_dequant_full_size_bit_exact(dev, bits, n, k):
+    from nativebit_b200 import ops
+    packed, cb, _ = o.make_packed_linear(n, k, bits, seed=1)
+    ref = o.dequant_packed(packed, cb, n, k, bits)
+    w = ops.dequant(_cu(packed, dev), _cu(cb, dev), bits, 128, (n, k), torch.float16)
+    assert np.array_equal(w.cpu().numpy().view(np.uint16), ref.view(np.uint16))
+
+
+# ------------------------------------------------------------------ GEMV
+def _gemv_case(dev, bits, n, k, m, seed, x_dtype=torch.bfloat16, y_dtype=torch.float32, cb_dtype=torch.float16):
+    from nativebit_b200 import ops
+    packed, cb, _ = o.make_packed_linear(n, k, bits, seed)
+    x = o.make_activation(m, k, seed)
+    ref = o.packed_linear_forward(x, packed, cb.astype(np.float32), n, k, bits, acc_dtype=np.float64)
+    y = ops.gemv(_cu(x, dev).to(x_dtype), _cu(packed, dev), _cu(cb, dev).to(cb_dtype), bits, 128, n, k, out_dtype=y_dtype)
+    torch.cuda.synchronize()
+    return y.float().cpu().numpy().astype(np.float64), ref
+
+
+@pytest.mark.parametrize("bits", [3, 2])
+@pytest.mark.parametrize("n,k", [(16, 128), (48, 384), (40, 256), (17, 512), (256, 2560), (1000, 640), (64, 6912)])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 8, 9, 16])
+def test_gemv_small_shapes(dev, bits, n, k, m):
+    y, ref = _gemv_case(dev, bits, n, k, m, seed=n + k + m)
+    assert np.abs(y - ref).max() <= 2e-5 * np.abs(ref).max()      # fp32 output: far inside TOL
+    assert np.abs(y - ref).max() <= TOL * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("n,k", [(2560, 2560), (6912, 2560), (2560, 6912), (7680, 2560)])
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_gemv_model_shapes(dev, n, k, m):
+    y, ref = _gemv_case(dev, 3, n, k, m, seed=3)
+    assert np.abs(y - ref).max() <= 2e-5 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("n,k,m", [(6912, 2560, 1), (2560, 6912, 16)])
+def test_gemv_2bit_model_shapes(dev, n, k, m):
+    y, ref = _gemv_case(dev, 2, n, k, m, seed=4)
+    assert np.abs(y - ref).max() <= 2e-5 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("x_dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("y_dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_gemv_dtypes(dev, x_dtype, y_dtype):
+    y, ref = _gemv_case(dev, 3, 320, 2560, 5, seed=9, x_dtype=x_dtype, y_dtype=y_dtype)
+    # 16-bit outputs add at most half an ulp of the output type (2^-9 for bf16)
+    tol = {torch.float32: 2e-5, torch.float16: 6e-4, torch.bfloat16: TOL}[y_dtype]
+    assert np.abs(y - ref).max() <= tol * np.abs(ref).max()
+
+
+def test_gemv_fp32_codebook(dev):
+    y, ref = _gemv_case(dev, 3, 320, 2560, 2, seed=11, cb_dtype=torch.float32)
+    assert np.abs(y - ref).max() <= 2e-5 * np.abs(ref).max()
+
+
+def test_gemv_golden_reference_output(dev, golden):
+    """Against y computed by the reference's own NativeBitInferenceLinear / PackedLinear on CPU."""
+    from nativebit_b200 import ops
+    for bits in (3, 2):
+        tag = f"lin{bits}"
+        n, k = (int(v) for v in golden[f"{tag}_shape"])
+        y = ops.gemv(_cu(golden[f"{tag}_x"], dev).bfloat16(), _cu(golden[f"{tag}_packed"], dev),
+                     _cu(golden[f"{tag}_cb16"], dev), bits, 128, n, k, out_dtype=torch.float32)
+        ref = golden[f"{tag}_y"]
+        assert np.abs(y.cpu().numpy() - ref).max() <= 2e-5 * np.abs(ref).max()
+
+
+def test_gemv_is_deterministic_and_leaves_workspace_clean(dev):
+    from nativebit_b200 import ops
+    packed, cb, _ = o.make_packed_linear(2560, 6912, 3, 21)
+    x = _cu(o.make_activation(16, 6912, 21), dev).bfloat16()
+    p, c = _cu(packed, dev), _cu(cb, dev)
+    ws = torch.zeros(8 << 20, dtype=torch.uint8, device=dev)
+    y0 = ops.gemv(x, p, c, 3, 128, 2560, 6912, out_dtype=torch.float32, ws=ws).clone()
+    for _ in range(5):
+        y = ops.gemv(x, p, c, 3, 128, 2560, 6912, out_dtype=torch.float32, ws=ws)
+        assert torch.equal(y, y0)
+    torch.cuda.synchronize()
+    n_counter_bytes = 4096
+    assert int(ws[:n_counter_bytes].view(torch.int32).abs().sum()) == 0   # ticket counters were reset
+
+
+def test_gemv_linearity_full_size(dev):
+    """Size-independent property at the benchmark's full size: W(a*x1 + x2) = a*W x1 + W x2."""
+    from nativebit_b200 import ops
+    n, k = 6912, 2560
+    packed, cb, _ = o.make_packed_linear(n, k, 3, 33)
+    p, c = _cu(packed, dev), _cu(cb, dev)
+    x1 = _cu(o.make_activation(1, k, 1), dev)
+    x2 = _cu(o.make_activation(1, k, 2), dev)
+    y1 = ops.gemv(x1, p, c, 3, 128, n, k)
+    y2 = ops.gemv(x2, p, c, 3, 128, n, k)
+    # 0.5*x1 + x2 is not exactly representable in fp16 in general, so compare in fp64 with the
+    # fp16 rounding of the combined input taken into account: 2^-11 relative per element
+    xs = (0.5 * x1 + x2).half().float()
+    ys = ops.gemv(xs, p, c, 3, 128, n, k)
+    w = ops.dequant(p, c, 3, 128, (n, k), torch.float32).double()
+    ref = (xs.double() @ w.T)
+    assert (ys.double() - ref).abs().max() <= 2e-5 * ref.abs().max()
+    assert (0.5 * y1 + y2 - ys).abs().max() <= 2e-3 * ys.abs().max()
+
+
+def test_gemv_zero_and_extreme_activations(dev):
+    from nativebit_b200 import ops
+    n, k = 64, 256
+    packed, cb, _ = o.make_packed_linear(n, k, 3, 2)
+    p, c = _cu(packed, dev), _cu(cb, dev)
+    y = ops.gemv(torch.zeros(1, k, device=dev, dtype=torch.bfloat16), p, c, 3, 128, n, k, out_dtype=torch.float32)
+    assert float(y.abs().max()) == 0.0
+    x = torch.full((1, k), 1e6, device=dev, dtype=torch.float32)   # beyond fp16 range: clamped, stays finite
+    y = ops.gemv(x, p, c, 3, 128, n, k)
+    assert torch.isfinite(y).all()
+
+
+# ------------------------------------------------------------------ module API
+def test_packed_linear_module_matches_reference_outputs(dev, golden):
+    import nativebit_b200 as nbt
+    n, k = (int(v) for v in golden["lin3_shape"])
+    idx = golden["lin3_idx"].reshape(-1, 128)
+    lin = nbt.PackedLinear.from_packed(idx, golden["lin3_cb16"].astype(np.float32), (n, k), device=dev)
+    assert np.array_equal(lin.packed_indices.cpu().numpy(), golden["lin3_packed"])
+    x = _cu(golden["lin3_x"], dev)
+    ref = golden["lin3_y"]
+    y = lin(x)                                     # (3, k) fp32
+    assert y.dtype == torch.float32 and y.shape == (3, n)
+    assert np.abs(y.cpu().numpy() - ref).max() <= 2e-5 * np.abs(ref).max()
+    y1 = lin(x[0])                                 # 1-D input, like the reference's M == 1 path
+    assert y1.shape == (n,)
+    assert np.abs(y1.cpu().numpy() - ref[0]).max() <= 2e-5 * np.abs(ref).max()
+    y3 = lin(x.reshape(3, 1, k))                   # arbitrary leading dims
+    assert y3.shape == (3, 1, n)
+    yv = nbt.dequant_matvec_3bit(x[1], lin.packed_indices, lin.codebook, n, k)
+    assert yv.dtype == torch.float32 and np.abs(yv.cpu().numpy() - ref[1]).max() <= 2e-5 * np.abs(ref).max()
+    yu = nbt.dequant_matvec(x[2], _cu(idx, dev), lin.codebook, n, k)
+    assert np.abs(yu.cpu().numpy() - ref[2]).max() <= 2e-5 * np.abs(ref).max()
+    yc = nbt.dequant_matvec_3bit_cuda(x[0], lin.packed_indices, lin.codebook, n, k)
+    assert torch.equal(yc, nbt.dequant_matvec_3bit(x[0], lin.packed_indices, lin.codebook, n, k))
+    assert torch.equal(nbt.pack_indices_to_3bit(_cu(idx, dev)), lin.packed_indices)
+    assert np.array_equal(lin.dequantized_weight().cpu().numpy(), golden["lin3_w"])
+
+
+@pytest.mark.parametrize("m", [17, 40, 64, 65, 200])
+def test_packed_linear_many_rows(dev, m):
+    import nativebit_b200 as nbt
+    n, k = 320, 640
+    packed, cb, _ = o.make_packed_linear(n, k, 3, 5)
+    lin = nbt.PackedLinear(_cu(packed, dev), _cu(cb, dev), n, k)
+    x = o.make_activation(m, k, 6)
+    ref = o.packed_linear_forward(x, packed, cb.astype(np.float32), n, k, 3, acc_dtype=np.float64)
+    y = lin(_cu(x, dev)).double().cpu().numpy()
+    assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max()
+
+
+def test_inference_linear_mirror(dev, golden):
+    from nativebit_b200.inference import NativeBitInferenceLinear
+    n, k = (int(v) for v in golden["lin3_shape"])
+    idx = _cu(golden["lin3_idx"].reshape(-1, 128).astype(np.int64), dev)
+    lin = NativeBitInferenceLinear(k, n, _cu(golden["lin3_cb16"].astype(np.float32), dev), idx, 128)
+    y = lin(_cu(golden["lin3_x"], dev)).cpu().numpy()
+    assert np.abs(y - golden["lin3_y"]).max() <= 2e-5 * np.abs(golden["lin3_y"]).max()
