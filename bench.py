@@ -118,6 +118,15 @@ def cpu_sample(batch: int, repeats: int):
     return nbytes, times, torch.get_num_threads()
 
 
+def workload_config(m, world):
+    return {"workload": f"2.2B FFN decode matvecs (gate/up 6912x2560, down 2560x6912) x {LAYERS} layers, "
+                        f"3-bit block-128 K=8 fp16 codebooks, bf16 activations batch {m} (configs[1])",
+            "l2": "weights of one step total 691 MB (> 126 MB L2); each launch reads weights not touched "
+                  "for 77 launches",
+            "parallelism": f"tp{world}" if world > 1 else "single",
+            "launch": "one CUDA graph of 78 kernels per step"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -130,7 +139,7 @@ def run_reference(args):
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"2.2B FFN decode matvecs 3-bit, batch {args.batch} (configs[1])", "sample": sample},
+            "config": workload_config(args.batch, args.gpus),
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -309,12 +318,7 @@ def run_ours(args):
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16xf16->f32",
                 "data": "synthetic",
-                "config": {"workload": f"2.2B FFN decode matvecs (gate/up 6912x2560, down 2560x6912) x {LAYERS} layers, "
-                                       f"3-bit block-128 K=8 fp16 codebooks, bf16 activations batch {m} (configs[1])",
-                           "l2": "weights of one step total 691 MB (> 126 MB L2); each launch reads weights not touched "
-                                 "for 77 launches",
-                           "parallelism": f"tp{world}" if world > 1 else "single",
-                           "launch": "one CUDA graph of 78 kernels per step"},
+                "config": workload_config(m, world),
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": ms_e2e, "api": "PackedLinear.forward per matvec, pinned host in/out"},
                 "gpu_launches": launches_per_step * args.steps,
@@ -329,6 +333,29 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_kernel_only(args):
+    """A few plain launches of one shape over weight copies larger than L2 — the small case
+    that profiler captures are taken on (python bench.py --kernel-only N K M)."""
+    import torch
+    from nativebit_b200 import ops, synthetic
+    n, k, m = args.kernel_only
+    dev = torch.device("cuda", 0)
+    copies = max(2, int(160e6 // (n * k * 3 // 8)) + 1)
+    ws = [synthetic.synthetic_packed(n, k, BITS, seed=i, device=dev) for i in range(copies)]
+    x = synthetic.synthetic_activation(m, k, 0, dev)
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    wsp = ops.workspace(dev, 8 << 20)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for rep in range(3):
+        e0.record()
+        for p, c in ws:
+            ops.gemv(x, p, c, BITS, BLOCK, n, k, out=y, ws=wsp)
+        e1.record()
+        torch.cuda.synchronize()
+    print(json.dumps({"kernel_only": [n, k, m], "copies": copies, "us_per_launch_stream": e0.elapsed_time(e1) * 1e3 / copies}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -337,9 +364,13 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--kernel-only", type=int, nargs=3, metavar=("N", "K", "M"), default=None,
+                    help="launch one GEMV shape a few times and exit (profiling case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    if args.kernel_only:
+        run_kernel_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -75,13 +75,24 @@ int nb_dequant(const uint8_t* packed, const void* codebook, int cb_dtype, int bi
  * packed and codebook must be 16-byte aligned.  Weights enter the tensor-core contraction as
  * exact fp16 values (an fp32 codebook is rounded to fp16); activations are converted to fp16
  * (exact for bf16 inputs of magnitude 6.1e-5..65504; larger magnitudes are clamped).
- * workspace: device scratch of at least nb_gemv_workspace_bytes() bytes, zero-filled once
- * before its first use and then owned by calls on one stream at a time (the kernel leaves it
- * zeroed).  It carries the partial sums of split-K launches. */
+ * workspace: device scratch of at least nb_gemv_workspace_bytes() bytes whose first 16 KB were
+ * zero-filled once before its first use; it is then owned by calls on one stream at a time.
+ * The first 16 KB hold ticket counters, which every launch leaves zeroed, and a status word
+ * (int index 4095) that a launch sets to NB_ERR_TIMEOUT if a bounded wait ran out; the rest
+ * carries the partial sums of split-K launches.  One workspace may serve launches of
+ * different shapes.  Weights and codebooks are requested before the kernel waits for earlier
+ * work of the stream (programmatic dependent launch), so they must not be produced by an
+ * nb_gemv launch directly before it; x and y are touched only after that wait. */
 size_t nb_gemv_workspace_bytes(int M, int N, int K, int bits, int block_size);
 int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype,
             int bits, int block_size, int N, int K, void* y, int y_dtype, void* workspace,
             size_t workspace_bytes, void* stream);
+
+/* Launch geometry nb_gemv will use for a shape on the current device (no launch; works without
+ * a GPU, assuming 148 SMs): out6 = {grid.x, grid.y (k partitions), threads per CTA, dynamic
+ * shared memory bytes, row tiles per CTA, k-groups per partition}.  No counterpart in the
+ * reference; used for reporting and tests. */
+int nb_gemv_plan(int M, int N, int K, int bits, int block_size, int cb_dtype, int* out6);
 
 #ifdef __cplusplus
 }

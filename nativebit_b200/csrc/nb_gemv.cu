@@ -1,24 +1,33 @@
 // Fused decode GEMV / skinny GEMM for NativeBit packed linears on sm_100a (M = 1..16 rows).
 //
-// Work decomposition.  A "unit" is 16 output rows x 4 codebook blocks (512 input columns):
-// lane (g, t) of a warp (g = lane/4, t = lane%4) owns the block of row g and the block of row
-// g+8 at k-block 4*kgroup+t.  It loads the packed indices of its two blocks with 16-byte
-// loads (48 bytes per 3-bit block) plus the two 16-byte codebooks, turns them into nibble
-// selectors with a handful of mask operations (nb_common.cuh), and gathers four fp16 weights
-// per byte-permute pair from a low-byte / high-byte plane of the codebook held in registers.
-// Four weights of row g and four of row g+8 form the A fragment of one m16n8k16 tensor-core
-// MMA whose B fragment is the matching four activations of up to 8 batch rows, so the
-// multiply-accumulate (fp16 x fp16 products are exact, fp32 accumulation) costs one
-// instruction per 256 weights and all remaining issue slots go to the unpack.  Because the
-// weights are consumed in "slot" order rather than position order, the activation tile is
-// staged into shared memory once per CTA in the same slot order (and as fp16).
+// Data movement.  A CTA owns `tr` row tiles (16 output rows each) x one contiguous range of
+// k-blocks.  In its first cycles every thread issues 16-byte asynchronous copies (cp.async,
+// L2 -> shared, no register or L1 staging) for the CTA's index rows and codebook rows,
+// consecutive threads on consecutive chunks of a row, and posts one deferred arrival per row
+// tile on that tile's mbarrier: every byte the CTA will read from HBM is requested before
+// anything else happens, and a warp can start on a row tile as soon as that tile has landed.
+// (Bulk cp.async.bulk copies were measured first: one copy per 960-byte row costs the issuing
+// thread about 30 ns per copy, 3 us per CTA, so the per-row form is not used.)  The kernel is
+// launched with programmatic stream serialization: after requesting its weights it lets the
+// next launch of the stream begin (which requests its own weights) and only then waits for
+// the previous kernel, whose output may be this kernel's x.
 //
-// A CTA owns `tr` row tiles x one contiguous range of k-groups; its warps take units round
-// robin and add their 16 x 8 partial tiles into a shared fp32 accumulator.  When the k range
-// is split over several CTAs (grid.y > 1) each CTA writes its partial tile to scratch, takes a
-// ticket, and the CTA that takes the last ticket adds the partials in fixed order, writes y and
-// resets the ticket counter, so results are deterministic and the scratch needs no per-launch
-// clearing.
+// Compute.  A "unit" is 16 rows x 4 k-blocks: lane (g, t) (g = lane/4, t = lane%4) owns the
+// 128-weight block of row g and of row g+8 at k-block 4*kgroup+t.  It reads its two 48-byte
+// index blocks and 16-byte codebooks from shared memory (conflict free: row stride is 64 mod
+// 128 bytes), turns the packed 3-bit fields into nibble selectors with a few mask operations
+// (nb_common.cuh) and gathers four fp16 weights per pair of byte-permutes from a low-byte and a
+// high-byte plane of the codebook held in registers.  Four weights of row g and four of row
+// g+8 form the A fragment of one m16n8k16 tensor-core MMA whose B fragment is the matching
+// four activations of up to 8 batch rows: fp16 x fp16 products are exact, accumulation is
+// fp32, and the multiply-accumulate costs one instruction per 256 weights, leaving the issue
+// slots to the unpack.  Weights are consumed in "slot" order rather than position order, so
+// the activation tile is staged into shared memory once per CTA in that order, as fp16.
+//
+// Reduction.  Warps add their 16 x 8 partial tiles into a shared fp32 accumulator.  When the k
+// range is split over several CTAs (grid.y > 1) each CTA writes its partial tile to scratch and
+// takes a ticket; the CTA that takes the last ticket adds the partials in fixed order, writes
+// y and resets the counter: deterministic, and the scratch needs no clearing between launches.
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
@@ -28,19 +37,41 @@
 #include "nb_common.cuh"
 #include "nb_host.h"
 
+// Optional phase tracing for tuning builds (-DNB_TRACE): block 0..63 thread 0 stores %globaltimer.
+#ifdef NB_TRACE
+__device__ unsigned long long nb_trace_buf[64 * 8];
+#define NB_TRACE_MARK(i)                                                                  \
+  do {                                                                                    \
+    if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < 64) {                         \
+      unsigned long long t_;                                                              \
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_));                               \
+      nb_trace_buf[blockIdx.x * 8 + (i)] = t_;                                            \
+    }                                                                                     \
+  } while (0)
+extern "C" int nb_trace_read(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, nb_trace_buf, sizeof(nb_trace_buf));
+}
+#else
+#define NB_TRACE_MARK(i) do {} while (0)
+#endif
+
 namespace nb {
 
-constexpr int kGemvWarps = 16;
-constexpr int kGemvThreads = kGemvWarps * 32;
-constexpr int kXBlockBytes = 32 * 8 * 8 + 32;  // one k-block of one 8-row activation tile, +32 B skew
-constexpr int kMaxSmem = 200 * 1024;
+constexpr int kMaxWarps = 16;
+constexpr int kMaxTr = 16;                      // row tiles per CTA (one mbarrier each)
+constexpr int kXBlockBytes = 32 * 8 * 8 + 32;   // one k-block of one 8-row activation tile, +32 B skew
+constexpr int kMaxSmem = 110 * 1024;            // two CTAs (of consecutive launches) fit one SM
+constexpr int kCounterInts = 4096;              // workspace head: ticket counters + status word
+constexpr uint32_t kSpinLimit = 1u << 22;       // bounded wait on the copy barriers (about 0.1 s)
 
 struct GemvPlan {
   int tr;           // row tiles (of 16 rows) per CTA
   int parts;        // k partitions = grid.y
   int kg_per_part;  // k-groups (of 4 blocks) per partition
   int grid_x;
+  int warps;
   size_t smem;
+  int w_stride, c_stride;
 };
 
 struct GemvParams {
@@ -50,9 +81,13 @@ struct GemvParams {
   void* y;
   float* scratch;
   int* counters;
+  int* status;      // set to NB_ERR_TIMEOUT if a copy barrier never completes (may be null)
   int M, N, bpr, row_tiles, kgroups;
   int tr, kg_per_part;
   int x_dtype, y_dtype, cb_dtype;
+  int x_vec;        // x is 16-byte aligned: staged with 16-byte loads
+  int w_stride, c_stride;  // shared-memory row strides (bytes) of the index and codebook tiles
+  int cb_bulk;      // codebook rows satisfy the 16-byte rules of bulk copies (else plain loads)
 };
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
@@ -61,11 +96,31 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
   return d;
 }
 
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Non-blocking probe of a barrier phase.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// 16-byte asynchronous copy global -> shared (L2 only), and a deferred barrier arrival that fires
+// once all earlier asynchronous copies of the executing thread have completed.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -88,52 +143,45 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// Loads one block's codebook and splits it into byte planes.  Invalid blocks get a zero table.
+// One block's codebook (in shared memory) -> byte planes for lookup4; zero table if !valid.
 template <int BITS>
-__device__ __forceinline__ void load_table(const void* codebook, int cb_dtype, size_t block, bool valid, uint32_t (&T)[4]) {
-  uint32_t e0 = 0, e1 = 0, e2 = 0, e3 = 0;  // 2^BITS fp16 entries, two per register
+__device__ __forceinline__ void make_table(const uint8_t* cb, int cb_dtype, bool valid, uint32_t (&T)[4]) {
+  uint32_t e[4] = {0, 0, 0, 0};  // 2^BITS fp16 entries, two per register
   if (valid) {
     if (BITS == 3) {
       if (cb_dtype == NB_F16) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(codebook) + block);
-        e0 = v.x; e1 = v.y; e2 = v.z; e3 = v.w;
+        const uint4 v = *reinterpret_cast<const uint4*>(cb);
+        e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
       } else {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(codebook) + 2 * block);
-        const float4 b = __ldg(reinterpret_cast<const float4*>(codebook) + 2 * block + 1);
-        e0 = pack_half2(a.x, a.y); e1 = pack_half2(a.z, a.w); e2 = pack_half2(b.x, b.y); e3 = pack_half2(b.z, b.w);
+        const float4 a = *reinterpret_cast<const float4*>(cb);
+        const float4 b = *reinterpret_cast<const float4*>(cb + 16);
+        e[0] = pack_half2(a.x, a.y); e[1] = pack_half2(a.z, a.w); e[2] = pack_half2(b.x, b.y); e[3] = pack_half2(b.z, b.w);
       }
     } else {
       if (cb_dtype == NB_F16) {
-        const uint2 v = __ldg(reinterpret_cast<const uint2*>(codebook) + block);
-        e0 = v.x; e1 = v.y;
+        const uint2 v = *reinterpret_cast<const uint2*>(cb);
+        e[0] = v.x; e[1] = v.y;
       } else {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(codebook) + block);
-        e0 = pack_half2(a.x, a.y); e1 = pack_half2(a.z, a.w);
+        const float4 a = *reinterpret_cast<const float4*>(cb);
+        e[0] = pack_half2(a.x, a.y); e[1] = pack_half2(a.z, a.w);
       }
     }
   }
   if (BITS == 3) {
-    T[0] = prmt(e0, e1, 0x6420); T[1] = prmt(e2, e3, 0x6420);
-    T[2] = prmt(e0, e1, 0x7531); T[3] = prmt(e2, e3, 0x7531);
+    T[0] = prmt(e[0], e[1], 0x6420); T[1] = prmt(e[2], e[3], 0x6420);
+    T[2] = prmt(e[0], e[1], 0x7531); T[3] = prmt(e[2], e[3], 0x7531);
   } else {  // 4 entries: selector values 0..3 pick from the first operand
-    T[0] = prmt(e0, e1, 0x6420); T[2] = prmt(e0, e1, 0x7531);
+    T[0] = prmt(e[0], e[1], 0x6420); T[2] = prmt(e[0], e[1], 0x7531);
     T[1] = T[2]; T[3] = T[0];
   }
 }
 
 template <int BITS>
-__device__ __forceinline__ void load_block(const uint8_t* packed, size_t block, bool valid, uint32_t (&w)[Fmt<BITS>::kWords]) {
-  constexpr int kVec = Fmt<BITS>::kWords / 4;
-  if (valid) {
-    const uint4* p = reinterpret_cast<const uint4*>(packed + block * (size_t)(16 * BITS));
+__device__ __forceinline__ void read_block(const uint8_t* blk, uint32_t (&w)[Fmt<BITS>::kWords]) {
 #pragma unroll
-    for (int i = 0; i < kVec; ++i) {
-      const uint4 v = ldg_stream(p + i);
-      w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < Fmt<BITS>::kWords; ++i) w[i] = 0;
+  for (int i = 0; i < Fmt<BITS>::kWords / 4; ++i) {
+    const uint4 v = *reinterpret_cast<const uint4*>(blk + 16 * i);
+    w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
   }
 }
 
@@ -143,17 +191,45 @@ __device__ __forceinline__ float load_x(const void* x, int dtype, size_t i) {
   return reinterpret_cast<const float*>(x)[i];
 }
 
+// Eight consecutive activations (index i is a multiple of 8, pointer 16-byte aligned) as floats.
+__device__ __forceinline__ void load_x8(const void* x, int dtype, size_t i, float (&v)[8]) {
+  if (dtype == NB_F32) {
+    const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + i);
+    const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + i + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    const uint4 r = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + i);
+    const uint32_t u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (dtype == NB_BF16) {
+        v[2 * j] = __uint_as_float(u[j] << 16);
+        v[2 * j + 1] = __uint_as_float(u[j] & 0xFFFF0000u);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[j]));
+        v[2 * j] = f.x; v[2 * j + 1] = f.y;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void store_y(void* y, int dtype, size_t i, float v) {
   if (dtype == NB_BF16) reinterpret_cast<__nv_bfloat16*>(y)[i] = __float2bfloat16_rn(v);
   else if (dtype == NB_F16) reinterpret_cast<__half*>(y)[i] = __float2half_rn(v);
   else reinterpret_cast<float*>(y)[i] = v;
 }
 
+__device__ __forceinline__ __half to_half_clamped(float v) {
+  return __float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f));
+}
+
 template <int BITS, int NT>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p) {
-  extern __shared__ __align__(16) uint8_t smem[];
+__global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kWords = Fmt<BITS>::kWords;
+  constexpr int kBlkBytes = 16 * BITS;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int n_warps = blockDim.x >> 5, n_threads = blockDim.x;
 
   const int rt0 = blockIdx.x * p.tr;
   const int rt_n = min(p.tr, p.row_tiles - rt0);
@@ -163,57 +239,148 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   const int kb_n = min(kg_n * 4, p.bpr - kb0);
   const int n_units = rt_n * kg_n;
   const int K = p.bpr * kBlock;
+  const int cb_blk = (p.cb_dtype == NB_F16 ? 2 : 4) << BITS;  // codebook bytes per block
 
-  // shared memory carve-up
-  const int x_tile_bytes = kg_n * 4 * kXBlockBytes;
-  __half* xs = reinterpret_cast<__half*>(smem);
-  float* acc = reinterpret_cast<float*>(smem + NT * x_tile_bytes);
+  // shared memory: index rows | codebook rows | activation tile(s) | fp32 accumulator | slot offsets
+  const int x_tile_bytes = p.kg_per_part * 4 * kXBlockBytes;
+  uint8_t* w_s = smem;
+  uint8_t* c_s = w_s + p.tr * 16 * p.w_stride;
+  uint8_t* x_s = c_s + p.tr * 16 * p.c_stride;
+  float* acc = reinterpret_cast<float*>(x_s + NT * x_tile_bytes);
   const int acc_n = p.tr * 16 * NT * 8;
-  uint8_t* inv = reinterpret_cast<uint8_t*>(acc + acc_n);
+  uint16_t* dst_off = reinterpret_cast<uint16_t*>(acc + acc_n);  // position -> offset (halves) inside a k-block tile
+  __shared__ __align__(8) uint64_t bars[kMaxTr];
   __shared__ int s_last;
 
-  // First unit's loads go out before the activation tile is staged.
-  uint32_t wa[kWords], wb[kWords], TA[4], TB[4];
-  auto issue = [&](int u) {
-    const int rtl = u / kg_n, kgl = u - rtl * kg_n;
-    const int row_a = 16 * (rt0 + rtl) + g, row_b = row_a + 8;
-    const int kb = kb0 + 4 * kgl + t;
-    const bool vk = kb < p.bpr;
-    const bool va = vk && row_a < p.N, vb = vk && row_b < p.N;
-    const size_t ba = (size_t)row_a * p.bpr + kb, bb = (size_t)row_b * p.bpr + kb;
-    load_block<BITS>(p.packed, ba, va, wa);
-    load_block<BITS>(p.packed, bb, vb, wb);
-    load_table<BITS>(p.codebook, p.cb_dtype, ba, va, TA);
-    load_table<BITS>(p.codebook, p.cb_dtype, bb, vb, TB);
-  };
-  if (warp < n_units) issue(warp);
-
-  if (tid < kBlock) inv[slot_to_position<BITS>(tid)] = (uint8_t)tid;
-  for (int i = tid; i < acc_n; i += kGemvThreads) acc[i] = 0.f;
+  NB_TRACE_MARK(0);
+  if (tid < rt_n) mbar_init(&bars[tid], n_threads);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncthreads();
+
+  // ---- request every byte of weights and codebooks this CTA needs (constant data: no need to
+  // wait for earlier kernels) with 16-byte asynchronous copies, consecutive threads on
+  // consecutive chunks of a row; each thread then posts one deferred arrival per row tile
+  // that fires when its copies of that tile have landed.
   {
-    // k-blocks past the end of the row (last k-group) are staged as zeros: their weights are
-    // zero too, and 0 x garbage must not produce a NaN.
-    const int per_row = kg_n * 4 * kBlock;
-    for (int e = tid; e < p.M * per_row; e += kGemvThreads) {
-      const int m = e / per_row, r = e - m * per_row;
-      const int kbl = r >> 7, pos = r & 127;
-      float v = 0.f;
-      if (kbl < kb_n) v = load_x(p.x, p.x_dtype, (size_t)m * K + (size_t)kb0 * kBlock + r);
-      v = fminf(fmaxf(v, -65504.f), 65504.f);
-      const int slot = inv[pos];
-      const int off = (m >> 3) * (x_tile_bytes / 2) + kbl * (kXBlockBytes / 2) + (slot >> 2) * 32 + (m & 7) * 4 + (slot & 3);
-      xs[off] = __float2half_rn(v);
+    const int wch = kb_n * kBlkBytes / 16;                    // 16-byte chunks per index row
+    const int cch = p.cb_bulk ? kb_n * cb_blk / 16 : 0;       // ... per codebook row
+    const uint8_t* cbase = reinterpret_cast<const uint8_t*>(p.codebook);
+    for (int rtl = 0; rtl < rt_n; ++rtl) {
+      for (int lr = warp; lr < 16; lr += n_warps) {           // one warp per row
+        const int r = rtl * 16 + lr;
+        const size_t row = (size_t)rt0 * 16 + r;
+        if (row < (size_t)p.N) {
+          const size_t blk0 = row * p.bpr + kb0;
+          const uint8_t* wsrc = p.packed + blk0 * kBlkBytes;
+          uint8_t* wdst = w_s + r * p.w_stride;
+          for (int j = lane; j < wch; j += 32) cp_async16(wdst + 16 * j, wsrc + 16 * j);
+          const uint8_t* csrc = cbase + blk0 * cb_blk;
+          uint8_t* cdst = c_s + r * p.c_stride;
+          for (int j = lane; j < cch; j += 32) cp_async16(cdst + 16 * j, csrc + 16 * j);
+        }
+      }
+      cp_async_arrive(&bars[rtl]);
+    }
+  }
+  if (!p.cb_bulk) {
+    // codebook rows that are not 16-byte granular (2-bit fp16 with an odd block count): 8-byte loads
+    const int gpr = kb_n * cb_blk / 8;  // granules per row
+    for (int i = tid; i < rt_n * 16 * gpr; i += n_threads) {
+      const int r = i / gpr, j = i - r * gpr;
+      const size_t row = (size_t)rt0 * 16 + r;
+      if (row < (size_t)p.N)
+        *reinterpret_cast<uint2*>(c_s + r * p.c_stride + 8 * j) =
+            __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.codebook) + (row * p.bpr + kb0) * cb_blk) + j);
+    }
+  }
+  asm volatile("griddepcontrol.launch_dependents;");
+  NB_TRACE_MARK(1);
+
+  if (tid < kBlock) {
+    const int slot = tid, pos = slot_to_position<BITS>(slot);
+    dst_off[pos] = (uint16_t)((slot >> 2) * 32 + (slot & 3));
+  }
+  for (int i = tid; i < acc_n; i += n_threads) acc[i] = 0.f;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  NB_TRACE_MARK(2);
+  __syncthreads();
+
+  // ---- stage x as fp16 in slot order: x_s[tile m/8][k-block][step][row m%8][4].  A thread
+  // owns 8-position chunks; for each it loads four activation rows at a time, then scatters.
+  {
+    const int chunks = kg_n * 4 * 16;  // 8-position chunks per activation row
+    for (int c = tid; c < chunks; c += n_threads) {
+      const int kbl = c >> 4, p0 = (c & 15) << 3;
+      const uint4 o4 = *reinterpret_cast<const uint4*>(dst_off + p0);
+      const uint32_t o[4] = {o4.x, o4.y, o4.z, o4.w};
+      const bool live = kbl < kb_n;  // k-blocks past the end of the row are staged as zeros:
+                                     // their weights are zero, and 0 x garbage must not be NaN
+      const size_t at0 = (size_t)kb0 * kBlock + (size_t)c * 8;
+      for (int m0 = 0; m0 < p.M; m0 += 4) {
+        float v[4][8];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int m = m0 + b;
+          if (live && m < p.M) {
+            const size_t at = (size_t)m * K + at0;
+            if (p.x_vec) {
+              load_x8(p.x, p.x_dtype, at, v[b]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[b][j] = load_x(p.x, p.x_dtype, at + j);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[b][j] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int m = m0 + b;
+          if (m < p.M) {
+            __half* blk = reinterpret_cast<__half*>(x_s + (m >> 3) * x_tile_bytes) + (m & 7) * 4 + kbl * (kXBlockBytes / 2);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              blk[o[j] & 0xFFFFu] = to_half_clamped(v[b][2 * j]);
+              blk[o[j] >> 16] = to_half_clamped(v[b][2 * j + 1]);
+            }
+          }
+        }
+      }
     }
   }
   __syncthreads();
+  NB_TRACE_MARK(3);
 
-  for (int u = warp; u < n_units; u += kGemvWarps) {
+  // ---- units
+#pragma unroll 1
+  for (int u = warp; u < n_units; u += n_warps) {
     const int rtl = u / kg_n, kgl = u - rtl * kg_n;
-    float c[NT][4];
+    {  // bounded wait for this row tile's copies
+      uint32_t spins = 0;
+      while (!mbar_try_wait(&bars[rtl], 0)) {
+        if (++spins > kSpinLimit) {
+          if (p.status) atomicExch(p.status, (int)NB_ERR_TIMEOUT);
+          break;
+        }
+      }
+    }
+    if (u == 0) NB_TRACE_MARK(4);
+    const int kbl = 4 * kgl + t;                 // this lane's k-block inside the CTA's range
+    const bool vk = kbl < kb_n;
+    const int ra = rtl * 16 + g, rb = ra + 8;
+    uint32_t wa[kWords], wb[kWords], TA[4], TB[4];
+    read_block<BITS>(w_s + ra * p.w_stride + (vk ? kbl : 0) * kBlkBytes, wa);
+    read_block<BITS>(w_s + rb * p.w_stride + (vk ? kbl : 0) * kBlkBytes, wb);
+    make_table<BITS>(c_s + ra * p.c_stride + (vk ? kbl : 0) * cb_blk, p.cb_dtype, vk, TA);
+    make_table<BITS>(c_s + rb * p.c_stride + (vk ? kbl : 0) * cb_blk, p.cb_dtype, vk, TB);
+
+    float c[2][NT][4];  // two accumulator sets: even and odd steps
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) { c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f; }
-    const uint8_t* xrow = smem + (4 * kgl + t) * kXBlockBytes + g * 8;
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) { c[j][nt][0] = c[j][nt][1] = c[j][nt][2] = c[j][nt][3] = 0.f; }
+    const uint8_t* xrow = x_s + kbl * kXBlockBytes + g * 8;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       uint32_t UA[4], UB[4];
@@ -232,93 +399,120 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             const uint2 xb = *reinterpret_cast<const uint2*>(xrow + nt * x_tile_bytes + s * 64);
-            mma_16816(c[nt], a0, a1, a2, a3, xb.x, xb.y);
+            mma_16816(c[h][nt], a0, a1, a2, a3, xb.x, xb.y);
           }
         }
       }
     }
-    if (u + kGemvWarps < n_units) issue(u + kGemvWarps);
     float* arow = acc + (rtl * 16 + g) * (NT * 8) + 2 * t;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int n = nt * 8 + 2 * t;
-      if (n < p.M) { atomicAdd(arow + nt * 8, c[nt][0]); atomicAdd(arow + 8 * NT * 8 + nt * 8, c[nt][2]); }
-      if (n + 1 < p.M) { atomicAdd(arow + nt * 8 + 1, c[nt][1]); atomicAdd(arow + 8 * NT * 8 + nt * 8 + 1, c[nt][3]); }
+      if (n < p.M) {
+        atomicAdd(arow + nt * 8, c[0][nt][0] + c[1][nt][0]);
+        atomicAdd(arow + 8 * NT * 8 + nt * 8, c[0][nt][2] + c[1][nt][2]);
+      }
+      if (n + 1 < p.M) {
+        atomicAdd(arow + nt * 8 + 1, c[0][nt][1] + c[1][nt][1]);
+        atomicAdd(arow + 8 * NT * 8 + nt * 8 + 1, c[0][nt][3] + c[1][nt][3]);
+      }
     }
   }
   __syncthreads();
+  NB_TRACE_MARK(5);
 
   const int rows_here = rt_n * 16;
   const int row0 = rt0 * 16;
-  if (gridDim.y == 1) {
-    for (int e = tid; e < p.M * rows_here; e += kGemvThreads) {
-      const int m = e / rows_here, r = e - m * rows_here;
-      if (row0 + r < p.N) store_y(p.y, p.y_dtype, (size_t)m * p.N + row0 + r, acc[r * (NT * 8) + m]);
+  if (gridDim.y > 1) {
+    // ---- split-K fix-up: the accumulator tile goes to scratch as is; the CTA that takes the last
+    // ticket of its row group adds all partial tiles in fixed order and writes y.
+    float4* mine = reinterpret_cast<float4*>(p.scratch + ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * acc_n);
+    const float4* acc4 = reinterpret_cast<const float4*>(acc);
+    for (int i = tid; i < acc_n / 4; i += n_threads) __stcg(mine + i, acc4[i]);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const int ticket = atomicAdd(p.counters + blockIdx.x, 1);
+      s_last = (ticket == (int)gridDim.y - 1);
     }
-    return;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float4* base = reinterpret_cast<const float4*>(p.scratch + (size_t)blockIdx.x * gridDim.y * acc_n);
+    const int parts = gridDim.y, stride4 = acc_n / 4;
+    for (int i = tid; i < acc_n / 4; i += n_threads) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int part0 = 0; part0 < parts; part0 += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          t[j] = (part0 + j < parts) ? __ldcg(base + (size_t)(part0 + j) * stride4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
+      }
+      reinterpret_cast<float4*>(acc)[i] = v;
+    }
+    if (tid == 0) p.counters[blockIdx.x] = 0;
+    __syncthreads();
   }
-  // split-K fix-up
-  const int tile_elems = p.tr * 16 * p.M;
-  float* mine = p.scratch + ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * tile_elems;
-  for (int e = tid; e < p.M * rows_here; e += kGemvThreads) {
-    const int m = e / rows_here, r = e - m * rows_here;
-    __stcg(mine + e, acc[r * (NT * 8) + m]);
-  }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int ticket = atomicAdd(p.counters + blockIdx.x, 1);
-    s_last = (ticket == (int)gridDim.y - 1);
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  const float* base = p.scratch + (size_t)blockIdx.x * gridDim.y * tile_elems;
-  for (int e = tid; e < p.M * rows_here; e += kGemvThreads) {
-    const int m = e / rows_here, r = e - m * rows_here;
-    float v = 0.f;
-    for (int part = 0; part < (int)gridDim.y; ++part) v += __ldcg(base + (size_t)part * tile_elems + e);
-    if (row0 + r < p.N) store_y(p.y, p.y_dtype, (size_t)m * p.N + row0 + r, v);
-  }
-  if (tid == 0) p.counters[blockIdx.x] = 0;
+  for (int m = 0; m < p.M; ++m)
+    for (int r = tid; r < rows_here; r += n_threads)
+      if (row0 + r < p.N) store_y(p.y, p.y_dtype, (size_t)m * p.N + row0 + r, acc[r * (NT * 8) + m]);
+  NB_TRACE_MARK(6);
 }
 
-static size_t plan_smem(int tr, int kg_per_part, int nt) {
-  return (size_t)nt * kg_per_part * 4 * kXBlockBytes + (size_t)tr * 16 * nt * 8 * 4 + kBlock + 16;
+// Shared-memory row stride: at least `bytes`, 16-byte aligned, and equal to 64 mod 128 so that
+// the 16-byte reads of rows g and g+1 land in different banks.
+static int skew_stride(int bytes) {
+  int s = (bytes + 15) / 16 * 16;
+  while (s % 128 != 64) s += 16;
+  return s;
 }
 
 // Picks rows-per-CTA and the k split so that the grid is close to one full wave of CTAs with
 // about one unit per warp.  cost = waves * (latency + ceil(units/warps)) + fix-up penalty.
-static GemvPlan make_plan(int M, int N, int K, int sms) {
+static GemvPlan make_plan(int M, int N, int K, int bits, int cb_dtype, int sms) {
   const int nt = M > 8 ? 2 : 1;
   const int row_tiles = (N + 15) / 16, bpr = K / kBlock, kgroups = (bpr + 3) / 4;
+  const int blk_bytes = 16 * bits, cb_blk = (cb_dtype == NB_F16 ? 2 : 4) << bits;
   GemvPlan best{};
   double best_cost = 1e30;
   for (int parts_req = 1; parts_req <= std::min(kgroups, 32); ++parts_req) {
     const int kgp = (kgroups + parts_req - 1) / parts_req;
     const int parts = (kgroups + kgp - 1) / kgp;
     if (parts != parts_req) continue;
-    for (int tr = 1; tr <= std::min(row_tiles, 64); ++tr) {
-      const size_t smem = plan_smem(tr, kgp, nt);
+    const int kb_cnt = std::min(kgp * 4, bpr);
+    const int ws = skew_stride(kb_cnt * blk_bytes), cs = skew_stride(kb_cnt * cb_blk);
+    for (int tr = 1; tr <= std::min(row_tiles, kMaxTr); ++tr) {
+      const size_t smem = (size_t)tr * 16 * (ws + cs) + (size_t)nt * kgp * 4 * kXBlockBytes +
+                          (size_t)tr * 16 * nt * 8 * 4 + 2 * kBlock + 128;
       if (smem > (size_t)kMaxSmem) break;
       const int gx = (row_tiles + tr - 1) / tr;
+      if (parts > 1 && gx >= kCounterInts - 1) continue;  // one ticket counter per row group
       const long ctas = (long)gx * parts;
       const long waves = (ctas + sms - 1) / sms;
-      const int rounds = (tr * kgp + kGemvWarps - 1) / kGemvWarps;
+      const int upc = tr * kgp;
+      const int rounds = (upc + kMaxWarps - 1) / kMaxWarps;
       double cost = waves * (1.5 + rounds) + (parts > 1 ? 0.4 + 0.02 * parts : 0.0);
       if (cost < best_cost - 1e-9) {
         best_cost = cost;
-        best = GemvPlan{tr, parts, kgp, gx, smem};
+        int warps = std::min(kMaxWarps, std::max(4, (upc + 3) / 4 * 4));
+        best = GemvPlan{tr, parts, kgp, gx, warps, smem, ws, cs};
       }
     }
   }
   return best;
 }
 
+// workspace layout: a fixed 16 KB head of ticket counters (int 0..4094) and the status word (int
+// 4095), then the fp32 partial tiles.  The head is at the same place for every shape, so a
+// workspace shared by launches of different shapes never has partial sums where a later launch
+// expects zeroed counters.
+static size_t counter_bytes(const GemvPlan&) { return (size_t)kCounterInts * sizeof(int); }
+
 static size_t plan_workspace(const GemvPlan& pl, int M) {
-  const size_t counters = ((size_t)pl.grid_x * sizeof(int) + 255) / 256 * 256;
-  const size_t scratch = pl.parts > 1 ? (size_t)pl.grid_x * pl.parts * pl.tr * 16 * M * sizeof(float) : 0;
-  return counters + scratch;
+  const size_t scratch = pl.parts > 1 ? (size_t)pl.grid_x * pl.parts * pl.tr * 16 * (M > 8 ? 16 : 8) * sizeof(float) : 0;
+  return counter_bytes(pl) + scratch;
 }
 
 template <int BITS, int NT>
@@ -331,8 +525,19 @@ static int launch(const GemvParams& prm, const GemvPlan& pl, cudaStream_t st) {
     if (e != cudaSuccess) return record_cuda_error(e);
     attr_done[dev & 63] = true;
   }
-  gemv_kernel<BITS, NT><<<dim3(pl.grid_x, pl.parts), kGemvThreads, pl.smem, st>>>(prm);
-  return check_launch();
+  // Programmatic dependent launch: this grid may start (and request its weights) while the
+  // previous kernel of the stream is still running; it waits for that kernel before it reads x.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pl.grid_x, pl.parts);
+  cfg.blockDim = dim3(pl.warps * 32);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return record_cuda_error(cudaLaunchKernelEx(&cfg, gemv_kernel<BITS, NT>, prm));
 }
 
 }  // namespace nb
@@ -349,7 +554,18 @@ static int gemv_check_shape(int M, int N, int K, int bits, int block_size) {
 
 extern "C" size_t nb_gemv_workspace_bytes(int M, int N, int K, int bits, int block_size) {
   if (gemv_check_shape(M, N, K, bits, block_size) != NB_OK) return 0;
-  return plan_workspace(make_plan(M, N, K, sm_count()), M);
+  // the fp32-codebook plan never needs more scratch than the fp16 one needs counters for; take the max
+  const size_t a = plan_workspace(make_plan(M, N, K, bits, NB_F16, sm_count()), M);
+  const size_t b = plan_workspace(make_plan(M, N, K, bits, NB_F32, sm_count()), M);
+  return std::max(a, b);
+}
+
+extern "C" int nb_gemv_plan(int M, int N, int K, int bits, int block_size, int cb_dtype, int* out6) {
+  if (!out6) return NB_ERR_ARG;
+  if (int rc = gemv_check_shape(M, N, K, bits, block_size)) return rc;
+  const GemvPlan pl = make_plan(M, N, K, bits, cb_dtype, sm_count());
+  out6[0] = pl.grid_x; out6[1] = pl.parts; out6[2] = pl.warps * 32; out6[3] = (int)pl.smem; out6[4] = pl.tr; out6[5] = pl.kg_per_part;
+  return NB_OK;
 }
 
 extern "C" int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype,
@@ -361,19 +577,26 @@ extern "C" int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed,
   if (int rc = gemv_check_shape(M, N, K, bits, block_size)) return rc;
   if ((uintptr_t)packed % 16 || (uintptr_t)codebook % 16) return NB_ERR_ALIGN;
   if (int rc = check_device()) return rc;
-  const GemvPlan pl = make_plan(M, N, K, sm_count());
+  const GemvPlan pl = make_plan(M, N, K, bits, cb_dtype, sm_count());
+  if (pl.grid_x == 0) return NB_ERR_SHAPE;
   const size_t need = plan_workspace(pl, M);
-  if (pl.parts > 1 && (!workspace || workspace_bytes < need)) return NB_ERR_WORKSPACE;
-  if (pl.parts > 1 && (uintptr_t)workspace % 16) return NB_ERR_ALIGN;
+  const bool have_ws = workspace && workspace_bytes >= need;
+  if (pl.parts > 1 && !have_ws) return NB_ERR_WORKSPACE;
+  if (have_ws && (uintptr_t)workspace % 16) return NB_ERR_ALIGN;
 
   GemvParams prm{};
   prm.x = x; prm.packed = packed; prm.codebook = codebook; prm.y = y;
-  const size_t counters = ((size_t)pl.grid_x * sizeof(int) + 255) / 256 * 256;
-  prm.counters = reinterpret_cast<int*>(workspace);
-  prm.scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + counters);
+  if (have_ws) {
+    prm.counters = reinterpret_cast<int*>(workspace);
+    prm.status = prm.counters + (kCounterInts - 1);
+    prm.scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + counter_bytes(pl));
+  }
   prm.M = M; prm.N = N; prm.bpr = K / kBlock; prm.row_tiles = (N + 15) / 16; prm.kgroups = (prm.bpr + 3) / 4;
   prm.tr = pl.tr; prm.kg_per_part = pl.kg_per_part;
   prm.x_dtype = x_dtype; prm.y_dtype = y_dtype; prm.cb_dtype = cb_dtype;
+  prm.x_vec = ((uintptr_t)x % 16 == 0) ? 1 : 0;
+  prm.w_stride = pl.w_stride; prm.c_stride = pl.c_stride;
+  prm.cb_bulk = ((prm.bpr * ((cb_dtype == NB_F16 ? 2 : 4) << bits)) % 16 == 0) ? 1 : 0;
   cudaStream_t st = (cudaStream_t)stream;
   if (bits == 3) return M > 8 ? launch<3, 2>(prm, pl, st) : launch<3, 1>(prm, pl, st);
   return M > 8 ? launch<2, 2>(prm, pl, st) : launch<2, 1>(prm, pl, st);

@@ -179,7 +179,7 @@ def make_codebook(num_blocks: int, n_entries: int, seed: int, block_size: int = 
     z = rng.standard_normal((num_blocks, block_size)).astype(np.float32)
     q = np.quantile(z, np.linspace(0.0, 1.0, n_entries), axis=1).T.astype(np.float32)
     scale = rng.uniform(0.01, 0.05, size=(num_blocks, 1)).astype(np.float32)
-    return (q * scale).astype(np.float16)
+    return np.ascontiguousarray((q * scale).astype(np.float16))
 
 
 def make_packed_linear(out_features: int, in_features: int, bits: int, seed: int, block_size: int = BS):
