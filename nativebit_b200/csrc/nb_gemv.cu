@@ -6,8 +6,10 @@
 // consecutive threads on consecutive chunks of a row, and posts one deferred arrival per row
 // tile on that tile's mbarrier: every byte the CTA will read from HBM is requested before
 // anything else happens, and a warp can start on a row tile as soon as that tile has landed.
-// (Bulk cp.async.bulk copies were measured first: one copy per 960-byte row costs the issuing
-// thread about 30 ns per copy, 3 us per CTA, so the per-row form is not used.)  The kernel is
+// When the CTA covers whole rows (no k split) the 16 rows of a tile are one contiguous span and
+// are fetched instead by two bulk copies (cp.async.bulk, the 1-D form of TMA) issued by one
+// lane, which blocks no warp; one bulk copy per 960-byte row was measured at about 30 ns of
+// issue time per copy, which is why the split-k case uses the 16-byte copies.  The kernel is
 // launched with programmatic stream serialization: after requesting its weights it lets the
 // next launch of the stream begin (which requests its own weights) and only then waits for
 // the previous kernel, whose output may be this kernel's x.
@@ -59,7 +61,9 @@ namespace nb {
 
 constexpr int kMaxWarps = 16;
 constexpr int kMaxTr = 16;                      // row tiles per CTA (one mbarrier each)
-constexpr int kXBlockBytes = 32 * 8 * 8 + 32;   // one k-block of one 8-row activation tile, +32 B skew
+// Bytes of one k-block of an activation tile of XR rows (32 steps x XR rows x 4 fp16), plus a skew
+// that spreads the four k-blocks read by lanes t = 0..3 over different banks.
+__host__ __device__ constexpr int x_block_bytes(int xr) { return 32 * xr * 8 + (xr == 8 ? 32 : 8); }
 constexpr int kMaxSmem = 110 * 1024;            // two CTAs (of consecutive launches) fit one SM
 constexpr int kCounterInts = 4096;              // workspace head: ticket counters + status word
 constexpr uint32_t kSpinLimit = 1u << 22;       // bounded wait on the copy barriers (about 0.1 s)
@@ -87,7 +91,8 @@ struct GemvParams {
   int x_dtype, y_dtype, cb_dtype;
   int x_vec;        // x is 16-byte aligned: staged with 16-byte loads
   int w_stride, c_stride;  // shared-memory row strides (bytes) of the index and codebook tiles
-  int cb_bulk;      // codebook rows satisfy the 16-byte rules of bulk copies (else plain loads)
+  int cb_bulk;      // codebook rows are whole 16-byte chunks (else they are fetched with 8-byte loads)
+  int tile_bulk;    // the CTA covers whole rows: a row tile is one contiguous span, fetched by bulk copies
 };
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
@@ -113,6 +118,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
+}
+// 1-D bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completing on `bar`.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 // 16-byte asynchronous copy global -> shared (L2 only), and a deferred barrier arrival that fires
 // once all earlier asynchronous copies of the executing thread have completed.
@@ -223,11 +233,14 @@ __device__ __forceinline__ __half to_half_clamped(float v) {
   return __float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f));
 }
 
-template <int BITS, int NT>
+// XR = activation rows held per tile: 8, or 1 for a single activation vector (all eight B
+// columns then read the same row, so the tile is 8x smaller and column 0 carries the result).
+template <int BITS, int NT, int XR>
 __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kWords = Fmt<BITS>::kWords;
   constexpr int kBlkBytes = 16 * BITS;
+  constexpr int kXBlockBytes = x_block_bytes(XR);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int n_warps = blockDim.x >> 5, n_threads = blockDim.x;
 
@@ -253,7 +266,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p
   __shared__ int s_last;
 
   NB_TRACE_MARK(0);
-  if (tid < rt_n) mbar_init(&bars[tid], n_threads);
+  if (tid < rt_n) mbar_init(&bars[tid], p.tile_bulk ? 1 : n_threads);
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncthreads();
 
@@ -261,7 +274,20 @@ __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p
   // wait for earlier kernels) with 16-byte asynchronous copies, consecutive threads on
   // consecutive chunks of a row; each thread then posts one deferred arrival per row tile
   // that fires when its copies of that tile have landed.
-  {
+  if (p.tile_bulk) {
+    // Whole rows: the 16 rows of a tile are contiguous in global memory, so lane 0 of warp j
+    // fetches tile j (j + n_warps, ...) with one bulk copy for indices and one for codebooks.
+    if (lane == 0) {
+      for (int rtl = warp; rtl < rt_n; rtl += n_warps) {
+        const size_t row = (size_t)(rt0 + rtl) * 16;
+        const uint32_t rows = (uint32_t)min((size_t)16, (size_t)p.N - row);
+        const uint32_t wb = rows * (uint32_t)p.w_stride, cbb = rows * (uint32_t)p.c_stride;
+        mbar_arrive_expect_tx(&bars[rtl], wb + cbb);
+        bulk_g2s(w_s + rtl * 16 * p.w_stride, p.packed + row * p.bpr * kBlkBytes, wb, &bars[rtl]);
+        bulk_g2s(c_s + rtl * 16 * p.c_stride, reinterpret_cast<const uint8_t*>(p.codebook) + row * p.bpr * cb_blk, cbb, &bars[rtl]);
+      }
+    }
+  } else {
     const int wch = kb_n * kBlkBytes / 16;                    // 16-byte chunks per index row
     const int cch = p.cb_bulk ? kb_n * cb_blk / 16 : 0;       // ... per codebook row
     const uint8_t* cbase = reinterpret_cast<const uint8_t*>(p.codebook);
@@ -282,7 +308,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p
       cp_async_arrive(&bars[rtl]);
     }
   }
-  if (!p.cb_bulk) {
+  if (!p.cb_bulk && !p.tile_bulk) {
     // codebook rows that are not 16-byte granular (2-bit fp16 with an odd block count): 8-byte loads
     const int gpr = kb_n * cb_blk / 8;  // granules per row
     for (int i = tid; i < rt_n * 16 * gpr; i += n_threads) {
@@ -298,7 +324,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p
 
   if (tid < kBlock) {
     const int slot = tid, pos = slot_to_position<BITS>(slot);
-    dst_off[pos] = (uint16_t)((slot >> 2) * 32 + (slot & 3));
+    dst_off[pos] = (uint16_t)((slot >> 2) * (XR * 4) + (slot & 3));
   }
   for (int i = tid; i < acc_n; i += n_threads) acc[i] = 0.f;
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -338,7 +364,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p
         for (int b = 0; b < 4; ++b) {
           const int m = m0 + b;
           if (m < p.M) {
-            __half* blk = reinterpret_cast<__half*>(x_s + (m >> 3) * x_tile_bytes) + (m & 7) * 4 + kbl * (kXBlockBytes / 2);
+            __half* blk = reinterpret_cast<__half*>(x_s + (m / XR) * x_tile_bytes) + (m % XR) * 4 + kbl * (kXBlockBytes / 2);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               blk[o[j] & 0xFFFFu] = to_half_clamped(v[b][2 * j]);
@@ -380,7 +406,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p
     for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) { c[j][nt][0] = c[j][nt][1] = c[j][nt][2] = c[j][nt][3] = 0.f; }
-    const uint8_t* xrow = x_s + kbl * kXBlockBytes + g * 8;
+    const uint8_t* xrow = x_s + kbl * kXBlockBytes + (g % XR) * 8;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       uint32_t UA[4], UB[4];
@@ -398,7 +424,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p
           lookup4(sb, TB, a1, a3);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            const uint2 xb = *reinterpret_cast<const uint2*>(xrow + nt * x_tile_bytes + s * 64);
+            const uint2 xb = *reinterpret_cast<const uint2*>(xrow + nt * x_tile_bytes + s * (XR * 8));
             mma_16816(c[h][nt], a0, a1, a2, a3, xb.x, xb.y);
           }
         }
@@ -482,9 +508,12 @@ static GemvPlan make_plan(int M, int N, int K, int bits, int cb_dtype, int sms) 
     const int parts = (kgroups + kgp - 1) / kgp;
     if (parts != parts_req) continue;
     const int kb_cnt = std::min(kgp * 4, bpr);
-    const int ws = skew_stride(kb_cnt * blk_bytes), cs = skew_stride(kb_cnt * cb_blk);
+    // whole rows (one partition, 16-byte granular codebook rows): natural strides, bulk copies
+    const bool whole = parts == 1 && (bpr * cb_blk) % 16 == 0;
+    const int ws = whole ? kb_cnt * blk_bytes : skew_stride(kb_cnt * blk_bytes);
+    const int cs = whole ? kb_cnt * cb_blk : skew_stride(kb_cnt * cb_blk);
     for (int tr = 1; tr <= std::min(row_tiles, kMaxTr); ++tr) {
-      const size_t smem = (size_t)tr * 16 * (ws + cs) + (size_t)nt * kgp * 4 * kXBlockBytes +
+      const size_t smem = (size_t)tr * 16 * (ws + cs) + (size_t)nt * kgp * 4 * x_block_bytes(M == 1 ? 1 : 8) +
                           (size_t)tr * 16 * nt * 8 * 4 + 2 * kBlock + 128;
       if (smem > (size_t)kMaxSmem) break;
       const int gx = (row_tiles + tr - 1) / tr;
@@ -515,13 +544,13 @@ static size_t plan_workspace(const GemvPlan& pl, int M) {
   return counter_bytes(pl) + scratch;
 }
 
-template <int BITS, int NT>
+template <int BITS, int NT, int XR>
 static int launch(const GemvParams& prm, const GemvPlan& pl, cudaStream_t st) {
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BITS, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BITS, NT, XR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     if (e != cudaSuccess) return record_cuda_error(e);
     attr_done[dev & 63] = true;
   }
@@ -537,7 +566,7 @@ static int launch(const GemvParams& prm, const GemvPlan& pl, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return record_cuda_error(cudaLaunchKernelEx(&cfg, gemv_kernel<BITS, NT>, prm));
+  return record_cuda_error(cudaLaunchKernelEx(&cfg, gemv_kernel<BITS, NT, XR>, prm));
 }
 
 }  // namespace nb
@@ -597,7 +626,8 @@ extern "C" int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed,
   prm.x_vec = ((uintptr_t)x % 16 == 0) ? 1 : 0;
   prm.w_stride = pl.w_stride; prm.c_stride = pl.c_stride;
   prm.cb_bulk = ((prm.bpr * ((cb_dtype == NB_F16 ? 2 : 4) << bits)) % 16 == 0) ? 1 : 0;
+  prm.tile_bulk = (pl.parts == 1 && prm.cb_bulk) ? 1 : 0;
   cudaStream_t st = (cudaStream_t)stream;
-  if (bits == 3) return M > 8 ? launch<3, 2>(prm, pl, st) : launch<3, 1>(prm, pl, st);
-  return M > 8 ? launch<2, 2>(prm, pl, st) : launch<2, 1>(prm, pl, st);
+  if (bits == 3) return M > 8 ? launch<3, 2, 8>(prm, pl, st) : M > 1 ? launch<3, 1, 8>(prm, pl, st) : launch<3, 1, 1>(prm, pl, st);
+  return M > 8 ? launch<2, 2, 8>(prm, pl, st) : M > 1 ? launch<2, 1, 8>(prm, pl, st) : launch<2, 1, 1>(prm, pl, st);
 }

@@ -76,6 +76,7 @@ def dequant(packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size:
 
 
 _workspaces: dict = {}
+_ws_need: dict = {}
 
 
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
@@ -83,30 +84,46 @@ def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        ws = torch.zeros(max(nbytes, 4 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+def gemv_workspace_bytes(m: int, n: int, k: int, bits: int, block_size: int) -> int:
+    key = (m, n, k, bits, block_size)
+    need = _ws_need.get(key)
+    if need is None:
+        need = _ws_need[key] = int(_lib.lib().nb_gemv_workspace_bytes(m, n, k, bits, block_size))
+        if need == 0:
+            raise RuntimeError(f"nb_gemv does not support M={m} N={n} K={k} bits={bits} block_size={block_size} "
+                               "(needs 1 <= M <= 16, bits in {2,3}, block_size 128, K % 128 == 0)")
+    return need
 
 
 def gemv(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size: int,
          n: int, k: int, out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
          ws: torch.Tensor | None = None) -> torch.Tensor:
-    """y (M, n) = x (M, k) @ W.T for M <= 16, fused unpack + codebook gather + contraction."""
-    _need_cuda(x, packed, codebook)
-    if x.dim() != 2 or x.shape[1] != k:
-        raise RuntimeError(f"x must be (M, {k}); got {tuple(x.shape)}")
+    """y (M, n) = x (M, k) @ W.T for M <= 16, fused unpack + codebook gather + contraction.
+    Launches on torch's current stream of x's device."""
+    if not (x.is_cuda and packed.is_cuda and codebook.is_cuda):
+        _need_cuda(x, packed, codebook)
+    if x.dim() != 2 or x.shape[1] != k or not x.is_contiguous():
+        raise RuntimeError(f"x must be a contiguous (M, {k}) tensor; got {tuple(x.shape)}")
     m = x.shape[0]
-    if x.dtype not in _DTYPE:
+    xd = _DTYPE.get(x.dtype)
+    if xd is None:
         raise RuntimeError(f"unsupported activation dtype {x.dtype}")
-    out_dtype = out_dtype or x.dtype
     if out is None:
-        out = torch.empty(m, n, dtype=out_dtype, device=x.device)
-    l = _lib.lib()
-    with torch.cuda.device(x.device):
-        need = l.nb_gemv_workspace_bytes(m, n, k, bits, block_size)
-        if ws is None:
-            ws = workspace(x.device, need)
-        _lib.check(l.nb_gemv(x.data_ptr(), _DTYPE[x.dtype], m, packed.data_ptr(), codebook.data_ptr(),
-                             _DTYPE[codebook.dtype], bits, block_size, n, k, out.data_ptr(), _DTYPE[out.dtype],
-                             ws.data_ptr(), ws.numel(), _stream()), "nb_gemv")
+        out = torch.empty(m, n, dtype=out_dtype or x.dtype, device=x.device)
+    need = gemv_workspace_bytes(m, n, k, bits, block_size)
+    dev = x.device.index
+    if dev != torch.cuda.current_device():
+        with torch.cuda.device(dev):
+            return gemv(x, packed, codebook, bits, block_size, n, k, out=out, ws=ws)
+    if ws is None:
+        ws = workspace(x.device, need)
+    rc = _lib.lib().nb_gemv(x.data_ptr(), xd, m, packed.data_ptr(), codebook.data_ptr(), _DTYPE[codebook.dtype], bits,
+                            block_size, n, k, out.data_ptr(), _DTYPE[out.dtype], ws.data_ptr(), ws.numel(), _stream())
+    if rc:
+        _lib.check(rc, "nb_gemv")
     return out
