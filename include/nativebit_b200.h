@@ -88,6 +88,24 @@ int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed, const void
             int bits, int block_size, int N, int K, void* y, int y_dtype, void* workspace,
             size_t workspace_bytes, void* stream);
 
+/* ---- nb_gemv without a caller-provided workspace.  No counterpart in the reference.
+ * For callers that cannot allocate device memory — a plugin that is handed only its input and
+ * output buffers, code that runs while a stream is being captured or under a frozen memory
+ * budget — the split-K scratch is a 4 MiB array built into the library's device image (every GPU
+ * that loads the library holds it until the process exits).  Arguments are those of nb_gemv
+ * minus the workspace.  Limits and rules:
+ *  - shapes whose scratch need (nb_gemv_workspace_bytes) exceeds 4 MiB are refused with
+ *    NB_ERR_WORKSPACE and a message in nb_last_cuda_error(); nothing is launched;
+ *  - the first call on a device looks the array's address up (with that device current); make
+ *    that first call before any stream capture begins;
+ *  - the call enqueues a 16 KB clear of the array's head on `stream`, then the kernel; it calls no
+ *    allocation or free routine of CUDA or of any library;
+ *  - all calls on a device share the one array, which keeps the previous call's partial sums:
+ *    two calls that overlap on the GPU (different streams, or graph branches) race.  Serialise
+ *    them on one stream, or use nb_gemv with one workspace per stream. */
+int nb_gemv_static(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype,
+                   int bits, int block_size, int N, int K, void* y, int y_dtype, void* stream);
+
 /* Launch geometry nb_gemv will use for a shape on the current device (no launch; works without
  * a GPU, assuming 148 SMs): out6 = {grid.x, grid.y (k partitions), threads per CTA, dynamic
  * shared memory bytes, row tiles per CTA, k-groups per partition}.  No counterpart in the

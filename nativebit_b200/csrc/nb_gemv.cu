@@ -35,6 +35,8 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstdio>
+#include <mutex>
 
 #include "nb_common.cuh"
 #include "nb_host.h"
@@ -630,4 +632,55 @@ extern "C" int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed,
   cudaStream_t st = (cudaStream_t)stream;
   if (bits == 3) return M > 8 ? launch<3, 2, 8>(prm, pl, st) : M > 1 ? launch<3, 1, 8>(prm, pl, st) : launch<3, 1, 1>(prm, pl, st);
   return M > 8 ? launch<2, 2, 8>(prm, pl, st) : M > 1 ? launch<2, 1, 8>(prm, pl, st) : launch<2, 1, 1>(prm, pl, st);
+}
+
+// ------------------------------------------------------------------------------------------------
+// nb_gemv_static — the same fused GEMV for callers that may not allocate device memory.
+//
+// Some hosts of this library cannot hand nb_gemv a workspace: code running inside a CUDA-graph
+// capture or inside another framework's allocator-owned region, plugins whose interface gives
+// them input and output buffers and nothing else, and processes that run with a frozen memory
+// budget.  For them the split-K scratch lives in a fixed array in this module's device image
+// (4 MiB, resident on every GPU that loads the library until the process exits).  In host code
+// the array's name is only a handle, not a device pointer, so its address is looked up once per
+// device with cudaGetSymbolAddress while that device is current.
+// ------------------------------------------------------------------------------------------------
+namespace nb {
+constexpr size_t kStaticWsBytes = 4u << 20;
+static __device__ __align__(256) unsigned char g_static_ws[kStaticWsBytes];
+static std::mutex g_static_mu;
+static void* g_static_ptr[64];
+static bool g_static_ready[64];
+}  // namespace nb
+
+extern "C" int nb_gemv_static(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype,
+                              int bits, int block_size, int N, int K, void* y, int y_dtype, void* stream) {
+  if (!x || !packed || !codebook || !y) return NB_ERR_ARG;
+  if (int rc = gemv_check_shape(M, N, K, bits, block_size)) return rc;
+  const size_t need = nb_gemv_workspace_bytes(M, N, K, bits, block_size);
+  if (need > kStaticWsBytes) {
+    char msg[160];
+    std::snprintf(msg, sizeof(msg), "nb_gemv_static: M=%d N=%d K=%d needs %zu bytes of scratch, the built-in array holds %zu",
+                  M, N, K, need, (size_t)kStaticWsBytes);
+    set_last_error(msg);
+    return NB_ERR_WORKSPACE;
+  }
+  int dev = -1;
+  if (cudaError_t e = cudaGetDevice(&dev)) return record_cuda_error(e);
+  if (dev < 0 || dev >= 64) return NB_ERR_ARG;
+  void* ws = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ready[dev]) {  // set-up, once per device, with that device current
+      void* ptr = nullptr;
+      if (cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_ws)) return record_cuda_error(e);
+      g_static_ptr[dev] = ptr;
+      g_static_ready[dev] = true;
+    }
+    ws = g_static_ptr[dev];
+  }
+  // The array keeps whatever the previous call left.  Only the head (ticket counters and the
+  // status word) has to start at zero; partial sums are always written before they are read.
+  if (cudaError_t e = cudaMemsetAsync(ws, 0, (size_t)kCounterInts * sizeof(int), (cudaStream_t)stream)) return record_cuda_error(e);
+  return nb_gemv(x, x_dtype, M, packed, codebook, cb_dtype, bits, block_size, N, K, y, y_dtype, ws, kStaticWsBytes, stream);
 }

@@ -16,6 +16,8 @@ int record_cuda_error(cudaError_t e) {
   return NB_ERR_LAUNCH;
 }
 
+void set_last_error(const char* msg) { std::snprintf(g_last_error, sizeof(g_last_error), "%s", msg); }
+
 static int g_cc_major[64];
 static int g_sms[64];
 static bool g_known[64];

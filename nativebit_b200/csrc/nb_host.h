@@ -9,6 +9,9 @@ namespace nb {
 // Records `e` as this thread's last CUDA error text and maps it to a status.
 int record_cuda_error(cudaError_t e);
 
+// Stores a message as this thread's last error text (what nb_last_cuda_error() returns).
+void set_last_error(const char* msg);
+
 // NB_OK when the current device is compute capability 10.x, else NB_ERR_ARCH / NB_ERR_LAUNCH.
 int check_device();
 
