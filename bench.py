@@ -343,6 +343,31 @@ def run_ours(args):
                "sample": "gate+up+down matvec of one layer (3 of the step's 78 matvecs), best of 3 after 1 warm-up; "
                          "reference CPU PyTorch path: unpack + gather + matmul per call"}
 
+    # ---- the full 2.2B packed decoder (configs[3]): 128-token prompt, 256 greedy tokens, batch 1
+    decode = None
+    if not args.no_decode:
+        from nativebit_b200 import generate as G
+        del layers, y_gate, y_up, y_down
+        torch.cuda.empty_cache()
+        cfg = G.ModelConfig()
+        model = G.PackedGPT.random_init(cfg, seed=0, device=dev, tp_rank=rank, tp_size=world)
+        gen = torch.Generator().manual_seed(0)
+        prompt = torch.randint(0, cfg.vocab_size, (128,), generator=gen)
+        res = G.benchmark(model, prompt, n_generate=256, n_runs=2)
+        t = torch.tensor([res["per_token_ms"], res["prefill_ms"]], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        per_tok_ms, prefill_ms = float(t[0]), float(t[1])
+        lin_bytes = cfg.n_layers * (alg_bytes(1, 3 * HIDDEN, HIDDEN) + alg_bytes(1, HIDDEN, HIDDEN) +
+                                    2 * alg_bytes(1, FFN, HIDDEN) + alg_bytes(1, HIDDEN, FFN))
+        head_bytes = cfg.vocab_size * HIDDEN * 2
+        decode = {"tokens_per_s": 1e3 / per_tok_ms, "per_token_ms": per_tok_ms, "prefill_ms_128_tokens": prefill_ms,
+                  "n_generate": 256, "batch": 1, "tp": world,
+                  "packed_linear_bytes_per_token": lin_bytes, "lm_head_bytes_per_token": head_bytes,
+                  "weight_GBps": (lin_bytes + head_bytes) / (per_tok_ms * 1e-3) / 1e9,
+                  "model": "26 layers, hidden 2560, 32 heads, FFN 6912, vocab 32000, random-init 3-bit packed linears"}
+        del model
+
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -358,6 +383,8 @@ def run_ours(args):
             line["per_shape"] = extra
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if decode is not None:
+            line["decode"] = decode
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -394,6 +421,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-decode", action="store_true", help="skip the 2.2B decoder leg")
     ap.add_argument("--kernel-only", type=int, nargs=3, metavar=("N", "K", "M"), default=None,
                     help="launch one GEMV shape a few times and exit (profiling case)")
     args = ap.parse_args()

@@ -73,8 +73,9 @@ int nb_dequant(const uint8_t* packed, const void* codebook, int cb_dtype, int bi
  * x: (M, K) row-major of x_dtype; y: (M, N) row-major of y_dtype; fp32 accumulation.
  * bits in {2,3}; block_size 128 (or 64 for tensor-parallel sub-blocks); K % block_size == 0.
  * packed and codebook must be 16-byte aligned.  Weights enter the tensor-core contraction as
- * exact fp16 values (an fp32 codebook is rounded to fp16); activations are converted to fp16
- * (exact for bf16 inputs of magnitude 6.1e-5..65504; larger magnitudes are clamped).
+ * exact fp16 values (an fp32 codebook is rounded to fp16).  bf16/fp16 activations enter as fp16
+ * (exact for bf16 inputs of magnitude 6.1e-5..65504; larger magnitudes are clamped); fp32
+ * activations enter as the sum of two fp16 terms (about 22 significant bits).
  * workspace: device scratch of at least nb_gemv_workspace_bytes() bytes whose first 16 KB were
  * zero-filled once before its first use; it is then owned by calls on one stream at a time.
  * The first 16 KB hold ticket counters, which every launch leaves zeroed, and a status word

@@ -237,7 +237,10 @@ __device__ __forceinline__ __half to_half_clamped(float v) {
 
 // XR = activation rows held per tile: 8, or 1 for a single activation vector (all eight B
 // columns then read the same row, so the tile is 8x smaller and column 0 carries the result).
-template <int BITS, int NT, int XR>
+// XS = fp16 terms per activation: 1, or 2 for fp32 activations, which are carried as hi + lo fp16
+// parts (x = fp16(x) + fp16(x - fp16(x)), about 22 significant bits) and contracted by two MMAs
+// into the same accumulator, so that fp32 inputs are not rounded to 11 bits.
+template <int BITS, int NT, int XR, int XS>
 __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kWords = Fmt<BITS>::kWords;
@@ -261,7 +264,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p
   uint8_t* w_s = smem;
   uint8_t* c_s = w_s + p.tr * 16 * p.w_stride;
   uint8_t* x_s = c_s + p.tr * 16 * p.c_stride;
-  float* acc = reinterpret_cast<float*>(x_s + NT * x_tile_bytes);
+  float* acc = reinterpret_cast<float*>(x_s + NT * XS * x_tile_bytes);
   const int acc_n = p.tr * 16 * NT * 8;
   uint16_t* dst_off = reinterpret_cast<uint16_t*>(acc + acc_n);  // position -> offset (halves) inside a k-block tile
   __shared__ __align__(8) uint64_t bars[kMaxTr];
@@ -366,11 +369,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p
         for (int b = 0; b < 4; ++b) {
           const int m = m0 + b;
           if (m < p.M) {
-            __half* blk = reinterpret_cast<__half*>(x_s + (m / XR) * x_tile_bytes) + (m % XR) * 4 + kbl * (kXBlockBytes / 2);
+            __half* blk = reinterpret_cast<__half*>(x_s + (m / XR) * XS * x_tile_bytes) + (m % XR) * 4 + kbl * (kXBlockBytes / 2);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              blk[o[j] & 0xFFFFu] = to_half_clamped(v[b][2 * j]);
-              blk[o[j] >> 16] = to_half_clamped(v[b][2 * j + 1]);
+              const __half h0 = to_half_clamped(v[b][2 * j]), h1 = to_half_clamped(v[b][2 * j + 1]);
+              blk[o[j] & 0xFFFFu] = h0;
+              blk[o[j] >> 16] = h1;
+              if (XS == 2) {  // low-order parts go to the tile right behind
+                // (of the clamped value, so that out-of-range inputs stay finite)
+                const float c0 = fminf(fmaxf(v[b][2 * j], -65504.f), 65504.f), c1 = fminf(fmaxf(v[b][2 * j + 1], -65504.f), 65504.f);
+                blk[(x_tile_bytes / 2) + (o[j] & 0xFFFFu)] = __float2half_rn(c0 - __half2float(h0));
+                blk[(x_tile_bytes / 2) + (o[j] >> 16)] = __float2half_rn(c1 - __half2float(h1));
+              }
             }
           }
         }
@@ -426,8 +436,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p
           lookup4(sb, TB, a1, a3);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            const uint2 xb = *reinterpret_cast<const uint2*>(xrow + nt * x_tile_bytes + s * (XR * 8));
-            mma_16816(c[h][nt], a0, a1, a2, a3, xb.x, xb.y);
+#pragma unroll
+            for (int xs = 0; xs < XS; ++xs) {
+              const uint2 xb = *reinterpret_cast<const uint2*>(xrow + (nt * XS + xs) * x_tile_bytes + s * (XR * 8));
+              mma_16816(c[h][nt], a0, a1, a2, a3, xb.x, xb.y);
+            }
           }
         }
       }
@@ -499,7 +512,7 @@ static int skew_stride(int bytes) {
 
 // Picks rows-per-CTA and the k split so that the grid is close to one full wave of CTAs with
 // about one unit per warp.  cost = waves * (latency + ceil(units/warps)) + fix-up penalty.
-static GemvPlan make_plan(int M, int N, int K, int bits, int cb_dtype, int sms) {
+static GemvPlan make_plan(int M, int N, int K, int bits, int cb_dtype, int x_terms, int sms) {
   const int nt = M > 8 ? 2 : 1;
   const int row_tiles = (N + 15) / 16, bpr = K / kBlock, kgroups = (bpr + 3) / 4;
   const int blk_bytes = 16 * bits, cb_blk = (cb_dtype == NB_F16 ? 2 : 4) << bits;
@@ -515,7 +528,7 @@ static GemvPlan make_plan(int M, int N, int K, int bits, int cb_dtype, int sms) 
     const int ws = whole ? kb_cnt * blk_bytes : skew_stride(kb_cnt * blk_bytes);
     const int cs = whole ? kb_cnt * cb_blk : skew_stride(kb_cnt * cb_blk);
     for (int tr = 1; tr <= std::min(row_tiles, kMaxTr); ++tr) {
-      const size_t smem = (size_t)tr * 16 * (ws + cs) + (size_t)nt * kgp * 4 * x_block_bytes(M == 1 ? 1 : 8) +
+      const size_t smem = (size_t)tr * 16 * (ws + cs) + (size_t)nt * x_terms * kgp * 4 * x_block_bytes(M == 1 ? 1 : 8) +
                           (size_t)tr * 16 * nt * 8 * 4 + 2 * kBlock + 128;
       if (smem > (size_t)kMaxSmem) break;
       const int gx = (row_tiles + tr - 1) / tr;
@@ -546,13 +559,13 @@ static size_t plan_workspace(const GemvPlan& pl, int M) {
   return counter_bytes(pl) + scratch;
 }
 
-template <int BITS, int NT, int XR>
+template <int BITS, int NT, int XR, int XS>
 static int launch(const GemvParams& prm, const GemvPlan& pl, cudaStream_t st) {
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BITS, NT, XR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BITS, NT, XR, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     if (e != cudaSuccess) return record_cuda_error(e);
     attr_done[dev & 63] = true;
   }
@@ -568,7 +581,7 @@ static int launch(const GemvParams& prm, const GemvPlan& pl, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return record_cuda_error(cudaLaunchKernelEx(&cfg, gemv_kernel<BITS, NT, XR>, prm));
+  return record_cuda_error(cudaLaunchKernelEx(&cfg, gemv_kernel<BITS, NT, XR, XS>, prm));
 }
 
 }  // namespace nb
@@ -585,16 +598,17 @@ static int gemv_check_shape(int M, int N, int K, int bits, int block_size) {
 
 extern "C" size_t nb_gemv_workspace_bytes(int M, int N, int K, int bits, int block_size) {
   if (gemv_check_shape(M, N, K, bits, block_size) != NB_OK) return 0;
-  // the fp32-codebook plan never needs more scratch than the fp16 one needs counters for; take the max
-  const size_t a = plan_workspace(make_plan(M, N, K, bits, NB_F16, sm_count()), M);
-  const size_t b = plan_workspace(make_plan(M, N, K, bits, NB_F32, sm_count()), M);
-  return std::max(a, b);
+  // the plan depends on the codebook and activation types: report the largest need
+  size_t need = 0;
+  for (int cb = NB_F32; cb <= NB_F16; ++cb)
+    for (int xt = 1; xt <= 2; ++xt) need = std::max(need, plan_workspace(make_plan(M, N, K, bits, cb, xt, sm_count()), M));
+  return need;
 }
 
 extern "C" int nb_gemv_plan(int M, int N, int K, int bits, int block_size, int cb_dtype, int* out6) {
   if (!out6) return NB_ERR_ARG;
   if (int rc = gemv_check_shape(M, N, K, bits, block_size)) return rc;
-  const GemvPlan pl = make_plan(M, N, K, bits, cb_dtype, sm_count());
+  const GemvPlan pl = make_plan(M, N, K, bits, cb_dtype, 1, sm_count());
   out6[0] = pl.grid_x; out6[1] = pl.parts; out6[2] = pl.warps * 32; out6[3] = (int)pl.smem; out6[4] = pl.tr; out6[5] = pl.kg_per_part;
   return NB_OK;
 }
@@ -608,7 +622,8 @@ extern "C" int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed,
   if (int rc = gemv_check_shape(M, N, K, bits, block_size)) return rc;
   if ((uintptr_t)packed % 16 || (uintptr_t)codebook % 16) return NB_ERR_ALIGN;
   if (int rc = check_device()) return rc;
-  const GemvPlan pl = make_plan(M, N, K, bits, cb_dtype, sm_count());
+  const int x_terms = x_dtype == NB_F32 ? 2 : 1;
+  const GemvPlan pl = make_plan(M, N, K, bits, cb_dtype, x_terms, sm_count());
   if (pl.grid_x == 0) return NB_ERR_SHAPE;
   const size_t need = plan_workspace(pl, M);
   const bool have_ws = workspace && workspace_bytes >= need;
@@ -630,8 +645,11 @@ extern "C" int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed,
   prm.cb_bulk = ((prm.bpr * ((cb_dtype == NB_F16 ? 2 : 4) << bits)) % 16 == 0) ? 1 : 0;
   prm.tile_bulk = (pl.parts == 1 && prm.cb_bulk) ? 1 : 0;
   cudaStream_t st = (cudaStream_t)stream;
-  if (bits == 3) return M > 8 ? launch<3, 2, 8>(prm, pl, st) : M > 1 ? launch<3, 1, 8>(prm, pl, st) : launch<3, 1, 1>(prm, pl, st);
-  return M > 8 ? launch<2, 2, 8>(prm, pl, st) : M > 1 ? launch<2, 1, 8>(prm, pl, st) : launch<2, 1, 1>(prm, pl, st);
+#define NB_GEMV_DISPATCH(B, XSV)                                                               \
+  (M > 8 ? launch<B, 2, 8, XSV>(prm, pl, st) : M > 1 ? launch<B, 1, 8, XSV>(prm, pl, st) : launch<B, 1, 1, XSV>(prm, pl, st))
+  if (bits == 3) return x_terms == 2 ? NB_GEMV_DISPATCH(3, 2) : NB_GEMV_DISPATCH(3, 1);
+  return x_terms == 2 ? NB_GEMV_DISPATCH(2, 2) : NB_GEMV_DISPATCH(2, 1);
+#undef NB_GEMV_DISPATCH
 }
 
 // ------------------------------------------------------------------------------------------------

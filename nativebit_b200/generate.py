@@ -1,0 +1,390 @@
+"""Packed LLaMA-style decoder with a static KV cache, built from PackedLinear, tensor-parallel over
+1/2/4/8 GPUs.  Mirrors the reference's decode interface (inference/generate_torch.py): PackedGPT
+(:135-162: pre-norm blocks, fused qkv chunked [q|k|v] :74-75, interleaved-pair RoPE theta=1e4
+:41-60, RMSNorm x/sqrt(mean(x^2)+1e-6)*w :29-38, SwiGLU :109-117, tied LM head with 30*tanh(./30)
+soft-cap :157-159), init_kv_cache (:269-277), load_packed_model (:176-266, .nbpack.npz keys) and
+benchmark (:280-320, same result keys), plus prefill/step functions shaped like the JAX twin's
+(inference/generate.py:163-184).
+
+Differences, all deliberate: packed bytes go straight to the device (no unpack -> repack round
+trip); gate and up are one fused packed matrix; the decode step is captured once in a CUDA graph
+and replayed with the position and the next token held on the device (the reference syncs with
+the host every token); the cache is attended over its valid prefix only in eager mode and under a
+position mask in the captured step; ranks of a tensor-parallel group hold row shards of
+q/k/v/gate/up and whole-block column shards of out_proj/down and all-reduce after each of the two.
+"""
+from __future__ import annotations
+
+import math
+import re
+import time
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from . import ops, synthetic, tp
+from .packed_linear import PackedLinear
+
+
+@dataclass
+class ModelConfig:
+    """Shape of the packed decoder.  Defaults: the 2.2B benchmark configuration (26 layers, hidden
+    2560, 32 heads, SwiGLU 6912, vocab 32000, context 1024, 3-bit block-128 codebooks)."""
+    vocab_size: int = 32000
+    n_layers: int = 26
+    n_embd: int = 2560
+    n_head: int = 32
+    ffn_hidden: int = 6912
+    context_len: int = 1024
+    block_size: int = 128
+    bits: int = 3
+    rope_theta: float = 10000.0
+    norm_eps: float = 1e-6
+    logit_cap: float = 30.0
+
+    @property
+    def head_dim(self) -> int:
+        return self.n_embd // self.n_head
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return xf / torch.sqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * weight
+
+
+def precompute_rope(head_dim: int, max_len: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    freqs = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+    t = torch.arange(max_len, dtype=torch.float32, device=device)
+    f = torch.outer(t, freqs)
+    return torch.cos(f).repeat_interleave(2, dim=-1), torch.sin(f).repeat_interleave(2, dim=-1)
+
+
+def apply_rope(x: torch.Tensor, cos2: torch.Tensor, sin2: torch.Tensor) -> torch.Tensor:
+    """x (B, H, T, hd); cos2/sin2 (T, hd) already repeated per pair (interleaved-pair rotation)."""
+    x1, x2 = x[..., ::2], x[..., 1::2]
+    rot = torch.stack((-x2, x1), dim=-1).reshape(x.shape)
+    return x * cos2 + rot * sin2
+
+
+class PackedBlock(torch.nn.Module):
+    def __init__(self, qkv, out_proj, gate_up, down, ln1, ln2):
+        super().__init__()
+        self.qkv, self.out_proj, self.gate_up, self.down = qkv, out_proj, gate_up, down
+        self.register_buffer("ln1", ln1)
+        self.register_buffer("ln2", ln2)
+
+
+class PackedGPT(torch.nn.Module):
+    """Inference-only packed decoder (one tensor-parallel rank's shard)."""
+
+    def __init__(self, config: ModelConfig, embedding: torch.Tensor, blocks: list[PackedBlock], ln_f: torch.Tensor,
+                 tp_rank: int = 0, tp_size: int = 1, group=None):
+        super().__init__()
+        self.config = config
+        self.n_layers, self.n_embd, self.n_head, self.context_len = (config.n_layers, config.n_embd, config.n_head,
+                                                                     config.context_len)
+        self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
+        assert config.n_head % tp_size == 0
+        self.heads_local = config.n_head // tp_size
+        self.register_buffer("embedding", embedding)
+        self.blocks = torch.nn.ModuleList(blocks)
+        self.register_buffer("ln_f", ln_f)
+        cos2, sin2 = precompute_rope(config.head_dim, config.context_len, config.rope_theta, embedding.device)
+        self.register_buffer("cos2", cos2)
+        self.register_buffer("sin2", sin2)
+        # columns of the attention output this rank feeds to out_proj, and the whole codebook blocks covering them
+        c0 = self.heads_local * config.head_dim * tp_rank
+        c1 = c0 + self.heads_local * config.head_dim
+        self.o_col0 = c0 - (c0 // config.block_size) * config.block_size      # offset inside the first block
+        self.o_cols = blocks[0].out_proj.in_features if blocks else 0
+
+    # ------------------------------------------------------------------ pieces
+    def _all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.tp_size > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+        return t
+
+    def _attn_inputs(self, x, blk, pos0: int | torch.Tensor, T: int):
+        B = x.shape[0]
+        hd, Hl = self.config.head_dim, self.heads_local
+        qkv = blk.qkv(rms_norm(x, blk.ln1, self.config.norm_eps)).float()
+        q, k, v = qkv.split(Hl * hd, dim=-1)
+        q = q.reshape(B, T, Hl, hd).transpose(1, 2)
+        k = k.reshape(B, T, Hl, hd).transpose(1, 2)
+        v = v.reshape(B, T, Hl, hd).transpose(1, 2)
+        if isinstance(pos0, int):
+            cos2, sin2 = self.cos2[pos0:pos0 + T], self.sin2[pos0:pos0 + T]
+        else:  # device position (captured decode step, T == 1)
+            cos2, sin2 = self.cos2.index_select(0, pos0), self.sin2.index_select(0, pos0)
+        return apply_rope(q, cos2, sin2), apply_rope(k, cos2, sin2), v
+
+    def _finish_block(self, x, blk, attn_out):
+        """attn_out (B, T, Hl*hd) -> residual adds of out_proj and the SwiGLU FFN."""
+        if attn_out.shape[-1] != self.o_cols:  # pad to the whole codebook blocks covering this rank's columns
+            padded = attn_out.new_zeros(*attn_out.shape[:-1], self.o_cols)
+            padded[..., self.o_col0:self.o_col0 + attn_out.shape[-1]] = attn_out
+            attn_out = padded
+        x = x + self._all_reduce(blk.out_proj(attn_out).float())
+        gu = blk.gate_up(rms_norm(x, blk.ln2, self.config.norm_eps)).float()
+        gate, up = gu.split(gu.shape[-1] // 2, dim=-1)
+        return x + self._all_reduce(blk.down(F.silu(gate) * up).float())
+
+    def _logits(self, x):
+        x = rms_norm(x, self.ln_f, self.config.norm_eps)
+        logits = x.to(self.embedding.dtype) @ self.embedding.T
+        cap = self.config.logit_cap
+        return cap * torch.tanh(logits.float() / cap)
+
+    # ------------------------------------------------------------------ eager forward (prefill, tests)
+    @torch.no_grad()
+    def forward(self, idx: torch.Tensor, kv_caches=None):
+        """idx (B, T) int64 -> logits (B, T, V) fp32 [, new caches].  kv_caches: list of
+        (k_buf, v_buf, cache_len) as returned by init_kv_cache."""
+        B, T = idx.shape
+        x = self.embedding[idx].float()
+        new_caches = []
+        for i, blk in enumerate(self.blocks):
+            if kv_caches is not None:
+                k_buf, v_buf, cache_len = kv_caches[i]
+                q, k, v = self._attn_inputs(x, blk, cache_len, T)
+                k_buf[:, :, cache_len:cache_len + T] = k
+                v_buf[:, :, cache_len:cache_len + T] = v
+                new_len = cache_len + T
+                kk, vv = k_buf[:, :, :new_len], v_buf[:, :, :new_len]
+                q_pos = cache_len + torch.arange(T, device=x.device)
+                mask = torch.arange(new_len, device=x.device)[None, :] <= q_pos[:, None]
+                out = F.scaled_dot_product_attention(q, kk, vv, attn_mask=mask[None, None])
+                new_caches.append((k_buf, v_buf, new_len))
+            else:
+                q, k, v = self._attn_inputs(x, blk, 0, T)
+                out = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+            x = self._finish_block(x, blk, out.transpose(1, 2).reshape(B, T, -1))
+        logits = self._logits(x)
+        return (logits, new_caches) if kv_caches is not None else logits
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def random_init(config: ModelConfig, seed: int = 0, device="cuda", tp_rank: int = 0, tp_size: int = 1, group=None):
+        """Seeded random-init model: every rank generates the same global packed weights (per-layer
+        seeds seed*1000 + layer*10 + j) and keeps its shard; embedding ~N(0, 0.02) in bf16, norms 1."""
+        dev = torch.device(device)
+        g = torch.Generator(device=dev).manual_seed(seed)
+        emb = (torch.randn(config.vocab_size, config.n_embd, device=dev, generator=g) * 0.02).bfloat16()
+        C, Fh, bits = config.n_embd, config.ffn_hidden, config.bits
+        blocks = []
+        for l in range(config.n_layers):
+            s = seed * 1000 + l * 10
+            full = {"qkv": synthetic.synthetic_packed(3 * C, C, bits, s + 0, dev),
+                    "out_proj": synthetic.synthetic_packed(C, C, bits, s + 1, dev),
+                    "gate": synthetic.synthetic_packed(Fh, C, bits, s + 2, dev),
+                    "up": synthetic.synthetic_packed(Fh, C, bits, s + 3, dev),
+                    "down": synthetic.synthetic_packed(C, Fh, bits, s + 4, dev)}
+            ones = torch.ones(C, device=dev)
+            blocks.append(shard_block(config, full, ones, ones.clone(), tp_rank, tp_size))
+            del full
+        return PackedGPT(config, emb, blocks, torch.ones(C, device=dev), tp_rank, tp_size, group)
+
+
+def shard_block(config: ModelConfig, full: dict, ln1, ln2, tp_rank: int, tp_size: int) -> PackedBlock:
+    """Global packed (bytes, codebook) pairs of one layer -> this rank's PackedBlock."""
+    C, Fh, bits, bs, hd = config.n_embd, config.ffn_hidden, config.bits, config.block_size, config.head_dim
+    Hl = config.n_head // tp_size
+    rows = Hl * hd
+    r0 = tp_rank * rows
+    # q, k, v rows of this rank's heads out of the fused [q|k|v] row order
+    parts = [tp.slice_rows(*full["qkv"], 3 * C, C, bits, j * C + r0, rows, bs) for j in range(3)]
+    qkv = PackedLinear(torch.cat([p for p, _ in parts]), torch.cat([c for _, c in parts]), 3 * rows, C, bits, bs)
+    # out_proj: the whole codebook blocks that cover columns [r0, r0 + rows)
+    b0, b1 = r0 // bs, (r0 + rows + bs - 1) // bs
+    p, c = tp.slice_cols(*full["out_proj"], C, C, bits, b0, b1 - b0, bs)
+    out_proj = PackedLinear(p, c, C, (b1 - b0) * bs, bits, bs)
+    # FFN: whole blocks of hidden channels; gate rows then up rows in one matrix
+    ch0, chn = tp.ffn_shard_plan(Fh, tp_size, tp_rank, bs)
+    gp, gc = tp.slice_rows(*full["gate"], Fh, C, bits, ch0, chn, bs)
+    up, uc = tp.slice_rows(*full["up"], Fh, C, bits, ch0, chn, bs)
+    gate_up = PackedLinear(torch.cat([gp, up]), torch.cat([gc, uc]), 2 * chn, C, bits, bs)
+    dp, dc = tp.slice_cols(*full["down"], C, Fh, bits, ch0 // bs, chn // bs, bs)
+    down = PackedLinear(dp, dc, C, chn, bits, bs)
+    return PackedBlock(qkv, out_proj, gate_up, down, ln1, ln2)
+
+
+def init_kv_cache(model: PackedGPT, batch_size: int = 1, device="cuda"):
+    """fp32 (B, local heads, context_len, head_dim) key and value buffers per layer and a length
+    (inference/generate_torch.py:269-277)."""
+    hd = model.config.head_dim
+    caches = []
+    for _ in range(model.n_layers):
+        k = torch.zeros(batch_size, model.heads_local, model.context_len, hd, device=device, dtype=torch.float32)
+        caches.append((k, torch.zeros_like(k), 0))
+    return caches
+
+
+def prefill(model: PackedGPT, x: torch.Tensor, caches):
+    """(logits[:, -1, :], caches) for a prompt (inference/generate.py:169-175)."""
+    logits, caches = model(x, kv_caches=caches)
+    return logits[:, -1, :], caches
+
+
+def step(model: PackedGPT, x: torch.Tensor, caches):
+    """(logits[:, -1, :], caches) for one new token per sequence (inference/generate.py:177-183)."""
+    logits, caches = model(x, kv_caches=caches)
+    return logits[:, -1, :], caches
+
+
+class DecodeSession:
+    """Greedy decoding with the whole step in one CUDA graph: token, position and caches live on the
+    device, the next token is the argmax written back into the token buffer, so N steps are N graph
+    replays without a host round trip.  Attention in the captured step covers the full context
+    buffer under a position mask (static shapes), as the reference's cached path does
+    (inference/generate_torch.py:91-97)."""
+
+    def __init__(self, model: PackedGPT, batch_size: int = 1, use_graph: bool = True):
+        self.model, self.B = model, batch_size
+        dev = model.embedding.device
+        self.dev = dev
+        self.caches = init_kv_cache(model, batch_size, dev)
+        self.pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self.token = torch.zeros(batch_size, 1, dtype=torch.long, device=dev)
+        self.logits = torch.zeros(batch_size, model.config.vocab_size, dtype=torch.float32, device=dev)
+        self.k_idx = torch.arange(model.context_len, device=dev)
+        self.use_graph = use_graph
+        self.graph = None
+        self.stream = torch.cuda.Stream(device=dev)
+
+    @torch.no_grad()
+    def prefill(self, prompt: torch.Tensor) -> torch.Tensor:
+        """prompt (B, T): fills the caches, sets the position and the first generated token."""
+        caches = [(k, v, 0) for k, v, _ in self.caches]
+        logits, caches = self.model(prompt, kv_caches=caches)
+        self.caches = caches
+        self.pos.fill_(prompt.shape[1])
+        self.logits.copy_(logits[:, -1, :])
+        self.token.copy_(self.logits.argmax(-1, keepdim=True))
+        return self.logits
+
+    @torch.no_grad()
+    def _step_body(self):
+        m, cfg = self.model, self.model.config
+        B = self.B
+        x = m.embedding[self.token].float()                      # (B, 1, C)
+        mask = (self.k_idx <= self.pos)[None, None, None, :]     # (1, 1, 1, ctx)
+        for i, blk in enumerate(m.blocks):
+            k_buf, v_buf, _ = self.caches[i]
+            q, k, v = m._attn_inputs(x, blk, self.pos, 1)
+            k_buf.index_copy_(2, self.pos, k)
+            v_buf.index_copy_(2, self.pos, v)
+            out = F.scaled_dot_product_attention(q, k_buf, v_buf, attn_mask=mask)
+            x = m._finish_block(x, blk, out.transpose(1, 2).reshape(B, 1, -1))
+        self.logits.copy_(m._logits(x)[:, -1, :])
+        self.token.copy_(self.logits.argmax(-1, keepdim=True))
+        self.pos.add_(1)
+
+    def step(self) -> None:
+        """One decode step for every sequence: consumes self.token, leaves the next token there."""
+        if not self.use_graph:
+            self._step_body()
+            return
+        if self.graph is None:
+            with torch.cuda.stream(self.stream):
+                saved = (self.pos.clone(), self.token.clone(), self.logits.clone())
+                for _ in range(2):                                # warm-up outside capture
+                    self._step_body()
+                self.stream.synchronize()
+                self.pos.copy_(saved[0]); self.token.copy_(saved[1]); self.logits.copy_(saved[2])
+                self.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.graph, stream=self.stream):
+                    self._step_body()
+                # the capture does not execute: state is unchanged; stale cache slots past `pos` are masked
+            torch.cuda.current_stream().wait_stream(self.stream)
+        self.graph.replay()
+
+    @torch.no_grad()
+    def generate(self, prompt: torch.Tensor, n_generate: int) -> torch.Tensor:
+        """Greedy continuation (B, n_generate) of prompt (B, T)."""
+        self.prefill(prompt)
+        out = [self.token.clone()]
+        for _ in range(n_generate - 1):
+            self.step()
+            out.append(self.token.clone())
+        return torch.cat(out, dim=1)
+
+
+def benchmark(model: PackedGPT, prompt_tokens, n_generate: int = 128, n_runs: int = 3, device="cuda", batch_size: int = 1):
+    """Decode-speed benchmark with the reference's result keys (inference/generate_torch.py:280-320)
+    plus the JAX twin's prefill fields (inference/generate.py:270-280)."""
+    dev = model.embedding.device
+    prompt = torch.as_tensor(prompt_tokens, dtype=torch.long, device=dev).reshape(1, -1).repeat(batch_size, 1)
+    sess = DecodeSession(model, batch_size)
+    sess.prefill(prompt)
+    sess.step()
+    torch.cuda.synchronize()
+    pre, gen = [], []
+    for _ in range(n_runs):
+        t0 = time.perf_counter()
+        sess.prefill(prompt)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        for _ in range(n_generate):
+            sess.step()
+        torch.cuda.synchronize()
+        pre.append(t1 - t0)
+        gen.append(time.perf_counter() - t1)
+    g, p = sum(gen) / len(gen), sum(pre) / len(pre)
+    return {"label": f"b{batch_size}", "prompt_len": prompt.shape[1], "n_generate": n_generate, "n_runs": n_runs,
+            "prefill_ms": round(p * 1e3, 2), "prefill_tps": round(prompt.numel() / p, 1),
+            "generate_ms": round(g * 1e3, 2), "generate_tps": round(n_generate * batch_size / g, 1),
+            "per_token_ms": round(g / n_generate * 1e3, 3)}
+
+
+# ---------------------------------------------------------------------- checkpoints
+def _nat_key(s: str):
+    return [int(c) if c.isdigit() else c for c in re.split(r"(\d+)", s)]
+
+
+def load_packed_model(packed_path: str, config, device="cuda", tp_rank: int = 0, tp_size: int = 1, group=None) -> PackedGPT:
+    """Load a .nbpack.npz written by the reference's inference/pack.py (keys idx./cb./shape./idxshape./
+    param./__metadata__, :110-151) into a PackedGPT.  Layers are matched to the packed keys in natural
+    sort order, five per block in the order qkv, out_proj, gate, up, down
+    (inference/generate_torch.py:224-241).  Packed bytes are uploaded as stored; fp32 codebooks are
+    kept fp32."""
+    pack = np.load(packed_path)
+    dev = torch.device(device)
+    cfg = config if isinstance(config, ModelConfig) else ModelConfig(
+        vocab_size=config.vocab_size, n_layers=config.n_layers, n_embd=config.n_embd, n_head=config.n_head,
+        ffn_hidden=config.ffn_hidden, context_len=config.context_len,
+        block_size=getattr(config, "block_size", 128), bits=int(math.log2(getattr(config, "n_codebook", 8))))
+    keys = sorted((k[4:] for k in pack.files if k.startswith("idx.")), key=_nat_key)
+    if len(keys) != 5 * cfg.n_layers:
+        raise RuntimeError(f"expected {5 * cfg.n_layers} packed layers, found {len(keys)}")
+
+    def get(prefix):
+        p = torch.from_numpy(np.ascontiguousarray(pack[f"idx.{prefix}"])).to(dev)
+        c = torch.from_numpy(np.ascontiguousarray(pack[f"cb.{prefix}"])).to(dev)
+        return p, c
+
+    params = {}
+    for k in pack.files:
+        if k.startswith("param."):
+            arr = pack[k]
+            if arr.dtype.kind == "V":
+                arr = np.frombuffer(arr.tobytes(), dtype=np.float16).reshape(arr.shape)
+            params[k[6:].replace(".", "/")] = arr
+    C = cfg.n_embd
+    blocks = []
+    for l in range(cfg.n_layers):
+        names = keys[5 * l:5 * l + 5]
+        full = dict(zip(("qkv", "out_proj", "gate", "up", "down"), (get(n) for n in names)))
+        ln = []
+        for j in range(2):
+            w = params.get(f"params/block_{l}/RMSNorm_{j}/weight")
+            ln.append(torch.from_numpy(w.astype(np.float32)).to(dev) if w is not None else torch.ones(C, device=dev))
+        blocks.append(shard_block(cfg, full, ln[0], ln[1], tp_rank, tp_size))
+    emb = params.get("params/embedding")
+    if emb is None:
+        raise RuntimeError("checkpoint has no params/embedding")
+    emb_t = torch.from_numpy(np.ascontiguousarray(emb)).to(dev)
+    lnf = params.get("params/ln_f/weight")
+    lnf_t = torch.from_numpy(lnf.astype(np.float32)).to(dev) if lnf is not None else torch.ones(C, device=dev)
+    return PackedGPT(cfg, emb_t, blocks, lnf_t, tp_rank, tp_size, group)

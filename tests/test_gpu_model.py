@@ -1,0 +1,118 @@
+"""The packed decoder on the GPU against the reference's own PackedGPT logits (golden) and the dense
+oracle: eager prefill + cached steps, the CUDA-graph decode session, teacher-forced greedy agreement,
+and the tensor-parallel block shards evaluated on one GPU."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nb_model_oracle as mo
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def gm():
+    return np.load(os.path.join(ROOT, "tests", "golden", "reference_model.npz"))
+
+
+def _build(gm, dev, tp_rank=0, tp_size=1):
+    from nativebit_b200 import generate as G
+    V, L, C, H, Fh, ctx = (int(v) for v in gm["cfg"])
+    cfg = G.ModelConfig(vocab_size=V, n_layers=L, n_embd=C, n_head=H, ffn_hidden=Fh, context_len=ctx)
+    cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    blocks = []
+    for l in range(L):
+        full = {k2: (cu(gm[f"p_{k1}{l}"]), cu(gm[f"c_{k1}{l}"])) for k1, k2 in
+                (("qkv", "qkv"), ("out", "out_proj"), ("gate", "gate"), ("up", "up"), ("down", "down"))}
+        ones = torch.ones(C, device=dev)
+        blocks.append(G.shard_block(cfg, full, ones, ones.clone(), tp_rank, tp_size))
+    emb = cu(gm["embedding"])
+    return G.PackedGPT(cfg, emb, blocks, torch.ones(C, device=dev), tp_rank, tp_size), cfg
+
+
+def test_decoder_matches_reference_logits(built_lib, gm):
+    from nativebit_b200 import generate as G
+    dev = torch.device("cuda:0")
+    model, cfg = _build(gm, dev)
+    caches = G.init_kv_cache(model, 1, dev)
+    prompt = torch.from_numpy(gm["prompt"]).to(dev)
+    logits, caches = model(prompt, kv_caches=caches)
+    ref = gm["logits_prompt"]
+    # fp16 activations inside the packed linears: 2e-3 of max|logit| is the stated gate
+    assert np.abs(logits[0].cpu().numpy() - ref).max() <= 2e-3 * np.abs(ref).max()
+    for t, r in zip(gm["forced"].tolist(), gm["logits_steps"]):
+        lg, caches = G.step(model, torch.tensor([[t]], device=dev), caches)
+        assert np.abs(lg[0].cpu().numpy() - r).max() <= 2e-3 * np.abs(ref).max()
+    # no-cache forward equals the cached one
+    nc = model(prompt)
+    assert (nc - logits).abs().max() <= 1e-5
+
+
+def test_graph_session_equals_eager_and_oracle_greedy(built_lib, gm):
+    """Free-running greedy decode from the CUDA-graph session against the dense oracle run
+    teacher-forced on the session's tokens: the oracle's argmax must agree at >= 99 % of steps."""
+    from nativebit_b200 import generate as G
+    dev = torch.device("cuda:0")
+    model, cfg = _build(gm, dev)
+    prompt = torch.from_numpy(gm["prompt"]).to(dev)
+    n_gen = 20
+    toks_graph = G.DecodeSession(model, 1, use_graph=True).generate(prompt, n_gen)
+    toks_eager = G.DecodeSession(model, 1, use_graph=False).generate(prompt, n_gen)
+    assert torch.equal(toks_graph, toks_eager)
+    V, L, C, H, Fh, ctx = (int(v) for v in gm["cfg"])
+    layers = {f"{nm}{l}": (gm[f"p_{nm}{l}"], gm[f"c_{nm}{l}"], tuple(int(v) for v in gm[f"s_{nm}{l}"]))
+              for l in range(L) for nm in ("qkv", "out", "gate", "up", "down")}
+    om = mo.DenseModel(mo.dense_weights_from_packed(layers, gm["embedding"], L), L, H, ctx)
+    caches = om.init_cache()
+    lg = om.forward(torch.from_numpy(gm["prompt"]), caches)[0, -1]
+    agree, ours = 0, toks_graph[0].cpu().tolist()
+    for i, t in enumerate(ours):
+        agree += int(int(lg.argmax()) == t)
+        lg = om.forward(torch.tensor([[t]]), caches)[0, -1]
+    assert agree / len(ours) >= 0.99
+
+
+def test_batched_session(built_lib, gm):
+    from nativebit_b200 import generate as G
+    dev = torch.device("cuda:0")
+    model, cfg = _build(gm, dev)
+    prompt = torch.from_numpy(gm["prompt"]).to(dev)
+    one = G.DecodeSession(model, 1).generate(prompt, 8)
+    four = G.DecodeSession(model, 4).generate(prompt.repeat(4, 1), 8)
+    assert all(torch.equal(four[i:i + 1], one) for i in range(4))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_shards_sum_to_single_rank(built_lib, gm, world):
+    """All ranks' shards evaluated one after another on one GPU with the all-reduce done by hand:
+    the block output equals the unsharded block's (exact up to fp32 summation order)."""
+    from nativebit_b200 import generate as G
+    dev = torch.device("cuda:0")
+    full, cfg = _build(gm, dev)
+    ranks = [_build(gm, dev, r, world)[0] for r in range(world)]
+    x = torch.randn(1, 3, cfg.n_embd, device=dev, generator=torch.Generator(device=dev).manual_seed(1))
+    blk = full.blocks[0]
+    q, k, v = full._attn_inputs(x, blk, 0, 3)
+    att = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(1, 3, -1)
+    ref_o = blk.out_proj(att).float()
+    ref_ffn = blk.down(torch.nn.functional.silu(blk.gate_up(x).float()[..., :cfg.ffn_hidden]) *
+                       blk.gate_up(x).float()[..., cfg.ffn_hidden:]).float()
+    acc_o = torch.zeros_like(ref_o)
+    acc_f = torch.zeros_like(ref_ffn)
+    for r, m in enumerate(ranks):
+        b = m.blocks[0]
+        qr, kr, vr = m._attn_inputs(x, b, 0, 3)
+        hl = cfg.n_head // world
+        assert torch.equal(qr, q[:, r * hl:(r + 1) * hl]) and torch.equal(vr, v[:, r * hl:(r + 1) * hl])
+        a = torch.nn.functional.scaled_dot_product_attention(qr, kr, vr, is_causal=True).transpose(1, 2).reshape(1, 3, -1)
+        pad = a.new_zeros(1, 3, m.o_cols)
+        pad[..., m.o_col0:m.o_col0 + a.shape[-1]] = a
+        acc_o += b.out_proj(pad).float()
+        gu = b.gate_up(x).float()
+        g_, u_ = gu.split(gu.shape[-1] // 2, dim=-1)
+        acc_f += b.down(torch.nn.functional.silu(g_) * u_).float()
+    assert (acc_o - ref_o).abs().max() <= 1e-4 * ref_o.abs().max()
+    assert (acc_f - ref_ffn).abs().max() <= 1e-4 * ref_ffn.abs().max()

@@ -140,6 +140,18 @@ def test_gemv_dtypes(dev, x_dtype, y_dtype):
     assert np.abs(y - ref).max() <= tol * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("n,k,m", [(320, 2560, 1), (320, 2560, 5), (2560, 6912, 16), (6912, 2560, 1)])
+def test_gemv_fp32_activations_keep_their_precision(dev, n, k, m):
+    """fp32 activations that are not representable in 16 bits are carried as two fp16 terms: the
+    result is as accurate as an fp32 reference (the reference's kernels take fp32 x)."""
+    from nativebit_b200 import ops
+    packed, cb, _ = o.make_packed_linear(n, k, 3, 77)
+    x = np.random.default_rng(5).standard_normal((m, k)).astype(np.float32)
+    ref = o.packed_linear_forward(x, packed, cb.astype(np.float32), n, k, 3, acc_dtype=np.float64)
+    y = ops.gemv(_cu(x, dev), _cu(packed, dev), _cu(cb, dev), 3, 128, n, k).double().cpu().numpy()
+    assert np.abs(y - ref).max() <= 2e-6 * np.abs(ref).max()
+
+
 def test_gemv_fp32_codebook(dev):
     y, ref = _gemv_case(dev, 3, 320, 2560, 2, seed=11, cb_dtype=torch.float32)
     assert np.abs(y - ref).max() <= 2e-5 * np.abs(ref).max()
