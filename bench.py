@@ -387,7 +387,12 @@ def run_ours(args):
             line["decode"] = decode
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # NCCL communicators cannot be torn down while CUDA graphs that captured their kernels are
+        # alive (destroy_process_group blocks); everything is released with the process instead.
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def run_kernel_only(args):
