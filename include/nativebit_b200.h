@@ -89,6 +89,27 @@ int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed, const void
             int bits, int block_size, int N, int K, void* y, int y_dtype, void* workspace,
             size_t workspace_bytes, void* stream);
 
+/* ---- prefill GEMM (many activation rows) on the tcgen05 tensor cores:
+ * y (M, N) = x (M, K) . W^T.  Replaces the unpack + gather + matmul of
+ * inference/triton_kernel.py:258-275 for large M and follows the any-M contract of
+ * nativebit_jax/packed_kernel.py:86-97, 151-178 (bf16 operands, fp32 accumulation).
+ * x: (M, K) bf16 row-major, 16-byte aligned; y: (M, N) NB_BF16 or NB_F32; K % 64 == 0 and
+ * K % block_size == 0; bits in {2,3,4}.  The weight is first dequantised to bf16 (the fp16
+ * codebook entries rounded to nearest even) into `workspace`, which must be 256-byte aligned and
+ * hold nb_prefill_workspace_bytes(M, N, K) bytes (N*K*2 + 256); its last 256 bytes carry a
+ * status word that must be zero before the first call and is set to NB_ERR_TIMEOUT if a bounded
+ * wait inside the kernel ran out. */
+size_t nb_prefill_workspace_bytes(int M, int N, int K);
+int nb_gemm_prefill(const void* x, int M, const uint8_t* packed, const void* codebook, int cb_dtype, int bits,
+                    int block_size, int N, int K, void* y, int y_dtype, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/* The tensor-core kernel alone: y (M, N) = x (M, K) . w (N, K)^T with x and w bf16 row-major
+ * (16-byte aligned, K % 64 == 0), y NB_BF16 or NB_F32, fp32 accumulation in tensor memory.
+ * `status` is a device int (zero before the first call) or NULL.  No counterpart in the
+ * reference, which calls a library matmul here. */
+int nb_gemm_bf16(const void* x, const void* w, int M, int N, int K, void* y, int y_dtype, int* status, void* stream);
+
 /* ---- nb_gemv without a caller-provided workspace.  No counterpart in the reference.
  * For callers that cannot allocate device memory — a plugin that is handed only its input and
  * output buffers, code that runs while a stream is being captured or under a frozen memory

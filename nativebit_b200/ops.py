@@ -127,3 +127,50 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: in
     if rc:
         _lib.check(rc, "nb_gemv")
     return out
+
+
+_prefill_ws: dict = {}
+
+
+def prefill_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Scratch for the dequantised bf16 weight of the prefill GEMM, one per (device, stream)."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    ws = _prefill_ws.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        _prefill_ws[key] = ws
+    return ws
+
+
+def gemm_prefill(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size: int,
+                 n: int, k: int, out_dtype: torch.dtype = torch.bfloat16, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y (M, n) = x (M, k) @ W.T on the tcgen05 tensor cores; x must be bf16."""
+    _need_cuda(x, packed, codebook)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != k:
+        raise RuntimeError(f"x must be a bf16 (M, {k}) tensor; got {x.dtype} {tuple(x.shape)}")
+    m = x.shape[0]
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=x.device)
+    l = _lib.lib()
+    with torch.cuda.device(x.device):
+        need = l.nb_prefill_workspace_bytes(m, n, k)
+        ws = prefill_workspace(x.device, need)
+        _lib.check(l.nb_gemm_prefill(x.data_ptr(), m, packed.data_ptr(), codebook.data_ptr(), _DTYPE[codebook.dtype], bits,
+                                     block_size, n, k, out.data_ptr(), _DTYPE[out.dtype], ws.data_ptr(), ws.numel(),
+                                     _stream()), "nb_gemm_prefill")
+    return out
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """y = x @ w.T for bf16 x (M, K) and w (N, K) with the hand-written tcgen05 kernel."""
+    _need_cuda(x, w)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[1] != w.shape[1]:
+        raise RuntimeError("gemm_bf16 needs bf16 x (M, K) and w (N, K)")
+    m, k = x.shape
+    n = w.shape[0]
+    out = torch.empty(m, n, dtype=out_dtype, device=x.device)
+    status = torch.zeros(1, dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().nb_gemm_bf16(x.data_ptr(), w.data_ptr(), m, n, k, out.data_ptr(), _DTYPE[out_dtype],
+                                           status.data_ptr(), _stream()), "nb_gemm_bf16")
+    return out

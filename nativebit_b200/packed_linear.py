@@ -84,6 +84,10 @@ class PackedLinear(torch.nn.Module):
                 ops.gemv(x_flat[r:r + GEMV_MAX_M], self.packed_indices, self.codebook, self.bits, self.block_size,
                          self.out_features, self.in_features, out=y[r:r + GEMV_MAX_M])
             return y
+        if x_flat.dtype == torch.bfloat16 and self.in_features % 64 == 0 and self.bits in (2, 3, 4):
+            # prefill: dequantise once to bf16, then the tcgen05 GEMM (fp32 accumulation, bf16 result)
+            return ops.gemm_prefill(x_flat, self.packed_indices, self.codebook, self.bits, self.block_size,
+                                    self.out_features, self.in_features, out_dtype=torch.bfloat16)
         wdt = x_flat.dtype if x_flat.dtype in (torch.float16, torch.bfloat16) else torch.float32
         w = ops.dequant(self.packed_indices, self.codebook, self.bits, self.block_size,
                         (self.out_features, self.in_features), dtype=wdt)

@@ -1,0 +1,63 @@
+"""The tcgen05 prefill GEMM through the C ABI: the tensor-core kernel alone against an fp64
+product of the same bf16 operands, and the packed entry point against the oracle (weights rounded
+to bf16 as the kernel does: tight; exact fp16 weights: the stated 2e-3 gate)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nb_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    return torch.device("cuda:0")
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 128, 128), (128, 256, 512), (256, 384, 2560), (200, 384, 256),
+                                   (130, 200, 128), (1, 128, 64), (2048, 2560, 1024)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_bf16_kernel(built_lib, m, n, k, out_dtype):
+    from nativebit_b200 import ops
+    dev = _dev()
+    g = torch.Generator(device=dev).manual_seed(m + n + k)
+    x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+    w = (torch.randn(n, k, device=dev, generator=g) * 0.05).bfloat16()
+    y = ops.gemm_bf16(x, w, out_dtype=out_dtype)
+    torch.cuda.synchronize()
+    ref = x.double() @ w.double().T
+    tol = 2e-5 if out_dtype == torch.float32 else 2.0 ** -8     # bf16 output: half an ulp of bf16
+    assert (y.double() - ref).abs().max() <= tol * ref.abs().max()
+
+
+@pytest.mark.parametrize("bits,m,n,k", [(3, 128, 256, 384), (3, 300, 640, 1280), (2, 256, 256, 512), (3, 2048, 6912, 2560),
+                                        (3, 2048, 2560, 6912)])
+def test_gemm_prefill_packed(built_lib, bits, m, n, k):
+    from nativebit_b200 import ops
+    dev = _dev()
+    packed, cb, _ = o.make_packed_linear(n, k, bits, seed=m)
+    x = o.make_activation(m, k, seed=m)                                  # bf16-representable
+    xt = torch.from_numpy(x).to(dev)
+    y = ops.gemm_prefill(xt.bfloat16(), torch.from_numpy(packed).to(dev), torch.from_numpy(cb).to(dev), bits, 128, n, k,
+                         out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    W = torch.from_numpy(o.dequant_packed(packed, cb.astype(np.float32), n, k, bits)).to(dev)
+    ref_exact = xt.double() @ W.double().T                               # the reference's fp32 weights
+    ref_bf16 = xt.double() @ W.bfloat16().double().T                     # weights as the kernel sees them
+    assert (y.double() - ref_bf16).abs().max() <= 2e-5 * ref_bf16.abs().max()
+    assert (y.double() - ref_exact).abs().max() <= 2e-3 * ref_exact.abs().max()
+
+
+def test_packed_linear_uses_tensor_core_path_for_long_inputs(built_lib):
+    import nativebit_b200 as nbt
+    dev = _dev()
+    n, k, m = 640, 1280, 512
+    packed, cb, _ = o.make_packed_linear(n, k, 3, seed=3)
+    lin = nbt.PackedLinear(torch.from_numpy(packed).to(dev), torch.from_numpy(cb).to(dev), n, k)
+    x = torch.from_numpy(o.make_activation(m, k, 4)).to(dev).bfloat16()
+    y = lin(x)
+    assert y.dtype == torch.bfloat16 and y.shape == (m, n)
+    ref = o.packed_linear_forward(x.float().cpu().numpy(), packed, cb.astype(np.float32), n, k, 3, acc_dtype=np.float64)
+    assert np.abs(y.double().cpu().numpy() - ref).max() <= (2.0 ** -8 + 2e-3) * np.abs(ref).max()
