@@ -343,6 +343,33 @@ def run_ours(args):
                "sample": "gate+up+down matvec of one layer (3 of the step's 78 matvecs), best of 3 after 1 warm-up; "
                          "reference CPU PyTorch path: unpack + gather + matmul per call"}
 
+    # ---- prefill dequant-GEMM (configs[2]): 2048 tokens against both FFN shapes, tcgen05 path
+    prefill = None
+    if world == 1 and not args.no_prefill:
+        prefill = {}
+        pk_bf16 = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("bf16_tflops", 1590.0) \
+            if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else 1590.0
+        for n, k, key in ((FFN, HIDDEN, "gate"), (HIDDEN, FFN, "down")):
+            lin = layers[0][key]
+            xp = synthetic.synthetic_activation(2048, k, 5, dev)
+            yp = torch.empty(2048, n, dtype=torch.bfloat16, device=dev)
+            wbf = ops.dequant(lin.packed_indices, lin.codebook, BITS, BLOCK, (n, k), torch.bfloat16)
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    ops.gemm_prefill(xp, lin.packed_indices, lin.codebook, BITS, BLOCK, n, k, out=yp)
+                    ops.gemm_bf16(xp, wbf)
+                    torch.matmul(xp, wbf.T)
+            t_full = timed(lambda: ops.gemm_prefill(xp, lin.packed_indices, lin.codebook, BITS, BLOCK, n, k, out=yp), 20) / 20
+            t_mma = timed(lambda: ops.gemm_bf16(xp, wbf), 20) / 20
+            t_lib = timed(lambda: torch.matmul(xp, wbf.T), 20) / 20
+            fl = 2.0 * 2048 * n * k
+            prefill[f"2048x{n}x{k}"] = {"dequant_plus_gemm_us": round(t_full * 1e3, 1), "gemm_only_us": round(t_mma * 1e3, 1),
+                                        "library_gemm_us": round(t_lib * 1e3, 1),
+                                        "TFLOPs_fused_call": round(fl / (t_full * 1e-3) / 1e12, 1),
+                                        "TFLOPs_gemm_only": round(fl / (t_mma * 1e-3) / 1e12, 1),
+                                        "frac_of_measured_bf16_peak_gemm_only": round(fl / (t_mma * 1e-3) / 1e12 / pk_bf16, 3)}
+            del wbf, xp, yp
+
     # ---- the full 2.2B packed decoder (configs[3]): 128-token prompt, 256 greedy tokens, batch 1
     decode = None
     if not args.no_decode:
@@ -385,6 +412,8 @@ def run_ours(args):
             line["cpu_baseline"] = cpu
         if decode is not None:
             line["decode"] = decode
+        if prefill is not None:
+            line["prefill"] = prefill
         print(json.dumps(line))
     if world > 1:
         # NCCL communicators cannot be torn down while CUDA graphs that captured their kernels are
@@ -426,6 +455,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 2048-token prefill GEMM leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the 2.2B decoder leg")
     ap.add_argument("--kernel-only", type=int, nargs=3, metavar=("N", "K", "M"), default=None,
                     help="launch one GEMV shape a few times and exit (profiling case)")

@@ -7,15 +7,17 @@
 // rounded to bf16, as in the reference's any-M kernel, nativebit_jax/packed_kernel.py:151-159),
 // products are accumulated in fp32.
 //
-// Kernel: one CTA per 128 x BN output tile (BN = 256 or 128), 192 threads:
+// Kernel: persistent, one CTA per SM walking 128 x BN output tiles (BN = a multiple of 16 in
+// [128, 256] chosen to fill the last wave), two accumulator buffers in tensor memory, 192 threads:
 //   warp 0   one lane issues TMA tile loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of a
 //            128 x 64 slab of X and a BN x 64 slab of W per k-step into a ring of shared-memory
 //            stages, each completing on the stage's "full" mbarrier;
-//   warp 1   allocates BN columns of tensor memory; one lane waits for a full stage and issues
+//   warp 1   allocates the 512 columns of tensor memory; one lane waits for a full stage and issues
 //            four tcgen05.mma (M=128, N=BN, K=16) per stage from shared-memory descriptors, then
 //            tcgen05.commit on the stage's "empty" barrier (and on the accumulator barrier at the end);
-//   warps 2-5  epilogue: each warp owns one 32-lane quadrant of tensor memory, reads it with
-//            tcgen05.ld (32 columns at a time), converts and stores its 32 rows of Y.
+//   warps 2-5  epilogue: each warp owns one 32-lane quadrant of tensor memory, reads the finished
+//            buffer with tcgen05.ld (16 columns at a time), converts and stores its 32 rows of Y,
+//            then hands the buffer back, while the MMA warp already fills the other buffer.
 // Every mbarrier wait is bounded: after kSpinLimit probes the waiter raises a shared abort flag,
 // writes NB_ERR_TIMEOUT to the status word and all roles fall through to the common exit, where
 // tensor memory is freed.
@@ -23,6 +25,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <mutex>
 
@@ -79,41 +82,52 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s2u(bar)) : "memory");
 }
 
-template <int BN> struct GemmCfg {
-  static constexpr int kStages = BN == 256 ? 4 : 6;
-  static constexpr int kABytes = kBM * kBK * 2;
-  static constexpr int kBBytes = BN * kBK * 2;
-  static constexpr int kSmem = kStages * (kABytes + kBBytes) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+struct GemmCfg {
+  static constexpr int kMaxStages = 8;
+  static constexpr int kMaxBN = 256;
+  static constexpr int kABytes = kBM * kBK * 2;          // 16 KB
+  static constexpr int kRing = 4 * (kABytes + kMaxBN * kBK * 2);  // 192 KB of operand stages
+  static constexpr int kSmem = kRing + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  // number of stages that fit the ring for a tile width (4 at BN = 256, 5 at 144, 6 at 128)
+  __host__ __device__ static constexpr int stages(int bn) {
+    return kRing / (kABytes + bn * kBK * 2) < kMaxStages ? kRing / (kABytes + bn * kBK * 2) : kMaxStages;
+  }
+  static constexpr int kTmemCols = 512;                  // two accumulator buffers of up to 256 columns
 };
 
-template <int BN>
+// Persistent kernel: CTA b works on output tiles b, b + gridDim.x, ...; tile t covers rows
+// 128*(t % m_tiles) and columns BN*(t / m_tiles), so CTAs running together share a W slab in L2.
+// Two accumulator buffers in tensor memory let the epilogue of one tile overlap the MMAs of the next.
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* __restrict__ y,
-                 int y_dtype, int M, int N, int K, int* status) {
-  using Cfg = GemmCfg<BN>;
-  constexpr int S = Cfg::kStages;
+                 int y_dtype, int M, int N, int K, int BN, int m_tiles, int n_tiles, int* status) {
+  using Cfg = GemmCfg;
+  const int S = Cfg::stages(BN);
+  const int b_bytes = BN * kBK * 2;   // multiple of 1024 because BN is a multiple of 16
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
   uint8_t* sB = smem + S * Cfg::kABytes;
-  uint64_t* full = reinterpret_cast<uint64_t*>(sB + S * Cfg::kBBytes);
-  uint64_t* empty = full + S;
-  uint64_t* accum = empty + S;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::kRing);
+  uint64_t* empty = full + Cfg::kMaxStages;
+  uint64_t* acc_full = empty + Cfg::kMaxStages;     // [2] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + 2; // [2] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
   const int KT = K / kBK;
+  const int n_total = m_tiles * n_tiles;
+  const uint32_t stage_bytes = (uint32_t)(Cfg::kABytes + b_bytes);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { bar_init(&full[s], 1); bar_init(&empty[s], 1); }
-    bar_init(accum, 1);
+    for (int b = 0; b < 2; ++b) { bar_init(&acc_full[b], 1); bar_init(&acc_empty[b], 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // tensor-memory allocation is a warp-wide operation
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"((uint32_t)Cfg::kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -123,83 +137,115 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {  // ---- TMA producer
-      for (int kt = 0; kt < KT; ++kt) {
-        const int s = kt % S;
-        if (!bar_wait(&empty[s], ((kt / S) & 1) ^ 1, abort_flag, status)) break;
-        bar_expect_tx(&full[s], Cfg::kABytes + Cfg::kBBytes);
-        tma_load_2d(sA + s * Cfg::kABytes, &map_x, &full[s], kt * kBK, m0);
-        tma_load_2d(sB + s * Cfg::kBBytes, &map_w, &full[s], kt * kBK, n0);
+      int s = 0;           // ring position and its phase bit, carried across tiles
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < n_total; t += gridDim.x) {
+        const int m0 = (t % m_tiles) * kBM, n0 = (t / m_tiles) * BN;
+        bool ok = true;
+        for (int kt = 0; kt < KT; ++kt) {
+          ok = bar_wait(&empty[s], phase ^ 1, abort_flag, status);
+          if (!ok) break;
+          bar_expect_tx(&full[s], stage_bytes);
+          tma_load_2d(sA + s * Cfg::kABytes, &map_x, &full[s], kt * kBK, m0);
+          tma_load_2d(sB + s * b_bytes, &map_w, &full[s], kt * kBK, n0);
+          if (++s == S) { s = 0; phase ^= 1; }
+        }
+        if (!ok) break;
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ---- MMA issuer
       // instruction descriptor: fp32 accumulate, A and B bf16, both K-major, N = BN, M = 128
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-      bool ok = true;
-      for (int kt = 0; kt < KT && ok; ++kt) {
-        const int s = kt % S;
-        ok = bar_wait(&full[s], (kt / S) & 1, abort_flag, status);
-        if (!ok) break;
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      int s = 0, local = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < n_total; t += gridDim.x, ++local) {
+        const int buf = local & 1;
+        // wait until the epilogue has drained this accumulator buffer (first use passes at once)
+        bool ok = bar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag, status);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t da = smem_desc_sw128(sA + s * Cfg::kABytes), db = smem_desc_sw128(sB + s * Cfg::kBBytes);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * Cfg::kMaxBN);
+        for (int kt = 0; kt < KT && ok; ++kt) {
+          ok = bar_wait(&full[s], phase, abort_flag, status);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t da = smem_desc_sw128(sA + s * Cfg::kABytes), db = smem_desc_sw128(sB + s * b_bytes);
 #pragma unroll
-        for (int k4 = 0; k4 < kBK / 16; ++k4)  // 16 bf16 = 32 bytes = 2 descriptor address units per step
-          umma_bf16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
-        umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+          for (int k4 = 0; k4 < kBK / 16; ++k4)  // 16 bf16 = 32 bytes = 2 descriptor address units per step
+            umma_bf16(tmem_d, da + 2 * k4, db + 2 * k4, idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
+          umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+          if (++s == S) { s = 0; phase ^= 1; }
+        }
+        umma_commit(&acc_full[buf]);  // accumulator complete (or aborted: the epilogue checks the flag)
+        if (!ok) break;
       }
-      umma_commit(accum);        // accumulator complete (or pipeline aborted: the epilogue checks the flag)
     }
   } else {
     // ---- epilogue: warp w reads tensor-memory lanes 32*(w%4) .. +31 = rows m0 + 32*(w%4) + lane
     const int q = warp & 3;
-    const bool ok = bar_wait(accum, 0, abort_flag, status) && !*abort_flag;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int m = m0 + q * 32 + lane;
-    if (ok) {
+    int local = 0;
+    for (int t = blockIdx.x; t < n_total; t += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int m0 = (t % m_tiles) * kBM, n0 = (t / m_tiles) * BN;
+      const bool ok = bar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag, status) && !*abort_flag;
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int m = m0 + q * 32 + lane;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32);
+      for (int c = 0; c < BN / 16; ++c) {
+        uint32_t r[16];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::kMaxBN + c * 16);
         asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int n = n0 + c * 32;
+        const int n = n0 + c * 16;
         if (m < M && n < N) {
+          const bool whole = n + 16 <= N;
           if (y_dtype == NB_BF16) {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(y) + (size_t)m * N + n;
-            if (n + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-              uint32_t pk[16];
+            if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+              uint32_t pk[8];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
+              for (int j = 0; j < 8; ++j) {
                 const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
                 pk[j] = *reinterpret_cast<const uint32_t*>(&h);
               }
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                reinterpret_cast<uint4*>(dst)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+              reinterpret_cast<uint4*>(dst)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              reinterpret_cast<uint4*>(dst)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
             } else {
-              for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (n + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
             }
           } else {
             float* dst = reinterpret_cast<float*>(y) + (size_t)m * N + n;
-            for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __uint_as_float(r[j]);
+            if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                reinterpret_cast<uint4*>(dst)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (n + j < N) dst[j] = __uint_as_float(r[j]);
+            }
           }
         }
       }
+      // this warp is done with the buffer: one arrival per warp (4 in total) hands it back to the MMA warp
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s2u(&acc_empty[buf])) : "memory");
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
   }
 }
 
@@ -240,19 +286,34 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
   return NB_OK;
 }
 
-template <int BN>
-static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, void* y, int y_dtype, int M, int N, int K, int* status,
-                       cudaStream_t st) {
+// Tile width: the multiple of 16 in [128, 256] that wastes the least of the last wave of CTAs
+// (ties go to the wider tile, which reads X fewer times).
+static int pick_bn(int M, int N, int sms) {
+  const int m_tiles = (M + kBM - 1) / kBM;
+  int best = 256;
+  double best_eff = -1.0;
+  for (int bn = 256; bn >= 128; bn -= 16) {
+    const long tiles = (long)m_tiles * ((N + bn - 1) / bn);
+    const long waves = (tiles + sms - 1) / sms;
+    const double eff = (double)M * N / ((double)waves * sms * kBM * bn);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = bn; }
+  }
+  return best;
+}
+
+static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, void* y, int y_dtype, int M, int N, int K, int bn,
+                       int* status, cudaStream_t st) {
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    if (cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::kSmem))
+    if (cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg::kSmem))
       return record_cuda_error(e);
     attr_done[dev & 63] = true;
   }
-  const dim3 grid((N + BN - 1) / BN, (M + kBM - 1) / kBM);
-  gemm_bf16_kernel<BN><<<grid, 192, GemmCfg<BN>::kSmem, st>>>(mx, mw, y, y_dtype, M, N, K, status);
+  const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + bn - 1) / bn;
+  const int grid = std::min(sm_count(), m_tiles * n_tiles);
+  gemm_bf16_kernel<<<grid, 192, GemmCfg::kSmem, st>>>(mx, mw, y, y_dtype, M, N, K, bn, m_tiles, n_tiles, status);
   return check_launch();
 }
 
@@ -271,13 +332,12 @@ extern "C" int nb_gemm_bf16(const void* x, const void* w, int M, int N, int K, v
   if (K % kBK != 0) return NB_ERR_SHAPE;
   if ((uintptr_t)x % 16 || (uintptr_t)w % 16 || (uintptr_t)y % 4) return NB_ERR_ALIGN;
   if (int rc = check_device()) return rc;
-  const int bn = (N % 256 == 0 && (long)(N / 256) * ((M + kBM - 1) / kBM) >= sm_count()) ? 256 : 128;
+  const int bn = pick_bn(M, N, sm_count());
   CUtensorMap mx, mw;
   if (int rc = make_map(&mx, x, M, K, kBM)) return rc;
   if (int rc = make_map(&mw, w, N, K, bn)) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  return bn == 256 ? launch_gemm<256>(mx, mw, y, y_dtype, M, N, K, status, st)
-                   : launch_gemm<128>(mx, mw, y, y_dtype, M, N, K, status, st);
+  return launch_gemm(mx, mw, y, y_dtype, M, N, K, bn, status, st);
 }
 
 extern "C" int nb_gemm_prefill(const void* x, int M, const uint8_t* packed, const void* codebook, int cb_dtype, int bits,
