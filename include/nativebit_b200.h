@@ -110,6 +110,24 @@ int nb_gemm_prefill(const void* x, int M, const uint8_t* packed, const void* cod
  * reference, which calls a library matmul here. */
 int nb_gemm_bf16(const void* x, const void* w, int M, int N, int K, void* y, int y_dtype, int* status, void* stream);
 
+/* ---- decode-step glue (one new token per sequence, fp32 activations, position read from device
+ * memory so the step replays from a CUDA graph).  They restate the reference's cached decode path,
+ * inference/generate_torch.py: RMSNorm :29-38, RoPE on interleaved pairs :41-60, cache write and
+ * attention over the valid prefix :86-97, SwiGLU :116-117.
+ * nb_add_rmsnorm: x (B, C) += delta (may be NULL); out = x / sqrt(mean(x^2) + eps) * w; C <= 4096.
+ * nb_rope_kv_write: qkv (B, 3*H*hd) = [q|k|v] of this rank's H heads; cos2/sin2 (ctx, hd) are the
+ *   per-pair tables repeated twice; rotated k and v go to the caches (B, H, ctx, hd) at *pos, rotated
+ *   q to q_out (B, H, hd).
+ * nb_decode_attention: softmax(q . K[0..*pos] / sqrt(hd)) . V[0..*pos] per head, written to
+ *   out[b*out_stride + out_offset + h*hd + d]; hd <= 128, ctx + 9*hd <= 12288.
+ * nb_silu_mul: hmid (B, F) = silu(gu[:, :F]) * gu[:, F:]. */
+int nb_add_rmsnorm(float* x, const float* delta, const float* w, float eps, float* out, int B, int C, void* stream);
+int nb_rope_kv_write(const float* qkv, int B, int H, int hd, const float* cos2, const float* sin2, const int64_t* pos,
+                     float* k_cache, float* v_cache, int ctx, float* q_out, void* stream);
+int nb_decode_attention(const float* q, const float* k_cache, const float* v_cache, const int64_t* pos, int B, int H,
+                        int hd, int ctx, float* out, int out_stride, int out_offset, void* stream);
+int nb_silu_mul(const float* gu, int B, int F, float* hmid, void* stream);
+
 /* ---- nb_gemv without a caller-provided workspace.  No counterpart in the reference.
  * For callers that cannot allocate device memory — a plugin that is handed only its input and
  * output buffers, code that runs while a stream is being captured or under a frozen memory

@@ -32,6 +32,12 @@ _SIGNATURES = {
                                    _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "nb_gemm_bf16": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p,
                                 _c.c_void_p]),
+    "nb_add_rmsnorm": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_float, _c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p]),
+    "nb_rope_kv_write": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                    _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_void_p]),
+    "nb_decode_attention": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                       _c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p]),
+    "nb_silu_mul": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
     "nb_gemv_static": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
                                   _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p]),
     "nb_gemv_plan": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p]),

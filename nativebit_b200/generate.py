@@ -240,8 +240,9 @@ class DecodeSession:
     buffer under a position mask (static shapes), as the reference's cached path does
     (inference/generate_torch.py:91-97)."""
 
-    def __init__(self, model: PackedGPT, batch_size: int = 1, use_graph: bool = True):
+    def __init__(self, model: PackedGPT, batch_size: int = 1, use_graph: bool = True, fused: bool = True):
         self.model, self.B = model, batch_size
+        self.fused = fused
         dev = model.embedding.device
         self.dev = dev
         self.caches = init_kv_cache(model, batch_size, dev)
@@ -252,6 +253,53 @@ class DecodeSession:
         self.use_graph = use_graph
         self.graph = None
         self.stream = torch.cuda.Stream(device=dev)
+        if fused:  # static activation buffers of the fused step
+            cfg, B = model.config, batch_size
+            f32 = dict(dtype=torch.float32, device=dev)
+            blk = model.blocks[0]
+            self.bx = torch.zeros(B, cfg.n_embd, **f32)
+            self.bh = torch.zeros(B, cfg.n_embd, **f32)
+            self.bqkv = torch.zeros(B, blk.qkv.out_features, **f32)
+            self.bq = torch.zeros(B, model.heads_local, cfg.head_dim, **f32)
+            self.batt = torch.zeros(B, model.o_cols, **f32)      # columns outside this rank's heads stay zero
+            self.bo = torch.zeros(B, cfg.n_embd, **f32)
+            self.bgu = torch.zeros(B, blk.gate_up.out_features, **f32)
+            self.bhm = torch.zeros(B, blk.down.in_features, **f32)
+            self.bd = torch.zeros(B, cfg.n_embd, **f32)
+
+    @staticmethod
+    def _linear_into(lin: PackedLinear, x: torch.Tensor, out: torch.Tensor) -> None:
+        for r in range(0, x.shape[0], 16):
+            ops.gemv(x[r:r + 16], lin.packed_indices, lin.codebook, lin.bits, lin.block_size, lin.out_features,
+                     lin.in_features, out=out[r:r + 16])
+
+    @torch.no_grad()
+    def _step_body_fused(self):
+        """The decode step on the fused glue kernels: 9 launches per layer."""
+        m, cfg = self.model, self.model.config
+        eps = cfg.norm_eps
+        self.bx.copy_(m.embedding[self.token[:, 0]])
+        delta = None
+        for i, blk in enumerate(m.blocks):
+            k_buf, v_buf, _ = self.caches[i]
+            ops.add_rmsnorm(self.bx, delta, blk.ln1, eps, self.bh)
+            self._linear_into(blk.qkv, self.bh, self.bqkv)
+            ops.rope_kv_write(self.bqkv, m.heads_local, cfg.head_dim, m.cos2, m.sin2, self.pos, k_buf, v_buf, self.bq)
+            ops.decode_attention(self.bq, k_buf, v_buf, self.pos, self.batt, m.o_col0)
+            self._linear_into(blk.out_proj, self.batt, self.bo)
+            m._all_reduce(self.bo)
+            ops.add_rmsnorm(self.bx, self.bo, blk.ln2, eps, self.bh)
+            self._linear_into(blk.gate_up, self.bh, self.bgu)
+            ops.silu_mul(self.bgu, self.bhm)
+            self._linear_into(blk.down, self.bhm, self.bd)
+            m._all_reduce(self.bd)
+            delta = self.bd
+        ops.add_rmsnorm(self.bx, delta, m.ln_f, eps, self.bh)
+        logits = self.bh.to(m.embedding.dtype) @ m.embedding.T
+        cap = cfg.logit_cap
+        self.logits.copy_(cap * torch.tanh(logits.float() / cap))
+        self.token.copy_(self.logits.argmax(-1, keepdim=True))
+        self.pos.add_(1)
 
     @torch.no_grad()
     def prefill(self, prompt: torch.Tensor) -> torch.Tensor:
@@ -266,6 +314,8 @@ class DecodeSession:
 
     @torch.no_grad()
     def _step_body(self):
+        if self.fused:
+            return self._step_body_fused()
         m, cfg = self.model, self.model.config
         B = self.B
         x = m.embedding[self.token].float()                      # (B, 1, C)

@@ -174,3 +174,26 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.b
         _lib.check(_lib.lib().nb_gemm_bf16(x.data_ptr(), w.data_ptr(), m, n, k, out.data_ptr(), _DTYPE[out_dtype],
                                            status.data_ptr(), _stream()), "nb_gemm_bf16")
     return out
+
+
+# ---------------------------------------------------------------------- decode-step glue kernels
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """x (B, C) fp32 += delta; out = rmsnorm(x) * w."""
+    _lib.check(_lib.lib().nb_add_rmsnorm(x.data_ptr(), 0 if delta is None else delta.data_ptr(), w.data_ptr(), eps,
+                                         out.data_ptr(), x.shape[0], x.shape[1], _stream()), "nb_add_rmsnorm")
+
+
+def rope_kv_write(qkv, n_heads, head_dim, cos2, sin2, pos, k_cache, v_cache, q_out) -> None:
+    _lib.check(_lib.lib().nb_rope_kv_write(qkv.data_ptr(), qkv.shape[0], n_heads, head_dim, cos2.data_ptr(), sin2.data_ptr(),
+                                           pos.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[2],
+                                           q_out.data_ptr(), _stream()), "nb_rope_kv_write")
+
+
+def decode_attention(q, k_cache, v_cache, pos, out, out_offset: int) -> None:
+    b, h, ctx, hd = k_cache.shape
+    _lib.check(_lib.lib().nb_decode_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(), b, h, hd,
+                                              ctx, out.data_ptr(), out.shape[1], out_offset, _stream()), "nb_decode_attention")
+
+
+def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> None:
+    _lib.check(_lib.lib().nb_silu_mul(gu.data_ptr(), gu.shape[0], out.shape[1], out.data_ptr(), _stream()), "nb_silu_mul")
