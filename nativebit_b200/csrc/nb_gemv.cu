@@ -231,6 +231,13 @@ __device__ __forceinline__ void store_y(void* y, int dtype, size_t i, float v) {
   else reinterpret_cast<float*>(y)[i] = v;
 }
 
+// {a, b} -> packed fp16 pair (a in the low half), round to nearest, saturating to +-65504.
+__device__ __forceinline__ uint32_t f32x2_to_f16x2_sat(float a, float b) {
+  uint32_t d;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
+  return d;
+}
+
 __device__ __forceinline__ __half to_half_clamped(float v) {
   return __float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f));
 }
@@ -241,7 +248,7 @@ __device__ __forceinline__ __half to_half_clamped(float v) {
 // parts (x = fp16(x) + fp16(x - fp16(x)), about 22 significant bits) and contracted by two MMAs
 // into the same accumulator, so that fp32 inputs are not rounded to 11 bits.
 template <int BITS, int NT, int XR, int XS>
-__global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kWords = Fmt<BITS>::kWords;
   constexpr int kBlkBytes = 16 * BITS;
@@ -336,50 +343,99 @@ __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p
   NB_TRACE_MARK(2);
   __syncthreads();
 
-  // ---- stage x as fp16 in slot order: x_s[tile m/8][k-block][step][row m%8][4].  A thread
-  // owns 8-position chunks; for each it loads four activation rows at a time, then scatters.
+  // ---- stage x as fp16 in slot order: x_s[tile m/XR][k-block][step][row m%XR][4].  A thread owns
+  // 8-position chunks: it decodes the eight destination offsets once, then for four activation
+  // rows at a time loads 8 values each (all loads first), converts pairs with one saturating
+  // f32->f16x2 conversion and scatters them; rows differ only by a constant offset.
   {
     const int chunks = kg_n * 4 * 16;  // 8-position chunks per activation row
     for (int c = tid; c < chunks; c += n_threads) {
       const int kbl = c >> 4, p0 = (c & 15) << 3;
       const uint4 o4 = *reinterpret_cast<const uint4*>(dst_off + p0);
       const uint32_t o[4] = {o4.x, o4.y, o4.z, o4.w};
-      const bool live = kbl < kb_n;  // k-blocks past the end of the row are staged as zeros:
-                                     // their weights are zero, and 0 x garbage must not be NaN
+      const bool live = kbl < kb_n;  // k-blocks past the end of the row are staged as zeros: their
+                                     // weights are zero, and 0 x garbage must not be NaN
       const size_t at0 = (size_t)kb0 * kBlock + (size_t)c * 8;
+      __half* cblk = reinterpret_cast<__half*>(x_s) + kbl * (kXBlockBytes / 2);
       for (int m0 = 0; m0 < p.M; m0 += 4) {
-        float v[4][8];
+        // raw loads of all four rows first (nothing consumes them yet), then the conversions: the
+        // rows' memory round trips overlap instead of following one another
+        uint4 raw[4][2];
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
           const int m = m0 + b;
+          raw[b][0] = raw[b][1] = make_uint4(0u, 0u, 0u, 0u);
           if (live && m < p.M) {
             const size_t at = (size_t)m * K + at0;
             if (p.x_vec) {
-              load_x8(p.x, p.x_dtype, at, v[b]);
+              if (p.x_dtype == NB_F32) {
+                raw[b][0] = *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.x) + at);
+                raw[b][1] = *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.x) + at + 4);
+              } else {
+                raw[b][0] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.x) + at);
+              }
             } else {
+              float t[8];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) v[b][j] = load_x(p.x, p.x_dtype, at + j);
+              for (int j = 0; j < 8; ++j) t[j] = load_x(p.x, NB_F32 == p.x_dtype ? NB_F32 : p.x_dtype, at + j);
+              if (p.x_dtype == NB_F32) {
+                raw[b][0] = make_uint4(__float_as_uint(t[0]), __float_as_uint(t[1]), __float_as_uint(t[2]), __float_as_uint(t[3]));
+                raw[b][1] = make_uint4(__float_as_uint(t[4]), __float_as_uint(t[5]), __float_as_uint(t[6]), __float_as_uint(t[7]));
+              } else if (p.x_dtype == NB_BF16) {
+                raw[b][0] = make_uint4((__float_as_uint(t[0]) >> 16) | (__float_as_uint(t[1]) & 0xFFFF0000u),
+                                       (__float_as_uint(t[2]) >> 16) | (__float_as_uint(t[3]) & 0xFFFF0000u),
+                                       (__float_as_uint(t[4]) >> 16) | (__float_as_uint(t[5]) & 0xFFFF0000u),
+                                       (__float_as_uint(t[6]) >> 16) | (__float_as_uint(t[7]) & 0xFFFF0000u));
+              } else {
+                raw[b][0] = make_uint4(pack_half2(t[0], t[1]), pack_half2(t[2], t[3]), pack_half2(t[4], t[5]), pack_half2(t[6], t[7]));
+              }
             }
-          } else {
+          }
+        }
+        uint32_t hi[4][4], lo[4][4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[b][j] = 0.f;
+        for (int b = 0; b < 4; ++b) {
+          float v[8];
+          if (p.x_dtype == NB_F32) {
+            const uint32_t u[8] = {raw[b][0].x, raw[b][0].y, raw[b][0].z, raw[b][0].w, raw[b][1].x, raw[b][1].y, raw[b][1].z, raw[b][1].w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(u[j]);
+          } else {
+            const uint32_t u[4] = {raw[b][0].x, raw[b][0].y, raw[b][0].z, raw[b][0].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (p.x_dtype == NB_BF16) {
+                v[2 * j] = __uint_as_float(u[j] << 16);
+                v[2 * j + 1] = __uint_as_float(u[j] & 0xFFFF0000u);
+              } else {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[j]));
+                v[2 * j] = f.x; v[2 * j + 1] = f.y;
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            hi[b][j] = f32x2_to_f16x2_sat(v[2 * j], v[2 * j + 1]);
+            if (XS == 2) {  // low-order parts of the (clamped) values
+              const float2 r = __half22float2(*reinterpret_cast<const __half2*>(&hi[b][j]));
+              lo[b][j] = f32x2_to_f16x2_sat(fminf(fmaxf(v[2 * j], -65504.f), 65504.f) - r.x,
+                                            fminf(fmaxf(v[2 * j + 1], -65504.f), 65504.f) - r.y);
+            }
           }
         }
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
           const int m = m0 + b;
           if (m < p.M) {
-            __half* blk = reinterpret_cast<__half*>(x_s + (m / XR) * XS * x_tile_bytes) + (m % XR) * 4 + kbl * (kXBlockBytes / 2);
+            __half* blk = cblk + (m / XR) * XS * (x_tile_bytes / 2) + (m % XR) * 4;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const __half h0 = to_half_clamped(v[b][2 * j]), h1 = to_half_clamped(v[b][2 * j + 1]);
-              blk[o[j] & 0xFFFFu] = h0;
-              blk[o[j] >> 16] = h1;
-              if (XS == 2) {  // low-order parts go to the tile right behind
-                // (of the clamped value, so that out-of-range inputs stay finite)
-                const float c0 = fminf(fmaxf(v[b][2 * j], -65504.f), 65504.f), c1 = fminf(fmaxf(v[b][2 * j + 1], -65504.f), 65504.f);
-                blk[(x_tile_bytes / 2) + (o[j] & 0xFFFFu)] = __float2half_rn(c0 - __half2float(h0));
-                blk[(x_tile_bytes / 2) + (o[j] >> 16)] = __float2half_rn(c1 - __half2float(h1));
+              const uint32_t oa = o[j] & 0xFFFFu, ob = o[j] >> 16;
+              reinterpret_cast<uint16_t*>(blk)[oa] = (uint16_t)(hi[b][j] & 0xFFFFu);
+              reinterpret_cast<uint16_t*>(blk)[ob] = (uint16_t)(hi[b][j] >> 16);
+              if (XS == 2) {
+                reinterpret_cast<uint16_t*>(blk)[(x_tile_bytes / 2) + oa] = (uint16_t)(lo[b][j] & 0xFFFFu);
+                reinterpret_cast<uint16_t*>(blk)[(x_tile_bytes / 2) + ob] = (uint16_t)(lo[b][j] >> 16);
               }
             }
           }
@@ -496,9 +552,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32) gemv_kernel(const GemvParams p
     if (tid == 0) p.counters[blockIdx.x] = 0;
     __syncthreads();
   }
-  for (int m = 0; m < p.M; ++m)
-    for (int r = tid; r < rows_here; r += n_threads)
-      if (row0 + r < p.N) store_y(p.y, p.y_dtype, (size_t)m * p.N + row0 + r, acc[r * (NT * 8) + m]);
+  for (int e = tid; e < p.M * rows_here; e += n_threads) {
+    const int m = e / rows_here, r = e - m * rows_here;
+    if (row0 + r < p.N) store_y(p.y, p.y_dtype, (size_t)m * p.N + row0 + r, acc[r * (NT * 8) + m]);
+  }
   NB_TRACE_MARK(6);
 }
 
