@@ -33,6 +33,9 @@ if ROOT not in sys.path:
 
 HIDDEN, FFN, LAYERS, BITS, BLOCK = 2560, 6912, 26, 3, 128
 METRIC, UNIT = "dequant_matvec_hbm_gbs", "GB/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one 6912 x 2560 batch-1 launch, from the ncu capture
+# summarised in profiles/gemv_kernel_3bit_6912x2560_m1.md (algorithmic bytes: 8 866 304)
+NCU_TRAFFIC_B1 = 8905088
 
 
 def alg_bytes(m, n, k, bits=BITS):
@@ -48,14 +51,46 @@ def measured_peak():
 
 # ----------------------------------------------------------------------------- clocks
 class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU every few milliseconds while the timed region
+    runs (NVML, read-only), with `nvidia-smi --query-gpu` as the fallback."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index, self.proc, self.path = index, None, None
+        self.thread, self.stop_flag, self.samples, self.reasons, self.max_mhz = None, False, [], set(), None
+
+    def _nvml_loop(self, nv, handle):
+        bits = {"hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                for name, bit in bits.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.004)
 
     def start(self):
+        try:
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(vis.split(",")[self.index]) if vis and vis.split(",")[self.index].isdigit() else self.index
+            handle = nv.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -67,6 +102,13 @@ class ClockSampler:
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.thread is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            if self.samples:
+                out.update(sm_mhz=statistics.median(self.samples), sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons),
+                           samples=len(self.samples))
+            return out
         if self.proc is None:
             return out
         time.sleep(0.15)
@@ -306,7 +348,7 @@ def run_ours(args):
         ms_k1 = timed(g1.replay, reps) / (reps * len(gate_up))
         kb = alg_bytes(m, FFN, HIDDEN)
         ach = kb / (ms_k * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": NCU_TRAFFIC_B1 if m == 1 else None,
                     "kernel": "nb::gemv_kernel<3,%d,%d> 6912x2560 batch %d" % (2 if m > 8 else 1, 1 if m == 1 else 8, m),
                     "us_per_launch": ms_k * 1e3, "algorithmic_bytes": kb, "peak_source": peak_src,
                     "method": "52 launches over 52 distinct weight copies (461 MB), issued as the two independent "
@@ -447,6 +489,26 @@ def run_kernel_only(args):
     print(json.dumps({"kernel_only": [n, k, m], "copies": copies, "us_per_launch_stream": e0.elapsed_time(e1) * 1e3 / copies}))
 
 
+def run_gemm_only(args):
+    """A few plain launches of the prefill GEMM (dequant + tcgen05 kernel) on one shape — the small
+    case that profiler captures are taken on (python bench.py --gemm-only M N K)."""
+    import torch
+    from nativebit_b200 import ops, synthetic
+    m, n, k = args.gemm_only
+    dev = torch.device("cuda", 0)
+    p, c = synthetic.synthetic_packed(n, k, BITS, seed=0, device=dev)
+    x = synthetic.synthetic_activation(m, k, 0, dev)
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for rep in range(3):
+        e0.record()
+        for _ in range(4):
+            ops.gemm_prefill(x, p, c, BITS, BLOCK, n, k, out=y)
+        e1.record()
+        torch.cuda.synchronize()
+    print(json.dumps({"gemm_only": [m, n, k], "us_per_call_dequant_plus_gemm": e0.elapsed_time(e1) * 1e3 / 4}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -457,11 +519,15 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2048-token prefill GEMM leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the 2.2B decoder leg")
+    ap.add_argument("--gemm-only", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
+                    help="launch the prefill GEMM on one shape a few times and exit (profiling case)")
     ap.add_argument("--kernel-only", type=int, nargs=3, metavar=("N", "K", "M"), default=None,
                     help="launch one GEMV shape a few times and exit (profiling case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.kernel_only:
+    if args.gemm_only:
+        run_gemm_only(args)
+    elif args.kernel_only:
         run_kernel_only(args)
     elif args.impl == "reference":
         run_reference(args)

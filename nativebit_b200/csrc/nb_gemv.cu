@@ -605,6 +605,28 @@ static GemvPlan make_plan(int M, int N, int K, int bits, int cb_dtype, int x_ter
   return best;
 }
 
+// The search above costs a few microseconds; launches repeat a handful of shapes, so the last
+// plans are kept in a small table.
+static GemvPlan cached_plan(int M, int N, int K, int bits, int cb_dtype, int x_terms, int sms) {
+  struct Entry { int key[7]; GemvPlan plan; bool used; };
+  static Entry table[32];
+  static std::mutex mu;
+  const int key[7] = {M, N, K, bits, cb_dtype, x_terms, sms};
+  const unsigned h = ((unsigned)M * 2654435761u ^ (unsigned)N * 40503u ^ (unsigned)K * 9973u ^ (unsigned)(bits * 8 + cb_dtype * 2 + x_terms)) % 32u;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    Entry& e = table[h];
+    if (e.used && std::equal(key, key + 7, e.key)) return e.plan;
+  }
+  const GemvPlan pl = make_plan(M, N, K, bits, cb_dtype, x_terms, sms);
+  std::lock_guard<std::mutex> lock(mu);
+  Entry& e = table[h];
+  std::copy(key, key + 7, e.key);
+  e.plan = pl;
+  e.used = true;
+  return pl;
+}
+
 // workspace layout: a fixed 16 KB head of ticket counters (int 0..4094) and the status word (int
 // 4095), then the fp32 partial tiles.  The head is at the same place for every shape, so a
 // workspace shared by launches of different shapes never has partial sums where a later launch
@@ -680,7 +702,7 @@ extern "C" int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed,
   if ((uintptr_t)packed % 16 || (uintptr_t)codebook % 16) return NB_ERR_ALIGN;
   if (int rc = check_device()) return rc;
   const int x_terms = x_dtype == NB_F32 ? 2 : 1;
-  const GemvPlan pl = make_plan(M, N, K, bits, cb_dtype, x_terms, sm_count());
+  const GemvPlan pl = cached_plan(M, N, K, bits, cb_dtype, x_terms, sm_count());
   if (pl.grid_x == 0) return NB_ERR_SHAPE;
   const size_t need = plan_workspace(pl, M);
   const bool have_ws = workspace && workspace_bytes >= need;
