@@ -218,8 +218,19 @@ def run_ours(args):
     h = synthetic.synthetic_activation(m, ch_n, 2, dev)
     y_gate = torch.empty(LAYERS, m, ch_n, dtype=torch.bfloat16, device=dev)
     y_up = torch.empty_like(y_gate)
-    y_down = torch.empty(LAYERS, m, HIDDEN, dtype=torch.bfloat16, device=dev)
+    # with more than one rank the partial down outputs are summed in fp32
+    y_down = torch.empty(LAYERS, m, HIDDEN, dtype=torch.bfloat16 if world == 1 else torch.float32, device=dev)
     ws = ops.workspace(dev, 8 << 20)
+    oneshot = None
+    if world > 1 and args.allreduce == "oneshot":
+        from nativebit_b200.comm import OneShotAllReduce
+        oneshot = OneShotAllReduce(m * HIDDEN, dev)
+
+    def all_reduce(t):
+        if oneshot is not None:
+            oneshot(t)
+        else:
+            dist.all_reduce(t)
 
     # gate and up read the same x and are independent: they run on two streams, as in the model;
     # down follows both.  Each stream has its own split-K workspace.
@@ -240,7 +251,7 @@ def run_ours(args):
             cur.wait_stream(side)
             run_lin(mods["down"], hin, y_down[l], ws)
             if world > 1:
-                dist.all_reduce(y_down[l])
+                all_reduce(y_down[l])
 
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(stream):
@@ -291,7 +302,7 @@ def run_ours(args):
     # ---- end to end through the module API with host buffers
     x_host = x.cpu().pin_memory()
     h_host = h.cpu().pin_memory()
-    out_host = torch.empty(LAYERS, m, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    out_host = torch.empty(LAYERS, m, HIDDEN, dtype=y_down.dtype).pin_memory()
     xd, hd = torch.empty_like(x), torch.empty_like(h)
 
     def e2e_step():
@@ -302,7 +313,7 @@ def run_ours(args):
             u = mods["up"](xd)
             y_down[l] = mods["down"](hd)
             if world > 1:
-                dist.all_reduce(y_down[l])
+                all_reduce(y_down[l])
             del g, u
         out_host.copy_(y_down, non_blocking=True)
 
@@ -313,7 +324,7 @@ def run_ours(args):
     ms_e2e = timed(e2e_step, e2e_steps) / e2e_steps
     e2e_value = step_bytes / (ms_e2e * 1e-3) / 1e9
     h2d = x_host.numel() * 2 + h_host.numel() * 2
-    d2h = out_host.numel() * 2
+    d2h = out_host.numel() * out_host.element_size()
 
     # ---- roofline of the dominant kernel: the 6912 x 2560 matvec, timed alone (1 GPU only)
     roofline, extra = None, {}
@@ -420,6 +431,8 @@ def run_ours(args):
         torch.cuda.empty_cache()
         cfg = G.ModelConfig()
         model = G.PackedGPT.random_init(cfg, seed=0, device=dev, tp_rank=rank, tp_size=world)
+        if world > 1 and args.allreduce == "oneshot":
+            model.enable_oneshot_allreduce(max_batch=1)
         gen = torch.Generator().manual_seed(0)
         prompt = torch.randint(0, cfg.vocab_size, (128,), generator=gen)
         res = G.benchmark(model, prompt, n_generate=256, n_runs=2)
@@ -432,6 +445,7 @@ def run_ours(args):
         head_bytes = cfg.vocab_size * HIDDEN * 2
         decode = {"tokens_per_s": 1e3 / per_tok_ms, "per_token_ms": per_tok_ms, "prefill_ms_128_tokens": prefill_ms,
                   "n_generate": 256, "batch": 1, "tp": world,
+                  "allreduce": ("none" if world == 1 else args.allreduce),
                   "packed_linear_bytes_per_token": lin_bytes, "lm_head_bytes_per_token": head_bytes,
                   "weight_GBps": (lin_bytes + head_bytes) / (per_tok_ms * 1e-3) / 1e9,
                   "model": "26 layers, hidden 2560, 32 heads, FFN 6912, vocab 32000, random-init 3-bit packed linears"}
@@ -517,6 +531,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "nccl"],
+                    help="tensor-parallel all-reduce: the one-shot peer-memory kernel or NCCL")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2048-token prefill GEMM leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the 2.2B decoder leg")
     ap.add_argument("--gemm-only", type=int, nargs=3, metavar=("M", "N", "K"), default=None,

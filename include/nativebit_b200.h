@@ -128,6 +128,20 @@ int nb_decode_attention(const float* q, const float* k_cache, const float* v_cac
                         int hd, int ctx, float* out, int out_stride, int out_offset, void* stream);
 int nb_silu_mul(const float* gu, int B, int F, float* hmid, void* stream);
 
+/* ---- one-shot all-reduce (sum, fp32) over peer-mapped buffers, for the all-reduce after the
+ * row-sharded projections of the tensor-parallel decoder (the reference has no multi-GPU inference;
+ * NCCL all_reduce is the library equivalent).  Every rank owns one buffer of
+ * nb_allreduce_buffer_bytes(world, max_count) bytes, zero-filled once, that all ranks can address
+ * (peer-mapped, e.g. symmetric memory); peer_bufs is a HOST array of `world` device pointers, entry
+ * q = rank q's buffer as mapped into this process.  count and max_count are multiples of 4, in and
+ * out 16-byte aligned (in == out is allowed).  All ranks must issue the same sequence of calls.
+ * Results are bit-identical on all ranks.  spin_limit = 0 selects the default bound of the wait for
+ * the peers; when it runs out the kernel writes NB_ERR_TIMEOUT to *status (device int, may be NULL)
+ * and returns without hanging. */
+size_t nb_allreduce_buffer_bytes(int world, int max_count);
+int nb_allreduce(const float* in, float* out, int count, const uint64_t* peer_bufs, int world, int rank,
+                 int max_count, uint32_t spin_limit, int* status, void* stream);
+
 /* ---- nb_gemv without a caller-provided workspace.  No counterpart in the reference.
  * For callers that cannot allocate device memory — a plugin that is handed only its input and
  * output buffers, code that runs while a stream is being captured or under a frozen memory

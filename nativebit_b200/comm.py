@@ -1,0 +1,46 @@
+"""Low-latency all-reduce for the tensor-parallel decoder: peer-mapped buffers from
+torch.distributed's symmetric memory (plumbing) + the one-shot kernel of csrc/nb_comm.cu."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+class OneShotAllReduce:
+    """In-place sum of an fp32 tensor over the ranks of `group`.  max_count: largest numel (multiple of 4)."""
+
+    def __init__(self, max_count: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.max_count = (max_count + 3) // 4 * 4
+        nbytes = _lib.lib().nb_allreduce_buffer_bytes(self.world, self.max_count)
+        if nbytes == 0:
+            raise RuntimeError(f"one-shot all-reduce supports 1..8 ranks; got {self.world}")
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, self.group.group_name)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.peer_array = (ctypes.c_uint64 * self.world)(*ptrs)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)          # every rank's buffer is zeroed before anyone pushes into it
+
+    def __call__(self, t: torch.Tensor) -> torch.Tensor:
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.numel() % 4 or t.numel() > self.max_count:
+            raise RuntimeError("one-shot all-reduce needs a contiguous fp32 tensor whose numel is a multiple of 4 "
+                               f"and at most {self.max_count}")
+        rc = _lib.lib().nb_allreduce(t.data_ptr(), t.data_ptr(), t.numel(), self.peer_array, self.world, self.rank,
+                                     self.max_count, 0, self.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        if rc:
+            _lib.check(rc, "nb_allreduce")
+        return t
+
+    def check(self) -> None:
+        """Raises if a wait for the peers ever ran out (reads the device status word: synchronises)."""
+        if int(self.status.item()) != 0:
+            raise RuntimeError("nb_allreduce: a peer did not arrive within the bounded wait")

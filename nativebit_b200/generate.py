@@ -101,9 +101,21 @@ class PackedGPT(torch.nn.Module):
         self.o_cols = blocks[0].out_proj.in_features if blocks else 0
 
     # ------------------------------------------------------------------ pieces
+    def enable_oneshot_allreduce(self, max_batch: int = 64) -> None:
+        """Use the one-shot peer-memory all-reduce (csrc/nb_comm.cu) for decode-sized messages instead of
+        NCCL; larger messages (prefill) stay on NCCL."""
+        if self.tp_size > 1:
+            from .comm import OneShotAllReduce
+            self.oneshot = OneShotAllReduce(max_batch * self.n_embd, self.embedding.device, self.group)
+
     def _all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         if self.tp_size > 1:
-            torch.distributed.all_reduce(t, group=self.group)
+            ar = getattr(self, "oneshot", None)
+            if ar is not None and t.dtype == torch.float32 and t.is_contiguous() and t.numel() <= ar.max_count \
+                    and t.numel() % 4 == 0:
+                ar(t)
+            else:
+                torch.distributed.all_reduce(t, group=self.group)
         return t
 
     def _attn_inputs(self, x, blk, pos0: int | torch.Tensor, T: int):

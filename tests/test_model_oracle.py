@@ -107,3 +107,58 @@ def test_row_parallel_all_reduce_two_gloo_ranks():
         p.join(120)
         assert p.exitcode == 0
     assert q.get(timeout=10) <= 1e-12
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_block_shards_cover_every_weight_exactly_once(world):
+    """shard_block on CPU tensors for a head_dim-80 model whose per-rank attention columns are not
+    whole codebook blocks (the 2.2B case at 8 ranks: 320 columns = 2.5 blocks): every rank's out_proj
+    shard is the run of whole blocks covering its columns, activations outside its own columns are
+    zero, and the partial products add up to the unsharded product; FFN shards split 9 blocks
+    unevenly."""
+    from nativebit_b200 import generate as G
+    cfg = G.ModelConfig(vocab_size=64, n_layers=1, n_embd=640, n_head=8, ffn_hidden=1152, context_len=16)
+    C, Fh = cfg.n_embd, cfg.ffn_hidden
+    full_np = {"qkv": o.make_packed_linear(3 * C, C, 3, 1), "out_proj": o.make_packed_linear(C, C, 3, 2),
+               "gate": o.make_packed_linear(Fh, C, 3, 3), "up": o.make_packed_linear(Fh, C, 3, 4),
+               "down": o.make_packed_linear(C, Fh, 3, 5)}
+    full = {k: (torch.from_numpy(v[0]), torch.from_numpy(v[1])) for k, v in full_np.items()}
+    dense = {k: o.dequant_packed(v[0], v[1].astype(np.float32), *shape, 3) for (k, v), shape in
+             zip(full_np.items(), ((3 * C, C), (C, C), (Fh, C), (Fh, C), (C, Fh)))}
+    rng = np.random.default_rng(0)
+    att = rng.standard_normal((2, C)).astype(np.float32)           # attention output, all heads
+    hmid = rng.standard_normal((2, Fh)).astype(np.float32)         # SwiGLU output, all channels
+    acc_o = np.zeros((2, C)); acc_d = np.zeros((2, C))
+    hl = cfg.n_head // world
+    rows = hl * cfg.head_dim
+    seen_ffn = 0
+    for r in range(world):
+        blk = G.shard_block(cfg, full, torch.ones(C), torch.ones(C), r, world)
+        deq = lambda lin: o.dequant_packed(lin.packed_indices.numpy(), lin.codebook.numpy().astype(np.float32),
+                                           lin.out_features, lin.in_features, 3)
+        # qkv rows: this rank's heads out of q, k and v
+        Wq = deq(blk.qkv)
+        want = np.concatenate([dense["qkv"][j * C + r * rows: j * C + (r + 1) * rows] for j in range(3)])
+        assert np.array_equal(Wq, want)
+        # out_proj: whole blocks covering [r*rows, (r+1)*rows); zero-padded activations
+        Wo = deq(blk.out_proj)
+        b0 = (r * rows) // 128
+        assert np.array_equal(Wo, dense["out_proj"][:, b0 * 128: b0 * 128 + blk.out_proj.in_features])
+        pad = np.zeros((2, blk.out_proj.in_features), np.float32)
+        off = r * rows - b0 * 128
+        pad[:, off:off + rows] = att[:, r * rows:(r + 1) * rows]
+        acc_o += pad.astype(np.float64) @ Wo.T.astype(np.float64)
+        # FFN channels in whole blocks
+        ch0, chn = G.tp.ffn_shard_plan(Fh, world, r)
+        assert ch0 == seen_ffn
+        seen_ffn += chn
+        Wgu = deq(blk.gate_up)
+        assert np.array_equal(Wgu, np.concatenate([dense["gate"][ch0:ch0 + chn], dense["up"][ch0:ch0 + chn]]))
+        Wd = deq(blk.down)
+        assert np.array_equal(Wd, dense["down"][:, ch0:ch0 + chn])
+        acc_d += hmid[:, ch0:ch0 + chn].astype(np.float64) @ Wd.T.astype(np.float64)
+    assert seen_ffn == Fh
+    ref_o = att.astype(np.float64) @ dense["out_proj"].T.astype(np.float64)
+    ref_d = hmid.astype(np.float64) @ dense["down"].T.astype(np.float64)
+    assert np.abs(acc_o - ref_o).max() <= 1e-9 * np.abs(ref_o).max()
+    assert np.abs(acc_d - ref_d).max() <= 1e-9 * np.abs(ref_d).max()
