@@ -53,3 +53,32 @@ def reconstruct_weight(indices: torch.Tensor, codebook: torch.Tensor, shape, blo
         raise RuntimeError("total_weights must equal shape[0]*shape[1]")
     packed = ops.pack(indices.to(torch.uint8).reshape(-1).contiguous(), bits)
     return ops.dequant(packed, codebook.contiguous(), bits, block_size, shape, dtype=codebook.dtype)
+
+
+def load_packed_layers(path: str, device="cuda"):
+    """Read a torch .nbpack file written by the reference's export_packed (schema nativebit/pack.py:256-291:
+    format_version, config, bits, n_entries, quantized_layers[name] = {packed_indices, codebook (fp16), shape,
+    block_size, n_entries, num_blocks, total_weights[, bias]}, float_params) straight into device-resident packed
+    linears: the bytes and fp16 codebooks are uploaded as stored, nothing is unpacked or materialised (the reference's
+    load_packed reconstructs dense fp32 nn.Linear weights instead, nativebit/pack.py:343-415).
+
+    Returns (config dict, {layer name: PackedLinear}, {layer name: bias tensor}, {param name: fp16 tensor})."""
+    from .packed_linear import PackedLinear
+    blob = torch.load(path, map_location="cpu", weights_only=False)
+    if blob.get("format_version") != FORMAT_VERSION:
+        raise RuntimeError(f"unsupported .nbpack format_version {blob.get('format_version')!r}")
+    bits = int(blob["bits"])
+    if bits not in (2, 3, 4):
+        raise RuntimeError(f"{bits}-bit checkpoints are not supported (2, 3 and 4 are)")
+    dev = torch.device(device)
+    layers, biases = {}, {}
+    for name, d in blob["quantized_layers"].items():
+        out_f, in_f = (int(v) for v in d["shape"])
+        if int(d["total_weights"]) != out_f * in_f:
+            raise RuntimeError(f"{name}: total_weights does not match its shape")
+        layers[name] = PackedLinear(d["packed_indices"].contiguous().to(dev), d["codebook"].contiguous().to(dev), out_f, in_f,
+                                    bits=bits, block_size=int(d["block_size"]))
+        if "bias" in d:
+            biases[name] = d["bias"].to(dev)
+    floats = {k: v.to(dev) for k, v in blob["float_params"].items()}
+    return dict(blob["config"]), layers, biases, floats
