@@ -451,6 +451,26 @@ def run_ours(args):
                   "model": "26 layers, hidden 2560, 32 heads, FFN 6912, vocab 32000, random-init 3-bit packed linears"}
         del model
 
+    # ---- serving sweep (configs[4]): batch 1/8/32/64 decode after a 512-token prompt, 3-bit and 2-bit
+    serving = None
+    if args.serving:
+        from nativebit_b200 import generate as G
+        serving = {}
+        for bits in (3, 2):
+            cfg = G.ModelConfig(bits=bits)
+            model = G.PackedGPT.random_init(cfg, seed=0, device=dev, tp_rank=rank, tp_size=world)
+            if world > 1 and args.allreduce == "oneshot":
+                model.enable_oneshot_allreduce(max_batch=64)
+            prompt = torch.randint(0, cfg.vocab_size, (512,), generator=torch.Generator().manual_seed(1))
+            for b in (1, 8, 32, 64):
+                res = G.benchmark(model, prompt, n_generate=64, n_runs=1, batch_size=b)
+                t = torch.tensor([res["per_token_ms"]], device=dev)
+                if world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                serving[f"{bits}bit_b{b}"] = {"ms_per_step": round(float(t), 3), "tokens_per_s": round(b * 1e3 / float(t), 1)}
+            del model
+            torch.cuda.empty_cache()
+
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -470,6 +490,8 @@ def run_ours(args):
             line["decode"] = decode
         if prefill is not None:
             line["prefill"] = prefill
+        if serving is not None:
+            line["serving"] = serving
         print(json.dumps(line))
     if world > 1:
         # NCCL communicators cannot be torn down while CUDA graphs that captured their kernels are
@@ -534,6 +556,7 @@ def main():
     ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "nccl"],
                     help="tensor-parallel all-reduce: the one-shot peer-memory kernel or NCCL")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2048-token prefill GEMM leg")
+    ap.add_argument("--serving", action="store_true", help="add the batch 1/8/32/64, 3-bit and 2-bit decode sweep (configs[4])")
     ap.add_argument("--no-decode", action="store_true", help="skip the 2.2B decoder leg")
     ap.add_argument("--gemm-only", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
                     help="launch the prefill GEMM on one shape a few times and exit (profiling case)")
