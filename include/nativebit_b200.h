@@ -127,6 +127,11 @@ int nb_rope_kv_write(const float* qkv, int B, int H, int hd, const float* cos2, 
 int nb_decode_attention(const float* q, const float* k_cache, const float* v_cache, const int64_t* pos, int B, int H,
                         int hd, int ctx, float* out, int out_stride, int out_offset, void* stream);
 int nb_silu_mul(const float* gu, int B, int F, float* hmid, void* stream);
+/* nb_rope_kv_write and nb_decode_attention in one launch: rotates q and k of qkv (B, 3*H*hd), writes
+ * k and v to the caches at *pos and attends with the rotated q (same limits as nb_decode_attention). */
+int nb_decode_attention_rope(const float* qkv, const float* cos2, const float* sin2, const int64_t* pos, float* k_cache,
+                             float* v_cache, int B, int H, int hd, int ctx, float* out, int out_stride, int out_offset,
+                             void* stream);
 
 /* ---- one-shot all-reduce (sum, fp32) over peer-mapped buffers, for the all-reduce after the
  * row-sharded projections of the tensor-parallel decoder (the reference has no multi-GPU inference;

@@ -287,7 +287,7 @@ class DecodeSession:
 
     @torch.no_grad()
     def _step_body_fused(self):
-        """The decode step on the fused glue kernels: 9 launches per layer."""
+        """The decode step on the fused glue kernels: 8 launches per layer."""
         m, cfg = self.model, self.model.config
         eps = cfg.norm_eps
         self.bx.copy_(m.embedding[self.token[:, 0]])
@@ -296,8 +296,7 @@ class DecodeSession:
             k_buf, v_buf, _ = self.caches[i]
             ops.add_rmsnorm(self.bx, delta, blk.ln1, eps, self.bh)
             self._linear_into(blk.qkv, self.bh, self.bqkv)
-            ops.rope_kv_write(self.bqkv, m.heads_local, cfg.head_dim, m.cos2, m.sin2, self.pos, k_buf, v_buf, self.bq)
-            ops.decode_attention(self.bq, k_buf, v_buf, self.pos, self.batt, m.o_col0)
+            ops.decode_attention_rope(self.bqkv, m.cos2, m.sin2, self.pos, k_buf, v_buf, self.batt, m.o_col0)
             self._linear_into(blk.out_proj, self.batt, self.bo)
             m._all_reduce(self.bo)
             ops.add_rmsnorm(self.bx, self.bo, blk.ln2, eps, self.bh)

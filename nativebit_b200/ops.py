@@ -195,5 +195,13 @@ def decode_attention(q, k_cache, v_cache, pos, out, out_offset: int) -> None:
                                               ctx, out.data_ptr(), out.shape[1], out_offset, _stream()), "nb_decode_attention")
 
 
+def decode_attention_rope(qkv, cos2, sin2, pos, k_cache, v_cache, out, out_offset: int) -> None:
+    """RoPE + cache write + single-query attention in one launch."""
+    b, h, ctx, hd = k_cache.shape
+    _lib.check(_lib.lib().nb_decode_attention_rope(qkv.data_ptr(), cos2.data_ptr(), sin2.data_ptr(), pos.data_ptr(),
+                                                   k_cache.data_ptr(), v_cache.data_ptr(), b, h, hd, ctx, out.data_ptr(),
+                                                   out.shape[1], out_offset, _stream()), "nb_decode_attention_rope")
+
+
 def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> None:
     _lib.check(_lib.lib().nb_silu_mul(gu.data_ptr(), gu.shape[0], out.shape[1], out.data_ptr(), _stream()), "nb_silu_mul")

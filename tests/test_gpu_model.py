@@ -92,6 +92,27 @@ def test_fused_step_equals_torch_step(built_lib, gm):
             assert (a.logits - b.logits).abs().max() <= 1e-4 * b.logits.abs().max()
 
 
+def test_rope_attention_fusion_equals_two_kernels(built_lib):
+    from nativebit_b200 import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(0)
+    B, H, hd, ctx = 3, 4, 80, 64
+    from nativebit_b200.generate import precompute_rope
+    cos2, sin2 = precompute_rope(hd, ctx, 10000.0, dev)
+    ka = torch.randn(B, H, ctx, hd, device=dev, generator=g); va = torch.randn(B, H, ctx, hd, device=dev, generator=g)
+    kb, vb = ka.clone(), va.clone()
+    for p_ in (0, 5, 37):
+        pos = torch.tensor([p_], device=dev)
+        qkv = torch.randn(B, 3 * H * hd, device=dev, generator=g)
+        q = torch.empty(B, H, hd, device=dev)
+        o1 = torch.zeros(B, H * hd + 16, device=dev); o2 = torch.zeros_like(o1)
+        ops.rope_kv_write(qkv, H, hd, cos2, sin2, pos, ka, va, q)
+        ops.decode_attention(q, ka, va, pos, o1, 8)
+        ops.decode_attention_rope(qkv, cos2, sin2, pos, kb, vb, o2, 8)
+        torch.cuda.synchronize()
+        assert torch.equal(ka, kb) and torch.equal(va, vb) and torch.equal(o1, o2)
+
+
 def test_batched_session(built_lib, gm):
     from nativebit_b200 import generate as G
     dev = torch.device("cuda:0")
