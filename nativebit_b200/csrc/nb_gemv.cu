@@ -35,6 +35,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstdio>
 #include <mutex>
 
@@ -591,13 +592,18 @@ static GemvPlan make_plan(int M, int N, int K, int bits, int cb_dtype, int x_ter
       const int gx = (row_tiles + tr - 1) / tr;
       if (parts > 1 && gx >= kCounterInts - 1) continue;  // one ticket counter per row group
       const long ctas = (long)gx * parts;
-      const long waves = (ctas + sms - 1) / sms;
-      const int upc = tr * kgp;
-      const int rounds = (upc + kMaxWarps - 1) / kMaxWarps;
-      double cost = waves * (1.5 + rounds) + (parts > 1 ? 0.4 + 0.02 * parts : 0.0);
+      const int upc = tr * kgp;                            // units per CTA
+      const int warps = std::min(kMaxWarps, std::max(4, upc));
+      // CTAs of one launch that fit an SM together (64 registers per thread, 220 KB shared memory)
+      const int resident = std::max(1, std::min(std::min(65536 / (warps * 32 * 64), (int)(220 * 1024 / smem)), 2048 / (warps * 32)));
+      const long waves = (ctas + (long)sms * resident - 1) / ((long)sms * resident);
+      const int rounds = (upc + warps - 1) / warps;
+      // Measured on B200: about ten units per CTA with several CTAs per SM beats one large CTA per SM
+      // (phases of co-resident CTAs overlap), hence the mild pull towards upc = 10.
+      double cost = waves * (1.5 + rounds) + 0.05 * std::abs(upc - 10) + (parts > 1 ? 0.4 + 0.02 * parts : 0.0) +
+                    (ctas < sms ? 3.0 * (double)(sms - ctas) / sms : 0.0);
       if (cost < best_cost - 1e-9) {
         best_cost = cost;
-        int warps = std::min(kMaxWarps, std::max(4, (upc + 3) / 4 * 4));
         best = GemvPlan{tr, parts, kgp, gx, warps, smem, ws, cs};
       }
     }
