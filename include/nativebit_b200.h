@@ -66,6 +66,15 @@ int nb_pack(const uint8_t* idx, int bits, int64_t count, uint8_t* packed_out, vo
 int nb_dequant(const uint8_t* packed, const void* codebook, int cb_dtype, int bits, int block_size,
                int64_t n_rows, int64_t n_cols, void* w_out, int w_dtype, void* stream);
 
+/* ---- quantise a dense weight against its codebooks on the device: replaces the exporter's
+ * argmin, nativebit/pack.py:176-199 (_compute_indices, L1 distance, no active mask) and
+ * inference/pack.py:21-35 (quantize_weight, squared distance: the same argmin).
+ * idx_out[i] = argmin_e |w[i] - codebook[i/block_size][e]| (first minimum on ties) for
+ * i < ceil(total/block_size)*block_size; weights past `total` count as 0.  w: fp32 device array of
+ * `total` values in row-major weight order; n_entries 2..256. */
+int nb_quantize(const float* w, int64_t total, const void* codebook, int cb_dtype, int n_entries, int block_size,
+                uint8_t* idx_out, void* stream);
+
 /* ---- fused decode GEMV / skinny GEMM (M = 1..16 activation rows):
  * y[m][n] = sum_k W[n][k] * x[m][k].  Replaces inference/cuda_kernel.py:38-104
  * (dequant_matvec_3bit_kernel + wrapper), inference/triton_kernel.py:144-196 (Triton 3-bit kernel)

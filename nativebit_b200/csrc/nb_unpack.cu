@@ -139,6 +139,25 @@ __global__ void dequant_generic_kernel(const uint8_t* __restrict__ packed, int64
   out[i] = (OutT)v;
 }
 
+// ---- quantise: nearest codebook entry per weight (the exporter's argmin) ------------------------
+// idx[i] = argmin_e |w[i] - codebook[i / block_size][e]|, first minimum on ties; weights past `total`
+// (padding of the last block) count as 0, as in the reference's zero-padded argmin.
+template <typename CbT>
+__global__ void quantize_kernel(const float* __restrict__ w, int64_t total, int64_t padded, const CbT* __restrict__ codebook,
+                                int n_entries, int block_size, uint8_t* __restrict__ idx) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= padded) return;
+  const float v = i < total ? w[i] : 0.f;
+  const CbT* cb = codebook + (i / block_size) * n_entries;
+  float best = fabsf(v - (float)cb[0]);
+  int arg = 0;
+  for (int e = 1; e < n_entries; ++e) {
+    const float d = fabsf(v - (float)cb[e]);
+    if (d < best) { best = d; arg = e; }
+  }
+  idx[i] = (uint8_t)arg;
+}
+
 template <typename OutT>
 static int dequant_dispatch(const uint8_t* packed, const void* codebook, int cb_dtype, int bits, int block_size,
                             int64_t total, OutT* out, cudaStream_t st) {
@@ -220,4 +239,18 @@ extern "C" int nb_dequant(const uint8_t* packed, const void* codebook, int cb_dt
     case NB_BF16: return dequant_dispatch<__nv_bfloat16>(packed, codebook, cb_dtype, bits, block_size, total, (__nv_bfloat16*)w_out, st);
     default: return NB_ERR_ARG;
   }
+}
+
+extern "C" int nb_quantize(const float* w, int64_t total, const void* codebook, int cb_dtype, int n_entries, int block_size,
+                           uint8_t* idx_out, void* stream) {
+  if (!w || !codebook || !idx_out || total <= 0 || block_size <= 0 || n_entries < 2 || n_entries > 256) return NB_ERR_ARG;
+  if (cb_dtype != NB_F16 && cb_dtype != NB_F32) return NB_ERR_ARG;
+  if (int rc = check_device()) return rc;
+  const int64_t padded = (total + block_size - 1) / block_size * block_size;
+  const unsigned grid = (unsigned)((padded + 255) / 256);
+  if (cb_dtype == NB_F16)
+    quantize_kernel<__half><<<grid, 256, 0, (cudaStream_t)stream>>>(w, total, padded, (const __half*)codebook, n_entries, block_size, idx_out);
+  else
+    quantize_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(w, total, padded, (const float*)codebook, n_entries, block_size, idx_out);
+  return check_launch();
 }

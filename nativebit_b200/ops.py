@@ -75,6 +75,23 @@ def dequant(packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size:
     return out
 
 
+def quantize(weight: torch.Tensor, codebook: torch.Tensor, block_size: int) -> torch.Tensor:
+    """Nearest-entry indices (num_blocks * block_size,) uint8 of a dense fp32 weight
+    (nativebit/pack.py:176-199, inference/pack.py:21-35)."""
+    _need_cuda(weight, codebook)
+    if weight.dtype != torch.float32 or codebook.dtype not in (torch.float16, torch.float32):
+        raise RuntimeError("quantize needs an fp32 weight and an fp16/fp32 codebook")
+    total = weight.numel()
+    nb, ne = codebook.shape
+    if nb != (total + block_size - 1) // block_size:
+        raise RuntimeError(f"codebook has {nb} blocks, the weight needs {(total + block_size - 1) // block_size}")
+    out = torch.empty(nb * block_size, dtype=torch.uint8, device=weight.device)
+    with torch.cuda.device(weight.device):
+        _lib.check(_lib.lib().nb_quantize(weight.data_ptr(), total, codebook.data_ptr(), _DTYPE[codebook.dtype], ne, block_size,
+                                          out.data_ptr(), _stream()), "nb_quantize")
+    return out
+
+
 _workspaces: dict = {}
 _ws_need: dict = {}
 

@@ -55,6 +55,29 @@ def reconstruct_weight(indices: torch.Tensor, codebook: torch.Tensor, shape, blo
     return ops.dequant(packed, codebook.contiguous(), bits, block_size, shape, dtype=codebook.dtype)
 
 
+def _compute_indices(weight: torch.Tensor, codebook: torch.Tensor, block_size: int, total_weights: int,
+                     active_mask=None) -> torch.Tensor:
+    """Quantisation indices of a weight on the device (nativebit/pack.py:176-199).  active_mask is not
+    supported by the kernel."""
+    if active_mask is not None:
+        raise RuntimeError("active_mask is not supported by the device quantiser")
+    if total_weights != weight.numel():
+        raise RuntimeError("total_weights must equal weight.numel()")
+    return ops.quantize(weight.contiguous().float(), codebook.contiguous(), block_size)
+
+
+def pack_linear(weight: torch.Tensor, codebook: torch.Tensor, block_size: int = 128):
+    """Dense (out, in) weight + (num_blocks, n_entries) codebook -> PackedLinear with an fp16 codebook: the
+    per-layer work of the reference's export_packed (nativebit/pack.py:238-253: indices, bit-pack, codebook.half())."""
+    from .packed_linear import PackedLinear
+    bits = max(1, (codebook.shape[1] - 1).bit_length())
+    if bits not in (2, 3, 4):
+        raise RuntimeError(f"codebooks of {codebook.shape[1]} entries are not supported")
+    idx = _compute_indices(weight, codebook, block_size, weight.numel())
+    return PackedLinear(ops.pack(idx, bits), codebook.half().contiguous(), weight.shape[0], weight.shape[1], bits=bits,
+                        block_size=block_size)
+
+
 def load_packed_layers(path: str, device="cuda"):
     """Read a torch .nbpack file written by the reference's export_packed (schema nativebit/pack.py:256-291:
     format_version, config, bits, n_entries, quantized_layers[name] = {packed_indices, codebook (fp16), shape,

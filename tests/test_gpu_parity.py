@@ -261,3 +261,25 @@ def test_inference_linear_mirror(dev, golden):
     lin = NativeBitInferenceLinear(k, n, _cu(golden["lin3_cb16"].astype(np.float32), dev), idx, 128)
     y = lin(_cu(golden["lin3_x"], dev)).cpu().numpy()
     assert np.abs(y - golden["lin3_y"]).max() <= 2e-5 * np.abs(golden["lin3_y"]).max()
+
+
+# ------------------------------------------------------------------ exporter side
+def test_quantize_matches_reference_argmin(dev, golden):
+    """Indices from the device quantiser against the reference's quantize_weight on the same weight."""
+    from nativebit_b200 import ops, pack as nbpack
+    n, k = (int(v) for v in golden["lin3_shape"])
+    w = _cu(golden["quant_w"], dev)
+    cb = _cu(golden["lin3_cb16"].astype(np.float32), dev)
+    idx = ops.quantize(w, cb, 128)
+    assert np.array_equal(idx.cpu().numpy().reshape(-1, 128), golden["quant_idx"])
+    lin = nbpack.pack_linear(w, cb, 128)
+    assert np.array_equal(lin.packed_indices.cpu().numpy(), o.pack_3bit(golden["quant_idx"].reshape(-1)))
+    # the packed layer reproduces the codebook-snapped weight
+    snapped = o.reconstruct_weight(golden["quant_idx"].reshape(-1), golden["lin3_cb16"].astype(np.float32), (n, k), 128, n * k)
+    assert np.array_equal(lin.dequantized_weight().cpu().numpy(), snapped)
+    # padding: 10 weights in 2 blocks of 8 -> 16 indices, the tail quantised from zeros
+    w2 = torch.linspace(-1, 1, 10, device=dev)
+    cb2 = torch.tensor([[-1, -.5, -.2, 0, .2, .5, .8, 1.0]] * 2, device=dev)
+    idx2 = ops.quantize(w2, cb2, 8).cpu().numpy()
+    ref2 = np.abs(np.pad(w2.cpu().numpy(), (0, 6))[:, None] - cb2.cpu().numpy()[0][None, :]).argmin(1)
+    assert np.array_equal(idx2, ref2)
