@@ -52,9 +52,13 @@ __device__ __forceinline__ bool bar_test(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait; returns false (and raises the abort flag) when it gives up or someone else did.
+// kSleep > 0 backs off between probes (used by the 128 epilogue threads, whose wait spans a whole
+// main loop and must not take issue slots from the TMA and MMA threads).
+template <int kSleep = 0>
 __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
   for (uint32_t i = 0; i < kGemmSpinLimit; ++i) {
     if (bar_test(bar, parity)) return true;
+    if (kSleep > 0) __nanosleep(kSleep);
     if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;
@@ -187,7 +191,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     for (int t = blockIdx.x; t < n_total; t += gridDim.x, ++local) {
       const int buf = local & 1;
       const int m0 = (t % m_tiles) * kBM, n0 = (t / m_tiles) * BN;
-      const bool ok = bar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag, status) && !*abort_flag;
+      const bool ok = bar_wait<200>(&acc_full[buf], (local >> 1) & 1, abort_flag, status) && !*abort_flag;
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m = m0 + q * 32 + lane;

@@ -69,7 +69,7 @@ constexpr int kMaxTr = 16;                      // row tiles per CTA (one mbarri
 __host__ __device__ constexpr int x_block_bytes(int xr) { return 32 * xr * 8 + (xr == 8 ? 32 : 8); }
 constexpr int kMaxSmem = 110 * 1024;            // two CTAs (of consecutive launches) fit one SM
 constexpr int kCounterInts = 4096;              // workspace head: ticket counters + status word
-constexpr uint32_t kSpinLimit = 1u << 22;       // bounded wait on the copy barriers (about 0.1 s)
+constexpr uint32_t kSpinLimit = 1u << 21;       // bounded wait on the copy barriers (about 0.1 s with the back-off)
 
 struct GemvPlan {
   int tr;           // row tiles (of 16 rows) per CTA
@@ -454,6 +454,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
     {  // bounded wait for this row tile's copies
       uint32_t spins = 0;
       while (!mbar_try_wait(&bars[rtl], 0)) {
+        __nanosleep(40);  // back off: a spinning warp would take issue slots from the warps that unpack
         if (++spins > kSpinLimit) {
           if (p.status) atomicExch(p.status, (int)NB_ERR_TIMEOUT);
           break;
