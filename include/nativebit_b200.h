@@ -128,7 +128,8 @@ int nb_gemm_bf16(const void* x, const void* w, int M, int N, int K, void* y, int
  *   per-pair tables repeated twice; rotated k and v go to the caches (B, H, ctx, hd) at *pos, rotated
  *   q to q_out (B, H, hd).
  * nb_decode_attention: softmax(q . K[0..*pos] / sqrt(hd)) . V[0..*pos] per head, written to
- *   out[b*out_stride + out_offset + h*hd + d]; hd <= 128, ctx + 9*hd <= 12288.
+ *   out[b*out_stride + out_offset + h*hd + d]; hd a multiple of 4, <= 128; caches 16-byte aligned.  The
+ *   keys of a head are split over a cluster of up to 8 CTAs, merged through distributed shared memory.
  * nb_silu_mul: hmid (B, F) = silu(gu[:, :F]) * gu[:, F:]. */
 int nb_add_rmsnorm(float* x, const float* delta, const float* w, float eps, float* out, int B, int C, void* stream);
 int nb_rope_kv_write(const float* qkv, int B, int H, int hd, const float* cos2, const float* sin2, const int64_t* pos,
@@ -141,6 +142,22 @@ int nb_silu_mul(const float* gu, int B, int F, float* hmid, void* stream);
 int nb_decode_attention_rope(const float* qkv, const float* cos2, const float* sin2, const int64_t* pos, float* k_cache,
                              float* v_cache, int B, int H, int hd, int ctx, float* out, int out_stride, int out_offset,
                              void* stream);
+
+/* ---- nb_gemv with the preceding element-wise step of the decoder folded into the staging of its
+ * activations, so the step needs no separate launch for it (fp32 activations, M <= 8; everything
+ * else as nb_gemv).  The reference runs these as separate torch ops around each packed linear
+ * (inference/generate_torch.py:29-38 RMSNorm, :109-117 residual adds and SwiGLU).
+ *  NB_PRO_ADD_RMSNORM: v = x (M, K) + delta (M, K, may be NULL);
+ *      activation = v / sqrt(mean(v^2) + eps) * norm_weight (K);  v is also written to x_out (M, K; may
+ *      be NULL; must not be x: other CTAs still read x).  Same arithmetic, in the same order, as
+ *      nb_add_rmsnorm followed by nb_gemv.
+ *  NB_PRO_SILU_MUL: x is (M, 2K) = [gate | up]; activation = silu(gate) * up, as nb_silu_mul;
+ *      delta, norm_weight, x_out, eps are ignored.
+ * x, delta, norm_weight, x_out 16-byte aligned. */
+typedef enum { NB_PRO_NONE = 0, NB_PRO_ADD_RMSNORM = 1, NB_PRO_SILU_MUL = 2 } nb_prologue;
+int nb_gemv_fused(int prologue, const float* x, const float* delta, const float* norm_weight, float eps, float* x_out,
+                  int M, const uint8_t* packed, const void* codebook, int cb_dtype, int bits, int block_size, int N,
+                  int K, void* y, int y_dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- one-shot all-reduce (sum, fp32) over peer-mapped buffers, for the all-reduce after the
  * row-sharded projections of the tensor-parallel decoder (the reference has no multi-GPU inference;

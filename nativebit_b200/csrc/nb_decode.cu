@@ -5,13 +5,17 @@
 // and masked attention, :116-117 SwiGLU).  The position is read from device memory so that the
 // step can be replayed from a CUDA graph.
 #include <cuda_runtime.h>
+#include <cooperative_groups.h>
 
+#include <algorithm>
 #include <cfloat>
 
 #include "nb_common.cuh"
 #include "nb_host.h"
 
 namespace nb {
+
+namespace cg = cooperative_groups;
 
 // Every kernel of the decode chain is launched with programmatic stream serialization: it may be
 // scheduled while its predecessor still runs, lets its own successor do the same, and waits for
@@ -112,75 +116,102 @@ __global__ void rope_kv_kernel(const float* __restrict__ qkv, const float* __res
 }
 
 // Single-query attention for one (head, batch): scores over keys 0..pos, softmax, weighted sum of
-// values.  out[b, out_offset + h*hd + d].  grid (H, B), 256 threads.  Warps take keys round robin,
-// lanes run over the head dimension (rows of the cache are contiguous), four keys per iteration so
-// that a dozen loads per lane are in flight; head_dim <= 128.  Dynamic smem: ctx + 9*hd floats.
-constexpr int kAttnWarps = 8;
+// values; out[b, out_offset + h*hd + d].  grid (H, B, S) in clusters of S CTAs along z: the CTAs of
+// a cluster split the keys of one head into S contiguous ranges (the whole GPU works on the 32
+// heads of a batch-1 step instead of 32 SMs), each forms the softmax numerator and denominator of
+// its range, and rank 0 merges them through distributed shared memory.  Inside a CTA a warp takes
+// 8 keys per iteration: for the scores four lanes share a key (16-byte loads, two shuffles), for
+// the values a lane owns four head dimensions of all 8 keys.  The values of the first iteration
+// are requested before the scores are computed, so a context of up to 64*S keys costs one memory
+// round trip.  head_dim a multiple of 4, <= 128.  Dynamic smem: see attn_smem_floats.
+//
 // When `qkv` is given (B, 3*H*hd = [q|k|v]) the kernel first does the work of rope_kv_kernel for its
-// head: it rotates q and k by the position's angle, writes k and v into the caches at `pos` and
-// attends with the rotated q, so the step needs one launch instead of two.
+// head: it rotates q and k by the position's angle, the CTA that owns key `pos` writes k and v into
+// the caches, and all attend with the rotated q, so the step needs one launch instead of two.
+constexpr int kAttnWarps = 8;
+constexpr int kAttnKeysPerIter = kAttnWarps * 8;
+static int attn_per_max(int ctx, int S) { return (((ctx + S - 1) / S) + 7) & ~7; }
+static size_t attn_smem_floats(int ctx, int hd, int S) { return (size_t)attn_per_max(ctx, S) + (size_t)(2 + kAttnWarps) * hd + 4; }
+
 __global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(
-    const float* __restrict__ q, float* __restrict__ k_cache, float* __restrict__ v_cache,
-    const long long* __restrict__ pos_ptr, float* __restrict__ out, int H, int hd, int ctx, int out_stride, int out_offset,
-    const float* __restrict__ qkv, const float* __restrict__ cos2, const float* __restrict__ sin2) {
-  extern __shared__ float sc[];  // ctx scores | hd query values | kAttnWarps x hd partial outputs
+    const float* __restrict__ q, float* k_cache, float* v_cache, const long long* __restrict__ pos_ptr, float* __restrict__ out,
+    int H, int hd, int ctx, int out_stride, int out_offset, const float* __restrict__ qkv, const float* __restrict__ cos2,
+    const float* __restrict__ sin2) {
+  extern __shared__ __align__(16) float sm[];  // scores of this CTA's keys | q | per-warp outputs | exchange (o, max, sum)
   __shared__ float red[kAttnWarps];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int S = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pdl_enter();
   long long pos = *pos_ptr;
-  if (pos < 0) return;
+  if (pos < 0) return;  // the same for every CTA of the cluster
   if (pos >= ctx) pos = ctx - 1;
-  const int n = (int)pos + 1;
-  float* qs = sc + ctx;
+  const int n = (int)pos + 1, hd4 = hd >> 2;
+  const int per = (((n + S - 1) / S) + 7) & ~7;
+  const int k0 = rank * per;
+  const int cnt = max(0, min(n, k0 + per) - k0);
+  float* sc = sm;
+  float* qs = sc + ((((ctx + S - 1) / S) + 7) & ~7);
   float* part = qs + hd;
+  float* xch = part + kAttnWarps * hd;
   const size_t head = ((size_t)b * H + h);
+  float* kb = k_cache + head * ctx * hd;
+  float* vb = v_cache + head * ctx * hd;
   if (qkv) {
     const float* base = qkv + (size_t)b * 3 * H * hd;
     const float* qh = base + h * hd;
     const float* kh = base + H * hd + h * hd;
     const float* vh = base + 2 * H * hd + h * hd;
-    const size_t crow = (head * ctx + pos) * hd;
+    const bool owner = pos >= k0 && pos < k0 + cnt;
     for (int i = tid; i < hd; i += blockDim.x) {
       const float c = cos2[pos * hd + i], s = sin2[pos * hd + i];
       const int j = i ^ 1;
       const float sign = (i & 1) ? 1.f : -1.f;   // rot = (-x2, x1) on interleaved pairs
       qs[i] = (qh[i] * c + sign * qh[j] * s) * rsqrtf((float)hd);
-      k_cache[crow + i] = kh[i] * c + sign * kh[j] * s;
-      v_cache[crow + i] = vh[i];
+      if (owner) {
+        kb[(size_t)pos * hd + i] = kh[i] * c + sign * kh[j] * s;
+        vb[(size_t)pos * hd + i] = vh[i];
+      }
     }
   } else {
     for (int i = tid; i < hd; i += blockDim.x) qs[i] = q[head * hd + i] * rsqrtf((float)hd);
   }
-  __syncthreads();
-  const float* kb = k_cache + head * ctx * hd;
-  const float* vb = v_cache + head * ctx * hd;
-  float qv[4];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) qv[e] = (lane + 32 * e < hd) ? qs[lane + 32 * e] : 0.f;
+  __syncthreads();  // also orders the cache row written above before the reads below (same CTA)
 
+  const int iters = (cnt + kAttnKeysPerIter - 1) / kAttnKeysPerIter;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 vfirst[8];  // values of iteration 0, in flight while the scores are computed
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const int jl = warp * 8 + u;
+    vfirst[u] = (jl < cnt && lane < hd4) ? *reinterpret_cast<const float4*>(vb + (size_t)(k0 + jl) * hd + 4 * lane) : zero4;
+  }
+  const int kq = lane >> 2, t = lane & 3;
   float mx = -FLT_MAX;
-  for (int j0 = warp; j0 < n; j0 += 4 * kAttnWarps) {
-    float s[4];
+  for (int it = 0; it < iters; ++it) {
+    const int jl = (it * kAttnWarps + warp) * 8 + kq;
+    float s = 0.f;
+    if (jl < cnt) {
+      const float4* krow = reinterpret_cast<const float4*>(kb + (size_t)(k0 + jl) * hd);
+      float4 kv[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int j = j0 + u * kAttnWarps;
-      s[u] = 0.f;
-      if (j < n) {
+      for (int i = 0; i < 8; ++i) kv[i] = (t + 4 * i < hd4) ? krow[t + 4 * i] : zero4;
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (lane + 32 * e < hd) s[u] += qv[e] * kb[(size_t)j * hd + lane + 32 * e];
+      for (int i = 0; i < 8; ++i) {
+        if (t + 4 * i < hd4) {
+          const float4 qv = reinterpret_cast<const float4*>(qs)[t + 4 * i];
+          s += qv.x * kv[i].x + qv.y * kv[i].y + qv.z * kv[i].z + qv.w * kv[i].w;
+        }
       }
     }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int j = j0 + u * kAttnWarps;
-      const float t = warp_sum(s[u]);
-      if (j < n) {
-        if (lane == 0) sc[j] = t;
-        mx = fmaxf(mx, t);
-      }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    if (jl < cnt) {
+      if (t == 0) sc[jl] = s;
+      mx = fmaxf(mx, s);
     }
   }
+  mx = warp_max(mx);
   if (lane == 0) red[warp] = mx;
   __syncthreads();
   mx = red[0];
@@ -188,7 +219,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(
   for (int i = 1; i < kAttnWarps; ++i) mx = fmaxf(mx, red[i]);
   __syncthreads();
   float sum = 0.f;
-  for (int j = tid; j < n; j += blockDim.x) {
+  for (int j = tid; j < cnt; j += blockDim.x) {
     const float e = __expf(sc[j] - mx);
     sc[j] = e;
     sum += e;
@@ -199,34 +230,75 @@ __global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(
   float tot = 0.f;
 #pragma unroll
   for (int i = 0; i < kAttnWarps; ++i) tot += red[i];
-  const float inv = 1.0f / tot;
 
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int j0 = warp; j0 < n; j0 += 4 * kAttnWarps) {
-    float vv[4][4], pj[4];
+  float4 acc = zero4;
+  for (int it = 0; it < iters; ++it) {
+    const int j0 = (it * kAttnWarps + warp) * 8;
+    float4 vv[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int j = j0 + u * kAttnWarps;
-      pj[u] = (j < n) ? sc[j] : 0.f;
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        vv[u][e] = (j < n && lane + 32 * e < hd) ? vb[(size_t)j * hd + lane + 32 * e] : 0.f;
+    for (int u = 0; u < 8; ++u) {
+      if (it == 0) vv[u] = vfirst[u];
+      else vv[u] = (j0 + u < cnt && lane < hd4) ? *reinterpret_cast<const float4*>(vb + (size_t)(k0 + j0 + u) * hd + 4 * lane) : zero4;
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[e] += pj[u] * vv[u][e];
+    for (int u = 0; u < 8; ++u) {
+      const float pj = (j0 + u < cnt) ? sc[j0 + u] : 0.f;
+      acc.x += pj * vv[u].x; acc.y += pj * vv[u].y; acc.z += pj * vv[u].z; acc.w += pj * vv[u].w;
+    }
   }
-#pragma unroll
-  for (int e = 0; e < 4; ++e)
-    if (lane + 32 * e < hd) part[warp * hd + lane + 32 * e] = acc[e];
+  if (lane < hd4) reinterpret_cast<float4*>(part + warp * hd)[lane] = acc;
   __syncthreads();
   for (int d = tid; d < hd; d += blockDim.x) {
     float o = 0.f;
 #pragma unroll
     for (int wi = 0; wi < kAttnWarps; ++wi) o += part[wi * hd + d];
-    out[(size_t)b * out_stride + out_offset + h * hd + d] = o * inv;
+    xch[d] = o;
   }
+  if (tid == 0) { xch[hd] = mx; xch[hd + 1] = tot; }
+  cluster.sync();
+  if (rank == 0) {
+    for (int d = tid; d < hd; d += blockDim.x) {
+      float m_all = -FLT_MAX;
+      for (int r = 0; r < S; ++r) m_all = fmaxf(m_all, cluster.map_shared_rank(xch, r)[hd]);
+      float num = 0.f, den = 0.f;
+      for (int r = 0; r < S; ++r) {  // a rank without keys has max -FLT_MAX: its weight is exp(-inf) = 0
+        const float* rx = cluster.map_shared_rank(xch, r);
+        const float w = __expf(rx[hd] - m_all);
+        num += w * rx[d];
+        den += w * rx[hd + 1];
+      }
+      out[(size_t)b * out_stride + out_offset + h * hd + d] = num / den;
+    }
+  }
+  cluster.sync();  // the exchange buffers stay alive until rank 0 has read them
+}
+
+// Cluster size: enough CTAs for a few waves of the GPU, at most 8 per head.
+static int attn_split(int B, int H) {
+  const int want = 592 / std::max(1, B * H);
+  return want >= 8 ? 8 : want >= 4 ? 4 : want >= 2 ? 2 : 1;
+}
+
+template <typename... Args>
+static int launch_attention(int B, int H, int hd, int ctx, cudaStream_t st, Args... args) {
+  const int S = attn_split(B, H);
+  const size_t smem = attn_smem_floats(ctx, hd, S) * sizeof(float);
+  if (smem > 48 * 1024) return NB_ERR_SHAPE;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(H, B, S);
+  cfg.blockDim = dim3(kAttnWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 1;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = S;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return record_cuda_error(cudaLaunchKernelEx(&cfg, decode_attention_kernel, args...));
 }
 
 // h[b, i] = silu(gu[b, i]) * gu[b, F + i]
@@ -264,22 +336,22 @@ extern "C" int nb_decode_attention_rope(const float* qkv, const float* cos2, con
                                         void* stream) {
   if (!qkv || !cos2 || !sin2 || !k_cache || !v_cache || !pos || !out || B < 1 || H < 1 || hd < 2 || (hd & 1) || ctx < 1)
     return NB_ERR_ARG;
-  if (hd > 128 || (size_t)(ctx + 9 * hd) * sizeof(float) > 48 * 1024) return NB_ERR_SHAPE;
+  if (hd > 128 || hd % 4 != 0) return NB_ERR_SHAPE;
+  if ((uintptr_t)k_cache % 16 || (uintptr_t)v_cache % 16) return NB_ERR_ALIGN;
   if (int rc = check_device()) return rc;
-  return launch_pdl(decode_attention_kernel, dim3(H, B), dim3(kAttnWarps * 32), (size_t)(ctx + 9 * hd) * sizeof(float),
-                    (cudaStream_t)stream, (const float*)nullptr, k_cache, v_cache, reinterpret_cast<const long long*>(pos), out, H,
-                    hd, ctx, out_stride, out_offset, qkv, cos2, sin2);
+  return launch_attention(B, H, hd, ctx, (cudaStream_t)stream, (const float*)nullptr, k_cache, v_cache,
+                          reinterpret_cast<const long long*>(pos), out, H, hd, ctx, out_stride, out_offset, qkv, cos2, sin2);
 }
 
 extern "C" int nb_decode_attention(const float* q, const float* k_cache, const float* v_cache, const int64_t* pos, int B, int H,
                                    int hd, int ctx, float* out, int out_stride, int out_offset, void* stream) {
   if (!q || !k_cache || !v_cache || !pos || !out || B < 1 || H < 1 || hd < 1 || ctx < 1) return NB_ERR_ARG;
-  if (hd > 128 || (size_t)(ctx + 9 * hd) * sizeof(float) > 48 * 1024) return NB_ERR_SHAPE;
+  if (hd > 128 || hd % 4 != 0) return NB_ERR_SHAPE;
+  if ((uintptr_t)k_cache % 16 || (uintptr_t)v_cache % 16) return NB_ERR_ALIGN;
   if (int rc = check_device()) return rc;
-  return launch_pdl(decode_attention_kernel, dim3(H, B), dim3(kAttnWarps * 32), (size_t)(ctx + 9 * hd) * sizeof(float),
-                    (cudaStream_t)stream, q, const_cast<float*>(k_cache), const_cast<float*>(v_cache),
-                    reinterpret_cast<const long long*>(pos), out, H, hd, ctx, out_stride, out_offset, (const float*)nullptr,
-                    (const float*)nullptr, (const float*)nullptr);
+  return launch_attention(B, H, hd, ctx, (cudaStream_t)stream, q, const_cast<float*>(k_cache), const_cast<float*>(v_cache),
+                          reinterpret_cast<const long long*>(pos), out, H, hd, ctx, out_stride, out_offset, (const float*)nullptr,
+                          (const float*)nullptr, (const float*)nullptr);
 }
 
 extern "C" int nb_silu_mul(const float* gu, int B, int F, float* hmid, void* stream) {

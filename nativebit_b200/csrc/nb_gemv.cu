@@ -26,10 +26,12 @@
 // slots to the unpack.  Weights are consumed in "slot" order rather than position order, so
 // the activation tile is staged into shared memory once per CTA in that order, as fp16.
 //
-// Reduction.  Warps add their 16 x 8 partial tiles into a shared fp32 accumulator.  When the k
-// range is split over several CTAs (grid.y > 1) each CTA writes its partial tile to scratch and
-// takes a ticket; the CTA that takes the last ticket adds the partials in fixed order, writes
-// y and resets the counter: deterministic, and the scratch needs no clearing between launches.
+// Reduction.  Every unit stores its 16 x 8 partial tile into its own shared-memory slot and the
+// slots of a row tile are added in k order.  When the k range is split over several CTAs
+// (grid.y > 1) each CTA writes its partial tile to scratch and takes a ticket; the CTA that takes
+// the last ticket adds the partials in fixed order, writes y and resets the counter.  No sum
+// depends on which warp or CTA finished first: results are bit-identical from run to run, and the
+// scratch needs no clearing between launches.
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
@@ -96,6 +98,11 @@ struct GemvParams {
   int w_stride, c_stride;  // shared-memory row strides (bytes) of the index and codebook tiles
   int cb_bulk;      // codebook rows are whole 16-byte chunks (else they are fetched with 8-byte loads)
   int tile_bulk;    // the CTA covers whole rows: a row tile is one contiguous span, fetched by bulk copies
+  // activation prologue (template parameter PRO): see nb_gemv_fused
+  const float* pro_delta;   // PRO 1: added to x before the norm (may be null)
+  const float* pro_weight;  // PRO 1: RMSNorm weight (K)
+  float* pro_x_out;         // PRO 1: receives x + delta (M, K) (may be null; must not alias x)
+  float pro_eps;
 };
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
@@ -248,7 +255,14 @@ __device__ __forceinline__ __half to_half_clamped(float v) {
 // XS = fp16 terms per activation: 1, or 2 for fp32 activations, which are carried as hi + lo fp16
 // parts (x = fp16(x) + fp16(x - fp16(x)), about 22 significant bits) and contracted by two MMAs
 // into the same accumulator, so that fp32 inputs are not rounded to 11 bits.
-template <int BITS, int NT, int XR, int XS>
+//
+// PRO = activation prologue, computed while the activations are staged (fp32 activations only):
+//   0  none: the activation is x[m, k].
+//   1  residual add + RMSNorm: v = x[m, :] + delta[m, :]; activation = v[k] / sqrt(mean(v^2) + eps) * weight[k].
+//      Every CTA reads the whole rows once to form the mean (a fixed assignment of row segments to
+//      warps and a fixed summation order: all CTAs get the same bits), CTA (0, 0) writes v to x_out.
+//   2  SwiGLU: x is (M, 2K) = [gate | up]; activation = silu(gate[m, k]) * up[m, k].
+template <int BITS, int NT, int XR, int XS, int PRO>
 __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kWords = Fmt<BITS>::kWords;
@@ -267,16 +281,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
   const int K = p.bpr * kBlock;
   const int cb_blk = (p.cb_dtype == NB_F16 ? 2 : 4) << BITS;  // codebook bytes per block
 
-  // shared memory: index rows | codebook rows | activation tile(s) | fp32 accumulator | slot offsets
+  // shared memory: index rows | codebook rows | activation tile(s) | fp32 accumulator | per-unit tiles | slot offsets
   const int x_tile_bytes = p.kg_per_part * 4 * kXBlockBytes;
   uint8_t* w_s = smem;
   uint8_t* c_s = w_s + p.tr * 16 * p.w_stride;
   uint8_t* x_s = c_s + p.tr * 16 * p.c_stride;
   float* acc = reinterpret_cast<float*>(x_s + NT * XS * x_tile_bytes);
   const int acc_n = p.tr * 16 * NT * 8;
-  uint16_t* dst_off = reinterpret_cast<uint16_t*>(acc + acc_n);  // position -> offset (halves) inside a k-block tile
+  float* unit_acc = acc + acc_n;                                  // one 16 x (NT*8) tile per unit
+  uint16_t* dst_off = reinterpret_cast<uint16_t*>(unit_acc + (size_t)p.tr * p.kg_per_part * (16 * NT * 8));  // position -> offset (halves) inside a k-block tile
   __shared__ __align__(8) uint64_t bars[kMaxTr];
   __shared__ int s_last;
+  __shared__ float s_red[PRO == 1 ? 8 * kMaxWarps : 1];  // PRO 1: partial sums of squares [row][segment]
 
   NB_TRACE_MARK(0);
   if (tid < rt_n) mbar_init(&bars[tid], p.tile_bulk ? 1 : n_threads);
@@ -339,7 +355,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
     const int slot = tid, pos = slot_to_position<BITS>(slot);
     dst_off[pos] = (uint16_t)((slot >> 2) * (XR * 4) + (slot & 3));
   }
-  for (int i = tid; i < acc_n; i += n_threads) acc[i] = 0.f;
   asm volatile("griddepcontrol.wait;" ::: "memory");
   NB_TRACE_MARK(2);
   __syncthreads();
@@ -348,7 +363,105 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
   // 8-position chunks: it decodes the eight destination offsets once, then for four activation
   // rows at a time loads 8 values each (all loads first), converts pairs with one saturating
   // f32->f16x2 conversion and scatters them; rows differ only by a constant offset.
-  {
+  if (PRO != 0) {
+    float inv[8];
+#pragma unroll
+    for (int m = 0; m < 8; ++m) inv[m] = 1.f;
+    if (PRO == 1) {
+      // mean of squares of every row: the row is cut into segments, one per warp of the row's group
+      int mp = 1;
+      while (mp < p.M) mp <<= 1;
+      const int wpr = max(1, n_warps / mp);           // warps per row
+      const int rows_per_round = n_warps / wpr;
+      const int seg = warp % wpr;
+      const bool writer = blockIdx.x == 0 && blockIdx.y == 0 && p.pro_x_out != nullptr;
+      for (int m = warp / wpr; m < p.M; m += rows_per_round) {
+        const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (size_t)m * K);
+        const float4* dr = p.pro_delta ? reinterpret_cast<const float4*>(p.pro_delta + (size_t)m * K) : nullptr;
+        float ss = 0.f;
+        for (int i = seg * 32 + lane; i < K / 4; i += wpr * 32) {
+          float4 v = xr[i];
+          if (dr) { const float4 d = dr[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+          ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+          if (writer) reinterpret_cast<float4*>(p.pro_x_out + (size_t)m * K)[i] = v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) s_red[m * kMaxWarps + seg] = ss;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        if (m < p.M) {
+          float tot = 0.f;
+          for (int j = 0; j < wpr; ++j) tot += s_red[m * kMaxWarps + j];
+          inv[m] = 1.0f / sqrtf(tot / (float)K + p.pro_eps);
+        }
+      }
+    }
+    // stage: a thread owns 8-position chunks, one activation row at a time
+    const int chunks = kg_n * 4 * 16;
+    for (int c = tid; c < chunks; c += n_threads) {
+      const int kbl = c >> 4, p0 = (c & 15) << 3;
+      const uint4 o4 = *reinterpret_cast<const uint4*>(dst_off + p0);
+      const uint32_t o[4] = {o4.x, o4.y, o4.z, o4.w};
+      const bool live = kbl < kb_n;
+      const size_t col = (size_t)kb0 * kBlock + (size_t)c * 8;
+      __half* cblk = reinterpret_cast<__half*>(x_s) + kbl * (kXBlockBytes / 2);
+      float wv[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wv[j] = 1.f;
+      if (PRO == 1 && live) {
+        const float4 a = *reinterpret_cast<const float4*>(p.pro_weight + col), b = *reinterpret_cast<const float4*>(p.pro_weight + col + 4);
+        wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+      }
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        if (m < p.M) {
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = 0.f;
+          if (live) {
+            if (PRO == 1) {
+              const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)m * K + col;
+              const float4 a = *reinterpret_cast<const float4*>(xr), b = *reinterpret_cast<const float4*>(xr + 4);
+              v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+              if (p.pro_delta) {
+                const float* dr = p.pro_delta + (size_t)m * K + col;
+                const float4 da = *reinterpret_cast<const float4*>(dr), db = *reinterpret_cast<const float4*>(dr + 4);
+                v[0] += da.x; v[1] += da.y; v[2] += da.z; v[3] += da.w; v[4] += db.x; v[5] += db.y; v[6] += db.z; v[7] += db.w;
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = v[j] * inv[m] * wv[j];
+            } else {
+              const float* gr = reinterpret_cast<const float*>(p.x) + (size_t)m * 2 * K + col;
+              const float4 ga = *reinterpret_cast<const float4*>(gr), gb = *reinterpret_cast<const float4*>(gr + 4);
+              const float4 ua = *reinterpret_cast<const float4*>(gr + K), ub = *reinterpret_cast<const float4*>(gr + K + 4);
+              const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+              const float uu[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = gg[j] / (1.0f + __expf(-gg[j])) * uu[j];
+            }
+          }
+          __half* blk = cblk + (m / XR) * XS * (x_tile_bytes / 2) + (m % XR) * 4;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t hi = f32x2_to_f16x2_sat(v[2 * j], v[2 * j + 1]);
+            const uint32_t oa = o[j] & 0xFFFFu, ob = o[j] >> 16;
+            reinterpret_cast<uint16_t*>(blk)[oa] = (uint16_t)(hi & 0xFFFFu);
+            reinterpret_cast<uint16_t*>(blk)[ob] = (uint16_t)(hi >> 16);
+            if (XS == 2) {
+              const float2 r = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+              const uint32_t lo = f32x2_to_f16x2_sat(fminf(fmaxf(v[2 * j], -65504.f), 65504.f) - r.x,
+                                                     fminf(fmaxf(v[2 * j + 1], -65504.f), 65504.f) - r.y);
+              reinterpret_cast<uint16_t*>(blk)[(x_tile_bytes / 2) + oa] = (uint16_t)(lo & 0xFFFFu);
+              reinterpret_cast<uint16_t*>(blk)[(x_tile_bytes / 2) + ob] = (uint16_t)(lo >> 16);
+            }
+          }
+        }
+      }
+    }
+  } else {
     const int chunks = kg_n * 4 * 16;  // 8-position chunks per activation row
     for (int c = tid; c < chunks; c += n_threads) {
       const int kbl = c >> 4, p0 = (c & 15) << 3;
@@ -503,20 +616,26 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
         }
       }
     }
-    float* arow = acc + (rtl * 16 + g) * (NT * 8) + 2 * t;
+    // the unit's 16 x (NT*8) tile goes to its own slot (plain stores, no atomics): the sum over a row
+    // tile's units below has a fixed order, so results do not depend on which warp finished first
+    float* urow = unit_acc + (size_t)u * (16 * NT * 8) + g * (NT * 8) + 2 * t;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      const int n = nt * 8 + 2 * t;
-      if (n < p.M) {
-        atomicAdd(arow + nt * 8, c[0][nt][0] + c[1][nt][0]);
-        atomicAdd(arow + 8 * NT * 8 + nt * 8, c[0][nt][2] + c[1][nt][2]);
-      }
-      if (n + 1 < p.M) {
-        atomicAdd(arow + nt * 8 + 1, c[0][nt][1] + c[1][nt][1]);
-        atomicAdd(arow + 8 * NT * 8 + nt * 8 + 1, c[0][nt][3] + c[1][nt][3]);
-      }
+      *reinterpret_cast<float2*>(urow + nt * 8) = make_float2(c[0][nt][0] + c[1][nt][0], c[0][nt][1] + c[1][nt][1]);
+      *reinterpret_cast<float2*>(urow + 8 * NT * 8 + nt * 8) = make_float2(c[0][nt][2] + c[1][nt][2], c[0][nt][3] + c[1][nt][3]);
     }
   }
+  __syncthreads();
+  for (int i = tid; i < rt_n * 16 * NT * 8; i += n_threads) {
+    const int rtl = i / (16 * NT * 8), e = i - rtl * (16 * NT * 8);
+    float v = 0.f;
+    if ((e & (NT * 8 - 1)) < p.M) {  // columns past M hold products with unstaged activations
+      const float* src = unit_acc + (size_t)rtl * kg_n * (16 * NT * 8) + e;
+      for (int kgl = 0; kgl < kg_n; ++kgl) v += src[(size_t)kgl * (16 * NT * 8)];
+    }
+    acc[i] = v;
+  }
+  for (int i = rt_n * 16 * NT * 8 + tid; i < acc_n; i += n_threads) acc[i] = 0.f;
   __syncthreads();
   NB_TRACE_MARK(5);
 
@@ -588,7 +707,7 @@ static GemvPlan make_plan(int M, int N, int K, int bits, int cb_dtype, int x_ter
     const int cs = whole ? kb_cnt * cb_blk : skew_stride(kb_cnt * cb_blk);
     for (int tr = 1; tr <= std::min(row_tiles, kMaxTr); ++tr) {
       const size_t smem = (size_t)tr * 16 * (ws + cs) + (size_t)nt * x_terms * kgp * 4 * x_block_bytes(M == 1 ? 1 : 8) +
-                          (size_t)tr * 16 * nt * 8 * 4 + 2 * kBlock + 128;
+                          (size_t)tr * 16 * nt * 8 * 4 * (1 + kgp) + 2 * kBlock + 128;
       if (smem > (size_t)kMaxSmem) break;
       const int gx = (row_tiles + tr - 1) / tr;
       if (parts > 1 && gx >= kCounterInts - 1) continue;  // one ticket counter per row group
@@ -645,13 +764,13 @@ static size_t plan_workspace(const GemvPlan& pl, int M) {
   return counter_bytes(pl) + scratch;
 }
 
-template <int BITS, int NT, int XR, int XS>
+template <int BITS, int NT, int XR, int XS, int PRO = 0>
 static int launch(const GemvParams& prm, const GemvPlan& pl, cudaStream_t st) {
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BITS, NT, XR, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BITS, NT, XR, XS, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     if (e != cudaSuccess) return record_cuda_error(e);
     attr_done[dev & 63] = true;
   }
@@ -667,7 +786,7 @@ static int launch(const GemvParams& prm, const GemvPlan& pl, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return record_cuda_error(cudaLaunchKernelEx(&cfg, gemv_kernel<BITS, NT, XR, XS>, prm));
+  return record_cuda_error(cudaLaunchKernelEx(&cfg, gemv_kernel<BITS, NT, XR, XS, PRO>, prm));
 }
 
 }  // namespace nb
@@ -699,14 +818,31 @@ extern "C" int nb_gemv_plan(int M, int N, int K, int bits, int block_size, int c
   return NB_OK;
 }
 
-extern "C" int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype,
-                       int bits, int block_size, int N, int K, void* y, int y_dtype, void* workspace,
-                       size_t workspace_bytes, void* stream) {
+namespace nb {
+struct Prologue {
+  int kind = 0;                  // 0 none, 1 residual add + RMSNorm, 2 SwiGLU
+  const float* delta = nullptr;
+  const float* weight = nullptr;
+  float* x_out = nullptr;
+  float eps = 0.f;
+};
+}  // namespace nb
+
+static int gemv_impl(const Prologue& pro, const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook,
+                     int cb_dtype, int bits, int block_size, int N, int K, void* y, int y_dtype, void* workspace,
+                     size_t workspace_bytes, void* stream) {
   if (!x || !packed || !codebook || !y) return NB_ERR_ARG;
   if (x_dtype < NB_F32 || x_dtype > NB_BF16 || y_dtype < NB_F32 || y_dtype > NB_BF16) return NB_ERR_ARG;
   if (cb_dtype != NB_F16 && cb_dtype != NB_F32) return NB_ERR_ARG;
   if (int rc = gemv_check_shape(M, N, K, bits, block_size)) return rc;
   if ((uintptr_t)packed % 16 || (uintptr_t)codebook % 16) return NB_ERR_ALIGN;
+  if (pro.kind != 0) {
+    if (pro.kind != 1 && pro.kind != 2) return NB_ERR_ARG;
+    if (x_dtype != NB_F32) return NB_ERR_ARG;
+    if (M > 8) return NB_ERR_SHAPE;
+    if (pro.kind == 1 && (!pro.weight || pro.x_out == x)) return NB_ERR_ARG;
+    if ((uintptr_t)x % 16 || (uintptr_t)pro.delta % 16 || (uintptr_t)pro.weight % 16 || (uintptr_t)pro.x_out % 16) return NB_ERR_ALIGN;
+  }
   if (int rc = check_device()) return rc;
   const int x_terms = x_dtype == NB_F32 ? 2 : 1;
   const GemvPlan pl = cached_plan(M, N, K, bits, cb_dtype, x_terms, sm_count());
@@ -730,12 +866,36 @@ extern "C" int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed,
   prm.w_stride = pl.w_stride; prm.c_stride = pl.c_stride;
   prm.cb_bulk = ((prm.bpr * ((cb_dtype == NB_F16 ? 2 : 4) << bits)) % 16 == 0) ? 1 : 0;
   prm.tile_bulk = (pl.parts == 1 && prm.cb_bulk) ? 1 : 0;
+  prm.pro_delta = pro.delta; prm.pro_weight = pro.weight; prm.pro_x_out = pro.x_out; prm.pro_eps = pro.eps;
   cudaStream_t st = (cudaStream_t)stream;
+  if (pro.kind != 0) {
+#define NB_GEMV_PRO(B, P) (M > 1 ? launch<B, 1, 8, 2, P>(prm, pl, st) : launch<B, 1, 1, 2, P>(prm, pl, st))
+    if (bits == 3) return pro.kind == 1 ? NB_GEMV_PRO(3, 1) : NB_GEMV_PRO(3, 2);
+    return pro.kind == 1 ? NB_GEMV_PRO(2, 1) : NB_GEMV_PRO(2, 2);
+#undef NB_GEMV_PRO
+  }
 #define NB_GEMV_DISPATCH(B, XSV)                                                               \
   (M > 8 ? launch<B, 2, 8, XSV>(prm, pl, st) : M > 1 ? launch<B, 1, 8, XSV>(prm, pl, st) : launch<B, 1, 1, XSV>(prm, pl, st))
   if (bits == 3) return x_terms == 2 ? NB_GEMV_DISPATCH(3, 2) : NB_GEMV_DISPATCH(3, 1);
   return x_terms == 2 ? NB_GEMV_DISPATCH(2, 2) : NB_GEMV_DISPATCH(2, 1);
 #undef NB_GEMV_DISPATCH
+}
+
+extern "C" int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype,
+                       int bits, int block_size, int N, int K, void* y, int y_dtype, void* workspace,
+                       size_t workspace_bytes, void* stream) {
+  return gemv_impl(Prologue{}, x, x_dtype, M, packed, codebook, cb_dtype, bits, block_size, N, K, y, y_dtype, workspace,
+                   workspace_bytes, stream);
+}
+
+extern "C" int nb_gemv_fused(int prologue, const float* x, const float* delta, const float* norm_weight, float eps, float* x_out,
+                             int M, const uint8_t* packed, const void* codebook, int cb_dtype, int bits, int block_size, int N,
+                             int K, void* y, int y_dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  Prologue pro;
+  pro.kind = prologue;
+  if (prologue == NB_PRO_ADD_RMSNORM) { pro.delta = delta; pro.weight = norm_weight; pro.x_out = x_out; pro.eps = eps; }
+  return gemv_impl(pro, x, NB_F32, M, packed, codebook, cb_dtype, bits, block_size, N, K, y, y_dtype, workspace, workspace_bytes,
+                   stream);
 }
 
 // ------------------------------------------------------------------------------------------------

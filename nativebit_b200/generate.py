@@ -270,6 +270,7 @@ class DecodeSession:
             f32 = dict(dtype=torch.float32, device=dev)
             blk = model.blocks[0]
             self.bx = torch.zeros(B, cfg.n_embd, **f32)
+            self.bx2 = torch.zeros(B, cfg.n_embd, **f32)
             self.bh = torch.zeros(B, cfg.n_embd, **f32)
             self.bqkv = torch.zeros(B, blk.qkv.out_features, **f32)
             self.bq = torch.zeros(B, model.heads_local, cfg.head_dim, **f32)
@@ -287,25 +288,42 @@ class DecodeSession:
 
     @torch.no_grad()
     def _step_body_fused(self):
-        """The decode step on the fused glue kernels: 8 launches per layer."""
+        """The decode step on the fused kernels.  Up to 8 sequences: 5 launches per layer (residual add +
+        RMSNorm and SwiGLU are computed inside the packed GEMVs that consume them); more: 8 launches."""
         m, cfg = self.model, self.model.config
         eps = cfg.norm_eps
-        self.bx.copy_(m.embedding[self.token[:, 0]])
+        fold = self.B <= 8
+        xa, xb = self.bx, self.bx2                                # residual stream, ping-pong
+        xa.copy_(m.embedding[self.token[:, 0]])
         delta = None
+
+        def norm_linear(lin, delta, w, out):
+            nonlocal xa, xb
+            if fold:
+                ops.gemv_fused(ops.PRO_ADD_RMSNORM, xa, lin.packed_indices, lin.codebook, lin.bits, lin.block_size,
+                               lin.out_features, lin.in_features, out, delta=delta, norm_weight=w, eps=eps, x_out=xb)
+                xa, xb = xb, xa
+            else:
+                ops.add_rmsnorm(xa, delta, w, eps, self.bh)
+                self._linear_into(lin, self.bh, out)
+
         for i, blk in enumerate(m.blocks):
             k_buf, v_buf, _ = self.caches[i]
-            ops.add_rmsnorm(self.bx, delta, blk.ln1, eps, self.bh)
-            self._linear_into(blk.qkv, self.bh, self.bqkv)
+            norm_linear(blk.qkv, delta, blk.ln1, self.bqkv)
             ops.decode_attention_rope(self.bqkv, m.cos2, m.sin2, self.pos, k_buf, v_buf, self.batt, m.o_col0)
             self._linear_into(blk.out_proj, self.batt, self.bo)
             m._all_reduce(self.bo)
-            ops.add_rmsnorm(self.bx, self.bo, blk.ln2, eps, self.bh)
-            self._linear_into(blk.gate_up, self.bh, self.bgu)
-            ops.silu_mul(self.bgu, self.bhm)
-            self._linear_into(blk.down, self.bhm, self.bd)
+            norm_linear(blk.gate_up, self.bo, blk.ln2, self.bgu)
+            if fold:
+                lin = blk.down
+                ops.gemv_fused(ops.PRO_SILU_MUL, self.bgu, lin.packed_indices, lin.codebook, lin.bits, lin.block_size,
+                               lin.out_features, lin.in_features, self.bd)
+            else:
+                ops.silu_mul(self.bgu, self.bhm)
+                self._linear_into(blk.down, self.bhm, self.bd)
             m._all_reduce(self.bd)
             delta = self.bd
-        ops.add_rmsnorm(self.bx, delta, m.ln_f, eps, self.bh)
+        ops.add_rmsnorm(xa, delta, m.ln_f, eps, self.bh)
         logits = self.bh.to(m.embedding.dtype) @ m.embedding.T
         cap = cfg.logit_cap
         self.logits.copy_(cap * torch.tanh(logits.float() / cap))

@@ -146,6 +146,35 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: in
     return out
 
 
+PRO_ADD_RMSNORM, PRO_SILU_MUL = 1, 2
+
+
+def gemv_fused(prologue: int, x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size: int,
+               n: int, k: int, out: torch.Tensor, delta: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None,
+               eps: float = 0.0, x_out: torch.Tensor | None = None, ws: torch.Tensor | None = None) -> torch.Tensor:
+    """nb_gemv with the decoder's element-wise step before it computed while the activations are staged.
+    PRO_ADD_RMSNORM: x (M, k) fp32 residual, delta (M, k) or None, norm_weight (k); x + delta goes to x_out.
+    PRO_SILU_MUL: x (M, 2k) fp32 = [gate | up].  M <= 8."""
+    if not (x.is_cuda and packed.is_cuda and codebook.is_cuda):
+        _need_cuda(x, packed, codebook)
+    cols = 2 * k if prologue == PRO_SILU_MUL else k
+    if x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] != cols or not x.is_contiguous():
+        raise RuntimeError(f"x must be a contiguous fp32 (M, {cols}) tensor; got {x.dtype} {tuple(x.shape)}")
+    m = x.shape[0]
+    for name, t in (("delta", delta), ("norm_weight", norm_weight), ("x_out", x_out)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous()):
+            raise RuntimeError(f"{name} must be a contiguous fp32 CUDA tensor")
+    if ws is None:
+        ws = workspace(x.device, gemv_workspace_bytes(m, n, k, bits, block_size))
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    rc = _lib.lib().nb_gemv_fused(prologue, x.data_ptr(), ptr(delta), ptr(norm_weight), eps, ptr(x_out), m, packed.data_ptr(),
+                                  codebook.data_ptr(), _DTYPE[codebook.dtype], bits, block_size, n, k, out.data_ptr(),
+                                  _DTYPE[out.dtype], ws.data_ptr(), ws.numel(), _stream())
+    if rc:
+        _lib.check(rc, "nb_gemv_fused")
+    return out
+
+
 _prefill_ws: dict = {}
 
 

@@ -113,6 +113,26 @@ def test_rope_attention_fusion_equals_two_kernels(built_lib):
         assert torch.equal(ka, kb) and torch.equal(va, vb) and torch.equal(o1, o2)
 
 
+@pytest.mark.parametrize("B,H,hd,ctx", [(1, 32, 80, 1024), (1, 4, 80, 1024), (8, 32, 80, 512), (24, 32, 64, 256), (2, 3, 128, 200),
+                                         (1, 2, 4, 16)])
+def test_decode_attention_against_torch(built_lib, B, H, hd, ctx):
+    """Every cluster size (8, 4, 2, 1 CTAs per head), positions at the edges of the key ranges."""
+    from nativebit_b200 import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(B * 1000 + H)
+    k = torch.randn(B, H, ctx, hd, device=dev, generator=g)
+    v = torch.randn(B, H, ctx, hd, device=dev, generator=g)
+    for p_ in sorted({0, 1, 7, 8, 63, 64, 65, 127, 128, ctx // 2, ctx - 2, ctx - 1} & set(range(ctx))):
+        pos = torch.tensor([p_], device=dev)
+        q = torch.randn(B, H, hd, device=dev, generator=g)
+        out = torch.zeros(B, H * hd, device=dev)
+        ops.decode_attention(q, k, v, pos, out, 0)
+        n = p_ + 1
+        sc = torch.einsum("bhd,bhjd->bhj", q.double(), k[:, :, :n].double()) / hd ** 0.5
+        ref = torch.einsum("bhj,bhjd->bhd", torch.softmax(sc, -1), v[:, :, :n].double()).reshape(B, H * hd)
+        assert (out.double() - ref).abs().max() <= 2e-5 * ref.abs().max(), p_
+
+
 def test_batched_session(built_lib, gm):
     from nativebit_b200 import generate as G
     dev = torch.device("cuda:0")

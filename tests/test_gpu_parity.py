@@ -152,6 +152,67 @@ def test_gemv_fp32_activations_keep_their_precision(dev, n, k, m):
     assert np.abs(y - ref).max() <= 2e-6 * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("bits", [3, 2])
+@pytest.mark.parametrize("n,k,m", [(48, 384, 1), (320, 2560, 1), (320, 2560, 3), (7680, 2560, 1), (13824, 2560, 8), (2560, 2560, 5)])
+@pytest.mark.parametrize("with_delta", [True, False])
+def test_gemv_fused_add_rmsnorm(dev, bits, n, k, m, with_delta):
+    """Residual add + RMSNorm folded into the GEMV: y vs the fp64 oracle of the three steps, the
+    updated residual bit-exact, and the same bits from every launch."""
+    from nativebit_b200 import ops
+    rng = np.random.default_rng(n + k + m)
+    packed, cb, _ = o.make_packed_linear(n, k, bits, 21)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    d = (0.5 * rng.standard_normal((m, k))).astype(np.float32) if with_delta else None
+    w = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    eps = 1e-6
+    v32 = x + d if with_delta else x.copy()
+    v = v32.astype(np.float64)
+    act = v / np.sqrt((v * v).mean(axis=1, keepdims=True) + eps) * w
+    ref = o.packed_linear_forward(act, packed, cb.astype(np.float32), n, k, bits, acc_dtype=np.float64)
+    xd, pd, cd, wd = _cu(x, dev), _cu(packed, dev), _cu(cb, dev), _cu(w, dev)
+    dd = _cu(d, dev) if with_delta else None
+    outs = []
+    for _ in range(2):
+        y = torch.empty(m, n, device=dev)
+        x_out = torch.full((m, k), float("nan"), device=dev)
+        ops.gemv_fused(ops.PRO_ADD_RMSNORM, xd, pd, cd, bits, 128, n, k, y, delta=dd, norm_weight=wd, eps=eps, x_out=x_out)
+        torch.cuda.synchronize()
+        assert np.array_equal(x_out.cpu().numpy(), v32)
+        outs.append(y.cpu().numpy())
+    assert np.array_equal(outs[0], outs[1])
+    assert np.abs(outs[0] - ref).max() <= 2e-5 * np.abs(ref).max()
+    assert np.array_equal(xd.cpu().numpy(), x)                    # the input residual is not modified
+
+
+@pytest.mark.parametrize("bits", [3, 2])
+@pytest.mark.parametrize("n,k,m", [(48, 384, 1), (2560, 6912, 1), (2560, 6912, 4), (2560, 896, 8), (320, 1792, 2)])
+def test_gemv_fused_silu_mul(dev, bits, n, k, m):
+    from nativebit_b200 import ops
+    rng = np.random.default_rng(n + k + m)
+    packed, cb, _ = o.make_packed_linear(n, k, bits, 22)
+    gu = (2.0 * rng.standard_normal((m, 2 * k))).astype(np.float32)
+    g, u = gu[:, :k].astype(np.float64), gu[:, k:].astype(np.float64)
+    act = g / (1.0 + np.exp(-g)) * u
+    ref = o.packed_linear_forward(act, packed, cb.astype(np.float32), n, k, bits, acc_dtype=np.float64)
+    y = torch.empty(m, n, device=dev)
+    ops.gemv_fused(ops.PRO_SILU_MUL, _cu(gu, dev), _cu(packed, dev), _cu(cb, dev), bits, 128, n, k, y)
+    assert np.abs(y.double().cpu().numpy() - ref).max() <= 2e-5 * np.abs(ref).max()
+
+
+def test_gemv_fused_rejects_bad_arguments(dev):
+    from nativebit_b200 import ops
+    packed, cb, _ = o.make_packed_linear(48, 384, 3, 1)
+    x = torch.zeros(9, 384, device=dev)
+    w = torch.ones(384, device=dev)
+    with pytest.raises(RuntimeError):                              # M > 8
+        ops.gemv_fused(ops.PRO_ADD_RMSNORM, x, _cu(packed, dev), _cu(cb, dev), 3, 128, 48, 384, torch.empty(9, 48, device=dev),
+                       norm_weight=w, eps=1e-6)
+    x = torch.zeros(1, 384, device=dev)
+    with pytest.raises(RuntimeError):                              # in-place residual update is a race
+        ops.gemv_fused(ops.PRO_ADD_RMSNORM, x, _cu(packed, dev), _cu(cb, dev), 3, 128, 48, 384, torch.empty(1, 48, device=dev),
+                       norm_weight=w, eps=1e-6, x_out=x)
+
+
 def test_gemv_fp32_codebook(dev):
     y, ref = _gemv_case(dev, 3, 320, 2560, 2, seed=11, cb_dtype=torch.float32)
     assert np.abs(y - ref).max() <= 2e-5 * np.abs(ref).max()
@@ -181,6 +242,18 @@ def test_gemv_is_deterministic_and_leaves_workspace_clean(dev):
         assert torch.equal(y, y0)
     torch.cuda.synchronize()
     assert int(ws[:16].view(torch.int32).abs().sum()) == 0   # the ticket counters at the front were reset
+
+
+@pytest.mark.parametrize("n,k,m", [(7680, 2560, 1), (6912, 2560, 1), (2560, 6912, 1), (6912, 2560, 4), (2560, 2560, 16)])
+def test_gemv_same_bits_every_launch(dev, n, k, m):
+    """Several warps and CTAs contribute to one output: the order of their sums is fixed."""
+    from nativebit_b200 import ops
+    packed, cb, _ = o.make_packed_linear(n, k, 3, 23)
+    x = torch.randn(m, k, device=dev, generator=torch.Generator(device=dev).manual_seed(1))
+    p, c = _cu(packed, dev), _cu(cb, dev)
+    y0 = ops.gemv(x, p, c, 3, 128, n, k).clone()
+    for _ in range(20):
+        assert torch.equal(ops.gemv(x, p, c, 3, 128, n, k), y0)
 
 
 def test_gemv_linearity_full_size(dev):
