@@ -149,8 +149,8 @@ int nb_decode_attention_rope(const float* qkv, const float* cos2, const float* s
  * (inference/generate_torch.py:29-38 RMSNorm, :109-117 residual adds and SwiGLU).
  *  NB_PRO_ADD_RMSNORM: v = x (M, K) + delta (M, K, may be NULL);
  *      activation = v / sqrt(mean(v^2) + eps) * norm_weight (K);  v is also written to x_out (M, K; may
- *      be NULL; must not be x: other CTAs still read x).  Same arithmetic, in the same order, as
- *      nb_add_rmsnorm followed by nb_gemv.
+ *      be NULL; must not be x: other CTAs still read x).  Equal to nb_add_rmsnorm followed by nb_gemv up
+ *      to rounding: the factor 1/rms, a scalar per row, is applied to the output instead of the activations.
  *  NB_PRO_SILU_MUL: x is (M, 2K) = [gate | up]; activation = silu(gate) * up, as nb_silu_mul;
  *      delta, norm_weight, x_out, eps are ignored.
  * x, delta, norm_weight, x_out 16-byte aligned. */
@@ -158,6 +158,33 @@ typedef enum { NB_PRO_NONE = 0, NB_PRO_ADD_RMSNORM = 1, NB_PRO_SILU_MUL = 2 } nb
 int nb_gemv_fused(int prologue, const float* x, const float* delta, const float* norm_weight, float eps, float* x_out,
                   int M, const uint8_t* packed, const void* codebook, int cb_dtype, int bits, int block_size, int N,
                   int K, void* y, int y_dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- tensor-parallel decode: the all-reduce after a row-sharded projection folded into the GEMVs on
+ * both sides of it, so that no collective kernel runs between them (the reference has no multi-GPU
+ * inference; the library equivalent is nb_gemv, an NCCL all_reduce, nb_add_rmsnorm, nb_gemv).
+ *  push   = 1: the GEMV's fp32 result (M, N) is not written to y (may be NULL) but stored over NVLink into
+ *              slot `rank` of every rank's exchange buffer; the last CTA then raises this rank's flag there.
+ *  gather = 1 (with NB_PRO_ADD_RMSNORM): delta is the sum, in rank order, of the vectors (M, K) the ranks
+ *              pushed last; every CTA waits (bounded) for all flags.  All ranks compute the same bits.
+ * Every rank owns one buffer of nb_exchange_buffer_bytes(world, max_count) bytes that all ranks can
+ * address (peer-mapped, e.g. symmetric memory).  Set-up, once: zero-fill the buffer, call
+ * nb_exchange_init(own buffer, peer_bufs, ...) where peer_bufs is a HOST array of `world` device
+ * pointers, entry q = rank q's buffer as mapped into this process (entry `rank` = the own buffer; the
+ * table is copied into the buffer, synchronously), then synchronise all ranks before the first push.
+ * max_count >= M*N (push) and M*K (gather), a multiple of 4.  All ranks must issue the same sequence
+ * of push and gather calls, and a push must be consumed (a gather by nb_gemv_tp or nb_exchange_gather)
+ * before the next push.  A workspace is required (its status word receives NB_ERR_TIMEOUT when the
+ * wait of spin_limit probes, 0 = default of about a second, runs out; the kernel then continues with
+ * what has arrived and does not hang).  Plain loads and stores on peer memory only: no TMA, no multicast.
+ * nb_exchange_gather: the same sum written to out (count floats), for a consumer that is not a GEMV. */
+size_t nb_exchange_buffer_bytes(int world, int max_count);
+int nb_exchange_init(void* exchange, const uint64_t* peer_bufs, int world, int rank, int max_count);
+int nb_gemv_tp(int prologue, const float* x, const float* delta, const float* norm_weight, float eps, float* x_out, int M,
+               const uint8_t* packed, const void* codebook, int cb_dtype, int bits, int block_size, int N, int K, void* y,
+               int y_dtype, void* workspace, size_t workspace_bytes, void* exchange, int world, int rank, int max_count,
+               int gather, int push, uint32_t spin_limit, void* stream);
+int nb_exchange_gather(float* out, int count, const void* exchange, int world, int rank, int max_count, uint32_t spin_limit,
+                       int* status, void* stream);
 
 /* ---- one-shot all-reduce (sum, fp32) over peer-mapped buffers, for the all-reduce after the
  * row-sharded projections of the tensor-parallel decoder (the reference has no multi-GPU inference;

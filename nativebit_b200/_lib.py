@@ -47,6 +47,13 @@ _SIGNATURES = {
     "nb_gemv_fused": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_float, _c.c_void_p, _c.c_int, _c.c_void_p,
                                  _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p,
                                  _c.c_size_t, _c.c_void_p]),
+    "nb_exchange_buffer_bytes": (_c.c_size_t, [_c.c_int, _c.c_int]),
+    "nb_exchange_init": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int]),
+    "nb_gemv_tp": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_float, _c.c_void_p, _c.c_int, _c.c_void_p,
+                              _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p,
+                              _c.c_size_t, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_uint32, _c.c_void_p]),
+    "nb_exchange_gather": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_uint32, _c.c_void_p,
+                                      _c.c_void_p]),
     "nb_gemv_static": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
                                   _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p]),
     "nb_gemv_plan": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p]),

@@ -83,27 +83,103 @@ struct GemvPlan {
   int w_stride, c_stride;
 };
 
+// Kernel parameter block.  Kept small on purpose: together with GemvExtra it stays within 128
+// bytes (measured on B200: a launch whose parameters exceed 128 bytes costs 0.4 to 0.8 us more
+// inside a dependent chain).  The kernel expands it into a GemvView with one plain field per value.
 struct GemvParams {
+  const void* x;
+  const uint8_t* packed;
+  const void* codebook;
+  void* y;
+  int* counters;            // workspace head: ticket counters, status word at int kCounterInts - 1, then the partial tiles (may be null)
+  int N;
+  int w_stride, c_stride;   // shared-memory row strides (bytes) of the index and codebook tiles
+  uint16_t bpr, kg_per_part;
+  uint8_t M, tr;
+  uint8_t dtypes;           // x_dtype | y_dtype << 2 | cb_dtype << 4
+  uint8_t flags;            // x_vec | cb_bulk << 1 | tile_bulk << 2
+};
+static_assert(sizeof(GemvParams) <= 64, "keep the GEMV parameter block small");
+
+struct GemvView {
   const void* x;
   const uint8_t* packed;
   const void* codebook;
   void* y;
   float* scratch;
   int* counters;
-  int* status;      // set to NB_ERR_TIMEOUT if a copy barrier never completes (may be null)
+  int* status;      // set to NB_ERR_TIMEOUT if a bounded wait runs out (may be null)
   int M, N, bpr, row_tiles, kgroups;
   int tr, kg_per_part;
   int x_dtype, y_dtype, cb_dtype;
   int x_vec;        // x is 16-byte aligned: staged with 16-byte loads
-  int w_stride, c_stride;  // shared-memory row strides (bytes) of the index and codebook tiles
+  int w_stride, c_stride;
   int cb_bulk;      // codebook rows are whole 16-byte chunks (else they are fetched with 8-byte loads)
   int tile_bulk;    // the CTA covers whole rows: a row tile is one contiguous span, fetched by bulk copies
-  // activation prologue (template parameter PRO): see nb_gemv_fused
+  __device__ __forceinline__ explicit GemvView(const GemvParams& q)
+      : x(q.x), packed(q.packed), codebook(q.codebook), y(q.y),
+        scratch(q.counters ? reinterpret_cast<float*>(q.counters + kCounterInts) : nullptr), counters(q.counters),
+        status(q.counters ? q.counters + (kCounterInts - 1) : nullptr), M(q.M), N(q.N), bpr(q.bpr), row_tiles((q.N + 15) >> 4),
+        kgroups((q.bpr + 3) >> 2), tr(q.tr), kg_per_part(q.kg_per_part), x_dtype(q.dtypes & 3), y_dtype((q.dtypes >> 2) & 3),
+        cb_dtype((q.dtypes >> 4) & 3), x_vec(q.flags & 1), w_stride(q.w_stride), c_stride(q.c_stride), cb_bulk((q.flags >> 1) & 1),
+        tile_bulk((q.flags >> 2) & 1) {}
+};
+
+// Arguments of the activation prologues and of the tensor-parallel exchange.  Kernels without
+// either take an empty struct instead, which keeps their parameter block small.
+struct GemvExtra {
   const float* pro_delta;   // PRO 1: added to x before the norm (may be null)
   const float* pro_weight;  // PRO 1: RMSNorm weight (K)
   float* pro_x_out;         // PRO 1: receives x + delta (M, K) (may be null; must not alias x)
   float pro_eps;
+  uint32_t xchg_spin;       // bound of the wait for the peers' vectors
+  uint8_t* xchg_self;       // tensor-parallel exchange (see nb_gemv_tp): this rank's exchange buffer
+  int xchg_world, xchg_rank, xchg_max_count;
+  int gather;               // PRO 1: delta = sum over the ranks of the vectors pushed last
 };
+static_assert(sizeof(GemvParams) + sizeof(GemvExtra) <= 128, "keep the GEMV parameter block within 128 bytes");
+struct GemvNoExtra {
+  static constexpr const float* pro_delta = nullptr;
+  static constexpr const float* pro_weight = nullptr;
+  static constexpr float* pro_x_out = nullptr;
+  static constexpr float pro_eps = 0.f;
+  static constexpr uint8_t* xchg_self = nullptr;
+  static constexpr int xchg_world = 0, xchg_rank = 0, xchg_max_count = 0, gather = 0;
+  static constexpr uint32_t xchg_spin = 0;
+};
+template <bool kUsed> struct ExtraSel { using type = GemvExtra; };
+template <> struct ExtraSel<false> { using type = GemvNoExtra; };
+
+// Exchange buffer of one rank (the same layout on every rank):
+//   slots  [2 sets][world][max_count] fp32   slot r of a set is written by rank r (all of its CTAs)
+//   flags  [2 sets][world] uint32            written by rank r after its slot is complete: sequence number
+//   seq    uint32, ticket int                private to the owner: vectors pushed so far; CTA ticket counter
+//   table  [8] uint64                        every rank's buffer as mapped into the owner's process (nb_exchange_init)
+// Pushes alternate between the two sets.  A rank can be at most one push ahead of the slowest rank
+// (between two of its pushes it consumes a sum, which needs every rank's flag), so a set is never
+// overwritten while a peer still reads it.  The counters live in device memory: a captured CUDA
+// graph stays replayable.  The peer pointers live there too, not in the kernel parameters.
+__host__ __device__ inline size_t xchg_slots_bytes(int world, int max_count) { return (size_t)2 * world * max_count * sizeof(float); }
+__host__ __device__ inline uint32_t* xchg_flags(const uint8_t* buf, int world, int max_count) {
+  return reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(buf) + xchg_slots_bytes(world, max_count));
+}
+__host__ __device__ inline uint32_t* xchg_seq(const uint8_t* buf, int world, int max_count) {
+  return xchg_flags(buf, world, max_count) + 2 * world;
+}
+__host__ __device__ inline unsigned long long* xchg_table(const uint8_t* buf, int world, int max_count) {
+  return reinterpret_cast<unsigned long long*>(xchg_flags(buf, world, max_count) + 2 * world + 2);  // 2*world + 2 words: 8-byte aligned
+}
+__host__ __device__ inline size_t xchg_bytes(int world, int max_count) {
+  return xchg_slots_bytes(world, max_count) + (size_t)(2 * world + 2) * sizeof(uint32_t) + 8 * sizeof(unsigned long long);
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
   uint32_t d;
@@ -262,8 +338,10 @@ __device__ __forceinline__ __half to_half_clamped(float v) {
 //      Every CTA reads the whole rows once to form the mean (a fixed assignment of row segments to
 //      warps and a fixed summation order: all CTAs get the same bits), CTA (0, 0) writes v to x_out.
 //   2  SwiGLU: x is (M, 2K) = [gate | up]; activation = silu(gate[m, k]) * up[m, k].
-template <int BITS, int NT, int XR, int XS, int PRO>
-__global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParams p) {
+// PUSH = 1: the result goes to the ranks' exchange buffers instead of y (see nb_gemv_tp).
+template <int BITS, int NT, int XR, int XS, int PRO, int PUSH>
+__global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParams pp, const typename ExtraSel<(PRO != 0 || PUSH != 0)>::type ex) {
+  const GemvView p(pp);
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kWords = Fmt<BITS>::kWords;
   constexpr int kBlkBytes = 16 * BITS;
@@ -288,11 +366,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
   uint8_t* x_s = c_s + p.tr * 16 * p.c_stride;
   float* acc = reinterpret_cast<float*>(x_s + NT * XS * x_tile_bytes);
   const int acc_n = p.tr * 16 * NT * 8;
-  float* unit_acc = acc + acc_n;                                  // one 16 x (NT*8) tile per unit
-  uint16_t* dst_off = reinterpret_cast<uint16_t*>(unit_acc + (size_t)p.tr * p.kg_per_part * (16 * NT * 8));  // position -> offset (halves) inside a k-block tile
+  constexpr int kUnitCols = XR == 1 ? 1 : NT * 8;                 // a single activation row only has column 0
+  constexpr int kUnitTile = 16 * kUnitCols;
+  float* unit_acc = acc + acc_n;                                  // one 16 x kUnitCols tile per unit
+  uint16_t* dst_off = reinterpret_cast<uint16_t*>(unit_acc + (((size_t)p.tr * p.kg_per_part * kUnitTile + 3) & ~(size_t)3));  // position -> offset (halves) inside a k-block tile
   __shared__ __align__(8) uint64_t bars[kMaxTr];
   __shared__ int s_last;
   __shared__ float s_red[PRO == 1 ? 8 * kMaxWarps : 1];  // PRO 1: partial sums of squares [row][segment]
+  __shared__ float s_scale[PRO == 1 ? 8 : 1];            // PRO 1: 1/rms of each activation row
 
   NB_TRACE_MARK(0);
   if (tid < rt_n) mbar_init(&bars[tid], p.tile_bulk ? 1 : n_threads);
@@ -363,43 +444,102 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
   // 8-position chunks: it decodes the eight destination offsets once, then for four activation
   // rows at a time loads 8 values each (all loads first), converts pairs with one saturating
   // f32->f16x2 conversion and scatters them; rows differ only by a constant offset.
-  if (PRO != 0) {
-    float inv[8];
-#pragma unroll
-    for (int m = 0; m < 8; ++m) inv[m] = 1.f;
-    if (PRO == 1) {
-      // mean of squares of every row: the row is cut into segments, one per warp of the row's group
-      int mp = 1;
-      while (mp < p.M) mp <<= 1;
-      const int wpr = max(1, n_warps / mp);           // warps per row
-      const int rows_per_round = n_warps / wpr;
-      const int seg = warp % wpr;
-      const bool writer = blockIdx.x == 0 && blockIdx.y == 0 && p.pro_x_out != nullptr;
-      for (int m = warp / wpr; m < p.M; m += rows_per_round) {
-        const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (size_t)m * K);
-        const float4* dr = p.pro_delta ? reinterpret_cast<const float4*>(p.pro_delta + (size_t)m * K) : nullptr;
-        float ss = 0.f;
-        for (int i = seg * 32 + lane; i < K / 4; i += wpr * 32) {
-          float4 v = xr[i];
-          if (dr) { const float4 d = dr[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
-          ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-          if (writer) reinterpret_cast<float4*>(p.pro_x_out + (size_t)m * K)[i] = v;
+  if (PRO == 1) {
+    // One pass over the whole rows: v = x + delta (delta either a local vector or the sum over the
+    // ranks' pushed vectors), sum of squares, and v * weight staged (as fp16 hi + lo) where the
+    // column lies in this CTA's k range; the factor 1/rms is a scalar per row and is applied to the
+    // output.  A row is cut into segments, one per warp of the row's group, and the segment sums are
+    // added in a fixed order: every CTA (and every rank) computes the same bits.
+    const float* slots = nullptr;  // [world][max_count] vectors pushed by the ranks, if gathering
+    if (ex.gather) {
+      const uint8_t* self = ex.xchg_self;
+      const uint32_t seq = __ldcg(xchg_seq(self, ex.xchg_world, ex.xchg_max_count));  // vectors pushed so far = the one to collect
+      const int set = seq & 1;
+      if (tid < ex.xchg_world) {
+        const uint32_t* flag = xchg_flags(self, ex.xchg_world, ex.xchg_max_count) + set * ex.xchg_world + tid;
+        uint32_t spins = 0;
+        while (ld_acquire_sys_u32(flag) != seq) {
+          __nanosleep(100);
+          if (++spins > ex.xchg_spin) {
+            if (p.status) atomicExch(p.status, (int)NB_ERR_TIMEOUT);
+            break;
+          }
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) s_red[m * kMaxWarps + seg] = ss;
       }
       __syncthreads();
+      slots = reinterpret_cast<const float*>(self) + (size_t)set * ex.xchg_world * ex.xchg_max_count;
+    }
+    int mp = 1;
+    while (mp < p.M) mp <<= 1;
+    const int wpr = max(1, n_warps / mp);           // warps per row
+    const int rows_per_round = n_warps / wpr;
+    const int seg = warp % wpr;
+    const bool writer = blockIdx.x == 0 && blockIdx.y == 0 && ex.pro_x_out != nullptr;
+    for (int m = warp / wpr; m < p.M; m += rows_per_round) {
+      const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (size_t)m * K);
+      const float4* dr = ex.pro_delta ? reinterpret_cast<const float4*>(ex.pro_delta + (size_t)m * K) : nullptr;
+      __half* xrow = reinterpret_cast<__half*>(x_s) + (m / XR) * XS * (x_tile_bytes / 2) + (m % XR) * 4;
+      float ss = 0.f;
+      for (int i = seg * 32 + lane; i < K / 4; i += wpr * 32) {
+        float4 v = xr[i];
+        if (slots) {
+          float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int m = 0; m < 8; ++m) {
-        if (m < p.M) {
-          float tot = 0.f;
-          for (int j = 0; j < wpr; ++j) tot += s_red[m * kMaxWarps + j];
-          inv[m] = 1.0f / sqrtf(tot / (float)K + p.pro_eps);
+          for (int q = 0; q < 8; ++q) {
+            if (q < ex.xchg_world) {
+              const float4 e = __ldcv(reinterpret_cast<const float4*>(slots + (size_t)q * ex.xchg_max_count + (size_t)m * K) + i);
+              d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+            }
+          }
+          v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        } else if (dr) {
+          const float4 d = dr[i];
+          v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        }
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        if (writer) reinterpret_cast<float4*>(ex.pro_x_out + (size_t)m * K)[i] = v;
+        const int kbl = (i >> 5) - kb0;              // 32 float4 per k-block
+        if (kbl >= 0 && kbl < kb_n) {
+          const float4 w4 = reinterpret_cast<const float4*>(ex.pro_weight)[i];
+          const float u0 = v.x * w4.x, u1 = v.y * w4.y, u2 = v.z * w4.z, u3 = v.w * w4.w;
+          const uint2 o2 = *reinterpret_cast<const uint2*>(dst_off + ((i & 31) << 2));
+          uint16_t* blk = reinterpret_cast<uint16_t*>(xrow + kbl * (kXBlockBytes / 2));
+          const uint32_t h01 = f32x2_to_f16x2_sat(u0, u1), h23 = f32x2_to_f16x2_sat(u2, u3);
+          blk[o2.x & 0xFFFFu] = (uint16_t)(h01 & 0xFFFFu); blk[o2.x >> 16] = (uint16_t)(h01 >> 16);
+          blk[o2.y & 0xFFFFu] = (uint16_t)(h23 & 0xFFFFu); blk[o2.y >> 16] = (uint16_t)(h23 >> 16);
+          if (XS == 2) {
+            const float2 r01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+            const float2 r23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+            const uint32_t l01 = f32x2_to_f16x2_sat(fminf(fmaxf(u0, -65504.f), 65504.f) - r01.x, fminf(fmaxf(u1, -65504.f), 65504.f) - r01.y);
+            const uint32_t l23 = f32x2_to_f16x2_sat(fminf(fmaxf(u2, -65504.f), 65504.f) - r23.x, fminf(fmaxf(u3, -65504.f), 65504.f) - r23.y);
+            uint16_t* lo = blk + x_tile_bytes / 2;
+            lo[o2.x & 0xFFFFu] = (uint16_t)(l01 & 0xFFFFu); lo[o2.x >> 16] = (uint16_t)(l01 >> 16);
+            lo[o2.y & 0xFFFFu] = (uint16_t)(l23 & 0xFFFFu); lo[o2.y >> 16] = (uint16_t)(l23 >> 16);
+          }
         }
       }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) s_red[m * kMaxWarps + seg] = ss;
     }
-    // stage: a thread owns 8-position chunks, one activation row at a time
+    // k-blocks past the end of the row are staged as zeros (their weights are zero; 0 x garbage must not be NaN)
+    const int tail = kg_n * 4 - kb_n;
+    for (int i = tid; i < tail * kBlock * p.M; i += n_threads) {
+      const int m = i / (tail * kBlock), j = i - m * (tail * kBlock);
+      const int kbl = kb_n + (j >> 7), pos = j & 127;
+      uint16_t* blk = reinterpret_cast<uint16_t*>(reinterpret_cast<__half*>(x_s) + (m / XR) * XS * (x_tile_bytes / 2) + (m % XR) * 4 +
+                                                  kbl * (kXBlockBytes / 2));
+      blk[dst_off[pos]] = 0;
+      if (XS == 2) blk[x_tile_bytes / 2 + dst_off[pos]] = 0;
+    }
+    __syncthreads();
+    if (tid < p.M) {
+      float tot = 0.f;
+      for (int j = 0; j < wpr; ++j) tot += s_red[tid * kMaxWarps + j];
+      s_scale[tid] = 1.0f / sqrtf(tot / (float)K + ex.pro_eps);
+    }
+  } else if (PRO == 2) {
+    // SwiGLU: a thread owns 8-position chunks, one activation row at a time
     const int chunks = kg_n * 4 * 16;
     for (int c = tid; c < chunks; c += n_threads) {
       const int kbl = c >> 4, p0 = (c & 15) << 3;
@@ -408,13 +548,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
       const bool live = kbl < kb_n;
       const size_t col = (size_t)kb0 * kBlock + (size_t)c * 8;
       __half* cblk = reinterpret_cast<__half*>(x_s) + kbl * (kXBlockBytes / 2);
-      float wv[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) wv[j] = 1.f;
-      if (PRO == 1 && live) {
-        const float4 a = *reinterpret_cast<const float4*>(p.pro_weight + col), b = *reinterpret_cast<const float4*>(p.pro_weight + col + 4);
-        wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
-      }
 #pragma unroll
       for (int m = 0; m < 8; ++m) {
         if (m < p.M) {
@@ -422,26 +555,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
 #pragma unroll
           for (int j = 0; j < 8; ++j) v[j] = 0.f;
           if (live) {
-            if (PRO == 1) {
-              const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)m * K + col;
-              const float4 a = *reinterpret_cast<const float4*>(xr), b = *reinterpret_cast<const float4*>(xr + 4);
-              v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-              if (p.pro_delta) {
-                const float* dr = p.pro_delta + (size_t)m * K + col;
-                const float4 da = *reinterpret_cast<const float4*>(dr), db = *reinterpret_cast<const float4*>(dr + 4);
-                v[0] += da.x; v[1] += da.y; v[2] += da.z; v[3] += da.w; v[4] += db.x; v[5] += db.y; v[6] += db.z; v[7] += db.w;
-              }
+            const float* gr = reinterpret_cast<const float*>(p.x) + (size_t)m * 2 * K + col;
+            const float4 ga = *reinterpret_cast<const float4*>(gr), gb = *reinterpret_cast<const float4*>(gr + 4);
+            const float4 ua = *reinterpret_cast<const float4*>(gr + K), ub = *reinterpret_cast<const float4*>(gr + K + 4);
+            const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+            const float uu[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
 #pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = v[j] * inv[m] * wv[j];
-            } else {
-              const float* gr = reinterpret_cast<const float*>(p.x) + (size_t)m * 2 * K + col;
-              const float4 ga = *reinterpret_cast<const float4*>(gr), gb = *reinterpret_cast<const float4*>(gr + 4);
-              const float4 ua = *reinterpret_cast<const float4*>(gr + K), ub = *reinterpret_cast<const float4*>(gr + K + 4);
-              const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
-              const float uu[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = gg[j] / (1.0f + __expf(-gg[j])) * uu[j];
-            }
+            for (int j = 0; j < 8; ++j) v[j] = gg[j] / (1.0f + __expf(-gg[j])) * uu[j];
           }
           __half* blk = cblk + (m / XR) * XS * (x_tile_bytes / 2) + (m % XR) * 4;
 #pragma unroll
@@ -616,37 +736,98 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
         }
       }
     }
-    // the unit's 16 x (NT*8) tile goes to its own slot (plain stores, no atomics): the sum over a row
-    // tile's units below has a fixed order, so results do not depend on which warp finished first
-    float* urow = unit_acc + (size_t)u * (16 * NT * 8) + g * (NT * 8) + 2 * t;
+    // the unit's partial tile goes to its own slot (plain stores, no atomics): the sums over a row
+    // tile's units below have a fixed order, so results do not depend on which warp finished first
+    float* ut = unit_acc + (size_t)u * kUnitTile;
+    if (XR == 1) {
+      if (t == 0) {
+        ut[g] = c[0][0][0] + c[1][0][0];
+        ut[g + 8] = c[0][0][2] + c[1][0][2];
+      }
+    } else {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      *reinterpret_cast<float2*>(urow + nt * 8) = make_float2(c[0][nt][0] + c[1][nt][0], c[0][nt][1] + c[1][nt][1]);
-      *reinterpret_cast<float2*>(urow + 8 * NT * 8 + nt * 8) = make_float2(c[0][nt][2] + c[1][nt][2], c[0][nt][3] + c[1][nt][3]);
+      for (int nt = 0; nt < NT; ++nt) {
+        *reinterpret_cast<float2*>(ut + g * kUnitCols + nt * 8 + 2 * t) = make_float2(c[0][nt][0] + c[1][nt][0], c[0][nt][1] + c[1][nt][1]);
+        *reinterpret_cast<float2*>(ut + (g + 8) * kUnitCols + nt * 8 + 2 * t) = make_float2(c[0][nt][2] + c[1][nt][2], c[0][nt][3] + c[1][nt][3]);
+      }
     }
   }
-  __syncthreads();
-  for (int i = tid; i < rt_n * 16 * NT * 8; i += n_threads) {
-    const int rtl = i / (16 * NT * 8), e = i - rtl * (16 * NT * 8);
-    float v = 0.f;
-    if ((e & (NT * 8 - 1)) < p.M) {  // columns past M hold products with unstaged activations
-      const float* src = unit_acc + (size_t)rtl * kg_n * (16 * NT * 8) + e;
-      for (int kgl = 0; kgl < kg_n; ++kgl) v += src[(size_t)kgl * (16 * NT * 8)];
-    }
-    acc[i] = v;
-  }
-  for (int i = rt_n * 16 * NT * 8 + tid; i < acc_n; i += n_threads) acc[i] = 0.f;
   __syncthreads();
   NB_TRACE_MARK(5);
+  // sum over the k-groups of row r (local), column m, in k order
+  auto row_sum = [&](int r, int m) {
+    const float* src = unit_acc + (size_t)(r >> 4) * kg_n * kUnitTile + (r & 15) * kUnitCols + (XR == 1 ? 0 : m);
+    float v = 0.f;
+    for (int kg = 0; kg < kg_n; kg += 8) {  // eight loads in flight, then the adds in order
+      float part[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) part[j] = (kg + j < kg_n) ? src[(size_t)(kg + j) * kUnitTile] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v += part[j];
+    }
+    return v;
+  };
 
   const int rows_here = rt_n * 16;
   const int row0 = rt0 * 16;
-  if (gridDim.y > 1) {
-    // ---- split-K fix-up: the accumulator tile goes to scratch as is; the CTA that takes the last
-    // ticket of its row group adds all partial tiles in fixed order and writes y.
-    float4* mine = reinterpret_cast<float4*>(p.scratch + ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * acc_n);
-    const float4* acc4 = reinterpret_cast<const float4*>(acc);
-    for (int i = tid; i < acc_n / 4; i += n_threads) __stcg(mine + i, acc4[i]);
+  // Output: y, or (push) slot `rank` of the next set of every rank's exchange buffer.
+  uint32_t push_seq = 0;
+  size_t push_off = 0;
+  void* const out_y = p.y;
+  const int out_n = p.N, out_dtype = p.y_dtype;  // the lambdas below must not refer to the view struct itself
+  auto emit = [&](int m, int row, float v) {
+    if (PRO == 1) v *= s_scale[m];
+    if (PUSH) {
+      const size_t off = push_off + (size_t)m * out_n + row;
+      const unsigned long long* tab = xchg_table(ex.xchg_self, ex.xchg_world, ex.xchg_max_count);
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (q < ex.xchg_world) reinterpret_cast<float*>(__ldg(tab + q))[off] = v;
+    } else {
+      store_y(out_y, out_dtype, (size_t)m * out_n + row, v);
+    }
+  };
+  // After a CTA has written its rows: the last writer of the grid (one per row group) raises this
+  // rank's flag on every rank.  Each writer's stores are fenced at system scope before its ticket.
+  auto finish_push = [&]() {
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+      uint8_t* self = ex.xchg_self;
+      int* ticket = reinterpret_cast<int*>(xchg_seq(self, ex.xchg_world, ex.xchg_max_count) + 1);
+      if (atomicAdd(ticket, 1) == (int)gridDim.x - 1) {
+        __threadfence();
+        const int set = push_seq & 1;
+        const unsigned long long* tab = xchg_table(self, ex.xchg_world, ex.xchg_max_count);
+        for (int q = 0; q < ex.xchg_world; ++q)
+          st_release_sys_u32(xchg_flags(reinterpret_cast<const uint8_t*>(__ldg(tab + q)), ex.xchg_world, ex.xchg_max_count) +
+                                 set * ex.xchg_world + ex.xchg_rank, push_seq);
+        *xchg_seq(self, ex.xchg_world, ex.xchg_max_count) = push_seq;
+        *ticket = 0;
+      }
+    }
+  };
+  if (gridDim.y == 1) {
+    if (PUSH) {
+      push_seq = __ldcg(xchg_seq(ex.xchg_self, ex.xchg_world, ex.xchg_max_count)) + 1;
+      push_off = ((size_t)(push_seq & 1) * ex.xchg_world + ex.xchg_rank) * ex.xchg_max_count;
+    }
+    for (int e = tid; e < p.M * rows_here; e += n_threads) {
+      const int m = e / rows_here, r = e - m * rows_here;
+      if (row0 + r < p.N) emit(m, row0 + r, row_sum(r, m));
+    }
+    if (PUSH) finish_push();
+    NB_TRACE_MARK(6);
+    return;
+  }
+  // ---- split-K fix-up: this CTA's partial tile (rows x NT*8 columns) goes to scratch; the CTA that
+  // takes the last ticket of its row group adds all partial tiles in fixed order and writes y.
+  {
+    float* mine = p.scratch + ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * acc_n;
+    for (int i = tid; i < acc_n; i += n_threads) {
+      const int r = i / (NT * 8), m = i - r * (NT * 8);
+      __stcg(mine + i, (r < rows_here && m < p.M) ? row_sum(r, m) : 0.f);
+    }
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -673,10 +854,15 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
     if (tid == 0) p.counters[blockIdx.x] = 0;
     __syncthreads();
   }
+  if (PUSH) {
+    push_seq = __ldcg(xchg_seq(ex.xchg_self, ex.xchg_world, ex.xchg_max_count)) + 1;
+    push_off = ((size_t)(push_seq & 1) * ex.xchg_world + ex.xchg_rank) * ex.xchg_max_count;
+  }
   for (int e = tid; e < p.M * rows_here; e += n_threads) {
     const int m = e / rows_here, r = e - m * rows_here;
-    if (row0 + r < p.N) store_y(p.y, p.y_dtype, (size_t)m * p.N + row0 + r, acc[r * (NT * 8) + m]);
+    if (row0 + r < p.N) emit(m, row0 + r, acc[r * (NT * 8) + m]);
   }
+  if (PUSH) finish_push();
   NB_TRACE_MARK(6);
 }
 
@@ -707,7 +893,7 @@ static GemvPlan make_plan(int M, int N, int K, int bits, int cb_dtype, int x_ter
     const int cs = whole ? kb_cnt * cb_blk : skew_stride(kb_cnt * cb_blk);
     for (int tr = 1; tr <= std::min(row_tiles, kMaxTr); ++tr) {
       const size_t smem = (size_t)tr * 16 * (ws + cs) + (size_t)nt * x_terms * kgp * 4 * x_block_bytes(M == 1 ? 1 : 8) +
-                          (size_t)tr * 16 * nt * 8 * 4 * (1 + kgp) + 2 * kBlock + 128;
+                          (size_t)tr * 16 * nt * 8 * 4 + (size_t)tr * kgp * 16 * (M == 1 ? 1 : nt * 8) * 4 + 2 * kBlock + 144;
       if (smem > (size_t)kMaxSmem) break;
       const int gx = (row_tiles + tr - 1) / tr;
       if (parts > 1 && gx >= kCounterInts - 1) continue;  // one ticket counter per row group
@@ -764,13 +950,13 @@ static size_t plan_workspace(const GemvPlan& pl, int M) {
   return counter_bytes(pl) + scratch;
 }
 
-template <int BITS, int NT, int XR, int XS, int PRO = 0>
-static int launch(const GemvParams& prm, const GemvPlan& pl, cudaStream_t st) {
+template <int BITS, int NT, int XR, int XS, int PRO = 0, int PUSH = 0>
+static int launch(const GemvParams& prm, const GemvExtra& extra, const GemvPlan& pl, cudaStream_t st) {
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BITS, NT, XR, XS, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BITS, NT, XR, XS, PRO, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     if (e != cudaSuccess) return record_cuda_error(e);
     attr_done[dev & 63] = true;
   }
@@ -786,7 +972,11 @@ static int launch(const GemvParams& prm, const GemvPlan& pl, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return record_cuda_error(cudaLaunchKernelEx(&cfg, gemv_kernel<BITS, NT, XR, XS, PRO>, prm));
+  if constexpr (PRO != 0 || PUSH != 0) {
+    return record_cuda_error(cudaLaunchKernelEx(&cfg, gemv_kernel<BITS, NT, XR, XS, PRO, PUSH>, prm, extra));
+  } else {
+    return record_cuda_error(cudaLaunchKernelEx(&cfg, gemv_kernel<BITS, NT, XR, XS, PRO, PUSH>, prm, GemvNoExtra{}));
+  }
 }
 
 }  // namespace nb
@@ -825,13 +1015,49 @@ struct Prologue {
   const float* weight = nullptr;
   float* x_out = nullptr;
   float eps = 0.f;
+  // tensor-parallel exchange
+  void* exchange = nullptr;
+  int world = 0, rank = 0, max_count = 0, gather = 0, push = 0;
+  uint32_t spin_limit = 0;
 };
+constexpr uint32_t kXchgSpinLimit = 1u << 23;  // about a second with the 100 ns back-off
+
+// Sum over the ranks of the vectors pushed last -> out (count floats); grid of a few CTAs, each waits itself.
+__global__ void __launch_bounds__(256) exchange_gather_kernel(float* __restrict__ out, int count, const uint8_t* self, int world,
+                                                              int max_count, uint32_t spin_limit, int* status) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int tid = threadIdx.x;
+  const uint32_t seq = __ldcg(xchg_seq(self, world, max_count));
+  const int set = seq & 1;
+  if (tid < world) {
+    const uint32_t* flag = xchg_flags(self, world, max_count) + set * world + tid;
+    uint32_t spins = 0;
+    while (ld_acquire_sys_u32(flag) != seq) {
+      __nanosleep(100);
+      if (++spins > spin_limit) {
+        if (status) atomicExch(status, (int)NB_ERR_TIMEOUT);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  const float* slots = reinterpret_cast<const float*>(self) + (size_t)set * world * max_count;
+  for (int i = blockIdx.x * blockDim.x + tid; i < count / 4; i += gridDim.x * blockDim.x) {
+    float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int q = 0; q < world; ++q) {
+      const float4 e = __ldcv(reinterpret_cast<const float4*>(slots + (size_t)q * max_count) + i);
+      d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+    }
+    reinterpret_cast<float4*>(out)[i] = d;
+  }
+}
 }  // namespace nb
 
 static int gemv_impl(const Prologue& pro, const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook,
                      int cb_dtype, int bits, int block_size, int N, int K, void* y, int y_dtype, void* workspace,
                      size_t workspace_bytes, void* stream) {
-  if (!x || !packed || !codebook || !y) return NB_ERR_ARG;
+  if (!x || !packed || !codebook) return NB_ERR_ARG;
   if (x_dtype < NB_F32 || x_dtype > NB_BF16 || y_dtype < NB_F32 || y_dtype > NB_BF16) return NB_ERR_ARG;
   if (cb_dtype != NB_F16 && cb_dtype != NB_F32) return NB_ERR_ARG;
   if (int rc = gemv_check_shape(M, N, K, bits, block_size)) return rc;
@@ -843,6 +1069,14 @@ static int gemv_impl(const Prologue& pro, const void* x, int x_dtype, int M, con
     if (pro.kind == 1 && (!pro.weight || pro.x_out == x)) return NB_ERR_ARG;
     if ((uintptr_t)x % 16 || (uintptr_t)pro.delta % 16 || (uintptr_t)pro.weight % 16 || (uintptr_t)pro.x_out % 16) return NB_ERR_ALIGN;
   }
+  if (pro.gather || pro.push) {
+    if (!pro.exchange || pro.world < 1 || pro.world > 8 || pro.rank < 0 || pro.rank >= pro.world) return NB_ERR_ARG;
+    if (pro.max_count < 4 || (pro.max_count & 3)) return NB_ERR_ARG;
+    if (pro.gather && (pro.kind != 1 || (size_t)M * K > (size_t)pro.max_count)) return NB_ERR_SHAPE;
+    if (pro.push && (size_t)M * N > (size_t)pro.max_count) return NB_ERR_SHAPE;
+    if ((uintptr_t)pro.exchange % 16) return NB_ERR_ALIGN;
+  }
+  if (!pro.push && !y) return NB_ERR_ARG;
   if (int rc = check_device()) return rc;
   const int x_terms = x_dtype == NB_F32 ? 2 : 1;
   const GemvPlan pl = cached_plan(M, N, K, bits, cb_dtype, x_terms, sm_count());
@@ -854,28 +1088,36 @@ static int gemv_impl(const Prologue& pro, const void* x, int x_dtype, int M, con
 
   GemvParams prm{};
   prm.x = x; prm.packed = packed; prm.codebook = codebook; prm.y = y;
-  if (have_ws) {
-    prm.counters = reinterpret_cast<int*>(workspace);
-    prm.status = prm.counters + (kCounterInts - 1);
-    prm.scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + counter_bytes(pl));
-  }
-  prm.M = M; prm.N = N; prm.bpr = K / kBlock; prm.row_tiles = (N + 15) / 16; prm.kgroups = (prm.bpr + 3) / 4;
-  prm.tr = pl.tr; prm.kg_per_part = pl.kg_per_part;
-  prm.x_dtype = x_dtype; prm.y_dtype = y_dtype; prm.cb_dtype = cb_dtype;
-  prm.x_vec = ((uintptr_t)x % 16 == 0) ? 1 : 0;
+  if (have_ws) prm.counters = reinterpret_cast<int*>(workspace);
+  if (K / kBlock > 65535 || pl.kg_per_part > 65535) return NB_ERR_SHAPE;
+  prm.M = (uint8_t)M; prm.N = N; prm.bpr = (uint16_t)(K / kBlock);
+  prm.tr = (uint8_t)pl.tr; prm.kg_per_part = (uint16_t)pl.kg_per_part;
+  prm.dtypes = (uint8_t)(x_dtype | (y_dtype << 2) | (cb_dtype << 4));
   prm.w_stride = pl.w_stride; prm.c_stride = pl.c_stride;
-  prm.cb_bulk = ((prm.bpr * ((cb_dtype == NB_F16 ? 2 : 4) << bits)) % 16 == 0) ? 1 : 0;
-  prm.tile_bulk = (pl.parts == 1 && prm.cb_bulk) ? 1 : 0;
-  prm.pro_delta = pro.delta; prm.pro_weight = pro.weight; prm.pro_x_out = pro.x_out; prm.pro_eps = pro.eps;
+  const int cb_bulk = (((K / kBlock) * ((cb_dtype == NB_F16 ? 2 : 4) << bits)) % 16 == 0) ? 1 : 0;
+  const int tile_bulk = (pl.parts == 1 && cb_bulk) ? 1 : 0;
+  prm.flags = (uint8_t)((((uintptr_t)x % 16 == 0) ? 1 : 0) | (cb_bulk << 1) | (tile_bulk << 2));
   cudaStream_t st = (cudaStream_t)stream;
-  if (pro.kind != 0) {
-#define NB_GEMV_PRO(B, P) (M > 1 ? launch<B, 1, 8, 2, P>(prm, pl, st) : launch<B, 1, 1, 2, P>(prm, pl, st))
-    if (bits == 3) return pro.kind == 1 ? NB_GEMV_PRO(3, 1) : NB_GEMV_PRO(3, 2);
-    return pro.kind == 1 ? NB_GEMV_PRO(2, 1) : NB_GEMV_PRO(2, 2);
+  GemvExtra extra{};
+  extra.pro_delta = pro.delta; extra.pro_weight = pro.weight; extra.pro_x_out = pro.x_out; extra.pro_eps = pro.eps;
+  if (pro.gather || pro.push) {
+    extra.xchg_self = reinterpret_cast<uint8_t*>(pro.exchange);
+    extra.xchg_world = pro.world; extra.xchg_rank = pro.rank; extra.xchg_max_count = pro.max_count;
+    extra.gather = pro.gather;
+    extra.xchg_spin = pro.spin_limit ? pro.spin_limit : kXchgSpinLimit;
+    if (!prm.counters) return NB_ERR_WORKSPACE;  // the bounded wait reports through the workspace's status word
+  }
+  if (pro.kind != 0 || pro.push) {  // fp32 activations, M <= 8
+    if (M > 8 || x_dtype != NB_F32) return NB_ERR_SHAPE;
+#define NB_GEMV_PRO(B, P, E) (M > 1 ? launch<B, 1, 8, 2, P, E>(prm, extra, pl, st) : launch<B, 1, 1, 2, P, E>(prm, extra, pl, st))
+#define NB_GEMV_PRO_B(P, E) (bits == 3 ? NB_GEMV_PRO(3, P, E) : NB_GEMV_PRO(2, P, E))
+    if (pro.push) return pro.kind == 2 ? NB_GEMV_PRO_B(2, 1) : pro.kind == 0 ? NB_GEMV_PRO_B(0, 1) : NB_ERR_ARG;
+    return pro.kind == 1 ? NB_GEMV_PRO_B(1, 0) : NB_GEMV_PRO_B(2, 0);
+#undef NB_GEMV_PRO_B
 #undef NB_GEMV_PRO
   }
 #define NB_GEMV_DISPATCH(B, XSV)                                                               \
-  (M > 8 ? launch<B, 2, 8, XSV>(prm, pl, st) : M > 1 ? launch<B, 1, 8, XSV>(prm, pl, st) : launch<B, 1, 1, XSV>(prm, pl, st))
+  (M > 8 ? launch<B, 2, 8, XSV>(prm, extra, pl, st) : M > 1 ? launch<B, 1, 8, XSV>(prm, extra, pl, st) : launch<B, 1, 1, XSV>(prm, extra, pl, st))
   if (bits == 3) return x_terms == 2 ? NB_GEMV_DISPATCH(3, 2) : NB_GEMV_DISPATCH(3, 1);
   return x_terms == 2 ? NB_GEMV_DISPATCH(2, 2) : NB_GEMV_DISPATCH(2, 1);
 #undef NB_GEMV_DISPATCH
@@ -896,6 +1138,56 @@ extern "C" int nb_gemv_fused(int prologue, const float* x, const float* delta, c
   if (prologue == NB_PRO_ADD_RMSNORM) { pro.delta = delta; pro.weight = norm_weight; pro.x_out = x_out; pro.eps = eps; }
   return gemv_impl(pro, x, NB_F32, M, packed, codebook, cb_dtype, bits, block_size, N, K, y, y_dtype, workspace, workspace_bytes,
                    stream);
+}
+
+extern "C" size_t nb_exchange_buffer_bytes(int world, int max_count) {
+  if (world < 1 || world > 8 || max_count < 4 || (max_count & 3)) return 0;
+  return xchg_bytes(world, max_count);
+}
+
+extern "C" int nb_exchange_init(void* exchange, const uint64_t* peer_bufs, int world, int rank, int max_count) {
+  if (!exchange || !peer_bufs || world < 1 || world > 8 || rank < 0 || rank >= world) return NB_ERR_ARG;
+  if (max_count < 4 || (max_count & 3)) return NB_ERR_ARG;
+  unsigned long long table[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int q = 0; q < world; ++q) {
+    if (!peer_bufs[q] || peer_bufs[q] % 16) return NB_ERR_ALIGN;
+    table[q] = peer_bufs[q];
+  }
+  if (peer_bufs[rank] != (uint64_t)(uintptr_t)exchange) return NB_ERR_ARG;
+  return record_cuda_error(cudaMemcpy(xchg_table(reinterpret_cast<const uint8_t*>(exchange), world, max_count), table, sizeof(table),
+                                      cudaMemcpyHostToDevice));
+}
+
+extern "C" int nb_gemv_tp(int prologue, const float* x, const float* delta, const float* norm_weight, float eps, float* x_out, int M,
+                          const uint8_t* packed, const void* codebook, int cb_dtype, int bits, int block_size, int N, int K, void* y,
+                          int y_dtype, void* workspace, size_t workspace_bytes, void* exchange, int world, int rank, int max_count,
+                          int gather, int push, uint32_t spin_limit, void* stream) {
+  Prologue pro;
+  pro.kind = prologue;
+  if (prologue == NB_PRO_ADD_RMSNORM) { pro.delta = gather ? nullptr : delta; pro.weight = norm_weight; pro.x_out = x_out; pro.eps = eps; }
+  pro.exchange = exchange; pro.world = world; pro.rank = rank; pro.max_count = max_count;
+  pro.gather = gather ? 1 : 0; pro.push = push ? 1 : 0; pro.spin_limit = spin_limit;
+  return gemv_impl(pro, x, NB_F32, M, packed, codebook, cb_dtype, bits, block_size, N, K, y, push ? NB_F32 : y_dtype, workspace,
+                   workspace_bytes, stream);
+}
+
+extern "C" int nb_exchange_gather(float* out, int count, const void* exchange, int world, int rank, int max_count,
+                                  uint32_t spin_limit, int* status, void* stream) {
+  if (!out || !exchange || world < 1 || world > 8 || rank < 0 || rank >= world) return NB_ERR_ARG;
+  if (count < 4 || (count & 3) || count > max_count || (max_count & 3)) return NB_ERR_SHAPE;
+  if ((uintptr_t)out % 16 || (uintptr_t)exchange % 16) return NB_ERR_ALIGN;
+  if (int rc = check_device()) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(std::max(1, std::min(8, count / 4 / 256)));
+  cfg.blockDim = dim3(256);
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return record_cuda_error(cudaLaunchKernelEx(&cfg, exchange_gather_kernel, out, count, reinterpret_cast<const uint8_t*>(exchange),
+                                              world, max_count, spin_limit ? spin_limit : kXchgSpinLimit, status));
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -108,6 +108,15 @@ class PackedGPT(torch.nn.Module):
             from .comm import OneShotAllReduce
             self.oneshot = OneShotAllReduce(max_batch * self.n_embd, self.embedding.device, self.group)
 
+    def enable_fused_allreduce(self, max_batch: int = 8) -> None:
+        """Fold the decode step's all-reduces into the packed GEMVs on both sides of them (nb_gemv_tp):
+        the row-sharded projections push their partial results into every rank's exchange buffer and
+        the next GEMV sums them while it stages its activations.  Used by DecodeSession for up to 8
+        sequences; prefill and larger batches keep the collective."""
+        if self.tp_size > 1:
+            from .comm import Exchange
+            self.exchange = Exchange(max_batch * self.n_embd, self.embedding.device, self.group)
+
     def _all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         if self.tp_size > 1:
             ar = getattr(self, "oneshot", None)
@@ -293,35 +302,52 @@ class DecodeSession:
         m, cfg = self.model, self.model.config
         eps = cfg.norm_eps
         fold = self.B <= 8
+        xch = getattr(m, "exchange", None) if fold else None     # all-reduces folded into the GEMVs
         xa, xb = self.bx, self.bx2                                # residual stream, ping-pong
         xa.copy_(m.embedding[self.token[:, 0]])
         delta = None
+        pending = False                                           # a pushed vector waits to be gathered
 
         def norm_linear(lin, delta, w, out):
-            nonlocal xa, xb
-            if fold:
-                ops.gemv_fused(ops.PRO_ADD_RMSNORM, xa, lin.packed_indices, lin.codebook, lin.bits, lin.block_size,
-                               lin.out_features, lin.in_features, out, delta=delta, norm_weight=w, eps=eps, x_out=xb)
+            nonlocal xa, xb, pending
+            args = (lin.packed_indices, lin.codebook, lin.bits, lin.block_size, lin.out_features, lin.in_features)
+            if pending:
+                ops.gemv_tp(ops.PRO_ADD_RMSNORM, xa, *args, xch, out=out, gather=True, norm_weight=w, eps=eps, x_out=xb)
+                xa, xb = xb, xa
+                pending = False
+            elif fold:
+                ops.gemv_fused(ops.PRO_ADD_RMSNORM, xa, *args, out, delta=delta, norm_weight=w, eps=eps, x_out=xb)
                 xa, xb = xb, xa
             else:
                 ops.add_rmsnorm(xa, delta, w, eps, self.bh)
                 self._linear_into(lin, self.bh, out)
 
+        def row_parallel(lin, prologue, x, out):
+            """out_proj / down: the result is a partial sum over the ranks."""
+            nonlocal pending
+            args = (lin.packed_indices, lin.codebook, lin.bits, lin.block_size, lin.out_features, lin.in_features)
+            if xch is not None:
+                ops.gemv_tp(prologue, x, *args, xch, push=True)
+                pending = True
+                return None
+            if prologue == ops.PRO_SILU_MUL and fold:
+                ops.gemv_fused(prologue, x, *args, out)
+            elif prologue == ops.PRO_SILU_MUL:
+                ops.silu_mul(x, self.bhm)
+                self._linear_into(lin, self.bhm, out)
+            else:
+                self._linear_into(lin, x, out)
+            return m._all_reduce(out)
+
         for i, blk in enumerate(m.blocks):
             k_buf, v_buf, _ = self.caches[i]
             norm_linear(blk.qkv, delta, blk.ln1, self.bqkv)
             ops.decode_attention_rope(self.bqkv, m.cos2, m.sin2, self.pos, k_buf, v_buf, self.batt, m.o_col0)
-            self._linear_into(blk.out_proj, self.batt, self.bo)
-            m._all_reduce(self.bo)
-            norm_linear(blk.gate_up, self.bo, blk.ln2, self.bgu)
-            if fold:
-                lin = blk.down
-                ops.gemv_fused(ops.PRO_SILU_MUL, self.bgu, lin.packed_indices, lin.codebook, lin.bits, lin.block_size,
-                               lin.out_features, lin.in_features, self.bd)
-            else:
-                ops.silu_mul(self.bgu, self.bhm)
-                self._linear_into(blk.down, self.bhm, self.bd)
-            m._all_reduce(self.bd)
+            delta = row_parallel(blk.out_proj, ops.PRO_NONE, self.batt, self.bo)
+            norm_linear(blk.gate_up, delta, blk.ln2, self.bgu)
+            delta = row_parallel(blk.down, ops.PRO_SILU_MUL, self.bgu, self.bd)
+        if pending:
+            ops.exchange_gather(self.bd, xch, xch.status)
             delta = self.bd
         ops.add_rmsnorm(xa, delta, m.ln_f, eps, self.bh)
         logits = self.bh.to(m.embedding.dtype) @ m.embedding.T

@@ -106,6 +106,11 @@ def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     return ws
 
 
+def workspace_status(ws: torch.Tensor) -> int:
+    """The status word of a GEMV workspace (0, or NB_ERR_TIMEOUT = 6 if a bounded wait ran out); synchronises."""
+    return int(ws[4095 * 4:4096 * 4].view(torch.int32).item())
+
+
 def gemv_workspace_bytes(m: int, n: int, k: int, bits: int, block_size: int) -> int:
     key = (m, n, k, bits, block_size)
     need = _ws_need.get(key)
@@ -146,7 +151,7 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: in
     return out
 
 
-PRO_ADD_RMSNORM, PRO_SILU_MUL = 1, 2
+PRO_NONE, PRO_ADD_RMSNORM, PRO_SILU_MUL = 0, 1, 2
 
 
 def gemv_fused(prologue: int, x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size: int,
@@ -173,6 +178,36 @@ def gemv_fused(prologue: int, x: torch.Tensor, packed: torch.Tensor, codebook: t
     if rc:
         _lib.check(rc, "nb_gemv_fused")
     return out
+
+
+def gemv_tp(prologue: int, x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size: int,
+            n: int, k: int, exchange, out: torch.Tensor | None = None, gather: bool = False, push: bool = False,
+            norm_weight: torch.Tensor | None = None, eps: float = 0.0, x_out: torch.Tensor | None = None,
+            delta: torch.Tensor | None = None, ws: torch.Tensor | None = None) -> None:
+    """nb_gemv_fused with the tensor-parallel all-reduce folded in: push sends the result to every
+    rank's exchange buffer (comm.Exchange) instead of `out`; gather takes the residual delta as the sum
+    of the vectors the ranks pushed last."""
+    cols = 2 * k if prologue == PRO_SILU_MUL else k
+    if not x.is_cuda or x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] != cols or not x.is_contiguous():
+        raise RuntimeError(f"x must be a contiguous fp32 CUDA (M, {cols}) tensor; got {x.dtype} {tuple(x.shape)}")
+    m = x.shape[0]
+    if ws is None:
+        ws = workspace(x.device, gemv_workspace_bytes(m, n, k, bits, block_size))
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    rc = _lib.lib().nb_gemv_tp(prologue, x.data_ptr(), ptr(delta), ptr(norm_weight), eps, ptr(x_out), m, packed.data_ptr(),
+                               codebook.data_ptr(), _DTYPE[codebook.dtype], bits, block_size, n, k, ptr(out),
+                               _DTYPE[out.dtype] if out is not None else 0, ws.data_ptr(), ws.numel(), exchange.buf.data_ptr(),
+                               exchange.world, exchange.rank, exchange.max_count, int(gather), int(push), exchange.spin_limit,
+                               _stream())
+    if rc:
+        _lib.check(rc, "nb_gemv_tp")
+
+
+def exchange_gather(out: torch.Tensor, exchange, status: torch.Tensor) -> None:
+    rc = _lib.lib().nb_exchange_gather(out.data_ptr(), out.numel(), exchange.buf.data_ptr(), exchange.world, exchange.rank,
+                                       exchange.max_count, exchange.spin_limit, status.data_ptr(), _stream())
+    if rc:
+        _lib.check(rc, "nb_exchange_gather")
 
 
 _prefill_ws: dict = {}
