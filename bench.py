@@ -222,7 +222,7 @@ def run_ours(args):
     y_down = torch.empty(LAYERS, m, HIDDEN, dtype=torch.bfloat16 if world == 1 else torch.float32, device=dev)
     ws = ops.workspace(dev, 8 << 20)
     oneshot = None
-    if world > 1 and args.allreduce == "oneshot":
+    if world > 1 and args.allreduce in ("oneshot", "fused"):
         from nativebit_b200.comm import OneShotAllReduce
         oneshot = OneShotAllReduce(m * HIDDEN, dev)
 
@@ -431,8 +431,10 @@ def run_ours(args):
         torch.cuda.empty_cache()
         cfg = G.ModelConfig()
         model = G.PackedGPT.random_init(cfg, seed=0, device=dev, tp_rank=rank, tp_size=world)
-        if world > 1 and args.allreduce == "oneshot":
+        if world > 1 and args.allreduce in ("oneshot", "fused"):
             model.enable_oneshot_allreduce(max_batch=1)
+        if world > 1 and args.allreduce == "fused":
+            model.enable_fused_allreduce(max_batch=1)
         gen = torch.Generator().manual_seed(0)
         prompt = torch.randint(0, cfg.vocab_size, (128,), generator=gen)
         res = G.benchmark(model, prompt, n_generate=256, n_runs=2)
@@ -459,8 +461,10 @@ def run_ours(args):
         for bits in (3, 2):
             cfg = G.ModelConfig(bits=bits)
             model = G.PackedGPT.random_init(cfg, seed=0, device=dev, tp_rank=rank, tp_size=world)
-            if world > 1 and args.allreduce == "oneshot":
+            if world > 1 and args.allreduce in ("oneshot", "fused"):
                 model.enable_oneshot_allreduce(max_batch=64)
+            if world > 1 and args.allreduce == "fused":
+                model.enable_fused_allreduce(max_batch=8)
             prompt = torch.randint(0, cfg.vocab_size, (512,), generator=torch.Generator().manual_seed(1))
             for b in (1, 8, 32, 64):
                 res = G.benchmark(model, prompt, n_generate=64, n_runs=1, batch_size=b)
@@ -553,8 +557,9 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "nccl"],
-                    help="tensor-parallel all-reduce: the one-shot peer-memory kernel or NCCL")
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "oneshot", "nccl"],
+                    help="tensor-parallel all-reduce of the decoder: folded into the packed GEMVs (peer-memory push + gather; "
+                         "the one-shot kernel where that does not apply), the one-shot peer-memory kernel, or NCCL")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2048-token prefill GEMM leg")
     ap.add_argument("--serving", action="store_true", help="add the batch 1/8/32/64, 3-bit and 2-bit decode sweep (configs[4])")
     ap.add_argument("--no-decode", action="store_true", help="skip the 2.2B decoder leg")

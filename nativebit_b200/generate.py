@@ -386,6 +386,18 @@ class DecodeSession:
         self.token.copy_(self.logits.argmax(-1, keepdim=True))
         self.pos.add_(1)
 
+    def check(self) -> None:
+        """Raises if a bounded wait of the step's kernels ever ran out (a copy barrier, or a peer of the
+        tensor-parallel exchange that never arrived).  Reads device status words: synchronises."""
+        with torch.cuda.stream(self.stream):
+            ws = ops.workspace(self.model.embedding.device, 0)
+        if ops.workspace_status(ws) != 0:
+            raise RuntimeError("nb_gemv: a bounded wait ran out (status NB_ERR_TIMEOUT in the workspace)")
+        for name in ("oneshot", "exchange"):
+            obj = getattr(self.model, name, None)
+            if obj is not None and int(obj.status.item()) != 0:
+                raise RuntimeError(f"{name}: a peer did not arrive within the bounded wait")
+
     def step(self) -> None:
         """One decode step for every sequence: consumes self.token, leaves the next token there."""
         if not self.use_graph:
@@ -436,6 +448,7 @@ def benchmark(model: PackedGPT, prompt_tokens, n_generate: int = 128, n_runs: in
         torch.cuda.synchronize()
         pre.append(t1 - t0)
         gen.append(time.perf_counter() - t1)
+    sess.check()
     g, p = sum(gen) / len(gen), sum(pre) / len(pre)
     return {"label": f"b{batch_size}", "prompt_len": prompt.shape[1], "n_generate": n_generate, "n_runs": n_runs,
             "prefill_ms": round(p * 1e3, 2), "prefill_tps": round(prompt.numel() / p, 1),
