@@ -143,6 +143,15 @@ int nb_decode_attention_rope(const float* qkv, const float* cos2, const float* s
                              float* v_cache, int B, int H, int hd, int ctx, float* out, int out_stride, int out_offset,
                              void* stream);
 
+/* The two ends of a decode step (inference/generate_torch.py:142-160: embedding lookup; tied LM head,
+ * 30*tanh(x/30) soft-cap; :300-310 greedy argmax), for one sequence per CTA.
+ * nb_embed_rows: out (B, C) fp32 = table[token[b], :] of a bf16 (V, C) table.
+ * nb_softcap_argmax: logits (B, V) NB_BF16 or NB_F32 -> logits_out (B, V) fp32 = cap * tanh(x / cap);
+ *   token[b] = index of the largest capped logit (lowest index among equals); *pos += 1 if pos != NULL. */
+int nb_embed_rows(const void* table_bf16, const int64_t* token, int B, int V, int C, float* out, void* stream);
+int nb_softcap_argmax(const void* logits, int logits_dtype, int B, int V, float cap, float* logits_out, int64_t* token,
+                      int64_t* pos, void* stream);
+
 /* ---- nb_gemv with the preceding element-wise step of the decoder folded into the staging of its
  * activations, so the step needs no separate launch for it (fp32 activations, M <= 8; everything
  * else as nb_gemv).  The reference runs these as separate torch ops around each packed linear

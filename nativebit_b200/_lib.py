@@ -44,6 +44,9 @@ _SIGNATURES = {
     "nb_allreduce_buffer_bytes": (_c.c_size_t, [_c.c_int, _c.c_int]),
     "nb_allreduce": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_uint32,
                                 _c.c_void_p, _c.c_void_p]),
+    "nb_embed_rows": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
+    "nb_softcap_argmax": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_float, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                     _c.c_void_p]),
     "nb_gemv_fused": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_float, _c.c_void_p, _c.c_int, _c.c_void_p,
                                  _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p,
                                  _c.c_size_t, _c.c_void_p]),

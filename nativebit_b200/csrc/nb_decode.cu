@@ -5,6 +5,7 @@
 // and masked attention, :116-117 SwiGLU).  The position is read from device memory so that the
 // step can be replayed from a CUDA graph.
 #include <cuda_runtime.h>
+#include <cuda_bf16.h>
 #include <cooperative_groups.h>
 
 #include <algorithm>
@@ -311,9 +312,79 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, float* __restrict_
   hmid[i] = g / (1.0f + __expf(-g)) * u;
 }
 
+// out[b, :] = float(table[token[b], :]) for a bf16 (V, C) embedding table; one CTA per sequence.
+__global__ void embed_rows_kernel(const __nv_bfloat16* __restrict__ table, const long long* __restrict__ token, float* __restrict__ out,
+                                  int C, int V) {
+  pdl_enter();
+  long long t = token[blockIdx.x];
+  t = t < 0 ? 0 : (t >= V ? V - 1 : t);
+  const __nv_bfloat16* row = table + (size_t)t * C;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) out[(size_t)blockIdx.x * C + i] = __bfloat162float(row[i]);
+}
+
+// The end of a decode step for one sequence per CTA: logits_out[b, v] = cap * tanh(float(logits[b, v]) / cap),
+// token[b] = index of the largest capped logit (the lowest index among equals), and CTA 0 advances the
+// position.  logits are bf16 (the LM-head product) or fp32.
+constexpr int kFinishThreads = 1024;
+__global__ void __launch_bounds__(kFinishThreads) softcap_argmax_kernel(const void* __restrict__ logits, int is_bf16, int V, float cap,
+                                                                        float* __restrict__ logits_out, long long* __restrict__ token,
+                                                                        long long* __restrict__ pos) {
+  __shared__ float s_val[kFinishThreads / 32];
+  __shared__ int s_idx[kFinishThreads / 32];
+  pdl_enter();
+  const int b = blockIdx.x, tid = threadIdx.x;
+  float best = -FLT_MAX;
+  int best_i = 0x7fffffff;
+  for (int i = tid; i < V; i += kFinishThreads) {
+    const float x = is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[(size_t)b * V + i])
+                            : reinterpret_cast<const float*>(logits)[(size_t)b * V + i];
+    const float y = cap * tanhf(x / cap);
+    logits_out[(size_t)b * V + i] = y;
+    if (y > best || (y == best && i < best_i)) { best = y; best_i = i; }   // NaN never wins, as in a max-reduction that skips it
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  if ((tid & 31) == 0) { s_val[tid >> 5] = best; s_idx[tid >> 5] = best_i; }
+  __syncthreads();
+  if (tid < 32) {
+    best = s_val[tid]; best_i = s_idx[tid];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (tid == 0) {
+      token[b] = best_i == 0x7fffffff ? 0 : best_i;
+      if (b == 0 && pos) *pos += 1;
+    }
+  }
+}
+
 }  // namespace nb
 
 using namespace nb;
+
+extern "C" int nb_embed_rows(const void* table_bf16, const int64_t* token, int B, int V, int C, float* out, void* stream) {
+  if (!table_bf16 || !token || !out || B < 1 || V < 1 || C < 1) return NB_ERR_ARG;
+  if (int rc = check_device()) return rc;
+  return launch_pdl(embed_rows_kernel, dim3(B), dim3(256), 0, (cudaStream_t)stream, reinterpret_cast<const __nv_bfloat16*>(table_bf16),
+                    reinterpret_cast<const long long*>(token), out, C, V);
+}
+
+extern "C" int nb_softcap_argmax(const void* logits, int logits_dtype, int B, int V, float cap, float* logits_out, int64_t* token,
+                                 int64_t* pos, void* stream) {
+  if (!logits || !logits_out || !token || B < 1 || V < 1 || !(cap > 0.f)) return NB_ERR_ARG;
+  if (logits_dtype != NB_BF16 && logits_dtype != NB_F32) return NB_ERR_ARG;
+  if (int rc = check_device()) return rc;
+  return launch_pdl(softcap_argmax_kernel, dim3(B), dim3(kFinishThreads), 0, (cudaStream_t)stream, logits,
+                    logits_dtype == NB_BF16 ? 1 : 0, V, cap, logits_out, reinterpret_cast<long long*>(token),
+                    reinterpret_cast<long long*>(pos));
+}
 
 extern "C" int nb_add_rmsnorm(float* x, const float* delta, const float* w, float eps, float* out, int B, int C, void* stream) {
   if (!x || !w || !out || B < 1 || C < 1) return NB_ERR_ARG;

@@ -304,7 +304,10 @@ class DecodeSession:
         fold = self.B <= 8
         xch = getattr(m, "exchange", None) if fold else None     # all-reduces folded into the GEMVs
         xa, xb = self.bx, self.bx2                                # residual stream, ping-pong
-        xa.copy_(m.embedding[self.token[:, 0]])
+        if m.embedding.dtype == torch.bfloat16:
+            ops.embed_rows(m.embedding, self.token, xa)
+        else:
+            xa.copy_(m.embedding[self.token[:, 0]])
         delta = None
         pending = False                                           # a pushed vector waits to be gathered
 
@@ -350,11 +353,8 @@ class DecodeSession:
             ops.exchange_gather(self.bd, xch, xch.status)
             delta = self.bd
         ops.add_rmsnorm(xa, delta, m.ln_f, eps, self.bh)
-        logits = self.bh.to(m.embedding.dtype) @ m.embedding.T
-        cap = cfg.logit_cap
-        self.logits.copy_(cap * torch.tanh(logits.float() / cap))
-        self.token.copy_(self.logits.argmax(-1, keepdim=True))
-        self.pos.add_(1)
+        logits = self.bh.to(m.embedding.dtype) @ m.embedding.T   # the LM head is a plain library GEMM (bf16, 164 MB)
+        ops.softcap_argmax(logits, cfg.logit_cap, self.logits, self.token, self.pos)
 
     @torch.no_grad()
     def prefill(self, prompt: torch.Tensor) -> torch.Tensor:

@@ -284,5 +284,23 @@ def decode_attention_rope(qkv, cos2, sin2, pos, k_cache, v_cache, out, out_offse
                                                    out.shape[1], out_offset, _stream()), "nb_decode_attention_rope")
 
 
+def embed_rows(table: torch.Tensor, token: torch.Tensor, out: torch.Tensor) -> None:
+    """out (B, C) fp32 = table[token] for a bf16 (V, C) table and int64 token (B,)."""
+    if table.dtype != torch.bfloat16 or token.dtype != torch.int64 or out.dtype != torch.float32:
+        raise RuntimeError("embed_rows needs a bf16 table, int64 tokens and an fp32 output")
+    _lib.check(_lib.lib().nb_embed_rows(table.data_ptr(), token.data_ptr(), out.shape[0], table.shape[0], table.shape[1],
+                                        out.data_ptr(), _stream()), "nb_embed_rows")
+
+
+def softcap_argmax(logits: torch.Tensor, cap: float, logits_out: torch.Tensor, token: torch.Tensor,
+                   pos: torch.Tensor | None = None) -> None:
+    """logits_out = cap * tanh(logits / cap) (fp32); token[b] = argmax; pos += 1 (if given)."""
+    if logits.dtype not in (torch.bfloat16, torch.float32) or not logits.is_contiguous() or token.dtype != torch.int64:
+        raise RuntimeError("softcap_argmax needs contiguous bf16/fp32 logits and int64 tokens")
+    _lib.check(_lib.lib().nb_softcap_argmax(logits.data_ptr(), _DTYPE[logits.dtype], logits.shape[0], logits.shape[1], cap,
+                                            logits_out.data_ptr(), token.data_ptr(), pos.data_ptr() if pos is not None else None,
+                                            _stream()), "nb_softcap_argmax")
+
+
 def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> None:
     _lib.check(_lib.lib().nb_silu_mul(gu.data_ptr(), gu.shape[0], out.shape[1], out.data_ptr(), _stream()), "nb_silu_mul")

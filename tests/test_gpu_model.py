@@ -133,6 +133,35 @@ def test_decode_attention_against_torch(built_lib, B, H, hd, ctx):
         assert (out.double() - ref).abs().max() <= 2e-5 * ref.abs().max(), p_
 
 
+def test_step_ends_match_torch(built_lib):
+    """Embedding lookup and soft-cap + argmax kernels against the torch expressions of the reference's step."""
+    from nativebit_b200 import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(3)
+    V, C, B = 32000, 2560, 5
+    table = (0.02 * torch.randn(V, C, device=dev, generator=g)).bfloat16()
+    token = torch.tensor([[0], [V - 1], [17], [31999], [12345]], device=dev)
+    out = torch.empty(B, C, device=dev)
+    ops.embed_rows(table, token, out)
+    assert torch.equal(out, table[token[:, 0]].float())
+    for dtype in (torch.bfloat16, torch.float32):
+        logits = (40 * torch.randn(B, V, device=dev, generator=g)).to(dtype)
+        logits[1, 100] = logits[1, 7] = 1000.0                   # saturated: equal capped values, lowest index wins
+        cap = 30.0
+        ref = cap * torch.tanh(logits.float() / cap)
+        capped = torch.empty(B, V, device=dev)
+        tok = torch.zeros(B, 1, dtype=torch.long, device=dev)
+        pos = torch.tensor([41], device=dev)
+        ops.softcap_argmax(logits, cap, capped, tok, pos)
+        assert torch.equal(capped, ref)
+        assert int(pos.item()) == 42
+        best = ref.max(dim=1).values
+        for b in range(B):
+            first = int((ref[b] == best[b]).nonzero()[0])
+            assert int(tok[b, 0]) == first
+        assert int(tok[1, 0]) == int((ref[1] == ref[1].max()).nonzero()[0])
+
+
 def test_batched_session(built_lib, gm):
     from nativebit_b200 import generate as G
     dev = torch.device("cuda:0")
