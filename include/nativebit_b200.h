@@ -80,7 +80,8 @@ int nb_quantize(const float* w, int64_t total, const void* codebook, int cb_dtyp
  * (dequant_matvec_3bit_kernel + wrapper), inference/triton_kernel.py:144-196 (Triton 3-bit kernel)
  * and, for 2 <= M <= 16, the unpack+gather+matmul of inference/triton_kernel.py:258-275.
  * x: (M, K) row-major of x_dtype; y: (M, N) row-major of y_dtype; fp32 accumulation.
- * bits in {2,3}; block_size 128 (or 64 for tensor-parallel sub-blocks); K % block_size == 0.
+ * bits in {2,3,4} (codebooks of 4, 8, 16 entries; 4-bit in the nativebit/pack.py:75-90 nibble layout);
+ * block_size 128; K % 128 == 0.
  * packed and codebook must be 16-byte aligned.  Weights enter the tensor-core contraction as
  * exact fp16 values (an fp32 codebook is rounded to fp16).  bf16/fp16 activations enter as fp16
  * (exact for bf16 inputs of magnitude 6.1e-5..65504; larger magnitudes are clamped); fp32
@@ -183,8 +184,9 @@ int nb_gemv_fused(int prologue, const float* x, const float* delta, const float*
  * max_count >= M*N (push) and M*K (gather), a multiple of 4.  All ranks must issue the same sequence
  * of push and gather calls, and a push must be consumed (a gather by nb_gemv_tp or nb_exchange_gather)
  * before the next push.  A workspace is required (its status word receives NB_ERR_TIMEOUT when the
- * wait of spin_limit probes, 0 = default of about a second, runs out; the kernel then continues with
- * what has arrived and does not hang).  Plain loads and stores on peer memory only: no TMA, no multicast.
+ * wait of spin_limit probes, 0 = default of several seconds, runs out; the kernel then continues with
+ * what has arrived and does not hang, and later launches that find the status word set do not wait again).
+ * Plain loads and stores on peer memory only: no TMA, no multicast.
  * nb_exchange_gather: the same sum written to out (count floats), for a consumer that is not a GEMV. */
 size_t nb_exchange_buffer_bytes(int world, int max_count);
 int nb_exchange_init(void* exchange, const uint64_t* peer_bufs, int world, int rank, int max_count);

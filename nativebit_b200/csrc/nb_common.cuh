@@ -4,8 +4,8 @@
 // Packed layout consumed here is exactly what the reference's packer writes
 // (nativebit/pack.py:21-41 for 3-bit: index j of a group of 8 sits at bits [3j,3j+3) of a
 // little-endian 24-bit word; nativebit/pack.py:97-116 for 2-bit: LSB-first bit stream, so
-// index j of a byte sits at bits [2j,2j+2)).  A codebook block covers 128 consecutive
-// weights = 48 bytes (3-bit) or 32 bytes (2-bit).
+// index j of a byte sits at bits [2j,2j+2); nativebit/pack.py:75-82 for 4-bit: low nibble first).
+// A codebook block covers 128 consecutive weights = 48 bytes (3-bit), 32 bytes (2-bit) or 64 bytes (4-bit).
 #pragma once
 #include <cstdint>
 #include <cstddef>
@@ -25,6 +25,7 @@ constexpr int kBlock = 128;  // weights per codebook block handled by the fast k
 template <int BITS> struct Fmt;
 template <> struct Fmt<3> { static constexpr int kWords = 12; static constexpr int kEntries = 8; };
 template <> struct Fmt<2> { static constexpr int kWords = 8;  static constexpr int kEntries = 4; };
+template <> struct Fmt<4> { static constexpr int kWords = 16; static constexpr int kEntries = 16; };
 
 NB_HD uint32_t funnel_r(uint32_t lo, uint32_t hi, int s) {
 #if defined(__CUDA_ARCH__)
@@ -78,6 +79,9 @@ NB_HD void selectors2(uint32_t w0, uint32_t w1, uint32_t (&U)[4]) {
 template <int BITS> NB_HD int slot_position(int q, int u, int k);
 template <> NB_HD int slot_position<3>(int q, int u, int k) { return 32 * q + field3(u, k); }
 template <> NB_HD int slot_position<2>(int q, int u, int k) { return 32 * q + 16 * (u >> 1) + 2 * k + (u & 1); }
+// 4-bit (nativebit/pack.py:75-82: low nibble first): a packed word already holds eight indices in
+// order, one per nibble; bit 3 of a nibble is part of the index, so the lookup splits it off.
+template <> NB_HD int slot_position<4>(int q, int u, int k) { return 32 * q + 8 * u + k; }
 
 template <int BITS> NB_HD void group_selectors(const uint32_t* w, int q, uint32_t (&U)[4]);
 template <> NB_HD void group_selectors<3>(const uint32_t* w, int q, uint32_t (&U)[4]) {
@@ -85,6 +89,10 @@ template <> NB_HD void group_selectors<3>(const uint32_t* w, int q, uint32_t (&U
 }
 template <> NB_HD void group_selectors<2>(const uint32_t* w, int q, uint32_t (&U)[4]) {
   selectors2(w[2 * q], w[2 * q + 1], U);
+}
+
+template <> NB_HD void group_selectors<4>(const uint32_t* w, int q, uint32_t (&U)[4]) {
+  U[0] = w[4 * q]; U[1] = w[4 * q + 1]; U[2] = w[4 * q + 2]; U[3] = w[4 * q + 3];
 }
 
 // A contraction "step" consumes four weights of a block: step s = 8q + 2u + h uses nibbles

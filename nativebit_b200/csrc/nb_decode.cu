@@ -335,12 +335,25 @@ __global__ void __launch_bounds__(kFinishThreads) softcap_argmax_kernel(const vo
   const int b = blockIdx.x, tid = threadIdx.x;
   float best = -FLT_MAX;
   int best_i = 0x7fffffff;
-  for (int i = tid; i < V; i += kFinishThreads) {
-    const float x = is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[(size_t)b * V + i])
-                            : reinterpret_cast<const float*>(logits)[(size_t)b * V + i];
-    const float y = cap * tanhf(x / cap);
-    logits_out[(size_t)b * V + i] = y;
-    if (y > best || (y == best && i < best_i)) { best = y; best_i = i; }   // NaN never wins, as in a max-reduction that skips it
+  for (int i0 = tid; i0 < V; i0 += 8 * kFinishThreads) {  // eight loads in flight per thread
+    float x[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = i0 + j * kFinishThreads;
+      x[j] = 0.f;
+      if (i < V)
+        x[j] = is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[(size_t)b * V + i])
+                       : reinterpret_cast<const float*>(logits)[(size_t)b * V + i];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = i0 + j * kFinishThreads;
+      if (i < V) {
+        const float y = cap * tanhf(x[j] / cap);
+        logits_out[(size_t)b * V + i] = y;
+        if (y > best || (y == best && i < best_i)) { best = y; best_i = i; }   // NaN never wins, as in a max-reduction that skips it
+      }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -372,7 +385,7 @@ using namespace nb;
 extern "C" int nb_embed_rows(const void* table_bf16, const int64_t* token, int B, int V, int C, float* out, void* stream) {
   if (!table_bf16 || !token || !out || B < 1 || V < 1 || C < 1) return NB_ERR_ARG;
   if (int rc = check_device()) return rc;
-  return launch_pdl(embed_rows_kernel, dim3(B), dim3(256), 0, (cudaStream_t)stream, reinterpret_cast<const __nv_bfloat16*>(table_bf16),
+  return launch_pdl(embed_rows_kernel, dim3(B), dim3(1024), 0, (cudaStream_t)stream, reinterpret_cast<const __nv_bfloat16*>(table_bf16),
                     reinterpret_cast<const long long*>(token), out, C, V);
 }
 

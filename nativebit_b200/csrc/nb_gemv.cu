@@ -227,9 +227,24 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
 }
 
 // Four table lookups: selector nibbles 0..3 of `sel` -> two registers of two fp16 weights.
-// T = {low-byte plane lo, low-byte plane hi, high-byte plane lo, high-byte plane hi}.
-__device__ __forceinline__ void lookup4(uint32_t sel, const uint32_t (&T)[4], uint32_t& r01, uint32_t& r23) {
-  const uint32_t lo = prmt(T[0], T[1], sel), hi = prmt(T[2], T[3], sel);
+// Up to 8 entries: T = {low-byte plane lo, low-byte plane hi, high-byte plane lo, high-byte plane hi}.
+// 16 entries (4-bit): T[0..3] as above for entries 0..7, T[4..7] for entries 8..15; bit 3 of a nibble
+// selects between the two halves through a byte mask (0xFF where the index is >= 8) that a permute
+// of {0x00000000, 0xFFFFFFFF} produces from index >> 1.
+template <int BITS>
+__device__ __forceinline__ void lookup4(uint32_t sel, const uint32_t (&T)[BITS == 4 ? 8 : 4], uint32_t& r01, uint32_t& r23) {
+  uint32_t lo, hi;
+  if (BITS == 4) {
+    const uint32_t s7 = sel & 0x7777u;
+    const uint32_t m = prmt(0u, 0xFFFFFFFFu, (sel >> 1) & 0x7777u);
+    const uint32_t lo0 = prmt(T[0], T[1], s7), lo1 = prmt(T[4], T[5], s7);
+    const uint32_t hi0 = prmt(T[2], T[3], s7), hi1 = prmt(T[6], T[7], s7);
+    lo = (lo0 & ~m) | (lo1 & m);
+    hi = (hi0 & ~m) | (hi1 & m);
+  } else {
+    lo = prmt(T[0], T[1], sel);
+    hi = prmt(T[2], T[3], sel);
+  }
   r01 = prmt(lo, hi, 0x5140);
   r23 = prmt(lo, hi, 0x7362);
 }
@@ -241,34 +256,41 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 
 // One block's codebook (in shared memory) -> byte planes for lookup4; zero table if !valid.
 template <int BITS>
-__device__ __forceinline__ void make_table(const uint8_t* cb, int cb_dtype, bool valid, uint32_t (&T)[4]) {
-  uint32_t e[4] = {0, 0, 0, 0};  // 2^BITS fp16 entries, two per register
+__device__ __forceinline__ void make_table(const uint8_t* cb, int cb_dtype, bool valid, uint32_t (&T)[BITS == 4 ? 8 : 4]) {
+  constexpr int kRegs = BITS == 4 ? 8 : 4;
+  uint32_t e[kRegs];  // 2^BITS fp16 entries, two per register
+#pragma unroll
+  for (int i = 0; i < kRegs; ++i) e[i] = 0u;
   if (valid) {
-    if (BITS == 3) {
-      if (cb_dtype == NB_F16) {
-        const uint4 v = *reinterpret_cast<const uint4*>(cb);
-        e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
-      } else {
-        const float4 a = *reinterpret_cast<const float4*>(cb);
-        const float4 b = *reinterpret_cast<const float4*>(cb + 16);
-        e[0] = pack_half2(a.x, a.y); e[1] = pack_half2(a.z, a.w); e[2] = pack_half2(b.x, b.y); e[3] = pack_half2(b.z, b.w);
-      }
-    } else {
-      if (cb_dtype == NB_F16) {
+    constexpr int kEntries = 1 << BITS;
+    if (cb_dtype == NB_F16) {
+      if (BITS == 2) {
         const uint2 v = *reinterpret_cast<const uint2*>(cb);
         e[0] = v.x; e[1] = v.y;
       } else {
-        const float4 a = *reinterpret_cast<const float4*>(cb);
-        e[0] = pack_half2(a.x, a.y); e[1] = pack_half2(a.z, a.w);
+#pragma unroll
+        for (int i = 0; i < kEntries / 8; ++i) {
+          const uint4 v = *reinterpret_cast<const uint4*>(cb + 16 * i);
+          e[4 * i] = v.x; e[4 * i + 1] = v.y; e[4 * i + 2] = v.z; e[4 * i + 3] = v.w;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kEntries / 4; ++i) {
+        const float4 a = *reinterpret_cast<const float4*>(cb + 16 * i);
+        e[2 * i] = pack_half2(a.x, a.y); e[2 * i + 1] = pack_half2(a.z, a.w);
       }
     }
   }
-  if (BITS == 3) {
-    T[0] = prmt(e[0], e[1], 0x6420); T[1] = prmt(e[2], e[3], 0x6420);
-    T[2] = prmt(e[0], e[1], 0x7531); T[3] = prmt(e[2], e[3], 0x7531);
-  } else {  // 4 entries: selector values 0..3 pick from the first operand
+  if (BITS == 2) {  // 4 entries: selector values 0..3 pick from the first operand
     T[0] = prmt(e[0], e[1], 0x6420); T[2] = prmt(e[0], e[1], 0x7531);
     T[1] = T[2]; T[3] = T[0];
+  } else {
+#pragma unroll
+    for (int h = 0; h < kRegs / 4; ++h) {
+      T[4 * h + 0] = prmt(e[4 * h], e[4 * h + 1], 0x6420); T[4 * h + 1] = prmt(e[4 * h + 2], e[4 * h + 3], 0x6420);
+      T[4 * h + 2] = prmt(e[4 * h], e[4 * h + 1], 0x7531); T[4 * h + 3] = prmt(e[4 * h + 2], e[4 * h + 3], 0x7531);
+    }
   }
 }
 
@@ -457,7 +479,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
       const int set = seq & 1;
       if (tid < ex.xchg_world) {
         const uint32_t* flag = xchg_flags(self, ex.xchg_world, ex.xchg_max_count) + set * ex.xchg_world + tid;
-        uint32_t spins = 0;
+        // a wait that already ran out once is not repeated by later launches: the step finishes quickly
+        // and the host finds the status word
+        uint32_t spins = (p.status && *reinterpret_cast<volatile int*>(p.status) == (int)NB_ERR_TIMEOUT) ? ex.xchg_spin : 0;
         while (ld_acquire_sys_u32(flag) != seq) {
           __nanosleep(100);
           if (++spins > ex.xchg_spin) {
@@ -698,9 +722,15 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
     const int kbl = 4 * kgl + t;                 // this lane's k-block inside the CTA's range
     const bool vk = kbl < kb_n;
     const int ra = rtl * 16 + g, rb = ra + 8;
-    uint32_t wa[kWords], wb[kWords], TA[4], TB[4];
-    read_block<BITS>(w_s + ra * p.w_stride + (vk ? kbl : 0) * kBlkBytes, wa);
-    read_block<BITS>(w_s + rb * p.w_stride + (vk ? kbl : 0) * kBlkBytes, wb);
+    // 2 and 3 bits: the block's words are read up front; 4 bits: a group's four words are its selector
+    // words, read from shared memory group by group (16 + 16 words would not fit the register budget)
+    uint32_t wa[BITS == 4 ? 1 : kWords], wb[BITS == 4 ? 1 : kWords], TA[BITS == 4 ? 8 : 4], TB[BITS == 4 ? 8 : 4];
+    const uint8_t* blk_a = w_s + ra * p.w_stride + (vk ? kbl : 0) * kBlkBytes;
+    const uint8_t* blk_b = w_s + rb * p.w_stride + (vk ? kbl : 0) * kBlkBytes;
+    if (BITS != 4) {
+      read_block<BITS>(blk_a, reinterpret_cast<uint32_t (&)[kWords]>(wa));
+      read_block<BITS>(blk_b, reinterpret_cast<uint32_t (&)[kWords]>(wb));
+    }
     make_table<BITS>(c_s + ra * p.c_stride + (vk ? kbl : 0) * cb_blk, p.cb_dtype, vk, TA);
     make_table<BITS>(c_s + rb * p.c_stride + (vk ? kbl : 0) * cb_blk, p.cb_dtype, vk, TB);
 
@@ -713,8 +743,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       uint32_t UA[4], UB[4];
-      group_selectors<BITS>(wa, q, UA);
-      group_selectors<BITS>(wb, q, UB);
+      if (BITS == 4) {
+        const uint4 va = *reinterpret_cast<const uint4*>(blk_a + 16 * q), vb = *reinterpret_cast<const uint4*>(blk_b + 16 * q);
+        UA[0] = va.x; UA[1] = va.y; UA[2] = va.z; UA[3] = va.w;
+        UB[0] = vb.x; UB[1] = vb.y; UB[2] = vb.z; UB[3] = vb.w;
+      } else {
+        group_selectors<BITS>(wa, q, UA);
+        group_selectors<BITS>(wb, q, UB);
+      }
 #pragma unroll
       for (int uu = 0; uu < 4; ++uu) {
 #pragma unroll
@@ -723,8 +759,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
           const uint32_t sa = h ? (UA[uu] >> 16) : UA[uu];
           const uint32_t sb = h ? (UB[uu] >> 16) : UB[uu];
           uint32_t a0, a1, a2, a3;
-          lookup4(sa, TA, a0, a2);
-          lookup4(sb, TB, a1, a3);
+          lookup4<BITS>(sa, TA, a0, a2);
+          lookup4<BITS>(sb, TB, a1, a3);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -985,7 +1021,7 @@ using namespace nb;
 
 static int gemv_check_shape(int M, int N, int K, int bits, int block_size) {
   if (M < 1 || N < 1 || K < 1) return NB_ERR_ARG;
-  if (bits != 2 && bits != 3) return NB_ERR_SHAPE;
+  if (bits != 2 && bits != 3 && bits != 4) return NB_ERR_SHAPE;
   if (block_size != kBlock) return NB_ERR_SHAPE;
   if (M > 16 || K % kBlock != 0) return NB_ERR_SHAPE;
   return NB_OK;
@@ -1020,7 +1056,7 @@ struct Prologue {
   int world = 0, rank = 0, max_count = 0, gather = 0, push = 0;
   uint32_t spin_limit = 0;
 };
-constexpr uint32_t kXchgSpinLimit = 1u << 23;  // about a second with the 100 ns back-off
+constexpr uint32_t kXchgSpinLimit = 1u << 23;  // several seconds: a probe is an L2 round trip plus the 100 ns back-off
 
 // Sum over the ranks of the vectors pushed last -> out (count floats); grid of a few CTAs, each waits itself.
 __global__ void __launch_bounds__(256) exchange_gather_kernel(float* __restrict__ out, int count, const uint8_t* self, int world,
@@ -1032,7 +1068,7 @@ __global__ void __launch_bounds__(256) exchange_gather_kernel(float* __restrict_
   const int set = seq & 1;
   if (tid < world) {
     const uint32_t* flag = xchg_flags(self, world, max_count) + set * world + tid;
-    uint32_t spins = 0;
+    uint32_t spins = (status && *reinterpret_cast<volatile int*>(status) == (int)NB_ERR_TIMEOUT) ? spin_limit : 0;
     while (ld_acquire_sys_u32(flag) != seq) {
       __nanosleep(100);
       if (++spins > spin_limit) {
@@ -1110,7 +1146,7 @@ static int gemv_impl(const Prologue& pro, const void* x, int x_dtype, int M, con
   if (pro.kind != 0 || pro.push) {  // fp32 activations, M <= 8
     if (M > 8 || x_dtype != NB_F32) return NB_ERR_SHAPE;
 #define NB_GEMV_PRO(B, P, E) (M > 1 ? launch<B, 1, 8, 2, P, E>(prm, extra, pl, st) : launch<B, 1, 1, 2, P, E>(prm, extra, pl, st))
-#define NB_GEMV_PRO_B(P, E) (bits == 3 ? NB_GEMV_PRO(3, P, E) : NB_GEMV_PRO(2, P, E))
+#define NB_GEMV_PRO_B(P, E) (bits == 3 ? NB_GEMV_PRO(3, P, E) : bits == 2 ? NB_GEMV_PRO(2, P, E) : NB_GEMV_PRO(4, P, E))
     if (pro.push) return pro.kind == 2 ? NB_GEMV_PRO_B(2, 1) : pro.kind == 0 ? NB_GEMV_PRO_B(0, 1) : NB_ERR_ARG;
     return pro.kind == 1 ? NB_GEMV_PRO_B(1, 0) : NB_GEMV_PRO_B(2, 0);
 #undef NB_GEMV_PRO_B
@@ -1119,6 +1155,7 @@ static int gemv_impl(const Prologue& pro, const void* x, int x_dtype, int M, con
 #define NB_GEMV_DISPATCH(B, XSV)                                                               \
   (M > 8 ? launch<B, 2, 8, XSV>(prm, extra, pl, st) : M > 1 ? launch<B, 1, 8, XSV>(prm, extra, pl, st) : launch<B, 1, 1, XSV>(prm, extra, pl, st))
   if (bits == 3) return x_terms == 2 ? NB_GEMV_DISPATCH(3, 2) : NB_GEMV_DISPATCH(3, 1);
+  if (bits == 4) return x_terms == 2 ? NB_GEMV_DISPATCH(4, 2) : NB_GEMV_DISPATCH(4, 1);
   return x_terms == 2 ? NB_GEMV_DISPATCH(2, 2) : NB_GEMV_DISPATCH(2, 1);
 #undef NB_GEMV_DISPATCH
 }

@@ -74,7 +74,7 @@ template <int BITS> static bool selftest_bits(std::mt19937& rng) {
       uint32_t U[4];
       group_selectors<BITS>(w, q, U);
       for (int u = 0; u < 4; ++u) {
-        if (U[u] & 0x88888888u) return false;  // bit 3 of every nibble must be clear
+        if (BITS < 4 && (U[u] & 0x88888888u)) return false;  // bit 3 of every nibble must be clear (it belongs to the index at 4 bits)
         for (int k = 0; k < 8; ++k) {
           const int pos = slot_position<BITS>(q, u, k);
           if (pos < 0 || pos >= kBlock || seen[pos]) return false;
@@ -113,5 +113,6 @@ extern "C" int nb_selftest_tables(void) {
   std::mt19937 rng(1234);
   if (!nb::selftest_bits<3>(rng)) return NB_ERR_SHAPE;
   if (!nb::selftest_bits<2>(rng)) return NB_ERR_SHAPE;
+  if (!nb::selftest_bits<4>(rng)) return NB_ERR_SHAPE;
   return NB_OK;
 }

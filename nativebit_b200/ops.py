@@ -118,7 +118,7 @@ def gemv_workspace_bytes(m: int, n: int, k: int, bits: int, block_size: int) -> 
         need = _ws_need[key] = int(_lib.lib().nb_gemv_workspace_bytes(m, n, k, bits, block_size))
         if need == 0:
             raise RuntimeError(f"nb_gemv does not support M={m} N={n} K={k} bits={bits} block_size={block_size} "
-                               "(needs 1 <= M <= 16, bits in {2,3}, block_size 128, K % 128 == 0)")
+                               "(needs 1 <= M <= 16, bits in {2,3,4}, block_size 128, K % 128 == 0)")
     return need
 
 

@@ -68,8 +68,8 @@ class PackedLinear(torch.nn.Module):
         if not x_flat.is_contiguous():
             x_flat = x_flat.contiguous()
         m = x_flat.shape[0]
-        if self.block_size != BS or self.bits not in (2, 3):
-            # shapes outside the fused kernels (small codebook blocks, 4-bit): gather kernel + matmul
+        if self.block_size != BS or self.bits not in (2, 3, 4):
+            # shapes outside the fused kernels (small codebook blocks): gather kernel + matmul
             w = ops.dequant(self.packed_indices, self.codebook, self.bits, self.block_size,
                             (self.out_features, self.in_features),
                             dtype=x_flat.dtype if x_flat.dtype in (torch.float16, torch.bfloat16) else torch.float32)

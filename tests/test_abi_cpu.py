@@ -34,7 +34,7 @@ def test_argument_validation_needs_no_gpu(built_lib):
     assert l.nb_gemv(None, 2, 1, None, None, 1, 3, 128, 16, 128, None, 2, None, 0, None) == 1
     assert l.nb_gemv(fake, 2, 17, fake, fake, 1, 3, 128, 16, 128, fake, 2, None, 0, None) == 3   # M > 16
     assert l.nb_gemv(fake, 2, 1, fake, fake, 1, 3, 128, 16, 100, fake, 2, None, 0, None) == 3    # K % 128
-    assert l.nb_gemv(fake, 2, 1, fake, fake, 1, 4, 128, 16, 128, fake, 2, None, 0, None) == 3    # 4-bit GEMV
+    assert l.nb_gemv(fake, 2, 1, fake, fake, 1, 5, 128, 16, 128, fake, 2, None, 0, None) == 3    # 5-bit GEMV
     odd = ctypes.c_void_p(4100)
     assert l.nb_gemv(fake, 2, 1, odd, fake, 1, 3, 128, 16, 128, fake, 2, None, 0, None) == 2     # alignment
 

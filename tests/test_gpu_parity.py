@@ -107,7 +107,7 @@ def _gemv_case(dev, bits, n, k, m, seed, x_dtype=torch.bfloat16, y_dtype=torch.f
     return y.float().cpu().numpy().astype(np.float64), ref
 
 
-@pytest.mark.parametrize("bits", [3, 2])
+@pytest.mark.parametrize("bits", [3, 2, 4])
 @pytest.mark.parametrize("n,k", [(16, 128), (48, 384), (40, 256), (17, 512), (256, 2560), (1000, 640), (64, 6912)])
 @pytest.mark.parametrize("m", [1, 2, 3, 4, 8, 9, 16])
 def test_gemv_small_shapes(dev, bits, n, k, m):
@@ -126,6 +126,15 @@ def test_gemv_model_shapes(dev, n, k, m):
 @pytest.mark.parametrize("n,k,m", [(6912, 2560, 1), (2560, 6912, 16)])
 def test_gemv_2bit_model_shapes(dev, n, k, m):
     y, ref = _gemv_case(dev, 2, n, k, m, seed=4)
+    assert np.abs(y - ref).max() <= 2e-5 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("n,k,m", [(6912, 2560, 1), (2560, 6912, 4), (2560, 2560, 16)])
+def test_gemv_4bit_model_shapes(dev, n, k, m):
+    """16-entry codebooks (nativebit/pack.py:75-90 layout): the fused GEMV, fp16 and fp32 codebooks."""
+    y, ref = _gemv_case(dev, 4, n, k, m, seed=6)
+    assert np.abs(y - ref).max() <= 2e-5 * np.abs(ref).max()
+    y, ref = _gemv_case(dev, 4, n, k, m, seed=6, cb_dtype=torch.float32, x_dtype=torch.float32)
     assert np.abs(y - ref).max() <= 2e-5 * np.abs(ref).max()
 
 
@@ -152,7 +161,7 @@ def test_gemv_fp32_activations_keep_their_precision(dev, n, k, m):
     assert np.abs(y - ref).max() <= 2e-6 * np.abs(ref).max()
 
 
-@pytest.mark.parametrize("bits", [3, 2])
+@pytest.mark.parametrize("bits", [3, 2, 4])
 @pytest.mark.parametrize("n,k,m", [(48, 384, 1), (320, 2560, 1), (320, 2560, 3), (7680, 2560, 1), (13824, 2560, 8), (2560, 2560, 5)])
 @pytest.mark.parametrize("with_delta", [True, False])
 def test_gemv_fused_add_rmsnorm(dev, bits, n, k, m, with_delta):
