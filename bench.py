@@ -472,6 +472,13 @@ def run_ours(args):
                 if world > 1:
                     dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 serving[f"{bits}bit_b{b}"] = {"ms_per_step": round(float(t), 3), "tokens_per_s": round(b * 1e3 / float(t), 1)}
+                if b >= 32:   # the same batch with the packed linears on the tcgen05 GEMM (bf16 operands)
+                    res = G.benchmark(model, prompt, n_generate=64, n_runs=1, batch_size=b, batch_gemm=True)
+                    t = torch.tensor([res["per_token_ms"]], device=dev)
+                    if world > 1:
+                        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    serving[f"{bits}bit_b{b}_bf16_gemm"] = {"ms_per_step": round(float(t), 3),
+                                                            "tokens_per_s": round(b * 1e3 / float(t), 1)}
             del model
             torch.cuda.empty_cache()
 

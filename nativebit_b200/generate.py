@@ -261,9 +261,11 @@ class DecodeSession:
     buffer under a position mask (static shapes), as the reference's cached path does
     (inference/generate_torch.py:91-97)."""
 
-    def __init__(self, model: PackedGPT, batch_size: int = 1, use_graph: bool = True, fused: bool = True):
+    def __init__(self, model: PackedGPT, batch_size: int = 1, use_graph: bool = True, fused: bool = True,
+                 batch_gemm: bool = False):
         self.model, self.B = model, batch_size
         self.fused = fused
+        self.batch_gemm = batch_gemm          # batches >= 32: packed linears on the tensor-core GEMM (bf16 operands)
         dev = model.embedding.device
         self.dev = dev
         self.caches = init_kv_cache(model, batch_size, dev)
@@ -289,8 +291,13 @@ class DecodeSession:
             self.bhm = torch.zeros(B, blk.down.in_features, **f32)
             self.bd = torch.zeros(B, cfg.n_embd, **f32)
 
-    @staticmethod
-    def _linear_into(lin: PackedLinear, x: torch.Tensor, out: torch.Tensor) -> None:
+    def _linear_into(self, lin: PackedLinear, x: torch.Tensor, out: torch.Tensor) -> None:
+        if self.batch_gemm and x.shape[0] >= 32 and lin.in_features % 64 == 0:
+            # large batches, opt-in: dequantise once and multiply on the tcgen05 tensor cores (bf16 operands,
+            # fp32 accumulation: the prefill contract) instead of unpacking the weights once per 16 rows
+            ops.gemm_prefill(x.to(torch.bfloat16), lin.packed_indices, lin.codebook, lin.bits, lin.block_size,
+                             lin.out_features, lin.in_features, out=out)
+            return
         for r in range(0, x.shape[0], 16):
             ops.gemv(x[r:r + 16], lin.packed_indices, lin.codebook, lin.bits, lin.block_size, lin.out_features,
                      lin.in_features, out=out[r:r + 16])
@@ -428,12 +435,13 @@ class DecodeSession:
         return torch.cat(out, dim=1)
 
 
-def benchmark(model: PackedGPT, prompt_tokens, n_generate: int = 128, n_runs: int = 3, device="cuda", batch_size: int = 1):
+def benchmark(model: PackedGPT, prompt_tokens, n_generate: int = 128, n_runs: int = 3, device="cuda", batch_size: int = 1,
+              batch_gemm: bool = False):
     """Decode-speed benchmark with the reference's result keys (inference/generate_torch.py:280-320)
     plus the JAX twin's prefill fields (inference/generate.py:270-280)."""
     dev = model.embedding.device
     prompt = torch.as_tensor(prompt_tokens, dtype=torch.long, device=dev).reshape(1, -1).repeat(batch_size, 1)
-    sess = DecodeSession(model, batch_size)
+    sess = DecodeSession(model, batch_size, batch_gemm=batch_gemm)
     sess.prefill(prompt)
     sess.step()
     torch.cuda.synchronize()
