@@ -556,6 +556,35 @@ def run_gemm_only(args):
     print(json.dumps({"gemm_only": [m, n, k], "us_per_call_dequant_plus_gemm": e0.elapsed_time(e1) * 1e3 / 4}))
 
 
+def run_decode_only(args):
+    """Prefill and a few graph-replayed decode steps of the 2.2B packed decoder at batch 1; the last step
+    runs between cudaProfilerStart/Stop, so a profiler started with --profile-from-start off sees the
+    launches of exactly one step (python bench.py --decode-only STEPS)."""
+    import time
+    import torch
+    from nativebit_b200 import generate as G
+    dev = torch.device("cuda", 0)
+    cfg = G.ModelConfig()
+    model = G.PackedGPT.random_init(cfg, seed=0, device=dev)
+    prompt = torch.randint(0, cfg.vocab_size, (1, 128), generator=torch.Generator().manual_seed(0)).to(dev)
+    sess = G.DecodeSession(model, 1)
+    sess.prefill(prompt)
+    for _ in range(3):
+        sess.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.decode_only):
+        sess.step()
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) / args.decode_only * 1e3
+    torch.cuda.profiler.start()
+    sess.step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    sess.check()
+    print(json.dumps({"decode_only": args.decode_only, "per_token_ms": ms}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -570,13 +599,17 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2048-token prefill GEMM leg")
     ap.add_argument("--serving", action="store_true", help="add the batch 1/8/32/64, 3-bit and 2-bit decode sweep (configs[4])")
     ap.add_argument("--no-decode", action="store_true", help="skip the 2.2B decoder leg")
+    ap.add_argument("--decode-only", type=int, default=0, metavar="STEPS",
+                    help="time STEPS decode steps of the 2.2B decoder at batch 1 and exit (profiling case)")
     ap.add_argument("--gemm-only", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
                     help="launch the prefill GEMM on one shape a few times and exit (profiling case)")
     ap.add_argument("--kernel-only", type=int, nargs=3, metavar=("N", "K", "M"), default=None,
                     help="launch one GEMV shape a few times and exit (profiling case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.gemm_only:
+    if args.decode_only:
+        run_decode_only(args)
+    elif args.gemm_only:
         run_gemm_only(args)
     elif args.kernel_only:
         run_kernel_only(args)
