@@ -1108,6 +1108,7 @@ static int gemv_impl(const Prologue& pro, const void* x, int x_dtype, int M, con
   if (pro.gather || pro.push) {
     if (!pro.exchange || pro.world < 1 || pro.world > 8 || pro.rank < 0 || pro.rank >= pro.world) return NB_ERR_ARG;
     if (pro.max_count < 4 || (pro.max_count & 3)) return NB_ERR_ARG;
+    if (pro.push && pro.kind == 1) return NB_ERR_ARG;  // a row-sharded projection follows attention or SwiGLU, never a norm
     if (pro.gather && (pro.kind != 1 || (size_t)M * K > (size_t)pro.max_count)) return NB_ERR_SHAPE;
     if (pro.push && (size_t)M * N > (size_t)pro.max_count) return NB_ERR_SHAPE;
     if ((uintptr_t)pro.exchange % 16) return NB_ERR_ALIGN;

@@ -58,3 +58,38 @@ def test_python_wrappers_refuse_cpu_tensors(built_lib):
     lin = nbt.PackedLinear(torch.zeros(48 * 16, dtype=torch.uint8), torch.zeros(16, 8, dtype=torch.float16), 16, 128)
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         lin(torch.zeros(1, 128))
+
+
+def test_fused_and_exchange_argument_checks(built_lib):
+    """Argument validation of the prologue / tensor-parallel entry points runs before any device call."""
+    from nativebit_b200 import _lib
+    l = _lib.lib()
+    fake = ctypes.c_void_p(4096)
+    ws = ctypes.c_void_p(8192)
+    # nb_gemv_fused(prologue, x, delta, norm_weight, eps, x_out, M, packed, codebook, cb_dtype, bits, bs, N, K, y, y_dtype, ws, bytes, stream)
+    assert l.nb_gemv_fused(3, fake, None, fake, 1e-6, None, 1, fake, fake, 1, 3, 128, 16, 128, fake, 0, ws, 1 << 20, None) == 1   # unknown prologue
+    assert l.nb_gemv_fused(1, fake, None, None, 1e-6, None, 1, fake, fake, 1, 3, 128, 16, 128, fake, 0, ws, 1 << 20, None) == 1   # no norm weight
+    assert l.nb_gemv_fused(1, fake, None, fake, 1e-6, fake, 1, fake, fake, 1, 3, 128, 16, 128, fake, 0, ws, 1 << 20, None) == 1   # x_out == x
+    assert l.nb_gemv_fused(1, fake, None, fake, 1e-6, None, 9, fake, fake, 1, 3, 128, 16, 128, fake, 0, ws, 1 << 20, None) == 3   # M > 8
+    odd = ctypes.c_void_p(4100)
+    assert l.nb_gemv_fused(2, odd, None, None, 0.0, None, 1, fake, fake, 1, 3, 128, 16, 128, fake, 0, ws, 1 << 20, None) == 2     # x alignment
+    # exchange
+    assert l.nb_exchange_buffer_bytes(9, 1024) == 0 and l.nb_exchange_buffer_bytes(2, 1022) == 0
+    assert l.nb_exchange_buffer_bytes(4, 2560) == 2 * 4 * 2560 * 4 + (2 * 4 + 2) * 4 + 64
+    arr = (ctypes.c_uint64 * 2)(4096, 8192)
+    assert l.nb_exchange_init(fake, arr, 2, 2, 1024) == 1            # rank out of range
+    assert l.nb_exchange_init(fake, arr, 2, 1, 1024) == 1            # entry `rank` is not the own buffer
+    assert l.nb_exchange_init(fake, (ctypes.c_uint64 * 2)(4096, 8200), 2, 0, 1024) == 2   # peer alignment
+    # nb_gemv_tp(..., ws, bytes, exchange, world, rank, max_count, gather, push, spin, stream)
+    common = (fake, None, fake, 1e-6, None, 1, fake, fake, 1, 3, 128, 16, 128, fake, 0, ws, 1 << 20)
+    assert l.nb_gemv_tp(1, *common, None, 2, 0, 1024, 1, 0, 0, None) == 1       # no exchange buffer
+    assert l.nb_gemv_tp(0, *common, fake, 2, 0, 1024, 1, 0, 0, None) == 3       # gather needs the RMSNorm prologue
+    assert l.nb_gemv_tp(1, *common, fake, 2, 0, 64, 1, 0, 0, None) == 3         # M*K > max_count
+    assert l.nb_gemv_tp(0, *common, fake, 2, 0, 8, 0, 1, 0, None) == 3          # M*N > max_count
+    assert l.nb_gemv_tp(1, *common, fake, 2, 0, 1024, 0, 1, 0, None) == 1       # push after the RMSNorm prologue is not a row-parallel layer
+    assert l.nb_exchange_gather(fake, 6, fake, 2, 0, 1024, 0, None, None) == 3  # count % 4
+    # step ends
+    assert l.nb_softcap_argmax(fake, 1, 1, 32000, 30.0, fake, fake, None, None) == 1     # fp16 logits are not supported
+    assert l.nb_softcap_argmax(fake, 2, 1, 32000, 0.0, fake, fake, None, None) == 1      # cap must be positive
+    assert l.nb_embed_rows(None, fake, 1, 10, 8, fake, None) == 1
+    assert l.nb_decode_attention(fake, fake, fake, fake, 1, 4, 82, 64, fake, 328, 0, None) == 3   # head_dim % 4
