@@ -13,7 +13,13 @@ from ._lib import NB_BF16, NB_F16, NB_F32
 _DTYPE = {torch.float32: NB_F32, torch.float16: NB_F16, torch.bfloat16: NB_BF16}
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """cudaStream_t of torch's current stream on the current device."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -142,10 +148,13 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: in
     if dev != torch.cuda.current_device():
         with torch.cuda.device(dev):
             return gemv(x, packed, codebook, bits, block_size, n, k, out=out, ws=ws)
+    st = _stream()
     if ws is None:
-        ws = workspace(x.device, need)
+        ws = _workspaces.get((dev, st))
+        if ws is None or ws.numel() < need:
+            ws = workspace(x.device, need)
     rc = _lib.lib().nb_gemv(x.data_ptr(), xd, m, packed.data_ptr(), codebook.data_ptr(), _DTYPE[codebook.dtype], bits,
-                            block_size, n, k, out.data_ptr(), _DTYPE[out.dtype], ws.data_ptr(), ws.numel(), _stream())
+                            block_size, n, k, out.data_ptr(), _DTYPE[out.dtype], ws.data_ptr(), ws.numel(), st)
     if rc:
         _lib.check(rc, "nb_gemv")
     return out
