@@ -504,10 +504,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
       const float4* dr = ex.pro_delta ? reinterpret_cast<const float4*>(ex.pro_delta + (size_t)m * K) : nullptr;
       __half* xrow = reinterpret_cast<__half*>(x_s) + (m / XR) * XS * (x_tile_bytes / 2) + (m % XR) * 4;
       float ss = 0.f;
-      for (int i = seg * 32 + lane; i < K / 4; i += wpr * 32) {
+      const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      auto load_v = [&](int i) {  // x + delta at float4 index i of row m
         float4 v = xr[i];
         if (slots) {
-          float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+          float4 d = zero4;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             if (q < ex.xchg_world) {
@@ -520,11 +521,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
           const float4 d = dr[i];
           v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
         }
+        return v;
+      };
+      auto in_range = [&](int i) { const int kbl = (i >> 5) - kb0; return kbl >= 0 && kbl < kb_n; };  // 32 float4 per k-block
+      auto consume = [&](int i, const float4& v, const float4& w4) {
         ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         if (writer) reinterpret_cast<float4*>(ex.pro_x_out + (size_t)m * K)[i] = v;
-        const int kbl = (i >> 5) - kb0;              // 32 float4 per k-block
-        if (kbl >= 0 && kbl < kb_n) {
-          const float4 w4 = reinterpret_cast<const float4*>(ex.pro_weight)[i];
+        if (in_range(i)) {
+          const int kbl = (i >> 5) - kb0;
           const float u0 = v.x * w4.x, u1 = v.y * w4.y, u2 = v.z * w4.z, u3 = v.w * w4.w;
           const uint2 o2 = *reinterpret_cast<const uint2*>(dst_off + ((i & 31) << 2));
           uint16_t* blk = reinterpret_cast<uint16_t*>(xrow + kbl * (kXBlockBytes / 2));
@@ -541,6 +545,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
             lo[o2.y & 0xFFFFu] = (uint16_t)(l23 & 0xFFFFu); lo[o2.y >> 16] = (uint16_t)(l23 >> 16);
           }
         }
+      };
+      // two segments per iteration, all loads first: a row costs one memory round trip per two steps
+      const int stride = wpr * 32;
+      for (int i0 = seg * 32 + lane; i0 < K / 4; i0 += 2 * stride) {
+        const int i1 = i0 + stride;
+        const bool has1 = i1 < K / 4;
+        const float4 v0 = load_v(i0);
+        const float4 v1 = has1 ? load_v(i1) : zero4;
+        const float4 w0 = in_range(i0) ? reinterpret_cast<const float4*>(ex.pro_weight)[i0] : zero4;
+        const float4 w1 = (has1 && in_range(i1)) ? reinterpret_cast<const float4*>(ex.pro_weight)[i1] : zero4;
+        consume(i0, v0, w0);
+        if (has1) consume(i1, v1, w1);
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -563,68 +579,76 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
       s_scale[tid] = 1.0f / sqrtf(tot / (float)K + ex.pro_eps);
     }
   } else if (PRO == 2) {
-    // SwiGLU: a thread owns 8-position chunks, one activation row at a time
+    // SwiGLU: a thread owns 8-position chunks and handles two of them at a time (all loads first), one
+    // activation row after the other
     const int chunks = kg_n * 4 * 16;
-    for (int c = tid; c < chunks; c += n_threads) {
-      const int kbl = c >> 4, p0 = (c & 15) << 3;
-      const uint4 o4 = *reinterpret_cast<const uint4*>(dst_off + p0);
-      const uint32_t o[4] = {o4.x, o4.y, o4.z, o4.w};
-      const bool live = kbl < kb_n;
-      const size_t col = (size_t)kb0 * kBlock + (size_t)c * 8;
-      __half* cblk = reinterpret_cast<__half*>(x_s) + kbl * (kXBlockBytes / 2);
+    for (int c0 = tid; c0 < chunks; c0 += 2 * n_threads) {
+#pragma unroll 1
+      for (int m = 0; m < p.M; ++m) {
+        float4 gv[2][2], uv[2][2];
 #pragma unroll
-      for (int m = 0; m < 8; ++m) {
-        if (m < p.M) {
-          float v[8];
+        for (int b = 0; b < 2; ++b) {
+          const int c = c0 + b * n_threads;
+          gv[b][0] = gv[b][1] = uv[b][0] = uv[b][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (c < chunks && (c >> 4) < kb_n) {  // k-blocks past the end of the row are staged as zeros
+            const float* gr = reinterpret_cast<const float*>(p.x) + (size_t)m * 2 * K + (size_t)kb0 * kBlock + (size_t)c * 8;
+            gv[b][0] = *reinterpret_cast<const float4*>(gr); gv[b][1] = *reinterpret_cast<const float4*>(gr + 4);
+            uv[b][0] = *reinterpret_cast<const float4*>(gr + K); uv[b][1] = *reinterpret_cast<const float4*>(gr + K + 4);
+          }
+        }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = 0.f;
-          if (live) {
-            const float* gr = reinterpret_cast<const float*>(p.x) + (size_t)m * 2 * K + col;
-            const float4 ga = *reinterpret_cast<const float4*>(gr), gb = *reinterpret_cast<const float4*>(gr + 4);
-            const float4 ua = *reinterpret_cast<const float4*>(gr + K), ub = *reinterpret_cast<const float4*>(gr + K + 4);
-            const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
-            const float uu[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+        for (int b = 0; b < 2; ++b) {
+          const int c = c0 + b * n_threads;
+          if (c < chunks) {
+            const float gg[8] = {gv[b][0].x, gv[b][0].y, gv[b][0].z, gv[b][0].w, gv[b][1].x, gv[b][1].y, gv[b][1].z, gv[b][1].w};
+            const float uu[8] = {uv[b][0].x, uv[b][0].y, uv[b][0].z, uv[b][0].w, uv[b][1].x, uv[b][1].y, uv[b][1].z, uv[b][1].w};
+            float v[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = gg[j] / (1.0f + __expf(-gg[j])) * uu[j];
-          }
-          __half* blk = cblk + (m / XR) * XS * (x_tile_bytes / 2) + (m % XR) * 4;
+            const uint4 o4 = *reinterpret_cast<const uint4*>(dst_off + ((c & 15) << 3));
+            const uint32_t o[4] = {o4.x, o4.y, o4.z, o4.w};
+            uint16_t* blk = reinterpret_cast<uint16_t*>(reinterpret_cast<__half*>(x_s) + (c >> 4) * (kXBlockBytes / 2) +
+                                                        (m / XR) * XS * (x_tile_bytes / 2) + (m % XR) * 4);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t hi = f32x2_to_f16x2_sat(v[2 * j], v[2 * j + 1]);
-            const uint32_t oa = o[j] & 0xFFFFu, ob = o[j] >> 16;
-            reinterpret_cast<uint16_t*>(blk)[oa] = (uint16_t)(hi & 0xFFFFu);
-            reinterpret_cast<uint16_t*>(blk)[ob] = (uint16_t)(hi >> 16);
-            if (XS == 2) {
-              const float2 r = __half22float2(*reinterpret_cast<const __half2*>(&hi));
-              const uint32_t lo = f32x2_to_f16x2_sat(fminf(fmaxf(v[2 * j], -65504.f), 65504.f) - r.x,
-                                                     fminf(fmaxf(v[2 * j + 1], -65504.f), 65504.f) - r.y);
-              reinterpret_cast<uint16_t*>(blk)[(x_tile_bytes / 2) + oa] = (uint16_t)(lo & 0xFFFFu);
-              reinterpret_cast<uint16_t*>(blk)[(x_tile_bytes / 2) + ob] = (uint16_t)(lo >> 16);
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t hi = f32x2_to_f16x2_sat(v[2 * j], v[2 * j + 1]);
+              const uint32_t oa = o[j] & 0xFFFFu, ob = o[j] >> 16;
+              blk[oa] = (uint16_t)(hi & 0xFFFFu);
+              blk[ob] = (uint16_t)(hi >> 16);
+              if (XS == 2) {
+                const float2 rr = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+                const uint32_t lo = f32x2_to_f16x2_sat(fminf(fmaxf(v[2 * j], -65504.f), 65504.f) - rr.x,
+                                                       fminf(fmaxf(v[2 * j + 1], -65504.f), 65504.f) - rr.y);
+                blk[(x_tile_bytes / 2) + oa] = (uint16_t)(lo & 0xFFFFu);
+                blk[(x_tile_bytes / 2) + ob] = (uint16_t)(lo >> 16);
+              }
             }
           }
         }
       }
     }
   } else {
+    // A thread handles four (chunk, row) items at a time: the raw loads of all four first (nothing
+    // consumes them yet), then the conversions, so that the items' memory round trips overlap instead
+    // of following one another.  Several rows: the items are four rows of one 8-position chunk.  A
+    // single row (XR == 1): they are four chunks, which stages a long row in one round trip.
     const int chunks = kg_n * 4 * 16;  // 8-position chunks per activation row
-    for (int c = tid; c < chunks; c += n_threads) {
-      const int kbl = c >> 4, p0 = (c & 15) << 3;
-      const uint4 o4 = *reinterpret_cast<const uint4*>(dst_off + p0);
-      const uint32_t o[4] = {o4.x, o4.y, o4.z, o4.w};
-      const bool live = kbl < kb_n;  // k-blocks past the end of the row are staged as zeros: their
-                                     // weights are zero, and 0 x garbage must not be NaN
-      const size_t at0 = (size_t)kb0 * kBlock + (size_t)c * 8;
-      __half* cblk = reinterpret_cast<__half*>(x_s) + kbl * (kXBlockBytes / 2);
-      for (int m0 = 0; m0 < p.M; m0 += 4) {
-        // raw loads of all four rows first (nothing consumes them yet), then the conversions: the
-        // rows' memory round trips overlap instead of following one another
+    const int c_step = XR == 1 ? 4 * n_threads : n_threads;
+    const int m_rounds = XR == 1 ? 1 : (p.M + 3) / 4;
+    for (int c0 = tid; c0 < chunks; c0 += c_step) {
+      // several rows: the four items share the chunk, whose destination offsets are read once
+      const uint4 o4_chunk = XR == 1 ? make_uint4(0u, 0u, 0u, 0u) : *reinterpret_cast<const uint4*>(dst_off + ((c0 & 15) << 3));
+      for (int r = 0; r < m_rounds; ++r) {
         uint4 raw[4][2];
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          const int m = m0 + b;
+          const int c = XR == 1 ? c0 + b * n_threads : c0;
+          const int m = XR == 1 ? 0 : 4 * r + b;
           raw[b][0] = raw[b][1] = make_uint4(0u, 0u, 0u, 0u);
-          if (live && m < p.M) {
-            const size_t at = (size_t)m * K + at0;
+          // k-blocks past the end of the row are staged as zeros: their weights are zero, and
+          // 0 x garbage must not be NaN
+          if (c < chunks && (c >> 4) < kb_n && m < p.M) {
+            const size_t at = (size_t)m * K + (size_t)kb0 * kBlock + (size_t)c * 8;
             if (p.x_vec) {
               if (p.x_dtype == NB_F32) {
                 raw[b][0] = *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.x) + at);
@@ -650,50 +674,45 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
             }
           }
         }
-        uint32_t hi[4][4], lo[4][4];
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          float v[8];
-          if (p.x_dtype == NB_F32) {
-            const uint32_t u[8] = {raw[b][0].x, raw[b][0].y, raw[b][0].z, raw[b][0].w, raw[b][1].x, raw[b][1].y, raw[b][1].z, raw[b][1].w};
+          const int c = XR == 1 ? c0 + b * n_threads : c0;
+          const int m = XR == 1 ? 0 : 4 * r + b;
+          if (c < chunks && m < p.M) {
+            float v[8];
+            if (p.x_dtype == NB_F32) {
+              const uint32_t u[8] = {raw[b][0].x, raw[b][0].y, raw[b][0].z, raw[b][0].w, raw[b][1].x, raw[b][1].y, raw[b][1].z, raw[b][1].w};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(u[j]);
-          } else {
-            const uint32_t u[4] = {raw[b][0].x, raw[b][0].y, raw[b][0].z, raw[b][0].w};
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(u[j]);
+            } else {
+              const uint32_t u[4] = {raw[b][0].x, raw[b][0].y, raw[b][0].z, raw[b][0].w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (p.x_dtype == NB_BF16) {
-                v[2 * j] = __uint_as_float(u[j] << 16);
-                v[2 * j + 1] = __uint_as_float(u[j] & 0xFFFF0000u);
-              } else {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[j]));
-                v[2 * j] = f.x; v[2 * j + 1] = f.y;
+              for (int j = 0; j < 4; ++j) {
+                if (p.x_dtype == NB_BF16) {
+                  v[2 * j] = __uint_as_float(u[j] << 16);
+                  v[2 * j + 1] = __uint_as_float(u[j] & 0xFFFF0000u);
+                } else {
+                  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[j]));
+                  v[2 * j] = f.x; v[2 * j + 1] = f.y;
+                }
               }
             }
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            hi[b][j] = f32x2_to_f16x2_sat(v[2 * j], v[2 * j + 1]);
-            if (XS == 2) {  // low-order parts of the (clamped) values
-              const float2 r = __half22float2(*reinterpret_cast<const __half2*>(&hi[b][j]));
-              lo[b][j] = f32x2_to_f16x2_sat(fminf(fmaxf(v[2 * j], -65504.f), 65504.f) - r.x,
-                                            fminf(fmaxf(v[2 * j + 1], -65504.f), 65504.f) - r.y);
-            }
-          }
-        }
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const int m = m0 + b;
-          if (m < p.M) {
-            __half* blk = cblk + (m / XR) * XS * (x_tile_bytes / 2) + (m % XR) * 4;
+            const uint4 o4 = XR == 1 ? *reinterpret_cast<const uint4*>(dst_off + ((c & 15) << 3)) : o4_chunk;
+            const uint32_t o[4] = {o4.x, o4.y, o4.z, o4.w};
+            uint16_t* blk = reinterpret_cast<uint16_t*>(reinterpret_cast<__half*>(x_s) + (c >> 4) * (kXBlockBytes / 2) +
+                                                        (m / XR) * XS * (x_tile_bytes / 2) + (m % XR) * 4);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
+              const uint32_t hi = f32x2_to_f16x2_sat(v[2 * j], v[2 * j + 1]);
               const uint32_t oa = o[j] & 0xFFFFu, ob = o[j] >> 16;
-              reinterpret_cast<uint16_t*>(blk)[oa] = (uint16_t)(hi[b][j] & 0xFFFFu);
-              reinterpret_cast<uint16_t*>(blk)[ob] = (uint16_t)(hi[b][j] >> 16);
-              if (XS == 2) {
-                reinterpret_cast<uint16_t*>(blk)[(x_tile_bytes / 2) + oa] = (uint16_t)(lo[b][j] & 0xFFFFu);
-                reinterpret_cast<uint16_t*>(blk)[(x_tile_bytes / 2) + ob] = (uint16_t)(lo[b][j] >> 16);
+              blk[oa] = (uint16_t)(hi & 0xFFFFu);
+              blk[ob] = (uint16_t)(hi >> 16);
+              if (XS == 2) {  // low-order parts of the (clamped) values
+                const float2 rr = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+                const uint32_t lo = f32x2_to_f16x2_sat(fminf(fmaxf(v[2 * j], -65504.f), 65504.f) - rr.x,
+                                                       fminf(fmaxf(v[2 * j + 1], -65504.f), 65504.f) - rr.y);
+                blk[(x_tile_bytes / 2) + oa] = (uint16_t)(lo & 0xFFFFu);
+                blk[(x_tile_bytes / 2) + ob] = (uint16_t)(lo >> 16);
               }
             }
           }
