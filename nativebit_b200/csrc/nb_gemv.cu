@@ -396,6 +396,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
   __shared__ int s_last;
   __shared__ float s_red[PRO == 1 ? 8 * kMaxWarps : 1];  // PRO 1: partial sums of squares [row][segment]
   __shared__ float s_scale[PRO == 1 ? 8 : 1];            // PRO 1: 1/rms of each activation row
+  __shared__ unsigned long long s_peer[PUSH ? 8 : 1];    // PUSH: every rank's exchange buffer
+  __shared__ uint32_t s_push_seq;                        // PUSH: sequence number of this push
 
   NB_TRACE_MARK(0);
   if (tid < rt_n) mbar_init(&bars[tid], p.tile_bulk ? 1 : n_threads);
@@ -460,6 +462,12 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   NB_TRACE_MARK(2);
+  if (PUSH) {
+    // peer pointers and the sequence number of this push: requested now, used after the units, so
+    // their latency is hidden (the barrier after the activation staging publishes them)
+    if (tid < ex.xchg_world) s_peer[tid] = __ldg(xchg_table(ex.xchg_self, ex.xchg_world, ex.xchg_max_count) + tid);
+    if (tid == 32) s_push_seq = __ldcg(xchg_seq(ex.xchg_self, ex.xchg_world, ex.xchg_max_count)) + 1;
+  }
   __syncthreads();
 
   // ---- stage x as fp16 in slot order: x_s[tile m/XR][k-block][step][row m%XR][4].  A thread owns
@@ -834,28 +842,27 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
     if (PRO == 1) v *= s_scale[m];
     if (PUSH) {
       const size_t off = push_off + (size_t)m * out_n + row;
-      const unsigned long long* tab = xchg_table(ex.xchg_self, ex.xchg_world, ex.xchg_max_count);
 #pragma unroll
       for (int q = 0; q < 8; ++q)
-        if (q < ex.xchg_world) reinterpret_cast<float*>(__ldg(tab + q))[off] = v;
+        if (q < ex.xchg_world) reinterpret_cast<float*>(s_peer[PUSH ? q : 0])[off] = v;
     } else {
       store_y(out_y, out_dtype, (size_t)m * out_n + row, v);
     }
   };
   // After a CTA has written its rows: the last writer of the grid (one per row group) raises this
-  // rank's flag on every rank.  Each writer's stores are fenced at system scope before its ticket.
+  // rank's flag on every rank.  Each writer CTA fences its stores at system scope (one thread, after a
+  // CTA barrier) before it takes its ticket.
   auto finish_push = [&]() {
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();          // the CTA's stores happen before thread 0's fence, which is cumulative
     if (tid == 0) {
+      __threadfence_system();
       uint8_t* self = ex.xchg_self;
       int* ticket = reinterpret_cast<int*>(xchg_seq(self, ex.xchg_world, ex.xchg_max_count) + 1);
       if (atomicAdd(ticket, 1) == (int)gridDim.x - 1) {
         __threadfence();
         const int set = push_seq & 1;
-        const unsigned long long* tab = xchg_table(self, ex.xchg_world, ex.xchg_max_count);
         for (int q = 0; q < ex.xchg_world; ++q)
-          st_release_sys_u32(xchg_flags(reinterpret_cast<const uint8_t*>(__ldg(tab + q)), ex.xchg_world, ex.xchg_max_count) +
+          st_release_sys_u32(xchg_flags(reinterpret_cast<const uint8_t*>(s_peer[PUSH ? q : 0]), ex.xchg_world, ex.xchg_max_count) +
                                  set * ex.xchg_world + ex.xchg_rank, push_seq);
         *xchg_seq(self, ex.xchg_world, ex.xchg_max_count) = push_seq;
         *ticket = 0;
@@ -864,7 +871,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
   };
   if (gridDim.y == 1) {
     if (PUSH) {
-      push_seq = __ldcg(xchg_seq(ex.xchg_self, ex.xchg_world, ex.xchg_max_count)) + 1;
+      push_seq = s_push_seq;
       push_off = ((size_t)(push_seq & 1) * ex.xchg_world + ex.xchg_rank) * ex.xchg_max_count;
     }
     for (int e = tid; e < p.M * rows_here; e += n_threads) {
@@ -910,7 +917,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
     __syncthreads();
   }
   if (PUSH) {
-    push_seq = __ldcg(xchg_seq(ex.xchg_self, ex.xchg_world, ex.xchg_max_count)) + 1;
+    push_seq = s_push_seq;
     push_off = ((size_t)(push_seq & 1) * ex.xchg_world + ex.xchg_rank) * ex.xchg_max_count;
   }
   for (int e = tid; e < p.M * rows_here; e += n_threads) {
