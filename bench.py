@@ -593,9 +593,10 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--allreduce", default="fused", choices=["fused", "oneshot", "nccl"],
-                    help="tensor-parallel all-reduce of the decoder: folded into the packed GEMVs (peer-memory push + gather; "
-                         "the one-shot kernel where that does not apply), the one-shot peer-memory kernel, or NCCL")
+    ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "fused", "nccl"],
+                    help="tensor-parallel all-reduce of the decoder: the one-shot peer-memory kernel (default, the fastest "
+                         "measured), folded into the packed GEMVs (peer-memory push + gather; the one-shot kernel where that "
+                         "does not apply), or NCCL")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2048-token prefill GEMM leg")
     ap.add_argument("--serving", action="store_true", help="add the batch 1/8/32/64, 3-bit and 2-bit decode sweep (configs[4])")
     ap.add_argument("--no-decode", action="store_true", help="skip the 2.2B decoder leg")

@@ -850,16 +850,19 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
     }
   };
   // After a CTA has written its rows: the last writer of the grid (one per row group) raises this
-  // rank's flag on every rank.  Each writer CTA fences its stores at system scope (one thread, after a
-  // CTA barrier) before it takes its ticket.
+  // rank's flag on every rank.  Each writer CTA fences its stores at device scope (one thread, after a
+  // CTA barrier) before it takes its ticket; the last one fences at system scope before the flags.
   auto finish_push = [&]() {
     __syncthreads();          // the CTA's stores happen before thread 0's fence, which is cumulative
     if (tid == 0) {
-      __threadfence_system();
+      __threadfence();        // device scope: orders this CTA's stores before its ticket
       uint8_t* self = ex.xchg_self;
       int* ticket = reinterpret_cast<int*>(xchg_seq(self, ex.xchg_world, ex.xchg_max_count) + 1);
       if (atomicAdd(ticket, 1) == (int)gridDim.x - 1) {
-        __threadfence();
+        // the one system-scope fence of the launch: every writer's stores are ordered before its ticket,
+        // all tickets before this point, this point before the flags (a system fence in each of some
+        // hundred CTAs was measured to cost about 6 us per launch)
+        __threadfence_system();
         const int set = push_seq & 1;
         for (int q = 0; q < ex.xchg_world; ++q)
           st_release_sys_u32(xchg_flags(reinterpret_cast<const uint8_t*>(s_peer[PUSH ? q : 0]), ex.xchg_world, ex.xchg_max_count) +

@@ -411,6 +411,9 @@ class DecodeSession:
             self._step_body()
             return
         if self.graph is None:
+            # the warm-up and the capture run on the session's stream: it must first see what the caller's
+            # stream has written (prefill: caches, position, first token)
+            self.stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.stream):
                 saved = (self.pos.clone(), self.token.clone(), self.logits.clone())
                 for _ in range(2):                                # warm-up outside capture

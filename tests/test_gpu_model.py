@@ -218,3 +218,25 @@ def test_large_batch_tensor_core_option(built_lib, gm):
     a.step(); b.step()
     torch.cuda.synchronize()
     assert (a.logits - b.logits).abs().max() <= 3e-2 * a.logits.abs().max()
+
+
+def test_graph_session_equals_eager_session_full_size(built_lib):
+    """The 2.2B configuration, no synchronisation between prefill and the first (capturing) step: the
+    graph session's logits equal the eager session's bit for bit, step after step."""
+    from nativebit_b200 import generate as G
+    dev = torch.device("cuda:0")
+    cfg = G.ModelConfig()
+    model = G.PackedGPT.random_init(cfg, seed=0, device=dev)
+    prompt = torch.randint(0, cfg.vocab_size, (1, 128), generator=torch.Generator().manual_seed(0)).to(dev)
+    outs = {}
+    for graph in (False, True):
+        s = G.DecodeSession(model, 1, use_graph=graph)
+        s.prefill(prompt)
+        outs[graph] = []
+        for _ in range(6):
+            s.step()
+            outs[graph].append((s.token.clone(), s.logits.clone()))
+        s.check()
+    torch.cuda.synchronize()
+    for (ta, la), (tb, lb) in zip(outs[False], outs[True]):
+        assert torch.equal(ta, tb) and torch.equal(la, lb)
