@@ -143,22 +143,30 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: in
         raise RuntimeError(f"unsupported activation dtype {x.dtype}")
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype or x.dtype, device=x.device)
-    need = gemv_workspace_bytes(m, n, k, bits, block_size)
     dev = x.device.index
     if dev != torch.cuda.current_device():
         with torch.cuda.device(dev):
             return gemv(x, packed, codebook, bits, block_size, n, k, out=out, ws=ws)
-    st = _stream()
+    st = _raw_stream(dev) if _raw_stream is not None else torch.cuda.current_stream().cuda_stream
     if ws is None:
         ws = _workspaces.get((dev, st))
-        if ws is None or ws.numel() < need:
-            ws = workspace(x.device, need)
-    rc = _lib.lib().nb_gemv(x.data_ptr(), xd, m, packed.data_ptr(), codebook.data_ptr(), _DTYPE[codebook.dtype], bits,
-                            block_size, n, k, out.data_ptr(), _DTYPE[out.dtype], ws.data_ptr(), ws.numel(), st)
+        if ws is None:
+            ws = workspace(x.device, gemv_workspace_bytes(m, n, k, bits, block_size))
+        elif ws.numel() < (32 << 20):       # a workspace of 32 MiB covers every shape the kernel accepts
+            need = gemv_workspace_bytes(m, n, k, bits, block_size)
+            if ws.numel() < need:
+                ws = workspace(x.device, need)
+    fn = _gemv_fn[0]
+    if fn is None:
+        fn = _gemv_fn[0] = _lib.lib().nb_gemv
+    rc = fn(x.data_ptr(), xd, m, packed.data_ptr(), codebook.data_ptr(), _DTYPE[codebook.dtype], bits,
+            block_size, n, k, out.data_ptr(), _DTYPE[out.dtype], ws.data_ptr(), ws.numel(), st)
     if rc:
         _lib.check(rc, "nb_gemv")
     return out
 
+
+_gemv_fn = [None]
 
 PRO_NONE, PRO_ADD_RMSNORM, PRO_SILU_MUL = 0, 1, 2
 
