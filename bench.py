@@ -33,8 +33,8 @@ if ROOT not in sys.path:
 
 HIDDEN, FFN, LAYERS, BITS, BLOCK = 2560, 6912, 26, 3, 128
 METRIC, UNIT = "dequant_matvec_hbm_gbs", "GB/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one 6912 x 2560 batch-1 launch, from the ncu capture
-# summarised in profiles/gemv_kernel_3bit_6912x2560_m1.md (algorithmic bytes: 8 866 304)
+# dram__bytes_read.sum + dram__bytes_write.sum of one 6912 x 2560 batch-1 launch, from one ncu capture
+# (algorithmic bytes: 8 866 304)
 NCU_TRAFFIC_B1 = 8912128
 
 

@@ -92,23 +92,31 @@ int nb_quantize(const float* w, int64_t total, const void* codebook, int cb_dtyp
  * (int index 4095) that a launch sets to NB_ERR_TIMEOUT if a bounded wait ran out; the rest
  * carries the partial sums of split-K launches.  One workspace may serve launches of
  * different shapes.  Weights and codebooks are requested before the kernel waits for earlier
- * work of the stream (programmatic dependent launch), so they must not be produced by an
- * nb_gemv launch directly before it; x and y are touched only after that wait. */
+ * work of the stream (programmatic dependent launch), so they must not be written by any kernel or
+ * copy of the stream that may still be in flight (use nb_gemv_ordered then); x and y are touched
+ * only after that wait. */
 size_t nb_gemv_workspace_bytes(int M, int N, int K, int bits, int block_size);
 int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype,
             int bits, int block_size, int N, int K, void* y, int y_dtype, void* workspace,
             size_t workspace_bytes, void* stream);
+/* nb_gemv launched fully stream-ordered (no early start): use it when `packed` or `codebook` were
+ * written by ANY earlier kernel or copy of the same stream that may still be in flight (e.g. nb_pack
+ * directly before it, as in inference/triton_kernel.py:119-140 where the indices are packed per call).
+ * nb_gemv itself requests its weights before it waits for earlier work of the stream. */
+int nb_gemv_ordered(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype,
+                    int bits, int block_size, int N, int K, void* y, int y_dtype, void* workspace,
+                    size_t workspace_bytes, void* stream);
 
 /* ---- prefill GEMM (many activation rows) on the tcgen05 tensor cores:
  * y (M, N) = x (M, K) . W^T.  Replaces the unpack + gather + matmul of
  * inference/triton_kernel.py:258-275 for large M and follows the any-M contract of
- * nativebit_jax/packed_kernel.py:86-97, 151-178 (bf16 operands, fp32 accumulation).
+ * nativebit_jax/packed_kernel.py:86-97, 151-178 (16-bit operands, fp32 accumulation) with one
+ * difference: the weights enter as the fp16 codebook entries themselves (exact), not rounded to bf16.
  * x: (M, K) bf16 row-major, 16-byte aligned; y: (M, N) NB_BF16 or NB_F32; K % 64 == 0 and
- * K % block_size == 0; bits in {2,3,4}.  The weight is first dequantised to bf16 (the fp16
- * codebook entries rounded to nearest even) into `workspace`, which must be 256-byte aligned and
- * hold nb_prefill_workspace_bytes(M, N, K) bytes (N*K*2 + 256); its last 256 bytes carry a
- * status word that must be zero before the first call and is set to NB_ERR_TIMEOUT if a bounded
- * wait inside the kernel ran out. */
+ * K % block_size == 0; bits in {2,3,4}.  `workspace` must be 256-byte aligned and hold
+ * nb_prefill_workspace_bytes(M, N, K) bytes: its first 256 bytes carry a status word that must be
+ * zero before the first call and is set to NB_ERR_TIMEOUT if a bounded wait inside the kernel ran
+ * out; the rest is scratch for dequantised weights. */
 size_t nb_prefill_workspace_bytes(int M, int N, int K);
 int nb_gemm_prefill(const void* x, int M, const uint8_t* packed, const void* codebook, int cb_dtype, int bits,
                     int block_size, int N, int K, void* y, int y_dtype, void* workspace, size_t workspace_bytes,
@@ -228,6 +236,10 @@ int nb_allreduce(const float* in, float* out, int count, const uint64_t* peer_bu
  *    them on one stream, or use nb_gemv with one workspace per stream. */
 int nb_gemv_static(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype,
                    int bits, int block_size, int N, int K, void* y, int y_dtype, void* stream);
+/* Status word of the built-in array on the current device: *host_out = 0, or NB_ERR_TIMEOUT if a
+ * bounded wait of any nb_gemv_static call ran out since the word was last cleared (clear != 0 resets
+ * it).  Synchronises the device; no counterpart in the reference. */
+int nb_gemv_static_status(int* host_out, int clear);
 
 /* Launch geometry nb_gemv will use for a shape on the current device (no launch; works without
  * a GPU, assuming 148 SMs): out6 = {grid.x, grid.y (k partitions), threads per CTA, dynamic

@@ -59,6 +59,9 @@ _SIGNATURES = {
                                       _c.c_void_p]),
     "nb_gemv_static": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
                                   _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p]),
+    "nb_gemv_static_status": (_c.c_int, [_c.c_void_p, _c.c_int]),
+    "nb_gemv_ordered": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
+                                   _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "nb_gemv_plan": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p]),
     "nb_gemv": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
                            _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_size_t, _c.c_void_p]),

@@ -1,11 +1,12 @@
 // Prefill GEMM for NativeBit packed linears on sm_100a: Y (M, N) = X (M, K) . W (N, K)^T for many
 // activation rows, on the 5th-generation tensor cores (tcgen05.mma, accumulator in tensor memory).
 //
-// nb_gemm_prefill dequantises the packed weight once into a bf16 (N, K) scratch matrix (35 MB for
+// nb_gemm_prefill dequantises the packed weight once into an fp16 (N, K) scratch matrix (35 MB for
 // 6912 x 2560: it stays in the 126 MB L2) with the gather kernel of nb_unpack.cu, then runs the
-// kernel below on X and that matrix.  Operands are bf16 (weights are the fp16 codebook entries
-// rounded to bf16, as in the reference's any-M kernel, nativebit_jax/packed_kernel.py:151-159),
-// products are accumulated in fp32.
+// kernel below on X and that matrix.  X enters as bf16 and W as fp16 (the codebook entries
+// themselves, so the weights are exact; the reference's any-M kernel rounds them to bf16,
+// nativebit_jax/packed_kernel.py:151-159): the tensor-core instruction takes the two operand formats
+// independently.  Products are accumulated in fp32.
 //
 // Kernel: persistent, one CTA per SM walking 128 x BN output tiles (BN = a multiple of 16 in
 // [128, 256] chosen to fill the last wave), two accumulator buffers in tensor memory, 192 threads:
@@ -104,7 +105,7 @@ struct GemmCfg {
 // Two accumulator buffers in tensor memory let the epilogue of one tile overlap the MMAs of the next.
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* __restrict__ y,
-                 int y_dtype, int M, int N, int K, int BN, int m_tiles, int n_tiles, int* status) {
+                 int y_dtype, int M, int N, int K, int BN, int m_tiles, int n_tiles, int w_f16, int* status) {
   using Cfg = GemmCfg;
   const int S = Cfg::stages(BN);
   const int b_bytes = BN * kBK * 2;   // multiple of 1024 because BN is a multiple of 16
@@ -159,8 +160,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ---- MMA issuer
-      // instruction descriptor: fp32 accumulate, A and B bf16, both K-major, N = BN, M = 128
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      // instruction descriptor: fp32 accumulate (bit 4), A = X bf16 (format 1 at bit 7), B = W bf16 or
+      // fp16 (format 1 or 0 at bit 10), both K-major, N = BN, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | ((w_f16 ? 0u : 1u) << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       int s = 0, local = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < n_total; t += gridDim.x, ++local) {
@@ -306,7 +308,7 @@ static int pick_bn(int M, int N, int sms) {
 }
 
 static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, void* y, int y_dtype, int M, int N, int K, int bn,
-                       int* status, cudaStream_t st) {
+                       int w_f16, int* status, cudaStream_t st) {
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -317,7 +319,7 @@ static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, void* y, in
   }
   const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + bn - 1) / bn;
   const int grid = std::min(sm_count(), m_tiles * n_tiles);
-  gemm_bf16_kernel<<<grid, 192, GemmCfg::kSmem, st>>>(mx, mw, y, y_dtype, M, N, K, bn, m_tiles, n_tiles, status);
+  gemm_bf16_kernel<<<grid, 192, GemmCfg::kSmem, st>>>(mx, mw, y, y_dtype, M, N, K, bn, m_tiles, n_tiles, w_f16, status);
   return check_launch();
 }
 
@@ -327,10 +329,11 @@ using namespace nb;
 
 extern "C" size_t nb_prefill_workspace_bytes(int M, int N, int K) {
   if (M < 1 || N < 1 || K < 1) return 0;
-  return (size_t)N * K * 2 + 256;  // bf16 weight + status word
+  return (size_t)N * K * 2 + 256;  // status word (first 256 bytes) + fp16 weight
 }
 
-extern "C" int nb_gemm_bf16(const void* x, const void* w, int M, int N, int K, void* y, int y_dtype, int* status, void* stream) {
+// x (M, K) bf16 times w (N, K) bf16 or fp16 (w_f16).  The tensor maps copy 2-byte elements either way.
+static int gemm_16bit(const void* x, const void* w, int w_f16, int M, int N, int K, void* y, int y_dtype, int* status, void* stream) {
   if (!x || !w || !y || M < 1 || N < 1 || K < 1) return NB_ERR_ARG;
   if (y_dtype != NB_BF16 && y_dtype != NB_F32) return NB_ERR_ARG;
   if (K % kBK != 0) return NB_ERR_SHAPE;
@@ -341,7 +344,11 @@ extern "C" int nb_gemm_bf16(const void* x, const void* w, int M, int N, int K, v
   if (int rc = make_map(&mx, x, M, K, kBM)) return rc;
   if (int rc = make_map(&mw, w, N, K, bn)) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  return launch_gemm(mx, mw, y, y_dtype, M, N, K, bn, status, st);
+  return launch_gemm(mx, mw, y, y_dtype, M, N, K, bn, w_f16, status, st);
+}
+
+extern "C" int nb_gemm_bf16(const void* x, const void* w, int M, int N, int K, void* y, int y_dtype, int* status, void* stream) {
+  return gemm_16bit(x, w, 0, M, N, K, y, y_dtype, status, stream);
 }
 
 extern "C" int nb_gemm_prefill(const void* x, int M, const uint8_t* packed, const void* codebook, int cb_dtype, int bits,
@@ -351,7 +358,7 @@ extern "C" int nb_gemm_prefill(const void* x, int M, const uint8_t* packed, cons
   if (!workspace || workspace_bytes < nb_prefill_workspace_bytes(M, N, K)) return NB_ERR_WORKSPACE;
   if ((uintptr_t)workspace % 256) return NB_ERR_ALIGN;
   if (K % kBK != 0 || K % block_size != 0) return NB_ERR_SHAPE;
-  if (int rc = nb_dequant(packed, codebook, cb_dtype, bits, block_size, N, K, workspace, NB_BF16, stream)) return rc;
-  int* status = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(workspace) + (size_t)N * K * 2);
-  return nb_gemm_bf16(x, workspace, M, N, K, y, y_dtype, status, stream);
+  uint8_t* w = reinterpret_cast<uint8_t*>(workspace) + 256;
+  if (int rc = nb_dequant(packed, codebook, cb_dtype, bits, block_size, N, K, w, NB_F16, stream)) return rc;
+  return gemm_16bit(x, w, 1, M, N, K, y, y_dtype, reinterpret_cast<int*>(workspace), stream);
 }

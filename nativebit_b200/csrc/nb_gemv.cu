@@ -1015,6 +1015,11 @@ static size_t plan_workspace(const GemvPlan& pl, int M) {
   return counter_bytes(pl) + scratch;
 }
 
+// `pdl`: launch with programmatic stream serialization (the grid may start, and request its weights,
+// while the previous kernel of the stream still runs).  Without it the launch is fully stream
+// ordered and the griddepcontrol instructions in the kernel do nothing.
+static thread_local bool g_launch_pdl = true;
+
 template <int BITS, int NT, int XR, int XS, int PRO = 0, int PUSH = 0>
 static int launch(const GemvParams& prm, const GemvExtra& extra, const GemvPlan& pl, cudaStream_t st) {
   static bool attr_done[64] = {false};
@@ -1036,7 +1041,7 @@ static int launch(const GemvParams& prm, const GemvExtra& extra, const GemvPlan&
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = g_launch_pdl ? 1 : 0;
   if constexpr (PRO != 0 || PUSH != 0) {
     return record_cuda_error(cudaLaunchKernelEx(&cfg, gemv_kernel<BITS, NT, XR, XS, PRO, PUSH>, prm, extra));
   } else {
@@ -1197,6 +1202,16 @@ extern "C" int nb_gemv(const void* x, int x_dtype, int M, const uint8_t* packed,
                    workspace_bytes, stream);
 }
 
+extern "C" int nb_gemv_ordered(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype,
+                               int bits, int block_size, int N, int K, void* y, int y_dtype, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  g_launch_pdl = false;
+  const int rc = gemv_impl(Prologue{}, x, x_dtype, M, packed, codebook, cb_dtype, bits, block_size, N, K, y, y_dtype, workspace,
+                           workspace_bytes, stream);
+  g_launch_pdl = true;
+  return rc;
+}
+
 extern "C" int nb_gemv_fused(int prologue, const float* x, const float* delta, const float* norm_weight, float eps, float* x_out,
                              int M, const uint8_t* packed, const void* codebook, int cb_dtype, int bits, int block_size, int N,
                              int K, void* y, int y_dtype, void* workspace, size_t workspace_bytes, void* stream) {
@@ -1280,7 +1295,11 @@ extern "C" int nb_gemv_static(const void* x, int x_dtype, int M, const uint8_t* 
                               int bits, int block_size, int N, int K, void* y, int y_dtype, void* stream) {
   if (!x || !packed || !codebook || !y) return NB_ERR_ARG;
   if (int rc = gemv_check_shape(M, N, K, bits, block_size)) return rc;
-  const size_t need = nb_gemv_workspace_bytes(M, N, K, bits, block_size);
+  // the scratch need of a shape is the largest over codebook and activation types (as
+  // nb_gemv_workspace_bytes reports it), from the plan cache
+  size_t need = 0;
+  for (int cb = NB_F32; cb <= NB_F16; ++cb)
+    for (int xt = 1; xt <= 2; ++xt) need = std::max(need, plan_workspace(cached_plan(M, N, K, bits, cb, xt, sm_count()), M));
   if (need > kStaticWsBytes) {
     char msg[160];
     std::snprintf(msg, sizeof(msg), "nb_gemv_static: M=%d N=%d K=%d needs %zu bytes of scratch, the built-in array holds %zu",
@@ -1302,8 +1321,27 @@ extern "C" int nb_gemv_static(const void* x, int x_dtype, int M, const uint8_t* 
     }
     ws = g_static_ptr[dev];
   }
-  // The array keeps whatever the previous call left.  Only the head (ticket counters and the
-  // status word) has to start at zero; partial sums are always written before they are read.
-  if (cudaError_t e = cudaMemsetAsync(ws, 0, (size_t)kCounterInts * sizeof(int), (cudaStream_t)stream)) return record_cuda_error(e);
+  // The array keeps whatever the previous call left.  Only the ticket counters have to start at
+  // zero; partial sums are always written before they are read, and the status word (the last int of
+  // the head) is left alone so that a timeout stays visible to nb_gemv_static_status.
+  if (cudaError_t e = cudaMemsetAsync(ws, 0, (size_t)(kCounterInts - 1) * sizeof(int), (cudaStream_t)stream)) return record_cuda_error(e);
   return nb_gemv(x, x_dtype, M, packed, codebook, cb_dtype, bits, block_size, N, K, y, y_dtype, ws, kStaticWsBytes, stream);
+}
+
+extern "C" int nb_gemv_static_status(int* host_out, int clear) {
+  if (!host_out) return NB_ERR_ARG;
+  int dev = -1;
+  if (cudaError_t e = cudaGetDevice(&dev)) return record_cuda_error(e);
+  if (dev < 0 || dev >= 64) return NB_ERR_ARG;
+  void* ws = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ready[dev]) { *host_out = 0; return NB_OK; }  // never used on this device
+    ws = g_static_ptr[dev];
+  }
+  int* word = reinterpret_cast<int*>(ws) + (kCounterInts - 1);
+  if (cudaError_t e = cudaMemcpy(host_out, word, sizeof(int), cudaMemcpyDeviceToHost)) return record_cuda_error(e);
+  if (clear && *host_out != 0)
+    if (cudaError_t e = cudaMemset(word, 0, sizeof(int))) return record_cuda_error(e);
+  return NB_OK;
 }

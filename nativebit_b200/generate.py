@@ -270,6 +270,7 @@ class DecodeSession:
         self.dev = dev
         self.caches = init_kv_cache(model, batch_size, dev)
         self.pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self.pos_host = 0                     # the same position, tracked on the host: steps past the context are refused
         self.token = torch.zeros(batch_size, 1, dtype=torch.long, device=dev)
         self.logits = torch.zeros(batch_size, model.config.vocab_size, dtype=torch.float32, device=dev)
         self.k_idx = torch.arange(model.context_len, device=dev)
@@ -366,10 +367,13 @@ class DecodeSession:
     @torch.no_grad()
     def prefill(self, prompt: torch.Tensor) -> torch.Tensor:
         """prompt (B, T): fills the caches, sets the position and the first generated token."""
+        if prompt.shape[1] > self.model.context_len:
+            raise RuntimeError(f"prompt of {prompt.shape[1]} tokens exceeds the context of {self.model.context_len}")
         caches = [(k, v, 0) for k, v, _ in self.caches]
         logits, caches = self.model(prompt, kv_caches=caches)
         self.caches = caches
         self.pos.fill_(prompt.shape[1])
+        self.pos_host = int(prompt.shape[1])
         self.logits.copy_(logits[:, -1, :])
         self.token.copy_(self.logits.argmax(-1, keepdim=True))
         return self.logits
@@ -406,9 +410,14 @@ class DecodeSession:
                 raise RuntimeError(f"{name}: a peer did not arrive within the bounded wait")
 
     def step(self) -> None:
-        """One decode step for every sequence: consumes self.token, leaves the next token there."""
+        """One decode step for every sequence: consumes self.token, leaves the next token there.
+        Raises (before anything is launched) when the cache has no free slot left."""
+        ctx = self.model.context_len
+        if self.pos_host >= ctx:
+            raise RuntimeError(f"decode position {self.pos_host} is past the end of the context ({ctx}): the KV cache is full")
         if not self.use_graph:
             self._step_body()
+            self.pos_host += 1
             return
         if self.graph is None:
             # the warm-up and the capture run on the session's stream: it must first see what the caller's
@@ -416,7 +425,7 @@ class DecodeSession:
             self.stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.stream):
                 saved = (self.pos.clone(), self.token.clone(), self.logits.clone())
-                for _ in range(2):                                # warm-up outside capture
+                for _ in range(min(2, ctx - self.pos_host)):      # warm-up outside capture, inside the context
                     self._step_body()
                 self.stream.synchronize()
                 self.pos.copy_(saved[0]); self.token.copy_(saved[1]); self.logits.copy_(saved[2])
@@ -426,6 +435,7 @@ class DecodeSession:
                 # the capture does not execute: state is unchanged; stale cache slots past `pos` are masked
             torch.cuda.current_stream().wait_stream(self.stream)
         self.graph.replay()
+        self.pos_host += 1
 
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, n_generate: int) -> torch.Tensor:

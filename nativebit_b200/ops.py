@@ -130,9 +130,10 @@ def gemv_workspace_bytes(m: int, n: int, k: int, bits: int, block_size: int) -> 
 
 def gemv(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size: int,
          n: int, k: int, out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
-         ws: torch.Tensor | None = None) -> torch.Tensor:
+         ws: torch.Tensor | None = None, ordered: bool = False) -> torch.Tensor:
     """y (M, n) = x (M, k) @ W.T for M <= 16, fused unpack + codebook gather + contraction.
-    Launches on torch's current stream of x's device."""
+    Launches on torch's current stream of x's device.  ordered=True: the launch does not start early
+    (needed when `packed` or `codebook` were just written by earlier work of the stream)."""
     if not (x.is_cuda and packed.is_cuda and codebook.is_cuda):
         _need_cuda(x, packed, codebook)
     if x.dim() != 2 or x.shape[1] != k or not x.is_contiguous():
@@ -146,7 +147,7 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: in
     dev = x.device.index
     if dev != torch.cuda.current_device():
         with torch.cuda.device(dev):
-            return gemv(x, packed, codebook, bits, block_size, n, k, out=out, ws=ws)
+            return gemv(x, packed, codebook, bits, block_size, n, k, out=out, ws=ws, ordered=ordered)
     st = _raw_stream(dev) if _raw_stream is not None else torch.cuda.current_stream().cuda_stream
     if ws is None:
         ws = _workspaces.get((dev, st))
@@ -156,9 +157,9 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: in
             need = gemv_workspace_bytes(m, n, k, bits, block_size)
             if ws.numel() < need:
                 ws = workspace(x.device, need)
-    fn = _gemv_fn[0]
+    fn = _gemv_fn[1 if ordered else 0]
     if fn is None:
-        fn = _gemv_fn[0] = _lib.lib().nb_gemv
+        fn = _gemv_fn[1 if ordered else 0] = _lib.lib().nb_gemv_ordered if ordered else _lib.lib().nb_gemv
     rc = fn(x.data_ptr(), xd, m, packed.data_ptr(), codebook.data_ptr(), _DTYPE[codebook.dtype], bits,
             block_size, n, k, out.data_ptr(), _DTYPE[out.dtype], ws.data_ptr(), ws.numel(), st)
     if rc:
@@ -166,7 +167,7 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: in
     return out
 
 
-_gemv_fn = [None]
+_gemv_fn = [None, None]
 
 PRO_NONE, PRO_ADD_RMSNORM, PRO_SILU_MUL = 0, 1, 2
 

@@ -28,8 +28,10 @@ def pack_indices_to_3bit(indices_uint8: torch.Tensor) -> torch.Tensor:
 def dequant_matvec_3bit(x, packed_indices, codebook, N, K, tile_n=TILE_N):
     """y (N,) fp32 = W @ x for one activation vector, 3-bit packed indices
     (inference/triton_kernel.py:186-196)."""
+    # the caller may have produced packed_indices on this stream a moment ago (dequant_matvec packs per
+    # call): the launch is fully stream-ordered
     y = ops.gemv(x.reshape(1, int(K)).contiguous(), packed_indices, codebook.contiguous(), 3, BS, int(N), int(K),
-                 out_dtype=torch.float32)
+                 out_dtype=torch.float32, ordered=True)
     return y.reshape(int(N))
 
 
@@ -61,6 +63,9 @@ class PackedLinear(torch.nn.Module):
         self.in_features = int(in_features)
         self.bits = int(bits)
         self.block_size = int(block_size)
+        # The buffers may have been written by kernels still in flight (from_packed / pack_linear pack on
+        # the device): the first fused launch is fully stream-ordered, later ones may start early.
+        self._fresh = True
 
     def forward(self, x):
         shape = x.shape
@@ -76,7 +81,8 @@ class PackedLinear(torch.nn.Module):
             y = x_flat @ w.T
         elif m <= GEMV_MAX_M:
             y = ops.gemv(x_flat, self.packed_indices, self.codebook, self.bits, self.block_size,
-                         self.out_features, self.in_features)
+                         self.out_features, self.in_features, ordered=self._fresh)
+            self._fresh = False
         else:
             y = self._forward_many(x_flat)
         return y.reshape(*shape[:-1], self.out_features)

@@ -206,8 +206,8 @@ def test_tensor_parallel_shards_sum_to_single_rank(built_lib, gm, world):
 
 
 def test_large_batch_tensor_core_option(built_lib, gm):
-    """batch_gemm=True routes batches >= 32 through the bf16 tensor-core GEMM: same greedy tokens as
-    the exact path on the tiny model for most steps, logits within bf16 rounding."""
+    """batch_gemm=True routes batches >= 32 through the tensor-core GEMM (bf16 activations, exact fp16
+    weights): logits within the stated 2e-3 of the exact path."""
     from nativebit_b200 import generate as G
     dev = torch.device("cuda:0")
     model, cfg = _build(gm, dev)
@@ -217,7 +217,7 @@ def test_large_batch_tensor_core_option(built_lib, gm):
     a.prefill(prompt); b.prefill(prompt)
     a.step(); b.step()
     torch.cuda.synchronize()
-    assert (a.logits - b.logits).abs().max() <= 3e-2 * a.logits.abs().max()
+    assert (a.logits - b.logits).abs().max() <= 2e-3 * a.logits.abs().max()
 
 
 def test_graph_session_equals_eager_session_full_size(built_lib):

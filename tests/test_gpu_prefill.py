@@ -1,6 +1,7 @@
 """The tcgen05 prefill GEMM through the C ABI: the tensor-core kernel alone against an fp64
-product of the same bf16 operands, and the packed entry point against the oracle (weights rounded
-to bf16 as the kernel does: tight; exact fp16 weights: the stated 2e-3 gate)."""
+product of the same bf16 operands, and the packed entry point against the oracle (the weights
+enter the tensor cores as the exact fp16 codebook entries, so the result matches the fp64 product
+of the reference's weights to fp32-accumulation accuracy, far inside the stated 2e-3 gate)."""
 import numpy as np
 import pytest
 import torch
@@ -45,9 +46,7 @@ def test_gemm_prefill_packed(built_lib, bits, m, n, k):
     torch.cuda.synchronize()
     W = torch.from_numpy(o.dequant_packed(packed, cb.astype(np.float32), n, k, bits)).to(dev)
     ref_exact = xt.double() @ W.double().T                               # the reference's fp32 weights
-    ref_bf16 = xt.double() @ W.bfloat16().double().T                     # weights as the kernel sees them
-    assert (y.double() - ref_bf16).abs().max() <= 2e-5 * ref_bf16.abs().max()
-    assert (y.double() - ref_exact).abs().max() <= 2e-3 * ref_exact.abs().max()
+    assert (y.double() - ref_exact).abs().max() <= 2e-5 * ref_exact.abs().max()
 
 
 def test_packed_linear_uses_tensor_core_path_for_long_inputs(built_lib):
@@ -60,4 +59,4 @@ def test_packed_linear_uses_tensor_core_path_for_long_inputs(built_lib):
     y = lin(x)
     assert y.dtype == torch.bfloat16 and y.shape == (m, n)
     ref = o.packed_linear_forward(x.float().cpu().numpy(), packed, cb.astype(np.float32), n, k, 3, acc_dtype=np.float64)
-    assert np.abs(y.double().cpu().numpy() - ref).max() <= (2.0 ** -8 + 2e-3) * np.abs(ref).max()
+    assert np.abs(y.double().cpu().numpy() - ref).max() <= 2.0 ** -8 * np.abs(ref).max()     # bf16 output: half an ulp

@@ -45,6 +45,8 @@ def test_static_scratch_matches_workspace_entry_point(built_lib, n, k, m):
         oracle = o.packed_linear_forward(x.float().cpu().numpy(), packed, cb.astype(np.float32), n, k, 3,
                                          acc_dtype=np.float64)
         assert np.abs(y.cpu().numpy() - oracle).max() <= 2e-5 * np.abs(oracle).max()
+    word = ctypes.c_int(-1)
+    assert l.nb_gemv_static_status(ctypes.byref(word), 0) == 0 and word.value == 0   # no bounded wait ran out
 
 
 def test_static_scratch_refuses_oversized_shapes(built_lib):
