@@ -111,14 +111,15 @@ int nb_gemv_ordered(const void* x, int x_dtype, int M, const uint8_t* packed, co
  * y (M, N) = x (M, K) . W^T.  Replaces the unpack + gather + matmul of
  * inference/triton_kernel.py:258-275 for large M and follows the any-M contract of
  * nativebit_jax/packed_kernel.py:86-97, 151-178 (16-bit operands, fp32 accumulation) with one
- * difference: the weights enter as the fp16 codebook entries themselves (exact), not rounded to bf16.
- * x: (M, K) bf16 row-major, 16-byte aligned; y: (M, N) NB_BF16 or NB_F32; K % 64 == 0 and
+ * difference: the weights enter as the fp16 codebook entries themselves (exact), not rounded to bf16,
+ * and the bf16 activations are converted to fp16 (exact for magnitudes 6.1e-5..65504, clamped above).
+ * x: (M, K) NB_BF16 or NB_F16 row-major, 16-byte aligned; y: (M, N) NB_BF16 or NB_F32; K % 64 == 0 and
  * K % block_size == 0; bits in {2,3,4}.  `workspace` must be 256-byte aligned and hold
  * nb_prefill_workspace_bytes(M, N, K) bytes: its first 256 bytes carry a status word that must be
  * zero before the first call and is set to NB_ERR_TIMEOUT if a bounded wait inside the kernel ran
- * out; the rest is scratch for dequantised weights. */
+ * out; the rest is scratch (dequantised weights, fp16 activations). */
 size_t nb_prefill_workspace_bytes(int M, int N, int K);
-int nb_gemm_prefill(const void* x, int M, const uint8_t* packed, const void* codebook, int cb_dtype, int bits,
+int nb_gemm_prefill(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype, int bits,
                     int block_size, int N, int K, void* y, int y_dtype, void* workspace, size_t workspace_bytes,
                     void* stream);
 

@@ -3,10 +3,12 @@
 //
 // nb_gemm_prefill dequantises the packed weight once into an fp16 (N, K) scratch matrix (35 MB for
 // 6912 x 2560: it stays in the 126 MB L2) with the gather kernel of nb_unpack.cu, then runs the
-// kernel below on X and that matrix.  X enters as bf16 and W as fp16 (the codebook entries
-// themselves, so the weights are exact; the reference's any-M kernel rounds them to bf16,
-// nativebit_jax/packed_kernel.py:151-159): the tensor-core instruction takes the two operand formats
-// independently.  Products are accumulated in fp32.
+// kernel below on X and that matrix.  W enters as fp16 (the codebook entries themselves, so the
+// weights are exact; the reference's any-M kernel rounds them to bf16,
+// nativebit_jax/packed_kernel.py:151-159).  The tensor-core instruction wants both operands in one
+// 16-bit format (a bf16 A with an fp16 B is an illegal instruction on sm_100a), so bf16 activations
+// are first converted to fp16 (exact for magnitudes 6.1e-5..65504, saturating above, as in the
+// GEMV).  Products are accumulated in fp32.
 //
 // Kernel: persistent, one CTA per SM walking 128 x BN output tiles (BN = a multiple of 16 in
 // [128, 256] chosen to fill the last wave), two accumulator buffers in tensor memory, 192 threads:
@@ -105,7 +107,7 @@ struct GemmCfg {
 // Two accumulator buffers in tensor memory let the epilogue of one tile overlap the MMAs of the next.
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* __restrict__ y,
-                 int y_dtype, int M, int N, int K, int BN, int m_tiles, int n_tiles, int w_f16, int* status) {
+                 int y_dtype, int M, int N, int K, int BN, int m_tiles, int n_tiles, int f16, int* status) {
   using Cfg = GemmCfg;
   const int S = Cfg::stages(BN);
   const int b_bytes = BN * kBK * 2;   // multiple of 1024 because BN is a multiple of 16
@@ -160,9 +162,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ---- MMA issuer
-      // instruction descriptor: fp32 accumulate (bit 4), A = X bf16 (format 1 at bit 7), B = W bf16 or
-      // fp16 (format 1 or 0 at bit 10), both K-major, N = BN, M = 128
-      const uint32_t idesc = (1u << 4) | (1u << 7) | ((w_f16 ? 0u : 1u) << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      // instruction descriptor: fp32 accumulate (bit 4), A = X and B = W both bf16 (format 1) or both
+      // fp16 (format 0) at bits 7 and 10, both K-major, N = BN, M = 128
+      const uint32_t fmt = f16 ? 0u : 1u;
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       int s = 0, local = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < n_total; t += gridDim.x, ++local) {
@@ -308,7 +311,7 @@ static int pick_bn(int M, int N, int sms) {
 }
 
 static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, void* y, int y_dtype, int M, int N, int K, int bn,
-                       int w_f16, int* status, cudaStream_t st) {
+                       int f16, int* status, cudaStream_t st) {
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -319,7 +322,7 @@ static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, void* y, in
   }
   const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + bn - 1) / bn;
   const int grid = std::min(sm_count(), m_tiles * n_tiles);
-  gemm_bf16_kernel<<<grid, 192, GemmCfg::kSmem, st>>>(mx, mw, y, y_dtype, M, N, K, bn, m_tiles, n_tiles, w_f16, status);
+  gemm_bf16_kernel<<<grid, 192, GemmCfg::kSmem, st>>>(mx, mw, y, y_dtype, M, N, K, bn, m_tiles, n_tiles, f16, status);
   return check_launch();
 }
 
@@ -329,11 +332,29 @@ using namespace nb;
 
 extern "C" size_t nb_prefill_workspace_bytes(int M, int N, int K) {
   if (M < 1 || N < 1 || K < 1) return 0;
-  return (size_t)N * K * 2 + 256;  // status word (first 256 bytes) + fp16 weight
+  // status word (first 256 bytes) + fp16 weight + fp16 copy of the activations
+  return 256 + (((size_t)N * K * 2 + 255) & ~(size_t)255) + (size_t)M * K * 2;
 }
 
-// x (M, K) bf16 times w (N, K) bf16 or fp16 (w_f16).  The tensor maps copy 2-byte elements either way.
-static int gemm_16bit(const void* x, const void* w, int w_f16, int M, int N, int K, void* y, int y_dtype, int* status, void* stream) {
+namespace nb {
+// bf16 -> fp16, eight elements per thread, saturating to +-65504.
+__global__ void __launch_bounds__(256) bf16_to_f16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, size_t n8) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const uint4 v = in[i];
+  const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+  uint32_t r[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float a = __uint_as_float(u[j] << 16), b = __uint_as_float(u[j] & 0xFFFF0000u);
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r[j]) : "f"(b), "f"(a));
+  }
+  out[i] = make_uint4(r[0], r[1], r[2], r[3]);
+}
+}  // namespace nb
+
+// x (M, K) times w (N, K), both bf16 or both fp16 (f16).  The tensor maps copy 2-byte elements either way.
+static int gemm_16bit(const void* x, const void* w, int f16, int M, int N, int K, void* y, int y_dtype, int* status, void* stream) {
   if (!x || !w || !y || M < 1 || N < 1 || K < 1) return NB_ERR_ARG;
   if (y_dtype != NB_BF16 && y_dtype != NB_F32) return NB_ERR_ARG;
   if (K % kBK != 0) return NB_ERR_SHAPE;
@@ -344,21 +365,29 @@ static int gemm_16bit(const void* x, const void* w, int w_f16, int M, int N, int
   if (int rc = make_map(&mx, x, M, K, kBM)) return rc;
   if (int rc = make_map(&mw, w, N, K, bn)) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  return launch_gemm(mx, mw, y, y_dtype, M, N, K, bn, w_f16, status, st);
+  return launch_gemm(mx, mw, y, y_dtype, M, N, K, bn, f16, status, st);
 }
 
 extern "C" int nb_gemm_bf16(const void* x, const void* w, int M, int N, int K, void* y, int y_dtype, int* status, void* stream) {
   return gemm_16bit(x, w, 0, M, N, K, y, y_dtype, status, stream);
 }
 
-extern "C" int nb_gemm_prefill(const void* x, int M, const uint8_t* packed, const void* codebook, int cb_dtype, int bits,
+extern "C" int nb_gemm_prefill(const void* x, int x_dtype, int M, const uint8_t* packed, const void* codebook, int cb_dtype, int bits,
                                int block_size, int N, int K, void* y, int y_dtype, void* workspace, size_t workspace_bytes,
                                void* stream) {
   if (!x || !packed || !codebook || !y) return NB_ERR_ARG;
+  if (x_dtype != NB_BF16 && x_dtype != NB_F16) return NB_ERR_ARG;
   if (!workspace || workspace_bytes < nb_prefill_workspace_bytes(M, N, K)) return NB_ERR_WORKSPACE;
   if ((uintptr_t)workspace % 256) return NB_ERR_ALIGN;
   if (K % kBK != 0 || K % block_size != 0) return NB_ERR_SHAPE;
+  if ((uintptr_t)x % 16) return NB_ERR_ALIGN;
   uint8_t* w = reinterpret_cast<uint8_t*>(workspace) + 256;
+  uint8_t* xh = w + (((size_t)N * K * 2 + 255) & ~(size_t)255);
   if (int rc = nb_dequant(packed, codebook, cb_dtype, bits, block_size, N, K, w, NB_F16, stream)) return rc;
-  return gemm_16bit(x, w, 1, M, N, K, y, y_dtype, reinterpret_cast<int*>(workspace), stream);
+  if (x_dtype == NB_F16) return gemm_16bit(x, w, 1, M, N, K, y, y_dtype, reinterpret_cast<int*>(workspace), stream);
+  const size_t n8 = (size_t)M * K / 8;  // K % 64 == 0
+  bf16_to_f16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const uint4*>(x),
+                                                                                    reinterpret_cast<uint4*>(xh), n8);
+  if (int rc = check_launch()) return rc;
+  return gemm_16bit(xh, w, 1, M, N, K, y, y_dtype, reinterpret_cast<int*>(workspace), stream);
 }

@@ -294,9 +294,9 @@ class DecodeSession:
 
     def _linear_into(self, lin: PackedLinear, x: torch.Tensor, out: torch.Tensor) -> None:
         if self.batch_gemm and x.shape[0] >= 32 and lin.in_features % 64 == 0:
-            # large batches, opt-in: dequantise once and multiply on the tcgen05 tensor cores (bf16 operands,
-            # fp32 accumulation: the prefill contract) instead of unpacking the weights once per 16 rows
-            ops.gemm_prefill(x.to(torch.bfloat16), lin.packed_indices, lin.codebook, lin.bits, lin.block_size,
+            # large batches, opt-in: dequantise once and multiply on the tcgen05 tensor cores (fp16 operands,
+            # fp32 accumulation) instead of unpacking the weights once per 16 rows
+            ops.gemm_prefill(x, lin.packed_indices, lin.codebook, lin.bits, lin.block_size,
                              lin.out_features, lin.in_features, out=out)
             return
         for r in range(0, x.shape[0], 16):

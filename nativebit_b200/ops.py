@@ -243,18 +243,23 @@ def prefill_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def gemm_prefill(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size: int,
                  n: int, k: int, out_dtype: torch.dtype = torch.bfloat16, out: torch.Tensor | None = None) -> torch.Tensor:
-    """y (M, n) = x (M, k) @ W.T on the tcgen05 tensor cores; x must be bf16."""
+    """y (M, n) = x (M, k) @ W.T on the tcgen05 tensor cores.  x bf16 or fp16; fp32 activations are
+    carried as fp16 (11 significant bits, clamped to the fp16 range)."""
     _need_cuda(x, packed, codebook)
-    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != k:
-        raise RuntimeError(f"x must be a bf16 (M, {k}) tensor; got {x.dtype} {tuple(x.shape)}")
+    if x.dtype == torch.float32:
+        x = x.clamp(-65504.0, 65504.0).half()
+    if x.dtype not in (torch.bfloat16, torch.float16) or x.dim() != 2 or x.shape[1] != k:
+        raise RuntimeError(f"x must be a 16-bit (M, {k}) tensor; got {x.dtype} {tuple(x.shape)}")
     m = x.shape[0]
+    if out is None and out_dtype == torch.float16:     # the kernel writes bf16 or fp32
+        return gemm_prefill(x, packed, codebook, bits, block_size, n, k, out_dtype=torch.float32).half()
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype, device=x.device)
     l = _lib.lib()
     with torch.cuda.device(x.device):
         need = l.nb_prefill_workspace_bytes(m, n, k)
         ws = prefill_workspace(x.device, need)
-        _lib.check(l.nb_gemm_prefill(x.data_ptr(), m, packed.data_ptr(), codebook.data_ptr(), _DTYPE[codebook.dtype], bits,
+        _lib.check(l.nb_gemm_prefill(x.data_ptr(), _DTYPE[x.dtype], m, packed.data_ptr(), codebook.data_ptr(), _DTYPE[codebook.dtype], bits,
                                      block_size, n, k, out.data_ptr(), _DTYPE[out.dtype], ws.data_ptr(), ws.numel(),
                                      _stream()), "nb_gemm_prefill")
     return out

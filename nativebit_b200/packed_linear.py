@@ -96,10 +96,11 @@ class PackedLinear(torch.nn.Module):
                 ops.gemv(x_flat[r:r + GEMV_MAX_M], self.packed_indices, self.codebook, self.bits, self.block_size,
                          self.out_features, self.in_features, out=y[r:r + GEMV_MAX_M])
             return y
-        if x_flat.dtype == torch.bfloat16 and self.in_features % 64 == 0 and self.bits in (2, 3, 4):
-            # prefill: dequantise once to bf16, then the tcgen05 GEMM (fp32 accumulation, bf16 result)
+        if self.in_features % 64 == 0 and self.bits in (2, 3, 4):
+            # prefill: the tcgen05 GEMM with exact fp16 weights and 16-bit activations (bf16 and fp16 as
+            # given, fp32 carried as fp16), fp32 accumulation, result in x's dtype
             return ops.gemm_prefill(x_flat, self.packed_indices, self.codebook, self.bits, self.block_size,
-                                    self.out_features, self.in_features, out_dtype=torch.bfloat16)
+                                    self.out_features, self.in_features, out_dtype=x_flat.dtype)
         wdt = x_flat.dtype if x_flat.dtype in (torch.float16, torch.bfloat16) else torch.float32
         w = ops.dequant(self.packed_indices, self.codebook, self.bits, self.block_size,
                         (self.out_features, self.in_features), dtype=wdt)

@@ -45,12 +45,15 @@ class DenseModel:
         self.w, self.L, self.H, self.ctx = weights, n_layers, n_head, context_len
         C = weights["embedding"].shape[1]
         self.hd = C // n_head
-        self.cos, self.sin = rope_tables(self.hd, context_len)
+        # the same torch ops run wherever the weights live (CPU here; a GPU for the full-size model,
+        # with TF32 off, so that every product is fp32)
+        self.dev = weights["embedding"].device
+        cos, sin = rope_tables(self.hd, context_len)
+        self.cos, self.sin = cos.to(self.dev), sin.to(self.dev)
 
     def init_cache(self, batch=1):
-        C = self.w["embedding"].shape[1]
-        return [[torch.zeros(batch, self.H, self.ctx, self.hd), torch.zeros(batch, self.H, self.ctx, self.hd), 0]
-                for _ in range(self.L)]
+        z = lambda: torch.zeros(batch, self.H, self.ctx, self.hd, device=self.dev)
+        return [[z(), z(), 0] for _ in range(self.L)]
 
     @torch.no_grad()
     def forward(self, idx: torch.Tensor, caches):
@@ -69,8 +72,8 @@ class DenseModel:
             vb[:, :, n:n + T] = v
             new = n + T
             att = torch.einsum("bhqd,bhkd->bhqk", q * self.hd ** -0.5, kb)
-            qp = n + torch.arange(T)
-            kp = torch.arange(self.ctx)
+            qp = n + torch.arange(T, device=self.dev)
+            kp = torch.arange(self.ctx, device=self.dev)
             mask = (kp[None, :] <= qp[:, None]) & (kp[None, :] < new)
             att = att.masked_fill(~mask[None, None], torch.finfo(att.dtype).min)
             out = torch.einsum("bhqk,bhkd->bhqd", F.softmax(att, dim=-1), vb)

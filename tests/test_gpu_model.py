@@ -240,3 +240,58 @@ def test_graph_session_equals_eager_session_full_size(built_lib):
     torch.cuda.synchronize()
     for (ta, la), (tb, lb) in zip(outs[False], outs[True]):
         assert torch.equal(ta, tb) and torch.equal(la, lb)
+
+
+def _dense_oracle_of(model, cfg, dev):
+    """The dense fp32 oracle of a single-rank PackedGPT: every packed linear is materialised on the CPU by
+    the oracle's own numpy gather (the reference's recipe, inference/compare.py:260-288) and evaluated with
+    the oracle's torch ops on the GPU in fp32 (TF32 off)."""
+    from oracle import nb_oracle as o
+    C, Fh, L = cfg.n_embd, cfg.ffn_hidden, cfg.n_layers
+    w = {"embedding": model.embedding.float()}
+    for l, blk in enumerate(model.blocks):
+        def dense(lin, rows=None):
+            p, c = lin.packed_indices.cpu().numpy(), lin.codebook.float().cpu().numpy()
+            W = o.dequant_packed(p, c, lin.out_features, lin.in_features, cfg.bits)
+            return torch.from_numpy(W).to(dev)
+        w[f"qkv{l}"], w[f"out{l}"], w[f"down{l}"] = dense(blk.qkv), dense(blk.out_proj), dense(blk.down)
+        gu = dense(blk.gate_up)
+        w[f"gate{l}"], w[f"up{l}"] = gu[:Fh].contiguous(), gu[Fh:].contiguous()
+        del gu
+        w[f"ln1_{l}"], w[f"ln2_{l}"] = blk.ln1.float(), blk.ln2.float()
+    w["ln_f"] = model.ln_f.float()
+    return mo.DenseModel(w, L, cfg.n_head, cfg.context_len)
+
+
+def test_full_size_decoder_against_dense_oracle_teacher_forced(built_lib):
+    """The 2.2B configuration (26 layers, hidden 2560, 32 heads, FFN 6912, vocab 32000, seed 0): a 128-token
+    prompt and 256 teacher-forced steps.  At every step both models are fed the ORACLE's greedy token;
+    the argmax of the CUDA-graph decode session must equal the oracle's at >= 99 % of the steps, and the
+    logits of the prompt's last position and of the last step must agree within 2e-3 of max|logit|."""
+    from nativebit_b200 import generate as G
+    dev = torch.device("cuda:0")
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    cfg = G.ModelConfig()
+    model = G.PackedGPT.random_init(cfg, seed=0, device=dev)
+    om = _dense_oracle_of(model, cfg, dev)
+    prompt = torch.randint(0, cfg.vocab_size, (1, 128), generator=torch.Generator().manual_seed(0)).to(dev)
+    n_steps = 256
+    ocache = om.init_cache()
+    olog = om.forward(prompt, ocache)[0, -1]
+    sess = G.DecodeSession(model, 1, use_graph=True)
+    sess.prefill(prompt)
+    scale = float(olog.abs().max())
+    assert float((sess.logits[0] - olog).abs().max()) <= 2e-3 * scale
+    agree, worst = 0, 0.0
+    for i in range(n_steps):
+        tok = olog.argmax().reshape(1, 1)
+        sess.token.copy_(tok)                       # teacher forcing: the oracle's token, not ours
+        sess.step()
+        olog = om.forward(tok, ocache)[0, -1]
+        agree += int(int(sess.token[0, 0]) == int(olog.argmax()))
+        worst = max(worst, float((sess.logits[0] - olog).abs().max()) / float(olog.abs().max()))
+    sess.check()
+    print(f"teacher-forced greedy agreement {agree}/{n_steps}, worst logit error {worst:.2e} of max|logit|")
+    assert agree / n_steps >= 0.99
+    assert worst <= 2e-3
