@@ -242,6 +242,78 @@ int nb_gemv_static(const void* x, int x_dtype, int M, const uint8_t* packed, con
  * it).  Synchronises the device; no counterpart in the reference. */
 int nb_gemv_static_status(int* host_out, int clear);
 
+/* ---- persistent multi-matrix decode kernel ("stream" programs).
+ * One launch runs a whole list of operations (a decode step: 26 x [qkv, attention, out_proj, gate_up,
+ * down] + LM head + argmax; or any group of packed matvecs) on one CTA per SM, with the packed weights
+ * streamed continuously through shared memory and device-side flags instead of kernel boundaries between
+ * dependent operations.  Replaces the per-token launch sequence of inference/generate_torch.py:150-162
+ * (forward) and :307-311 (greedy loop) and the per-call matvec of inference/cuda_kernel.py:38-104.
+ *
+ * Weights are read in a tile-major copy of the packed matrix, built once at load time by nb_stream_pack
+ * from the nativebit/pack.py byte stream and the codebooks (the reference's JAX path re-orders blocks at
+ * load time in the same spirit, nativebit_jax/packed_kernel.py:34-60).  row_mode 0 keeps the row order;
+ * row_mode 1 expects a fused [gate | up] matrix of N rows and interleaves groups of 8 gate rows with the
+ * matching 8 up rows, which the NB_SEPI_SWIGLU epilogue needs (N % 16 == 0).  The copy holds
+ * nb_stream_packed_bytes(N, K, bits) bytes (same size as indices + fp16 codebooks, rows padded to 16);
+ * codebooks are stored as fp16 (an fp32 codebook is rounded, as in nb_gemv).
+ *
+ * An operation is an nb_stream_op (160 bytes; unused fields zero).  Pointers are device pointers.
+ *  NB_SOP_GEMV   y = W x.  p[0] stream-layout weights; i[0] N, i[1] K (multiple of 128, <= 8192), i[2] bits.
+ *     prologue (how x is formed; i[3] = dtype of p[1] for NB_SPRO_VEC):
+ *       NB_SPRO_VEC         x = p[1][0..K) (NB_F32 carried as two fp16 terms, NB_F16 / NB_BF16 as one)
+ *       NB_SPRO_EMBED_NORM  h = table p[1] (bf16, row *p[2] (int64)); x = h * p[3] (K floats), result / rms(h)
+ *       NB_SPRO_ADD_NORM    h += sum of i[5] slots of p[1] (floats, i[7] apart); then as above (f[0] = eps)
+ *       NB_SPRO_ATTN_MERGE  x = attention output merged from the partials p[1] written by NB_SOP_ATTN:
+ *                           i[9] heads, i[10] splits, i[11] head_dim, i[12] first column (others are zero)
+ *       h is the residual stream; it lives in every CTA's shared memory for the whole launch.
+ *     epilogue (where y goes, p[4]):
+ *       NB_SEPI_STORE   y[n] of dtype i[4]                                   (needs NB_SOPF_ALIGN)
+ *       NB_SEPI_SLOTS   fp32 partial sums: i[6] slots, i[8] floats apart; the consumer adds the slots.
+ *                       i[6] >= nb_stream_slots(N, K, nb_stream_ctas())
+ *       NB_SEPI_SWIGLU  fp32 act[c] = silu(gate_c) * up_c, N/2 values (row_mode 1 weights, NB_SOPF_ALIGN)
+ *  NB_SOP_ATTN   RoPE + KV-cache write + single-query attention for one new token (inference/
+ *     generate_torch.py:48-60, 86-97): p[0] qkv as i[5] slots i[7] apart ([q|k|v] of i[0] local heads),
+ *     p[1]/p[2] cos/sin tables (ctx, head_dim) repeated per pair, p[3] position (int64), p[4]/p[5] key and
+ *     value caches (heads, ctx, head_dim) fp32, p[6] partials out: (heads * splits) x (head_dim + 2) floats.
+ *     i[1] head_dim (multiple of 4, <= 128), i[2] ctx, i[3] splits of the keys per head.
+ *  NB_SOP_HEAD   final RMSNorm + tied LM head + soft-cap (generate_torch.py:157-159): p[0] bf16 table
+ *     (i[0] rows, i[1] = C columns), p[1] last residual update as i[5] slots i[7] apart, p[3] norm weight,
+ *     p[4] logits out (i[0] floats), p[5] candidates out (2 x CTAs words); f[0] eps, f[1] cap; i[8] = index of
+ *     row 0 in the whole vocabulary.
+ *  NB_SOP_ARGMAX token = lowest index among the largest candidates: p[0] candidates, i[0] their count,
+ *     p[1] token out (int64), p[2] position (int64, incremented; may be NULL).
+ *  NB_SOP_REDUCE y (p[4], dtype i[4], i[0] values) = sum of i[5] slots of p[1], i[7] floats apart.
+ * flags: NB_SOPF_WAIT_PREV  the operation reads results of the operation before it: wait for all CTAs;
+ *        NB_SOPF_ALIGN      split the rows between CTAs in whole 16-row tiles (no partial slots);
+ *        NB_SOPF_REUSE_X    the activations staged by the previous NB_SOP_GEMV are used again.
+ *
+ * nb_stream_run takes the program twice: a host copy, which it validates, and the same bytes in device
+ * memory, which the kernel reads.  `state` is nb_stream_state_bytes() of device memory, zero-filled once;
+ * it carries the flag words, a sequence number that lets the launch be replayed from a CUDA graph, and a
+ * status word (uint32 index 257) set to NB_ERR_TIMEOUT if a bounded wait ran out (the launch then finishes
+ * without hanging; results are invalid).  One launch at a time per state buffer.  The launch is cooperative
+ * (all nb_stream_ctas() CTAs resident).  All packed matrices of a program share one `bits`.
+ * Limits: at most nb_stream_max_ops() operations; one activation row (batch 1). */
+typedef enum { NB_SOP_GEMV = 1, NB_SOP_ATTN = 2, NB_SOP_HEAD = 3, NB_SOP_ARGMAX = 4, NB_SOP_REDUCE = 5 } nb_stream_kind;
+typedef enum { NB_SPRO_VEC = 0, NB_SPRO_EMBED_NORM = 1, NB_SPRO_ADD_NORM = 2, NB_SPRO_ATTN_MERGE = 3 } nb_stream_prologue;
+typedef enum { NB_SEPI_STORE = 0, NB_SEPI_SLOTS = 1, NB_SEPI_SWIGLU = 2 } nb_stream_epilogue;
+enum { NB_SOPF_WAIT_PREV = 1, NB_SOPF_ALIGN = 2, NB_SOPF_REUSE_X = 4 };
+typedef struct {
+  int32_t kind, flags, pro, epi;
+  void* p[8];
+  int32_t i[16];
+  float f[4];
+} nb_stream_op;
+size_t nb_stream_packed_bytes(int N, int K, int bits);
+int nb_stream_pack(const uint8_t* packed, const void* codebook, int cb_dtype, int bits, int N, int K, int row_mode,
+                   uint8_t* out, void* stream);
+size_t nb_stream_state_bytes(void);
+int nb_stream_max_ops(void);
+int nb_stream_ctas(void);
+int nb_stream_slots(int N, int K, int ctas);
+int nb_stream_run(const nb_stream_op* ops_host, const nb_stream_op* ops_device, int n_ops, void* state, uint32_t spin_limit,
+                  void* stream);
+
 /* Launch geometry nb_gemv will use for a shape on the current device (no launch; works without
  * a GPU, assuming 148 SMs): out6 = {grid.x, grid.y (k partitions), threads per CTA, dynamic
  * shared memory bytes, row tiles per CTA, k-groups per partition}.  No counterpart in the

@@ -62,6 +62,14 @@ _SIGNATURES = {
     "nb_gemv_static_status": (_c.c_int, [_c.c_void_p, _c.c_int]),
     "nb_gemv_ordered": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
                                    _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "nb_stream_packed_bytes": (_c.c_size_t, [_c.c_int, _c.c_int, _c.c_int]),
+    "nb_stream_pack": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p,
+                                  _c.c_void_p]),
+    "nb_stream_state_bytes": (_c.c_size_t, []),
+    "nb_stream_max_ops": (_c.c_int, []),
+    "nb_stream_ctas": (_c.c_int, []),
+    "nb_stream_slots": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int]),
+    "nb_stream_run": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_uint32, _c.c_void_p]),
     "nb_gemv_plan": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p]),
     "nb_gemv": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
                            _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_size_t, _c.c_void_p]),

@@ -152,11 +152,25 @@ class PackedGPT(torch.nn.Module):
         gate, up = gu.split(gu.shape[-1] // 2, dim=-1)
         return x + self._all_reduce(blk.down(F.silu(gate) * up).float())
 
+    def _head(self, x: torch.Tensor) -> torch.Tensor:
+        """x (..., C) fp32 @ embedding.T with fp32 accumulation and an fp32 result.  A bf16 table is
+        multiplied by the activations split into two bf16 terms (16 significant bits) stacked into one
+        operand, so the table is read once and neither the activations nor the logits are rounded to 8 bits."""
+        emb = self.embedding
+        shape = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1]).float()
+        if emb.dtype != torch.bfloat16:
+            return (x2 @ emb.float().T).reshape(*shape, -1)
+        hi = x2.bfloat16()
+        lo = (x2 - hi.float()).bfloat16()
+        y = torch.mm(torch.cat((hi, lo)), emb.T, out_dtype=torch.float32)
+        m = x2.shape[0]
+        return (y[:m] + y[m:]).reshape(*shape, -1)
+
     def _logits(self, x):
-        x = rms_norm(x, self.ln_f, self.config.norm_eps)
-        logits = x.to(self.embedding.dtype) @ self.embedding.T
+        logits = self._head(rms_norm(x, self.ln_f, self.config.norm_eps))
         cap = self.config.logit_cap
-        return cap * torch.tanh(logits.float() / cap)
+        return cap * torch.tanh(logits / cap)
 
     # ------------------------------------------------------------------ eager forward (prefill, tests)
     @torch.no_grad()
@@ -262,9 +276,14 @@ class DecodeSession:
     (inference/generate_torch.py:91-97)."""
 
     def __init__(self, model: PackedGPT, batch_size: int = 1, use_graph: bool = True, fused: bool = True,
-                 batch_gemm: bool = False):
+                 batch_gemm: bool = False, stream: bool | None = None):
         self.model, self.B = model, batch_size
         self.fused = fused
+        # one sequence on one GPU: the whole step is ONE launch of the persistent kernel (stream.py);
+        # other cases run the step as a chain of fused kernels
+        from . import stream as _stream
+        self.stream_step = fused and _stream.stream_supported(model, batch_size) if stream is None else bool(stream)
+        self.prog = None
         self.batch_gemm = batch_gemm          # batches >= 32: packed linears on the tensor-core GEMM (bf16 operands)
         dev = model.embedding.device
         self.dev = dev
@@ -361,7 +380,7 @@ class DecodeSession:
             ops.exchange_gather(self.bd, xch, xch.status)
             delta = self.bd
         ops.add_rmsnorm(xa, delta, m.ln_f, eps, self.bh)
-        logits = self.bh.to(m.embedding.dtype) @ m.embedding.T   # the LM head is a plain library GEMM (bf16, 164 MB)
+        logits = m._head(self.bh)                                # the LM head is a plain library GEMM (bf16 table, 164 MB)
         ops.softcap_argmax(logits, cfg.logit_cap, self.logits, self.token, self.pos)
 
     @torch.no_grad()
@@ -380,6 +399,11 @@ class DecodeSession:
 
     @torch.no_grad()
     def _step_body(self):
+        if self.stream_step:
+            if self.prog is None:
+                from . import stream as _stream
+                self.prog = _stream.build_decode_program(self.model, self)
+            return self.prog.run()
         if self.fused:
             return self._step_body_fused()
         m, cfg = self.model, self.model.config
@@ -400,10 +424,13 @@ class DecodeSession:
     def check(self) -> None:
         """Raises if a bounded wait of the step's kernels ever ran out (a copy barrier, or a peer of the
         tensor-parallel exchange that never arrived).  Reads device status words: synchronises."""
-        with torch.cuda.stream(self.stream):
-            ws = ops.workspace(self.model.embedding.device, 0)
-        if ops.workspace_status(ws) != 0:
-            raise RuntimeError("nb_gemv: a bounded wait ran out (status NB_ERR_TIMEOUT in the workspace)")
+        if self.prog is not None and self.prog.status() != 0:
+            raise RuntimeError("nb_stream_run: a bounded wait ran out (status NB_ERR_TIMEOUT in the program state)")
+        for st in ((self.stream, torch.cuda.current_stream(self.dev)) if self.use_graph else (torch.cuda.current_stream(self.dev),)):
+            with torch.cuda.stream(st):          # the workspace of the stream the steps ran on
+                ws = ops.workspace(self.model.embedding.device, 0)
+            if ops.workspace_status(ws) != 0:
+                raise RuntimeError("nb_gemv: a bounded wait ran out (status NB_ERR_TIMEOUT in the workspace)")
         for name in ("oneshot", "exchange"):
             obj = getattr(self.model, name, None)
             if obj is not None and int(obj.status.item()) != 0:

@@ -243,11 +243,22 @@ def prefill_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def gemm_prefill(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size: int,
                  n: int, k: int, out_dtype: torch.dtype = torch.bfloat16, out: torch.Tensor | None = None) -> torch.Tensor:
-    """y (M, n) = x (M, k) @ W.T on the tcgen05 tensor cores.  x bf16 or fp16; fp32 activations are
-    carried as fp16 (11 significant bits, clamped to the fp16 range)."""
+    """y (M, n) = x (M, k) @ W.T on the tcgen05 tensor cores.  x bf16 or fp16.  fp32 activations are
+    carried as the sum of two fp16 terms (about 22 significant bits, as in the GEMV): the terms are
+    stacked into one (2M, k) operand, so the weights are dequantised once, and the two halves of the
+    fp32 result are added."""
     _need_cuda(x, packed, codebook)
     if x.dtype == torch.float32:
-        x = x.clamp(-65504.0, 65504.0).half()
+        xc = x.clamp(-65504.0, 65504.0)
+        hi = xc.half()
+        lo = (xc - hi.float()).half()
+        m = x.shape[0]
+        y2 = gemm_prefill(torch.cat((hi, lo)), packed, codebook, bits, block_size, n, k, out_dtype=torch.float32)
+        y = y2[:m].add_(y2[m:])
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y if out_dtype in (torch.float32, None) else y.to(out_dtype)
     if x.dtype not in (torch.bfloat16, torch.float16) or x.dim() != 2 or x.shape[1] != k:
         raise RuntimeError(f"x must be a 16-bit (M, {k}) tensor; got {x.dtype} {tuple(x.shape)}")
     m = x.shape[0]

@@ -1,0 +1,132 @@
+"""The persistent multi-matrix kernel (nb_stream_run) through the C ABI: groups of packed matvecs
+against the fp64 oracle (both epilogues, plain / fp32 activations, ragged shapes, 2-, 3- and 4-bit),
+replays that must be bit-identical, and the one-launch decode step against the chain of fused
+kernels and the reference's own logits."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nb_oracle as o
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _dev():
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    return torch.device("cuda:0")
+
+
+def _cu(a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+@pytest.mark.parametrize("bits,n,k", [(3, 6912, 2560), (3, 2560, 6912), (3, 1000, 640), (3, 24, 128), (2, 2560, 2560), (4, 512, 1280),
+                                      (3, 7680, 2560), (3, 320, 384)])
+@pytest.mark.parametrize("xdt", [torch.bfloat16, torch.float32])
+def test_group_of_matvecs_against_oracle(built_lib, bits, n, k, xdt):
+    from nativebit_b200 import stream as S
+    dev = _dev()
+    prog = S.StreamProgram(dev)
+    cases = []
+    slots = S.n_slots(n, k)
+    for j in range(3):
+        packed, cb, _ = o.make_packed_linear(n, k, bits, seed=10 * j + bits)
+        x = o.make_activation(1, k, seed=j)
+        if xdt == torch.float32:
+            x = (x.astype(np.float64) * (1.0 + 1e-4 * np.arange(k))).astype(np.float32)   # not fp16-representable
+        w = S.stream_pack(_cu(packed, dev), _cu(cb, dev), bits, n, k)
+        xt = _cu(x, dev).to(xdt).reshape(k)
+        y_store = torch.full((n,), float("nan"), dtype=torch.float32, device=dev)
+        part = torch.full((slots, n), float("nan"), dtype=torch.float32, device=dev)
+        y_red = torch.full((n,), float("nan"), dtype=torch.float32, device=dev)
+        prog.gemv_vec(w, n, k, bits, xt, y_store)                       # whole row tiles per CTA, final store
+        prog.gemv_vec(w, n, k, bits, xt, part, slots=slots, reuse_x=True)   # free split, partial slots
+        cases.append((packed, cb, xt, y_store, part, y_red))
+    for j, (_, _, _, _, part, y_red) in enumerate(cases):
+        prog.reduce(part, n, y_red, wait=(j == 0))
+    prog.run()
+    torch.cuda.synchronize()
+    assert prog.status() == 0
+    first = [(c[3].clone(), c[5].clone()) for c in cases]
+    for packed, cb, xt, y_store, part, y_red in cases:
+        ref = o.packed_linear_forward(xt.double().cpu().numpy().reshape(1, k), packed, cb.astype(np.float32), n, k, bits,
+                                      acc_dtype=np.float64)[0]
+        scale = np.abs(ref).max()
+        assert np.abs(y_store.double().cpu().numpy() - ref).max() <= 2e-5 * scale
+        assert np.abs(y_red.double().cpu().numpy() - ref).max() <= 2e-5 * scale
+    prog.run()                                                          # replay: same bits
+    torch.cuda.synchronize()
+    for (a, b), c in zip(first, cases):
+        assert torch.equal(a, c[3]) and torch.equal(b, c[5])
+    assert prog.status() == 0
+
+
+def test_chain_of_dependent_matvecs(built_lib):
+    """gate_up with the SwiGLU epilogue -> down with partial slots -> reduce, each waiting for the one
+    before: the FFN of one layer without norms, against the oracle."""
+    from nativebit_b200 import stream as S
+    dev = _dev()
+    C, F = 640, 1408
+    pg, cg, _ = o.make_packed_linear(F, C, 3, seed=1)
+    pu, cu_, _ = o.make_packed_linear(F, C, 3, seed=2)
+    pd, cd, _ = o.make_packed_linear(C, F, 3, seed=3)
+    x = o.make_activation(1, C, seed=4)
+    gu_p = torch.cat([_cu(pg, dev), _cu(pu, dev)])
+    gu_c = torch.cat([_cu(cg, dev), _cu(cu_, dev)])
+    w_gu = S.stream_pack(gu_p, gu_c, 3, 2 * F, C, row_mode=1)
+    w_d = S.stream_pack(_cu(pd, dev), _cu(cd, dev), 3, C, F)
+    xt = _cu(x, dev).float().reshape(C)
+    act = torch.zeros(F, device=dev)
+    slots = S.n_slots(C, F)
+    part = torch.zeros(slots, C, device=dev)
+    y = torch.zeros(C, device=dev)
+    prog = S.StreamProgram(dev)
+    prog.add(S._op(S.SOP_GEMV, S.SOPF_ALIGN, S.SPRO_VEC, S.SEPI_SWIGLU, p=(w_gu, xt, None, None, act),
+                   i=(2 * F, C, 3, S.NB_F32, 0, 0, 0, 0, 0)), w_gu, xt, act)
+    prog.gemv_vec(w_d, C, F, 3, act, part, slots=slots, wait=True)
+    prog.reduce(part, C, y, wait=True)
+    for _ in range(3):
+        prog.run()
+    torch.cuda.synchronize()
+    assert prog.status() == 0
+    f32 = np.float32
+    g = o.packed_linear_forward(x, pg, cg.astype(f32), F, C, 3, acc_dtype=np.float64)[0]
+    u = o.packed_linear_forward(x, pu, cu_.astype(f32), F, C, 3, acc_dtype=np.float64)[0]
+    a = g / (1.0 + np.exp(-g)) * u
+    assert np.abs(act.double().cpu().numpy() - a).max() <= 2e-5 * np.abs(a).max()
+    ref = o.packed_linear_forward(a.reshape(1, F), pd, cd.astype(f32), C, F, 3, acc_dtype=np.float64)[0]
+    assert np.abs(y.double().cpu().numpy() - ref).max() <= 2e-5 * np.abs(ref).max()
+
+
+def test_one_launch_decode_step_equals_kernel_chain_and_reference(built_lib):
+    """Tiny seeded model: the decode step as ONE persistent launch gives the tokens of the step run as a
+    chain of fused kernels, logits within fp32 rounding of it, and the reference's own PackedGPT logits
+    within the stated 2e-3."""
+    from nativebit_b200 import generate as G
+    from tests.test_gpu_model import _build
+    dev = _dev()
+    gm = np.load(os.path.join(ROOT, "tests", "golden", "reference_model.npz"))
+    model, cfg = _build(gm, dev)
+    prompt = torch.from_numpy(gm["prompt"]).to(dev)
+    for graph in (False, True):
+        a = G.DecodeSession(model, 1, use_graph=graph, stream=True)
+        b = G.DecodeSession(model, 1, use_graph=False, stream=False)
+        a.prefill(prompt); b.prefill(prompt)
+        for _ in range(12):
+            a.step(); b.step()
+            assert torch.equal(a.token, b.token)
+            assert (a.logits - b.logits).abs().max() <= 1e-4 * b.logits.abs().max()
+        a.check()
+    # teacher-forced against the reference's logits
+    s = G.DecodeSession(model, 1, use_graph=True, stream=True)
+    s.prefill(prompt)
+    ref0 = gm["logits_prompt"]
+    for t, r in zip(gm["forced"].tolist(), gm["logits_steps"]):
+        s.token.fill_(t)
+        s.step()
+        assert np.abs(s.logits[0].cpu().numpy() - r).max() <= 2e-3 * np.abs(ref0).max()
+    s.check()
