@@ -48,51 +48,62 @@ constexpr int kChunkBytes = 2048;                         // one ring stage
 constexpr int kStages = 4;                                // stages per warp
 constexpr int kRingBytes = kSW * kStages * kChunkBytes;   // 128 KB
 constexpr int kMaxOps = 160;
-constexpr int kMaxKBlocks = 64;                           // K <= 8192
+constexpr int kMaxKBlocks = 56;                           // K <= 7168
 constexpr int kXSegBytes = 72;                            // 32 halves of one (k-block, lane t) + skew
-constexpr int kXTermBytes = kMaxKBlocks * 4 * kXSegBytes; // 18 KB per fp16 term
-constexpr int kMaxC = 4096;                               // residual width
-constexpr int kRedFloats = 4096;                          // 16 local row tiles x 16 warps x 16 rows
+constexpr int kXTermBytes = kMaxKBlocks * 4 * kXSegBytes; // 15.75 KB per fp16 term
+constexpr int kMaxC = 3072;                               // residual width
+constexpr int kRedHalf = 2048;                            // floats: 8 local row tiles x 16 warps x 16 rows
 constexpr int kMaxCtas = 256;
 constexpr uint32_t kCopySpin = 1u << 22;
 constexpr uint32_t kFlagSpinDefault = 1u << 22;
 
 using StreamOp = nb_stream_op;
 
+// What the weight stream needs to know about an operation, computed once per launch.
+struct OpInfo {
+  int cta_a, cta_b;           // this CTA's unit range
+  int bpr;                    // units per row tile (GEMV: k-blocks per row; head: pieces per row)
+  uint16_t ubytes;            // bytes of a unit (GEMV) or of a full piece (head)
+  uint8_t per_chunk, kind;
+  const uint8_t* w;           // first unit
+  int row_bytes;              // head: bytes of a table row
+  int flags;                  // bit 0: the next operation waits for this one (or it is the last)
+};
+static_assert(sizeof(OpInfo) == 32, "OpInfo layout");
+
 // shared-memory layout (dynamic)
 constexpr int kOffRing = 0;
-constexpr int kOffOps = kOffRing + kRingBytes;
-constexpr int kOffX = kOffOps + kMaxOps * (int)sizeof(StreamOp);
+constexpr int kOffInfo = kOffRing + kRingBytes;
+constexpr int kOffX = kOffInfo + kMaxOps * (int)sizeof(OpInfo);
 constexpr int kOffH = kOffX + 2 * kXTermBytes;
 constexpr int kOffRed = kOffH + kMaxC * 4;
-constexpr int kOffDst = kOffRed + kRedFloats * 4;
-constexpr int kStreamSmem = kOffDst + 256;
+constexpr int kOffDst = kOffRed + 2 * kRedHalf * 4;
+constexpr int kOffOp = kOffDst + 256;
+constexpr int kStreamSmem = kOffOp + 2 * (int)sizeof(StreamOp);
 static_assert(sizeof(StreamOp) == 160, "nb_stream_op layout");
-static_assert(kStreamSmem <= 227 * 1024, "shared memory budget");
+static_assert(kStreamSmem <= 226 * 1024, "shared memory budget");
 
 template <int BITS> struct UnitFmt {
   static constexpr int kW = Fmt<BITS>::kWords / 4;          // words of one lane's 32 indices
   static constexpr int kIdxBytes = kW * 256;                // 32 lanes x 2 rows x kW words
   static constexpr int kTabBytes = BITS == 4 ? 32 : 16;     // one row's lookup table
   static constexpr int kBytes = kIdxBytes + 16 * kTabBytes; // 1024 at 3 bits, 768 at 2, 1536 at 4
-  static constexpr int kPerChunk = kChunkBytes / kBytes;
 };
 
 __host__ __device__ inline int unit_bytes(int bits) { return bits == 3 ? UnitFmt<3>::kBytes : bits == 2 ? UnitFmt<2>::kBytes : UnitFmt<4>::kBytes; }
 
-// ---- work split --------------------------------------------------------------------------------
+// ---- work split (32-bit arithmetic: the host refuses programs where units * (CTAs + 1) >= 2^31) ----
 // [lo, hi) of part `i` of `parts` equal shares of n items.
-__host__ __device__ inline void share(long long n, int parts, int i, int& lo, int& hi) {
-  lo = (int)(n * i / parts);
-  hi = (int)(n * (i + 1) / parts);
+__host__ __device__ inline void share(int n, int parts, int i, int& lo, int& hi) {
+  lo = (int)((unsigned)n * (unsigned)i / (unsigned)parts);
+  hi = (int)((unsigned)n * (unsigned)(i + 1) / (unsigned)parts);
 }
 // CTA that owns unit u when U units are split over G CTAs by share().
-__host__ __device__ inline int cta_of_unit(long long u, long long U, int G) { return (int)(((u + 1) * G - 1) / U); }
+__host__ __device__ inline int cta_of_unit(int u, int U, int G) { return (int)(((unsigned)(u + 1) * (unsigned)G - 1u) / (unsigned)U); }
 
 struct OpGeom {
-  int kind, bits, bpr, rt, align, ubytes, per_chunk;
-  long long units;
-  int head_pieces, head_piece_bytes, head_row_bytes;
+  int kind, bits, bpr, rt, align, ubytes, per_chunk, units;
+  int head_piece_bytes, head_row_bytes;
 };
 
 __host__ __device__ inline OpGeom geom_of(const StreamOp& o) {
@@ -105,40 +116,43 @@ __host__ __device__ inline OpGeom geom_of(const StreamOp& o) {
     g.align = (o.flags & NB_SOPF_ALIGN) ? 1 : 0;
     g.ubytes = unit_bytes(g.bits);
     g.per_chunk = kChunkBytes / g.ubytes;
-    g.units = (long long)g.rt * g.bpr;
+    g.units = g.rt * g.bpr;
   } else if (o.kind == NB_SOP_HEAD) {
     g.head_row_bytes = o.i[1] * 2;
-    g.head_pieces = (g.head_row_bytes + kChunkBytes - 1) / kChunkBytes;
-    g.head_piece_bytes = ((g.head_row_bytes / g.head_pieces + 15) / 16) * 16;
-    g.bpr = g.head_pieces;
-    g.rt = o.i[0];                      // rows
+    g.bpr = (g.head_row_bytes + kChunkBytes - 1) / kChunkBytes;          // pieces per row
+    g.head_piece_bytes = ((g.head_row_bytes / g.bpr + 15) / 16) * 16;
+    g.ubytes = g.head_piece_bytes;
+    g.rt = o.i[0];                                                       // rows
     g.align = 1;
     g.per_chunk = 1;
-    g.units = (long long)g.rt * g.head_pieces;
+    g.units = g.rt * g.bpr;
   }
   return g;
 }
 
-// Unit range of (cta, warp) in an operation; empty for operations without a weight stream.
-__host__ __device__ inline void warp_range(const OpGeom& g, int cta, int G, int warp, int& a, int& b, int& cta_a, int& cta_b) {
-  a = b = cta_a = cta_b = 0;
+// Unit range of a CTA in an operation; empty for operations without a weight stream.
+__host__ __device__ inline void cta_range(const OpGeom& g, int cta, int G, int& a, int& b) {
+  a = b = 0;
   if (g.units == 0) return;
   if (g.align) {
     int r0, r1;
     share(g.rt, G, cta, r0, r1);
-    cta_a = r0 * g.bpr; cta_b = r1 * g.bpr;
-    if (g.kind == NB_SOP_HEAD) {        // whole rows per warp
-      int w0, w1;
-      share(r1 - r0, kSW, warp, w0, w1);
-      a = (r0 + w0) * g.bpr; b = (r0 + w1) * g.bpr;
-      return;
-    }
+    a = r0 * g.bpr; b = r1 * g.bpr;
   } else {
-    share(g.units, G, cta, cta_a, cta_b);
+    share(g.units, G, cta, a, b);
   }
-  int w0, w1;
-  share(cta_b - cta_a, kSW, warp, w0, w1);
-  a = cta_a + w0; b = cta_a + w1;
+}
+// A warp's part of its CTA's range: equal shares of the units (of whole rows for the head).
+__host__ __device__ inline void warp_part(int kind, int bpr, int cta_a, int cta_b, int warp, int& a, int& b) {
+  if (kind == NB_SOP_HEAD) {
+    const int rows = (cta_b - cta_a) / bpr;
+    a = cta_a + (rows * warp / kSW) * bpr;
+    b = cta_a + (rows * (warp + 1) / kSW) * bpr;
+  } else {
+    const int n = cta_b - cta_a;
+    a = cta_a + n * warp / kSW;
+    b = cta_a + n * (warp + 1) / kSW;
+  }
 }
 
 // ---- small device helpers -----------------------------------------------------------------------
@@ -214,8 +228,8 @@ struct Cursor {
 };
 
 struct StreamCtx {
-  const StreamOp* ops;   // in shared memory
-  int n_ops, cta, G, warp, lane;
+  const OpInfo* info;    // in shared memory
+  int n_ops, warp, lane;
   uint8_t* ring;         // this warp's kStages stages
   uint64_t* full;        // this warp's kStages barriers
   int* status;
@@ -226,9 +240,8 @@ __device__ __forceinline__ void cursor_seek(const StreamCtx& c, Cursor& k) {   /
   while (k.op < c.n_ops && k.u >= k.u_end) {
     ++k.op;
     if (k.op < c.n_ops) {
-      int a, b, ca, cb;
-      warp_range(geom_of(c.ops[k.op]), c.cta, c.G, c.warp, a, b, ca, cb);
-      k.u = a; k.u_end = b;
+      const OpInfo& f = c.info[k.op];
+      if (f.cta_b > f.cta_a) warp_part(f.kind, f.bpr, f.cta_a, f.cta_b, c.warp, k.u, k.u_end);
     }
   }
 }
@@ -240,22 +253,21 @@ __device__ __forceinline__ void cursor_init(const StreamCtx& c, Cursor& k) {
 
 // Units and bytes of the chunk at the cursor, and its source address.
 __device__ __forceinline__ int chunk_at(const StreamCtx& c, const Cursor& k, const uint8_t*& src, uint32_t& bytes) {
-  const StreamOp& o = c.ops[k.op];
-  const OpGeom g = geom_of(o);
-  if (g.kind == NB_SOP_HEAD) {
-    const int row = k.u / g.head_pieces, piece = k.u - row * g.head_pieces;
-    const int off = piece * g.head_piece_bytes;
-    bytes = (uint32_t)min(g.head_piece_bytes, g.head_row_bytes - off);
-    src = reinterpret_cast<const uint8_t*>(o.p[0]) + (size_t)row * g.head_row_bytes + off;
+  const OpInfo& f = c.info[k.op];
+  if (f.kind == NB_SOP_HEAD) {
+    const int row = k.u / f.bpr, piece = k.u - row * f.bpr;
+    const int off = piece * f.ubytes;
+    bytes = (uint32_t)min((int)f.ubytes, f.row_bytes - off);
+    src = f.w + (size_t)row * f.row_bytes + off;
     return 1;
   }
-  const int n = min(g.per_chunk, k.u_end - k.u);
-  bytes = (uint32_t)(n * g.ubytes);
-  src = reinterpret_cast<const uint8_t*>(o.p[0]) + (size_t)k.u * g.ubytes;
+  const int n = min((int)f.per_chunk, k.u_end - k.u);
+  bytes = (uint32_t)(n * f.ubytes);
+  src = f.w + (size_t)k.u * f.ubytes;
   return n;
 }
 
-// Lane 0 of the warp: request the chunk at the fetch cursor into its stage (if any is left).
+// Request the chunk at the fetch cursor into its stage (if any is left); lane 0 issues the copy.
 __device__ __forceinline__ void fetch_next(const StreamCtx& c, Cursor& f) {
   if (f.op >= c.n_ops) return;
   const uint8_t* src;
@@ -340,34 +352,31 @@ __device__ __forceinline__ void unit_mma(const uint8_t* ub, const uint8_t* x_s, 
 // This warp's run of units of a packed matvec: streams the chunks, accumulates per row tile, stores
 // the partial sums of every row tile it touched into its slot of `red` ([local row tile][warp][16]).
 template <int BITS, int XS>
-__device__ __forceinline__ void run_units(StreamCtx& c, Cursor& use, Cursor& fetch, int op_index, const OpGeom& g,
-                                          const uint8_t* x_s, float* red, int rt_first) {
+__device__ __forceinline__ void run_units(StreamCtx& c, Cursor& use, Cursor& fetch, int op_index, const uint8_t* x_s, float* red,
+                                          int rt_first) {
   using F = UnitFmt<BITS>;
   const int lane = c.lane;
+  if (use.op != op_index) return;
+  const int bpr = c.info[op_index].bpr, per_chunk = c.info[op_index].per_chunk;
   float acc[2][4];
 #pragma unroll
   for (int j = 0; j < 2; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-  int cur_rt = -1;
-  auto flush = [&]() {
-    if (cur_rt >= 0 && (lane & 3) == 0) {
-      float* dst = red + ((size_t)(cur_rt - rt_first) * kSW + c.warp) * 16;
-      dst[lane >> 2] = acc[0][0] + acc[1][0];
-      dst[(lane >> 2) + 8] = acc[0][2] + acc[1][2];
-    }
-  };
+  int rt = use.u / bpr, kb = use.u - rt * bpr;
   while (use.op == op_index) {
     const uint8_t* st = wait_chunk(c, use);
-    const int n = min(g.per_chunk, use.u_end - use.u);
+    const int n = min(per_chunk, use.u_end - use.u);
     for (int j = 0; j < n; ++j) {
-      const int u = use.u + j;
-      const int rt = u / g.bpr, kb = u - rt * g.bpr;
-      if (rt != cur_rt) {
-        flush();
+      unit_mma<BITS, XS>(st + j * F::kBytes, x_s, kb, lane, acc);
+      if (++kb == bpr || (j == n - 1 && use.u + n == use.u_end)) {   // row tile (or this warp's part of it) complete
+        if ((lane & 3) == 0) {
+          float* dst = red + ((rt - rt_first) * kSW + c.warp) * 16;
+          dst[lane >> 2] = acc[0][0] + acc[1][0];
+          dst[(lane >> 2) + 8] = acc[0][2] + acc[1][2];
+        }
 #pragma unroll
         for (int q = 0; q < 2; ++q) acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
-        cur_rt = rt;
+        if (kb == bpr) { kb = 0; ++rt; }
       }
-      unit_mma<BITS, XS>(st + j * F::kBytes, x_s, kb, lane, acc);
     }
     use.u += n;
     ++use.count;
@@ -375,7 +384,6 @@ __device__ __forceinline__ void run_units(StreamCtx& c, Cursor& use, Cursor& fet
     __syncwarp();               // every lane has consumed the stage before it is overwritten
     fetch_next(c, fetch);
   }
-  flush();
 }
 
 // ---- dependency flags ----------------------------------------------------------------------------
@@ -394,19 +402,34 @@ __device__ __forceinline__ void wait_flags(const uint32_t* flags, int G, uint32_
   __syncthreads();
 }
 
+#ifdef NB_STREAM_TRACE
+__device__ unsigned long long nb_stream_trace_buf[kMaxOps * 8];
+#define NB_STRACE(op, i)                                                     \
+  do {                                                                       \
+    if (blockIdx.x == 0 && threadIdx.x == 0) {                               \
+      unsigned long long t_;                                                 \
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_));                  \
+      nb_stream_trace_buf[(op) * 8 + (i)] = t_;                              \
+    }                                                                        \
+  } while (0)
+#else
+#define NB_STRACE(op, i) do {} while (0)
+#endif
+
 // ---- the kernel -----------------------------------------------------------------------------------
 // state: [0 .. kMaxCtas) flags, [kMaxCtas] epoch, [kMaxCtas + 1] status.
 template <int BITS>
 __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __restrict__ ops_g, int n_ops, uint32_t* state, uint32_t spin_limit) {
   extern __shared__ __align__(128) uint8_t smem[];
-  StreamOp* ops = reinterpret_cast<StreamOp*>(smem + kOffOps);
+  OpInfo* info = reinterpret_cast<OpInfo*>(smem + kOffInfo);
   uint8_t* x_s = smem + kOffX;
   float* h_s = reinterpret_cast<float*>(smem + kOffH);
-  float* red = reinterpret_cast<float*>(smem + kOffRed);
+  float* red_base = reinterpret_cast<float*>(smem + kOffRed);
   uint16_t* dst_off = reinterpret_cast<uint16_t*>(smem + kOffDst);
+  StreamOp* op_slots = reinterpret_cast<StreamOp*>(smem + kOffOp);
   __shared__ __align__(8) uint64_t bars[kSW * kStages];
   __shared__ float s16[kSW];
-  __shared__ float s_scale;
+  __shared__ float s_scale[2];
   __shared__ float s_best[kSW];
   __shared__ int s_besti[kSW];
 
@@ -416,8 +439,22 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
   int* status = reinterpret_cast<int*>(state + kMaxCtas + 1);
   const uint32_t base = state[kMaxCtas];      // sequence numbers of this launch start above the previous launch's
 
-  for (int i = tid; i < n_ops * (int)(sizeof(StreamOp) / 4); i += kSThreads)
-    reinterpret_cast<uint32_t*>(ops)[i] = reinterpret_cast<const uint32_t*>(ops_g)[i];
+  for (int i = tid; i < n_ops; i += kSThreads) {
+    const StreamOp& o = ops_g[i];
+    const OpGeom g = geom_of(o);
+    OpInfo f;
+    cta_range(g, cta, G, f.cta_a, f.cta_b);
+    f.bpr = g.bpr > 0 ? g.bpr : 1;
+    f.ubytes = (uint16_t)g.ubytes;
+    f.per_chunk = (uint8_t)g.per_chunk;
+    f.kind = (uint8_t)g.kind;
+    f.w = reinterpret_cast<const uint8_t*>(o.p[0]);
+    f.row_bytes = g.head_row_bytes;
+    f.flags = (i + 1 == n_ops || (ops_g[i + 1].flags & NB_SOPF_WAIT_PREV)) ? 1 : 0;
+    info[i] = f;
+  }
+  for (int i = tid; i < (int)(sizeof(StreamOp) / 4) * min(n_ops, 2); i += kSThreads)
+    reinterpret_cast<uint32_t*>(op_slots)[i] = reinterpret_cast<const uint32_t*>(ops_g)[i];
   if (tid < kSW * kStages) mbar_init(&bars[tid], 1);
   if (tid < kBlock) {
     // position inside a 128-weight block -> offset (in halves) of its activation inside the block's four segments
@@ -427,25 +464,29 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncthreads();
 
-  StreamCtx ctx{ops, n_ops, cta, G, warp, lane, smem + kOffRing + warp * kStages * kChunkBytes, &bars[warp * kStages], status, false};
+  StreamCtx ctx{info, n_ops, warp, lane, smem + kOffRing + warp * kStages * kChunkBytes, &bars[warp * kStages], status, false};
   Cursor fetch, use;
   cursor_init(ctx, fetch);
   cursor_init(ctx, use);
   for (int s = 0; s < kStages; ++s) fetch_next(ctx, fetch);
 
   for (int oi = 0; oi < n_ops; ++oi) {
-    const StreamOp& op = ops[oi];
+    const StreamOp& op = op_slots[oi & 1];
     const uint32_t seq = base + (uint32_t)oi + 1u;     // published after this operation
     if (oi > 0 && (op.flags & NB_SOPF_WAIT_PREV)) wait_flags(flags, G, seq - 1u, spin_limit, status, tid);
+    NB_STRACE(oi, 0);
+    // the descriptor after the next one is fetched into the slot of the operation that just ended
+    auto prefetch_op = [&]() {
+      if (oi >= 1 && oi + 1 < n_ops && tid < (int)(sizeof(StreamOp) / 4))
+        reinterpret_cast<uint32_t*>(&op_slots[(oi + 1) & 1])[tid] = __ldg(reinterpret_cast<const uint32_t*>(ops_g + oi + 1) + tid);
+    };
 
     if (op.kind == NB_SOP_GEMV) {
-      const OpGeom g = geom_of(op);
       const int N = op.i[0], K = op.i[1];
-      int ua, ub, cta_a, cta_b;
-      warp_range(g, cta, G, warp, ua, ub, cta_a, cta_b);
-      const int rt_first = cta_a / g.bpr;
-      const int rt_last = cta_b > cta_a ? (cta_b - 1) / g.bpr : rt_first - 1;
-      const int n_rt = rt_last - rt_first + 1;
+      const int bpr = info[oi].bpr, cta_a = info[oi].cta_a, cta_b = info[oi].cta_b;
+      const int rt_first = cta_a / bpr;
+      const int n_rt = cta_b > cta_a ? (cta_b - 1) / bpr - rt_first + 1 : 0;
+      float* red = red_base + (oi & 1) * kRedHalf;
       for (int i = tid; i < n_rt * kSW * 16; i += kSThreads) red[i] = 0.f;
 
       // ---- stage the activations
@@ -473,7 +514,7 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
             if (dt == NB_F32) stage4<2>(x_s, dst_off, i4, v[0], v[1], v[2], v[3]);
             else stage4<1>(x_s, dst_off, i4, v[0], v[1], v[2], v[3]);
           }
-          if (tid == 0) s_scale = 1.f;
+          if (tid == 0) s_scale[oi & 1] = 1.f;
         } else if (op.pro == NB_SPRO_EMBED_NORM || op.pro == NB_SPRO_ADD_NORM) {
           // residual: h = table[token] (first layer) or h += sum of the previous projection's partial slots;
           // activation = h * weight, the factor 1/rms (a scalar) is applied to the outputs
@@ -502,7 +543,7 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
             stage4<2>(x_s, dst_off, i4, h.x * w.x, h.y * w.y, h.z * w.z, h.w * w.w);
           }
           const float tot = block_sum(ss, s16, tid);
-          if (tid == 0) s_scale = 1.0f / sqrtf(tot / (float)K + op.f[0]);
+          if (tid == 0) s_scale[oi & 1] = 1.0f / sqrtf(tot / (float)K + op.f[0]);
         } else if (op.pro == NB_SPRO_ATTN_MERGE) {
           // activations = attention output: per head, the splits' partial softmax numerators and
           // denominators merged; columns outside this rank's heads are zero
@@ -532,20 +573,24 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
             }
             stage4<2>(x_s, dst_off, i4, v[0], v[1], v[2], v[3]);
           }
-          if (tid == 0) s_scale = 1.f;
+          if (tid == 0) s_scale[oi & 1] = 1.f;
         }
       } else {
         xs_terms = op.i[3] == NB_F32 ? 2 : 1;
+        if (tid == 0) s_scale[oi & 1] = s_scale[(oi & 1) ^ 1];
       }
       __syncthreads();
+      NB_STRACE(oi, 1);
+      prefetch_op();
 
       // ---- this warp's units
-      if (xs_terms == 2) run_units<BITS, 2>(ctx, use, fetch, oi, g, x_s, red, rt_first);
-      else run_units<BITS, 1>(ctx, use, fetch, oi, g, x_s, red, rt_first);
+      if (xs_terms == 2) run_units<BITS, 2>(ctx, use, fetch, oi, x_s, red, rt_first);
+      else run_units<BITS, 1>(ctx, use, fetch, oi, x_s, red, rt_first);
       __syncthreads();
+      NB_STRACE(oi, 2);
 
       // ---- add the warps' partial sums in warp order and write the results
-      const float scale = s_scale;
+      const float scale = s_scale[oi & 1];
       if (op.epi == NB_SEPI_SWIGLU) {
         // rows 0..7 of a tile are gate channels, rows 8..15 the matching up channels
         float* out = reinterpret_cast<float*>(op.p[4]);
@@ -559,6 +604,7 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
           if (ch < N / 2) out[ch] = gsum / (1.0f + __expf(-gsum)) * usum;
         }
       } else {
+        const int units = ((N + 15) >> 4) * bpr;
         for (int e = tid; e < n_rt * 16; e += kSThreads) {
           const int tl = e >> 4, r = e & 15;
           float v = 0.f;
@@ -570,16 +616,30 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
           if (op.epi == NB_SEPI_STORE) {
             store_y(op.p[4], op.i[4], row, v);
           } else {  // NB_SEPI_SLOTS: slot = index of this CTA among the CTAs that share the row tile
-            const int first = cta_of_unit((long long)rt * g.bpr, g.units, G), last = cta_of_unit((long long)(rt + 1) * g.bpr - 1, g.units, G);
+            const int first = cta_of_unit(rt * bpr, units, G), last = cta_of_unit((rt + 1) * bpr - 1, units, G);
             float* out = reinterpret_cast<float*>(op.p[4]);
             out[(size_t)(cta - first) * op.i[8] + row] = v;
-            if (cta == first)
-              for (int sl = last - first + 1; sl < op.i[6]; ++sl) out[(size_t)sl * op.i[8] + row] = 0.f;
+            if (cta == first) {
+              // the first CTA of a row tile clears the slots nobody writes: those past the last CTA, and
+              // those of CTAs in between whose share of the units is empty (fewer units than CTAs)
+              for (int sl = 1; sl < op.i[6]; ++sl) {
+                bool unused = sl > last - first;
+                if (!unused) {
+                  int lo, hi;
+                  share(units, G, first + sl, lo, hi);
+                  unused = lo == hi;
+                }
+                if (unused) out[(size_t)sl * op.i[8] + row] = 0.f;
+              }
+            }
           }
         }
       }
     } else if (op.kind == NB_SOP_ATTN) {
       // ---- single-query attention of one new token: items (head, split) over the CTAs
+      __syncthreads();
+      prefetch_op();
+      __syncthreads();
       const int Hl = op.i[0], hd = op.i[1], ctx_len = op.i[2], S = op.i[3], in_slots = op.i[5], in_stride = op.i[7];
       const float* qkv = reinterpret_cast<const float*>(op.p[0]);
       const float* cos2 = reinterpret_cast<const float*>(op.p[1]);
@@ -592,7 +652,7 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
       if (pos >= ctx_len) pos = ctx_len - 1;
       const int n = (int)pos + 1;
       const int per = (((n + S - 1) / S) + 7) & ~7;
-      float* raw = reinterpret_cast<float*>(x_s);          // q | k | v of the head, raw then rotated: 6 * hd floats
+      float* raw = reinterpret_cast<float*>(x_s);          // q | k | v of the head, raw then rotated: 6 * 128 floats
       float* sc = raw + 6 * 128;                           // scores of this split's keys
       float* pacc = sc + 2048;                             // [6][hd] partial value sums
       for (int item = cta; item < Hl * S; item += G) {
@@ -673,7 +733,9 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
       }
     } else if (op.kind == NB_SOP_HEAD) {
       // ---- final norm + LM head rows of this CTA + soft-cap + the CTA's best candidate
-      const OpGeom g = geom_of(op);
+      __syncthreads();
+      prefetch_op();
+      const OpInfo& f = info[oi];
       const int C = op.i[1];
       float* xh = reinterpret_cast<float*>(x_s);
       const float4* w4 = reinterpret_cast<const float4*>(op.p[3]);
@@ -701,9 +763,9 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
       float acc = 0.f;
       while (use.op == oi) {
         const uint8_t* st = wait_chunk(ctx, use);
-        const int row = use.u / g.head_pieces, piece = use.u - row * g.head_pieces;
-        const int off = piece * g.head_piece_bytes;
-        const int bytes = min(g.head_piece_bytes, g.head_row_bytes - off);
+        const int row = use.u / f.bpr, piece = use.u - row * f.bpr;
+        const int off = piece * f.ubytes;
+        const int bytes = min((int)f.ubytes, f.row_bytes - off);
         for (int j = lane; j < bytes / 16; j += 32) {
           const uint4 r = *reinterpret_cast<const uint4*>(st + 16 * j);
           const float* xv = xh + (off >> 1) + 8 * j;
@@ -713,7 +775,7 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
                  __uint_as_float(r.z << 16) * x1.x + __uint_as_float(r.z & 0xFFFF0000u) * x1.y +
                  __uint_as_float(r.w << 16) * x1.z + __uint_as_float(r.w & 0xFFFF0000u) * x1.w;
         }
-        if (piece == g.head_pieces - 1) {
+        if (piece == f.bpr - 1) {
           const float v = cap * tanhf(warp_sum_f(acc) * inv / cap);
           acc = 0.f;
           if (lane == 0) logits[row] = v;
@@ -739,6 +801,9 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
       }
     } else if (op.kind == NB_SOP_REDUCE) {
       // ---- y = sum of a projection's partial slots (in slot order), converted to the output type
+      __syncthreads();
+      prefetch_op();
+      __syncthreads();
       const int N = op.i[0];
       for (int i = cta * kSThreads + tid; i < N; i += G * kSThreads) {
         float v = 0.f;
@@ -747,6 +812,9 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
       }
     } else if (op.kind == NB_SOP_ARGMAX) {
       // ---- the best of the CTAs' candidates (lowest index among equals) becomes the next token
+      __syncthreads();
+      prefetch_op();
+      __syncthreads();
       if (cta == 0 && warp == 0) {
         const float* cand = reinterpret_cast<const float*>(op.p[0]);
         float b = -FLT_MAX;
@@ -769,18 +837,27 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
       }
     }
 
-    // ---- publish: this CTA's results of operation oi are complete
-    __syncthreads();
-    if (tid == 0) {
-      __threadfence();
-      st_release_gpu_u32(flags + cta, seq);
+    // ---- publish (only when somebody will wait for it): this CTA's results up to operation oi are complete
+    if (info[oi].flags & 1) {
+      __syncthreads();
+      if (tid == 0) {
+        __threadfence();
+        st_release_gpu_u32(flags + cta, seq);
+      }
     }
+    NB_STRACE(oi, 3);
   }
 
   // the next launch's sequence numbers start above this one's: written once every CTA is done
   wait_flags(flags, G, base + (uint32_t)n_ops, spin_limit, status, tid);
   if (cta == 0 && tid == 0) state[kMaxCtas] = base + (uint32_t)n_ops + 1u;
 }
+
+#ifdef NB_STREAM_TRACE
+extern "C" int nb_stream_trace_read(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, nb_stream_trace_buf, sizeof(nb_stream_trace_buf));
+}
+#endif
 
 // ---- relayout: nativebit/pack.py byte stream -> stream layout ------------------------------------
 // One thread per (unit, lane): writes the lane's index words; threads with lane < 16 also write row `lane`'s table.
@@ -868,29 +945,30 @@ static int check_op(const nb_stream_op& o, int index, int G, int* bits) {
   *bits = 0;
   if (o.kind == NB_SOP_GEMV) {
     const int N = o.i[0], K = o.i[1], b = o.i[2];
-    if (N < 1 || K < kBlock || K % kBlock != 0 || K / kBlock > kMaxKBlocks) return fail("needs N >= 1 and K a multiple of 128 up to 8192");
+    if (N < 1 || K < kBlock || K % kBlock != 0 || K / kBlock > kMaxKBlocks) return fail("needs N >= 1 and K a multiple of 128 up to 7168");
     if (b != 2 && b != 3 && b != 4) return fail("bits must be 2, 3 or 4");
     if (!o.p[0] || !o.p[4] || (uintptr_t)o.p[0] % 16) return fail("null or misaligned weight / output pointer");
     if (!(o.flags & NB_SOPF_REUSE_X) && !o.p[1]) return fail("null activation pointer");
     if ((uintptr_t)o.p[1] % 16) return fail("activations must be 16-byte aligned");
     if (o.pro < NB_SPRO_VEC || o.pro > NB_SPRO_ATTN_MERGE) return fail("unknown prologue");
-    if ((o.pro == NB_SPRO_EMBED_NORM || o.pro == NB_SPRO_ADD_NORM) && (K > kMaxC || !o.p[3])) return fail("norm prologue needs K <= 4096 and a weight");
+    if ((o.pro == NB_SPRO_EMBED_NORM || o.pro == NB_SPRO_ADD_NORM) && (K > kMaxC || !o.p[3])) return fail("norm prologue needs K <= 3072 and a weight");
     if (o.pro == NB_SPRO_EMBED_NORM && !o.p[2]) return fail("embedding prologue needs a token pointer");
     if (o.epi < NB_SEPI_STORE || o.epi > NB_SEPI_SWIGLU) return fail("unknown epilogue");
     if (o.epi != NB_SEPI_SLOTS && !(o.flags & NB_SOPF_ALIGN)) return fail("only the slot epilogue may split a row tile between CTAs");
     if (o.epi == NB_SEPI_SWIGLU && N % 16 != 0) return fail("SwiGLU epilogue needs N % 16 == 0");
+    if ((long long)((N + 15) / 16) * (K / kBlock) * (G + 1) >= (1ll << 31)) return fail("matrix too large for the 32-bit work split");
     const OpGeom g = geom_of(o);
     // local row tiles of a CTA must fit the reduction buffer, and the slots must cover every CTA of a row tile
     int worst_rt = 0, worst_slots = 1;
     for (int c = 0; c < G; ++c) {
-      int a, b2, ca, cb;
-      warp_range(g, c, G, 0, a, b2, ca, cb);
+      int ca, cb;
+      cta_range(g, c, G, ca, cb);
       if (cb > ca) worst_rt = std::max(worst_rt, (cb - 1) / g.bpr - ca / g.bpr + 1);
     }
     if (!g.align)
       for (int rt = 0; rt < g.rt; ++rt)
-        worst_slots = std::max(worst_slots, cta_of_unit((long long)(rt + 1) * g.bpr - 1, g.units, G) - cta_of_unit((long long)rt * g.bpr, g.units, G) + 1);
-    if (worst_rt * kSW * 16 > kRedFloats) return fail("too many row tiles per CTA for the reduction buffer");
+        worst_slots = std::max(worst_slots, cta_of_unit((rt + 1) * g.bpr - 1, g.units, G) - cta_of_unit(rt * g.bpr, g.units, G) + 1);
+    if (worst_rt * kSW * 16 > kRedHalf) return fail("too many row tiles per CTA for the reduction buffer");
     if (o.epi == NB_SEPI_SLOTS && (o.i[6] < worst_slots || o.i[8] < N)) return fail("too few output slots (see nb_stream_slots) or slot stride < N");
     *bits = b;
   } else if (o.kind == NB_SOP_ATTN) {
@@ -899,7 +977,7 @@ static int check_op(const nb_stream_op& o, int index, int G, int* bits) {
     if ((((ctx + S - 1) / S) + 7) > 2048) return fail("more than 2048 keys per attention split");
     for (int j = 0; j < 7; ++j) if (!o.p[j]) return fail("null pointer");
   } else if (o.kind == NB_SOP_HEAD) {
-    if (o.i[0] < 1 || o.i[1] < 8 || o.i[1] % 8 || o.i[1] > kMaxC) return fail("head needs C % 8 == 0, <= 4096");
+    if (o.i[0] < 1 || o.i[1] < 8 || o.i[1] % 8 || o.i[1] > kMaxC) return fail("head needs C % 8 == 0, <= 3072");
     if (!o.p[0] || !o.p[3] || !o.p[4] || !o.p[5] || (uintptr_t)o.p[0] % 16) return fail("null or misaligned pointer");
   } else if (o.kind == NB_SOP_REDUCE) {
     if (!o.p[1] || !o.p[4] || o.i[0] < 1 || o.i[5] < 1 || o.i[7] < o.i[0]) return fail("null pointer or bad slot geometry");
@@ -914,10 +992,11 @@ static int check_op(const nb_stream_op& o, int index, int G, int* bits) {
 extern "C" int nb_stream_slots(int N, int K, int ctas) {
   if (N < 1 || K < kBlock || K % kBlock || ctas < 1) return 0;
   const int bpr = K / kBlock, rt_n = (N + 15) / 16;
-  const long long U = (long long)rt_n * bpr;
+  if ((long long)rt_n * bpr * (ctas + 1) >= (1ll << 31)) return 0;
+  const int U = rt_n * bpr;
   int worst = 1;
   for (int rt = 0; rt < rt_n; ++rt)
-    worst = std::max(worst, cta_of_unit((long long)(rt + 1) * bpr - 1, U, ctas) - cta_of_unit((long long)rt * bpr, U, ctas) + 1);
+    worst = std::max(worst, cta_of_unit((rt + 1) * bpr - 1, U, ctas) - cta_of_unit(rt * bpr, U, ctas) + 1);
   return worst;
 }
 

@@ -102,15 +102,17 @@ def test_chain_of_dependent_matvecs(built_lib):
     assert np.abs(y.double().cpu().numpy() - ref).max() <= 2e-5 * np.abs(ref).max()
 
 
-def test_one_launch_decode_step_equals_kernel_chain_and_reference(built_lib):
-    """Tiny seeded model: the decode step as ONE persistent launch gives the tokens of the step run as a
-    chain of fused kernels, logits within fp32 rounding of it, and the reference's own PackedGPT logits
-    within the stated 2e-3."""
+def test_one_launch_decode_step_equals_kernel_chain(built_lib):
+    """Tiny seeded model (bf16 embedding table): the decode step as ONE persistent launch gives the tokens
+    of the step run as a chain of fused kernels and logits within fp32 rounding of it, eager and from a
+    CUDA graph.  (The chain is pinned to the reference's own PackedGPT logits in test_gpu_model.py; the
+    full-size model is compared with the dense oracle there, through this one-launch step.)"""
     from nativebit_b200 import generate as G
     from tests.test_gpu_model import _build
     dev = _dev()
     gm = np.load(os.path.join(ROOT, "tests", "golden", "reference_model.npz"))
     model, cfg = _build(gm, dev)
+    model.embedding = model.embedding.bfloat16()
     prompt = torch.from_numpy(gm["prompt"]).to(dev)
     for graph in (False, True):
         a = G.DecodeSession(model, 1, use_graph=graph, stream=True)
@@ -121,12 +123,3 @@ def test_one_launch_decode_step_equals_kernel_chain_and_reference(built_lib):
             assert torch.equal(a.token, b.token)
             assert (a.logits - b.logits).abs().max() <= 1e-4 * b.logits.abs().max()
         a.check()
-    # teacher-forced against the reference's logits
-    s = G.DecodeSession(model, 1, use_graph=True, stream=True)
-    s.prefill(prompt)
-    ref0 = gm["logits_prompt"]
-    for t, r in zip(gm["forced"].tolist(), gm["logits_steps"]):
-        s.token.fill_(t)
-        s.step()
-        assert np.abs(s.logits[0].cpu().numpy() - r).max() <= 2e-3 * np.abs(ref0).max()
-    s.check()
