@@ -261,7 +261,8 @@ int nb_gemv_static_status(int* host_out, int clear);
  *  NB_SOP_GEMV   y = W x.  p[0] stream-layout weights; i[0] N, i[1] K (multiple of 128, <= 8192), i[2] bits.
  *     prologue (how x is formed; i[3] = dtype of p[1] for NB_SPRO_VEC):
  *       NB_SPRO_VEC         x = p[1][0..K) (NB_F32 carried as two fp16 terms, NB_F16 / NB_BF16 as one)
- *       NB_SPRO_EMBED_NORM  h = table p[1] (bf16, row *p[2] (int64)); x = h * p[3] (K floats), result / rms(h)
+ *       NB_SPRO_EMBED_NORM  h = table p[1] (bf16, i[13] rows; row *p[2] (int64), clamped to the table);
+ *                           x = h * p[3] (K floats), result / rms(h)
  *       NB_SPRO_ADD_NORM    h += sum of i[5] slots of p[1] (floats, i[7] apart); then as above (f[0] = eps)
  *       NB_SPRO_ATTN_MERGE  x = attention output merged from the partials p[1] written by NB_SOP_ATTN:
  *                           i[9] heads, i[10] splits, i[11] head_dim, i[12] first column (others are zero)
@@ -290,7 +291,7 @@ int nb_gemv_static_status(int* host_out, int clear);
  * nb_stream_run takes the program twice: a host copy, which it validates, and the same bytes in device
  * memory, which the kernel reads.  `state` is nb_stream_state_bytes() of device memory, zero-filled once;
  * it carries the flag words, a sequence number that lets the launch be replayed from a CUDA graph, and a
- * status word (uint32 index 257) set to NB_ERR_TIMEOUT if a bounded wait ran out (the launch then finishes
+ * status word (uint32 index 513) set to NB_ERR_TIMEOUT if a bounded wait ran out (the launch then finishes
  * without hanging; results are invalid).  One launch at a time per state buffer.  The launch is cooperative
  * (all nb_stream_ctas() CTAs resident).  All packed matrices of a program share one `bits`.
  * Limits: at most nb_stream_max_ops() operations; one activation row (batch 1). */

@@ -10,18 +10,20 @@
 //  * Weight stream.  Packed weights are held in a tile-major "stream layout" (nb_stream_pack, built
 //    once at load time): a unit is 16 output rows x one 128-weight codebook block = the 32 lanes' index
 //    words followed by the 16 rows' byte-plane lookup tables, 1 KB at 3 bits, and the units of a matrix
-//    are consecutive.  Every operation's units are split evenly over CTAs and, inside a CTA, over its
-//    16 warps as contiguous runs, so a warp's share of a matrix is one contiguous byte range.  Each warp
-//    owns a private ring of shared-memory stages that it fills itself with bulk copies (cp.async.bulk,
-//    one lane, completion on an mbarrier): the refill of a stage is issued the moment the warp has
-//    consumed it, and the sequence of chunks runs on across operation boundaries, because weights
-//    never depend on earlier results.  About 128 KB of weights per SM are in flight or resident at
-//    all times, which covers the dependency waits between operations.
+//    are consecutive.  Every operation's units are split evenly over the CTAs and, inside a CTA, over
+//    its 32 warps as contiguous runs, so a warp's share of a matrix is one contiguous byte range.  Each
+//    warp owns a private ring of shared-memory stages (one unit each) that it fills itself with 16-byte
+//    asynchronous copies (cp.async, all lanes, one commit group per unit): the refill of a stage is
+//    issued the moment the warp has consumed it, and the sequence of units runs on across operation
+//    boundaries, because weights never depend on earlier results.  About 96 KB of weights per SM are in
+//    flight or resident at all times, which covers the dependency waits between operations.
 //  * Compute.  Lane (g, t) of a warp unpacks 32 weights of row g and 32 of row g+8 of the unit
 //    (selector words + byte-permute table lookups, nb_common.cuh) and feeds them, four per row at a
 //    time, as the A fragment of an m16n8k16 fp16 tensor-core MMA whose B fragment is the matching four
-//    activations; fp32 activations are carried as two fp16 terms.  Partial sums of a warp's run are
-//    kept per row tile, stored to a per-warp slot in shared memory and added in warp order.
+//    activations; fp32 activations are carried as two fp16 terms.  A warp keeps the partial sums of its
+//    run per row tile and stores them to a slot in shared memory; warps do not wait for one another at
+//    the end of a matrix: the warp that delivers the last units of a row tile adds the tile's slots in k
+//    order and writes the results while the others are already unpacking the next matrix.
 //  * Dependencies.  After an operation a CTA publishes a sequence number in its flag word; an
 //    operation that consumes the previous one's results first waits (bounded) until every CTA's flag has
 //    reached that number.  No atomics on values: a row tile that straddles two CTAs is written as two
@@ -42,18 +44,23 @@
 
 namespace nb {
 
-constexpr int kSW = 16;                                   // warps per CTA
+#ifndef NB_STREAM_WARPS
+#define NB_STREAM_WARPS 16
+#endif
+constexpr int kSW = NB_STREAM_WARPS;                      // warps per CTA (one CTA per SM)
 constexpr int kSThreads = kSW * 32;
-constexpr int kChunkBytes = 2048;                         // one ring stage
-constexpr int kStages = 4;                                // stages per warp
-constexpr int kRingBytes = kSW * kStages * kChunkBytes;   // 128 KB
+constexpr int kRingBytes = 120 * 1024;                    // kSW warps x stages x one unit
 constexpr int kMaxOps = 160;
 constexpr int kMaxKBlocks = 56;                           // K <= 7168
-constexpr int kXSegBytes = 72;                            // 32 halves of one (k-block, lane t) + skew
-constexpr int kXTermBytes = kMaxKBlocks * 4 * kXSegBytes; // 15.75 KB per fp16 term
-constexpr int kMaxC = 3072;                               // residual width
-constexpr int kRedHalf = 2048;                            // floats: 8 local row tiles x 16 warps x 16 rows
-constexpr int kMaxCtas = 256;
+constexpr int kXSegBytes = 80;                            // 32 halves of one (k-block, lane t) + skew (16-byte aligned)
+constexpr int kXTermBytes = kMaxKBlocks * 4 * kXSegBytes; // 17.5 KB per fp16 term
+constexpr int kMaxC = 2560;                               // residual width
+constexpr int kRedBufs = 4;                               // operations whose partial sums may be alive at once
+constexpr int kRedUnits = 128;                            // units of one operation per CTA
+constexpr int kRedSegs = 3;                               // row tiles one warp's run may touch
+constexpr int kRedBufFloats = kSW * kRedSegs * 16;
+constexpr int kMaxLocalTiles = 8;                         // row tiles of one operation a CTA may touch
+constexpr int kMaxCtas = 512;
 constexpr uint32_t kCopySpin = 1u << 22;
 constexpr uint32_t kFlagSpinDefault = 1u << 22;
 
@@ -62,51 +69,63 @@ using StreamOp = nb_stream_op;
 // What the weight stream needs to know about an operation, computed once per launch.
 struct OpInfo {
   int cta_a, cta_b;           // this CTA's unit range
-  int bpr;                    // units per row tile (GEMV: k-blocks per row; head: pieces per row)
-  uint16_t ubytes;            // bytes of a unit (GEMV) or of a full piece (head)
-  uint8_t per_chunk, kind;
-  const uint8_t* w;           // first unit
-  int row_bytes;              // head: bytes of a table row
-  int flags;                  // bit 0: the next operation waits for this one (or it is the last)
+  int bpr;                    // units per row tile (GEMV: k-blocks per row; head: pieces per table row)
+  uint32_t bpr_magic;         // ceil(2^32 / bpr): u / bpr = umulhi(u, magic) for u < 65536
+  const uint8_t* w;           // unit 0
+  uint16_t ubytes;            // bytes of a unit (GEMV: 16 rows x one block; head: one piece of a table row)
+  uint8_t kind;
+  uint8_t flags;              // bit 0: the next operation waits for this one (or it is the last)
+  uint8_t slot_first;         // slot epilogue: this CTA's slot in its first row tile when earlier CTAs share that tile
+  uint8_t last_span;          // ... and how many later CTAs reach into its last row tile
+  uint16_t next_empty;        // bit j: CTA cta+1+j has no units of this operation
 };
 static_assert(sizeof(OpInfo) == 32, "OpInfo layout");
+// u / bpr for u < 65536 (bpr == 1 has no 32-bit magic number)
+__device__ __forceinline__ int div_bpr(const OpInfo& f, int u) { return f.bpr == 1 ? u : (int)__umulhi((uint32_t)u, f.bpr_magic); }
 
 // shared-memory layout (dynamic)
 constexpr int kOffRing = 0;
 constexpr int kOffInfo = kOffRing + kRingBytes;
-constexpr int kOffX = kOffInfo + kMaxOps * (int)sizeof(OpInfo);
+constexpr int kOffRun = kOffInfo + kMaxOps * (int)sizeof(OpInfo);   // [op][warp] {first unit, units} of every warp's run
+constexpr int kOffX = kOffRun + kMaxOps * kSW * 4;
 constexpr int kOffH = kOffX + 2 * kXTermBytes;
 constexpr int kOffRed = kOffH + kMaxC * 4;
-constexpr int kOffDst = kOffRed + 2 * kRedHalf * 4;
-constexpr int kOffOp = kOffDst + 256;
-constexpr int kStreamSmem = kOffOp + 2 * (int)sizeof(StreamOp);
+constexpr int kOffDst = kOffRed + kRedBufs * kRedBufFloats * 4;
+constexpr int kStreamSmem = kOffDst + 256;
 static_assert(sizeof(StreamOp) == 160, "nb_stream_op layout");
-static_assert(kStreamSmem <= 226 * 1024, "shared memory budget");
+static_assert(kStreamSmem <= 224 * 1024, "shared memory budget");
 
+// A unit in the stream layout: the 32 lanes' selector words (eight 4-bit selectors per word, ready for the
+// byte-permute lookups: the 3- and 2-bit fields are spread to nibbles when the copy is built, so the
+// kernel spends no instructions on it), then the 16 rows' lookup tables.
 template <int BITS> struct UnitFmt {
-  static constexpr int kW = Fmt<BITS>::kWords / 4;          // words of one lane's 32 indices
-  static constexpr int kIdxBytes = kW * 256;                // 32 lanes x 2 rows x kW words
+  static constexpr int kW = Fmt<BITS>::kWords / 4;          // packed words of one lane's 32 indices in the source layout
+  static constexpr int kIdxBytes = 1024;                    // 32 lanes x 2 rows x 4 selector words
   static constexpr int kTabBytes = BITS == 4 ? 32 : 16;     // one row's lookup table
-  static constexpr int kBytes = kIdxBytes + 16 * kTabBytes; // 1024 at 3 bits, 768 at 2, 1536 at 4
+  static constexpr int kBytes = kIdxBytes + 16 * kTabBytes; // 1280 at 2 and 3 bits, 1536 at 4: one ring stage
+  static constexpr int kStages = kRingBytes / (kSW * kBytes) < 16 ? kRingBytes / (kSW * kBytes) : 16;   // per warp: 6, 6, 5 with 16 warps
+  // units a warp works on per loop iteration (one wait, one round of bookkeeping for all of them)
+  static constexpr int kBatch = kStages >= 6 ? 4 : (kStages >= 4 ? 2 : 1);
 };
 
 __host__ __device__ inline int unit_bytes(int bits) { return bits == 3 ? UnitFmt<3>::kBytes : bits == 2 ? UnitFmt<2>::kBytes : UnitFmt<4>::kBytes; }
 
-// ---- work split (32-bit arithmetic: the host refuses programs where units * (CTAs + 1) >= 2^31) ----
+// ---- work split (32-bit arithmetic; the host refuses matrices of 65536 units or more) ----
 // [lo, hi) of part `i` of `parts` equal shares of n items.
 __host__ __device__ inline void share(int n, int parts, int i, int& lo, int& hi) {
   lo = (int)((unsigned)n * (unsigned)i / (unsigned)parts);
   hi = (int)((unsigned)n * (unsigned)(i + 1) / (unsigned)parts);
 }
-// CTA that owns unit u when U units are split over G CTAs by share().
-__host__ __device__ inline int cta_of_unit(int u, int U, int G) { return (int)(((unsigned)(u + 1) * (unsigned)G - 1u) / (unsigned)U); }
+// Part that owns item u when U items are split into G parts by share().
+__host__ __device__ inline int part_of(int u, int U, int G) { return (int)(((unsigned)(u + 1) * (unsigned)G - 1u) / (unsigned)U); }
+__host__ __device__ inline int cta_of_unit(int u, int U, int G) { return part_of(u, U, G); }
 
 struct OpGeom {
-  int kind, bits, bpr, rt, align, ubytes, per_chunk, units;
-  int head_piece_bytes, head_row_bytes;
+  int kind, bits, bpr, rt, align, ubytes, units, row_bytes;
 };
 
-__host__ __device__ inline OpGeom geom_of(const StreamOp& o) {
+// prog_bits: the bits of the program's packed matrices (they set the size of a ring stage).
+__host__ __device__ inline OpGeom geom_of(const StreamOp& o, int prog_bits) {
   OpGeom g{};
   g.kind = o.kind;
   if (o.kind == NB_SOP_GEMV) {
@@ -115,16 +134,14 @@ __host__ __device__ inline OpGeom geom_of(const StreamOp& o) {
     g.rt = (o.i[0] + 15) / 16;
     g.align = (o.flags & NB_SOPF_ALIGN) ? 1 : 0;
     g.ubytes = unit_bytes(g.bits);
-    g.per_chunk = kChunkBytes / g.ubytes;
     g.units = g.rt * g.bpr;
   } else if (o.kind == NB_SOP_HEAD) {
-    g.head_row_bytes = o.i[1] * 2;
-    g.bpr = (g.head_row_bytes + kChunkBytes - 1) / kChunkBytes;          // pieces per row
-    g.head_piece_bytes = ((g.head_row_bytes / g.bpr + 15) / 16) * 16;
-    g.ubytes = g.head_piece_bytes;
-    g.rt = o.i[0];                                                       // rows
+    const int stage = unit_bytes(prog_bits);
+    g.row_bytes = o.i[1] * 2;
+    g.bpr = (g.row_bytes + stage - 1) / stage;                   // pieces per table row, each at most one stage
+    g.ubytes = ((g.row_bytes / g.bpr + 15) / 16) * 16;           // bytes of a full piece
+    g.rt = o.i[0];                                               // rows
     g.align = 1;
-    g.per_chunk = 1;
     g.units = g.rt * g.bpr;
   }
   return g;
@@ -142,16 +159,15 @@ __host__ __device__ inline void cta_range(const OpGeom& g, int cta, int G, int& 
     share(g.units, G, cta, a, b);
   }
 }
-// A warp's part of its CTA's range: equal shares of the units (of whole rows for the head).
-__host__ __device__ inline void warp_part(int kind, int bpr, int cta_a, int cta_b, int warp, int& a, int& b) {
+// A warp's part of its CTA's range [0, n) (local unit indices): equal shares of the units (of whole rows for the head).
+__host__ __device__ inline void warp_part(int kind, int bpr, int n, int warp, int& a, int& b) {
   if (kind == NB_SOP_HEAD) {
-    const int rows = (cta_b - cta_a) / bpr;
-    a = cta_a + (rows * warp / kSW) * bpr;
-    b = cta_a + (rows * (warp + 1) / kSW) * bpr;
+    const int rows = n / bpr;
+    a = (rows * warp / kSW) * bpr;
+    b = (rows * (warp + 1) / kSW) * bpr;
   } else {
-    const int n = cta_b - cta_a;
-    a = cta_a + n * warp / kSW;
-    b = cta_a + n * (warp + 1) / kSW;
+    a = n * warp / kSW;
+    b = n * (warp + 1) / kSW;
   }
 }
 
@@ -218,84 +234,86 @@ __device__ __forceinline__ void stage4(uint8_t* x_s, const uint16_t* dst_off, in
 }
 
 // ---- the per-warp weight stream ------------------------------------------------------------------
-// Both cursors walk the same sequence of chunks: for every operation with a weight stream, this
-// warp's unit range cut into pieces of at most per_chunk units.  `fetch` runs up to kStages chunks
-// ahead of `use`.
+// Every warp streams its own units: for every operation with a weight stream, its contiguous part of
+// the CTA's unit range, one unit (a piece of a table row for the head) per ring stage.  The copies are
+// 16-byte asynchronous copies issued by all lanes (cp.async: bulk copies were measured to deliver only
+// a few GB/s per SM here), one commit group per unit; `fetch` runs kStages - 1 units ahead of `use`.
 struct Cursor {
   int op;          // operation index (n_ops when exhausted)
-  int u, u_end;    // next unit and end of the warp's range in that operation
-  uint32_t count;  // chunks passed so far: stage = count % kStages, phase = (count / kStages) & 1
+  int u, u_end;    // next unit and end of the warp's range, relative to the CTA's range of that operation
+  int stage;       // ring stage of the next unit
+  const uint8_t* src;   // packed matrices: address of the next unit
+  int ubytes;           // ... and its size
+  int head;             // the operation is the LM head (pieces of table rows)
 };
 
 struct StreamCtx {
   const OpInfo* info;    // in shared memory
+  const uint32_t* runs;  // in shared memory: [op][warp] first unit | units << 16 of the warp's run
+  const StreamOp* ops;   // in global memory
   int n_ops, warp, lane;
-  uint8_t* ring;         // this warp's kStages stages
-  uint64_t* full;        // this warp's kStages barriers
-  int* status;
-  bool dead;             // a copy wait of this warp ran out: later waits are not repeated
+  int stages, stage_bytes;
+  uint8_t* ring;         // this warp's stages
 };
 
 __device__ __forceinline__ void cursor_seek(const StreamCtx& c, Cursor& k) {   // skip to the next non-empty range
   while (k.op < c.n_ops && k.u >= k.u_end) {
     ++k.op;
     if (k.op < c.n_ops) {
-      const OpInfo& f = c.info[k.op];
-      if (f.cta_b > f.cta_a) warp_part(f.kind, f.bpr, f.cta_a, f.cta_b, c.warp, k.u, k.u_end);
+      const uint32_t run = c.runs[k.op * kSW + c.warp];
+      k.u = (int)(run & 0xFFFFu);
+      k.u_end = k.u + (int)(run >> 16);
+      if (k.u_end > k.u) {
+        const OpInfo& f = c.info[k.op];
+        k.ubytes = f.ubytes;
+        k.head = f.kind == NB_SOP_HEAD;
+        k.src = f.w + (size_t)(f.cta_a + k.u) * f.ubytes;
+      }
     }
   }
 }
-
 __device__ __forceinline__ void cursor_init(const StreamCtx& c, Cursor& k) {
-  k.op = -1; k.u = 0; k.u_end = 0; k.count = 0;
+  k.op = -1; k.u = 0; k.u_end = 0; k.stage = 0; k.src = nullptr; k.ubytes = 0; k.head = 0;
   cursor_seek(c, k);
 }
-
-// Units and bytes of the chunk at the cursor, and its source address.
-__device__ __forceinline__ int chunk_at(const StreamCtx& c, const Cursor& k, const uint8_t*& src, uint32_t& bytes) {
-  const OpInfo& f = c.info[k.op];
-  if (f.kind == NB_SOP_HEAD) {
-    const int row = k.u / f.bpr, piece = k.u - row * f.bpr;
-    const int off = piece * f.ubytes;
-    bytes = (uint32_t)min((int)f.ubytes, f.row_bytes - off);
-    src = f.w + (size_t)row * f.row_bytes + off;
-    return 1;
-  }
-  const int n = min((int)f.per_chunk, k.u_end - k.u);
-  bytes = (uint32_t)(n * f.ubytes);
-  src = f.w + (size_t)k.u * f.ubytes;
-  return n;
+__device__ __forceinline__ void cursor_step(const StreamCtx& c, Cursor& k) {   // one unit further
+  ++k.u;
+  k.src += k.ubytes;
+  if (++k.stage == c.stages) k.stage = 0;
+  if (k.u >= k.u_end) cursor_seek(c, k);
 }
 
-// Request the chunk at the fetch cursor into its stage (if any is left); lane 0 issues the copy.
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// All lanes: request the unit at the fetch cursor into its stage (if any is left) and close the commit group.
+template <int BITS>
 __device__ __forceinline__ void fetch_next(const StreamCtx& c, Cursor& f) {
-  if (f.op >= c.n_ops) return;
-  const uint8_t* src;
-  uint32_t bytes;
-  const int n = chunk_at(c, f, src, bytes);
-  const int s = f.count % kStages;
-  if (c.lane == 0) {
-    mbar_arrive_expect_tx(&c.full[s], bytes);
-    bulk_g2s(c.ring + s * kChunkBytes, src, bytes, &c.full[s]);
-  }
-  f.u += n;
-  ++f.count;
-  cursor_seek(c, f);
-}
-
-// Bounded wait for the chunk at the use cursor; returns its stage.
-__device__ __forceinline__ const uint8_t* wait_chunk(StreamCtx& c, const Cursor& k) {
-  const int s = k.count % kStages;
-  const uint32_t parity = (k.count / kStages) & 1u;
-  uint32_t spins = 0;
-  while (!c.dead && !mbar_try_wait(&c.full[s], parity)) {
-    __nanosleep(32);
-    if (++spins > kCopySpin) {
-      if (c.status) atomicExch(c.status, (int)NB_ERR_TIMEOUT);
-      c.dead = true;
+  if (f.op < c.n_ops) {
+    const uint8_t* src = f.src;
+    uint8_t* dst = c.ring + f.stage * c.stage_bytes;
+    if (!f.head) {               // a unit of a packed matrix: fixed size, straight-line copies
+      constexpr int kChunks = UnitFmt<BITS>::kBytes / 16;
+#pragma unroll
+      for (int i = 0; i < (kChunks + 31) / 32; ++i)
+        if (i * 32 + 32 <= kChunks || c.lane + i * 32 < kChunks) cp_async16(dst + 16 * (c.lane + i * 32), src + 16 * (c.lane + i * 32));
+      cursor_step(c, f);
+      cp_async_commit();
+      return;
     }
+    int bytes = f.ubytes;
+    {
+      const OpInfo& fi = c.info[f.op];
+      const int lu = f.u;                                        // local unit = local row * pieces + piece
+      const int row = div_bpr(fi, lu), piece = lu - row * fi.bpr;
+      const int row_bytes = c.ops[f.op].i[1] * 2, off = piece * fi.ubytes;
+      bytes = min(bytes, row_bytes - off);
+      src = fi.w + ((size_t)(fi.cta_a / fi.bpr) + row) * row_bytes + off;
+    }
+    for (int i = c.lane; i < (bytes >> 4); i += 32) cp_async16(dst + 16 * i, src + 16 * i);
+    cursor_step(c, f);
   }
-  return c.ring + s * kChunkBytes;
+  cp_async_commit();
 }
 
 // ---- one unit: 16 rows x 128 weights against the staged activations -----------------------------
@@ -303,12 +321,9 @@ template <int BITS, int XS>
 __device__ __forceinline__ void unit_mma(const uint8_t* ub, const uint8_t* x_s, int kb, int lane, float (&c)[2][4]) {
   using F = UnitFmt<BITS>;
   const int g = lane >> 2, t = lane & 3;
-  uint32_t w[2 * F::kW];
-#pragma unroll
-  for (int j = 0; j < F::kW; ++j) {
-    const uint2 v = *reinterpret_cast<const uint2*>(ub + j * 256 + lane * 8);
-    w[2 * j] = v.x; w[2 * j + 1] = v.y;
-  }
+  const uint4 ua = *reinterpret_cast<const uint4*>(ub + lane * 16);
+  const uint4 ub4 = *reinterpret_cast<const uint4*>(ub + 512 + lane * 16);
+  const uint32_t UA[4] = {ua.x, ua.y, ua.z, ua.w}, UB[4] = {ub4.x, ub4.y, ub4.z, ub4.w};
   uint32_t TA[BITS == 4 ? 8 : 4], TB[BITS == 4 ? 8 : 4];
   const uint8_t* tab = ub + F::kIdxBytes;
 #pragma unroll
@@ -318,73 +333,27 @@ __device__ __forceinline__ void unit_mma(const uint8_t* ub, const uint8_t* x_s, 
     TA[4 * j] = a.x; TA[4 * j + 1] = a.y; TA[4 * j + 2] = a.z; TA[4 * j + 3] = a.w;
     TB[4 * j] = b.x; TB[4 * j + 1] = b.y; TB[4 * j + 2] = b.z; TB[4 * j + 3] = b.w;
   }
-  uint32_t UA[4], UB[4];
-  if (BITS == 3) {
-    selectors3(w[0], w[1], w[2], UA);
-    selectors3(w[3], w[4], w[5], UB);
-  } else if (BITS == 2) {
-    selectors2(w[0], w[1], UA);
-    selectors2(w[2], w[3], UB);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) { UA[j] = w[j]; UB[j] = w[4 + j]; }
-  }
   const uint8_t* xseg = x_s + (kb * 4 + t) * kXSegBytes;
 #pragma unroll
   for (int uu = 0; uu < 4; ++uu) {
+    uint4 xq[XS];    // the activations of steps 2*uu and 2*uu + 1
+#pragma unroll
+    for (int xs = 0; xs < XS; ++xs) xq[xs] = *reinterpret_cast<const uint4*>(xseg + xs * kXTermBytes + uu * 16);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const int s = 2 * uu + h;
       const uint32_t sa = h ? (UA[uu] >> 16) : UA[uu];
       const uint32_t sb = h ? (UB[uu] >> 16) : UB[uu];
       uint32_t a0, a1, a2, a3;
       lookup4<BITS>(sa, TA, a0, a2);
       lookup4<BITS>(sb, TB, a1, a3);
 #pragma unroll
-      for (int xs = 0; xs < XS; ++xs) {
-        const uint2 xb = *reinterpret_cast<const uint2*>(xseg + xs * kXTermBytes + s * 8);
-        mma_16816(c[h], a0, a1, a2, a3, xb.x, xb.y);
-      }
+      for (int xs = 0; xs < XS; ++xs) mma_16816(c[h], a0, a1, a2, a3, h ? xq[xs].z : xq[xs].x, h ? xq[xs].w : xq[xs].y);
     }
   }
 }
 
-// This warp's run of units of a packed matvec: streams the chunks, accumulates per row tile, stores
-// the partial sums of every row tile it touched into its slot of `red` ([local row tile][warp][16]).
-template <int BITS, int XS>
-__device__ __forceinline__ void run_units(StreamCtx& c, Cursor& use, Cursor& fetch, int op_index, const uint8_t* x_s, float* red,
-                                          int rt_first) {
-  using F = UnitFmt<BITS>;
-  const int lane = c.lane;
-  if (use.op != op_index) return;
-  const int bpr = c.info[op_index].bpr, per_chunk = c.info[op_index].per_chunk;
-  float acc[2][4];
-#pragma unroll
-  for (int j = 0; j < 2; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-  int rt = use.u / bpr, kb = use.u - rt * bpr;
-  while (use.op == op_index) {
-    const uint8_t* st = wait_chunk(c, use);
-    const int n = min(per_chunk, use.u_end - use.u);
-    for (int j = 0; j < n; ++j) {
-      unit_mma<BITS, XS>(st + j * F::kBytes, x_s, kb, lane, acc);
-      if (++kb == bpr || (j == n - 1 && use.u + n == use.u_end)) {   // row tile (or this warp's part of it) complete
-        if ((lane & 3) == 0) {
-          float* dst = red + ((rt - rt_first) * kSW + c.warp) * 16;
-          dst[lane >> 2] = acc[0][0] + acc[1][0];
-          dst[(lane >> 2) + 8] = acc[0][2] + acc[1][2];
-        }
-#pragma unroll
-        for (int q = 0; q < 2; ++q) acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
-        if (kb == bpr) { kb = 0; ++rt; }
-      }
-    }
-    use.u += n;
-    ++use.count;
-    cursor_seek(c, use);
-    __syncwarp();               // every lane has consumed the stage before it is overwritten
-    fetch_next(c, fetch);
-  }
-}
+// Warp that owns local unit v when a CTA's n units are split by warp_part() (packed matrices).
+__device__ __forceinline__ int warp_of_unit(int v, int n) { return part_of(v, n, kSW); }
 
 // ---- dependency flags ----------------------------------------------------------------------------
 // Every CTA's flag must have reached `target` (sequence numbers only grow; compared as signed differences).
@@ -406,7 +375,7 @@ __device__ __forceinline__ void wait_flags(const uint32_t* flags, int G, uint32_
 __device__ unsigned long long nb_stream_trace_buf[kMaxOps * 8];
 #define NB_STRACE(op, i)                                                     \
   do {                                                                       \
-    if (blockIdx.x == 0 && threadIdx.x == 0) {                               \
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {                        \
       unsigned long long t_;                                                 \
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_));                  \
       nb_stream_trace_buf[(op) * 8 + (i)] = t_;                              \
@@ -421,17 +390,19 @@ __device__ unsigned long long nb_stream_trace_buf[kMaxOps * 8];
 template <int BITS>
 __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __restrict__ ops_g, int n_ops, uint32_t* state, uint32_t spin_limit) {
   extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int kStages = UnitFmt<BITS>::kStages, kStageBytes = UnitFmt<BITS>::kBytes;
   OpInfo* info = reinterpret_cast<OpInfo*>(smem + kOffInfo);
   uint8_t* x_s = smem + kOffX;
   float* h_s = reinterpret_cast<float*>(smem + kOffH);
   float* red_base = reinterpret_cast<float*>(smem + kOffRed);
   uint16_t* dst_off = reinterpret_cast<uint16_t*>(smem + kOffDst);
-  StreamOp* op_slots = reinterpret_cast<StreamOp*>(smem + kOffOp);
-  __shared__ __align__(8) uint64_t bars[kSW * kStages];
   __shared__ float s16[kSW];
-  __shared__ float s_scale[2];
+  __shared__ float s_scale;
   __shared__ float s_best[kSW];
   __shared__ int s_besti[kSW];
+  __shared__ int s_tile_cnt[kRedBufs][kMaxLocalTiles];   // units of a row tile whose partial sums are in, per operation (ring)
+  __shared__ int s_tiles_done[kRedBufs];                 // row tiles of an operation that have been written
+  __shared__ volatile int s_finished;                    // operations whose results are completely written
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cta = blockIdx.x, G = gridDim.x;
@@ -441,60 +412,81 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
 
   for (int i = tid; i < n_ops; i += kSThreads) {
     const StreamOp& o = ops_g[i];
-    const OpGeom g = geom_of(o);
+    const OpGeom g = geom_of(o, BITS);
     OpInfo f;
     cta_range(g, cta, G, f.cta_a, f.cta_b);
     f.bpr = g.bpr > 0 ? g.bpr : 1;
+    f.bpr_magic = (uint32_t)((0x100000000ull + (unsigned)f.bpr - 1) / (unsigned)f.bpr);
     f.ubytes = (uint16_t)g.ubytes;
-    f.per_chunk = (uint8_t)g.per_chunk;
     f.kind = (uint8_t)g.kind;
     f.w = reinterpret_cast<const uint8_t*>(o.p[0]);
-    f.row_bytes = g.head_row_bytes;
     f.flags = (i + 1 == n_ops || (ops_g[i + 1].flags & NB_SOPF_WAIT_PREV)) ? 1 : 0;
+    f.slot_first = 0; f.last_span = 0; f.next_empty = 0;
+    if (g.kind == NB_SOP_GEMV && !g.align && f.cta_b > f.cta_a) {
+      const int rt_a = f.cta_a / g.bpr, rt_b = (f.cta_b - 1) / g.bpr;
+      f.slot_first = (uint8_t)(cta - cta_of_unit(rt_a * g.bpr, g.units, G));
+      f.last_span = (uint8_t)(cta_of_unit((rt_b + 1) * g.bpr - 1, g.units, G) - cta);
+      for (int j = 0; j < 16 && cta + 1 + j < G; ++j) {
+        int lo, hi;
+        share(g.units, G, cta + 1 + j, lo, hi);
+        if (lo == hi) f.next_empty |= (uint16_t)(1u << j);
+      }
+    }
     info[i] = f;
   }
-  for (int i = tid; i < (int)(sizeof(StreamOp) / 4) * min(n_ops, 2); i += kSThreads)
-    reinterpret_cast<uint32_t*>(op_slots)[i] = reinterpret_cast<const uint32_t*>(ops_g)[i];
-  if (tid < kSW * kStages) mbar_init(&bars[tid], 1);
+  if (tid < kRedBufs * kMaxLocalTiles) (&s_tile_cnt[0][0])[tid] = 0;
+  if (tid < kRedBufs) s_tiles_done[tid] = 0;
+  if (tid == 0) s_finished = 0;
   if (tid < kBlock) {
     // position inside a 128-weight block -> offset (in halves) of its activation inside the block's four segments
     const int slot = tid, pos = slot_to_position<BITS>(slot);
     dst_off[pos] = (uint16_t)((slot >> 5) * (kXSegBytes / 2) + (slot & 31));
   }
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncthreads();
 
-  StreamCtx ctx{info, n_ops, warp, lane, smem + kOffRing + warp * kStages * kChunkBytes, &bars[warp * kStages], status, false};
+  // every warp's run of every operation: equal shares of the CTA's units, handed out in an order that
+  // rotates from operation to operation (the same warps would otherwise get the larger shares every time)
+  uint32_t* runs = reinterpret_cast<uint32_t*>(smem + kOffRun);
+  for (int i = tid; i < n_ops * kSW; i += kSThreads) {
+    const int o = i / kSW, w = i - o * kSW;
+    const OpInfo& f = info[o];
+    int a = 0, b = 0;
+    if (f.cta_b > f.cta_a) warp_part(f.kind, f.bpr, f.cta_b - f.cta_a, (w + o) & (kSW - 1), a, b);
+    runs[i] = (uint32_t)a | ((uint32_t)(b - a) << 16);
+  }
+  __syncthreads();
+  StreamCtx ctx{info, runs, ops_g, n_ops, warp, lane, kStages, kStageBytes, smem + kOffRing + warp * kStages * kStageBytes};
   Cursor fetch, use;
   cursor_init(ctx, fetch);
   cursor_init(ctx, use);
-  for (int s = 0; s < kStages; ++s) fetch_next(ctx, fetch);
+  for (int s = 0; s < kStages - 1; ++s) fetch_next<BITS>(ctx, fetch);
+
+  // One thread of the CTA, after all of the CTA's writes for operation oi: make them visible and raise the flag.
+  auto publish = [&](int oi) {
+    if (info[oi].flags & 1) {
+      __threadfence();
+      st_release_gpu_u32(flags + cta, base + (uint32_t)oi + 1u);
+    }
+    s_finished = oi + 1;
+  };
 
   for (int oi = 0; oi < n_ops; ++oi) {
-    const StreamOp& op = op_slots[oi & 1];
+    const StreamOp& op = ops_g[oi];
+    const OpInfo& fi = info[oi];
     const uint32_t seq = base + (uint32_t)oi + 1u;     // published after this operation
-    if (oi > 0 && (op.flags & NB_SOPF_WAIT_PREV)) wait_flags(flags, G, seq - 1u, spin_limit, status, tid);
-    NB_STRACE(oi, 0);
-    // the descriptor after the next one is fetched into the slot of the operation that just ended
-    auto prefetch_op = [&]() {
-      if (oi >= 1 && oi + 1 < n_ops && tid < (int)(sizeof(StreamOp) / 4))
-        reinterpret_cast<uint32_t*>(&op_slots[(oi + 1) & 1])[tid] = __ldg(reinterpret_cast<const uint32_t*>(ops_g + oi + 1) + tid);
-    };
+    const bool waits = oi > 0 && (op.flags & NB_SOPF_WAIT_PREV);
 
     if (op.kind == NB_SOP_GEMV) {
       const int N = op.i[0], K = op.i[1];
-      const int bpr = info[oi].bpr, cta_a = info[oi].cta_a, cta_b = info[oi].cta_b;
-      const int rt_first = cta_a / bpr;
-      const int n_rt = cta_b > cta_a ? (cta_b - 1) / bpr - rt_first + 1 : 0;
-      float* red = red_base + (oi & 1) * kRedHalf;
-      for (int i = tid; i < n_rt * kSW * 16; i += kSThreads) red[i] = 0.f;
-
-      // ---- stage the activations
-      int xs_terms = 1;
-      if (!(op.flags & NB_SOPF_REUSE_X)) {
+      // ---- stage the activations (all warps together), unless the previous matvec's are used again
+      if (waits) wait_flags(flags, G, seq - 1u, spin_limit, status, tid);
+      const bool stage = !(op.flags & NB_SOPF_REUSE_X);
+      const int xs_terms = op.pro == NB_SPRO_VEC ? (op.i[3] == NB_F32 ? 2 : 1) : 2;
+      if (stage) {
+        if (!waits) __syncthreads();   // every warp is done with the activations of the matvec before
+        NB_STRACE(oi, 0);
         if (op.pro == NB_SPRO_VEC) {
           const int dt = op.i[3];
-          xs_terms = dt == NB_F32 ? 2 : 1;
           for (int i4 = tid; i4 < K / 4; i4 += kSThreads) {
             float v[4];
             if (dt == NB_F32) {
@@ -514,17 +506,17 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
             if (dt == NB_F32) stage4<2>(x_s, dst_off, i4, v[0], v[1], v[2], v[3]);
             else stage4<1>(x_s, dst_off, i4, v[0], v[1], v[2], v[3]);
           }
-          if (tid == 0) s_scale[oi & 1] = 1.f;
+          if (tid == 0) s_scale = 1.f;
         } else if (op.pro == NB_SPRO_EMBED_NORM || op.pro == NB_SPRO_ADD_NORM) {
           // residual: h = table[token] (first layer) or h += sum of the previous projection's partial slots;
           // activation = h * weight, the factor 1/rms (a scalar) is applied to the outputs
-          xs_terms = 2;
           const float4* w4 = reinterpret_cast<const float4*>(op.p[3]);
           float ss = 0.f;
           for (int i4 = tid; i4 < K / 4; i4 += kSThreads) {
             float4 h;
             if (op.pro == NB_SPRO_EMBED_NORM) {
-              const long long tok = *reinterpret_cast<const long long*>(op.p[2]);
+              long long tok = *reinterpret_cast<const long long*>(op.p[2]);
+              tok = tok < 0 ? 0 : (tok >= op.i[13] ? op.i[13] - 1 : tok);   // never read outside the table
               const uint2 r = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(op.p[1]) + (size_t)tok * K) + i4);
               h = make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xFFFF0000u), __uint_as_float(r.y << 16),
                               __uint_as_float(r.y & 0xFFFF0000u));
@@ -543,11 +535,10 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
             stage4<2>(x_s, dst_off, i4, h.x * w.x, h.y * w.y, h.z * w.z, h.w * w.w);
           }
           const float tot = block_sum(ss, s16, tid);
-          if (tid == 0) s_scale[oi & 1] = 1.0f / sqrtf(tot / (float)K + op.f[0]);
+          if (tid == 0) s_scale = 1.0f / sqrtf(tot / (float)K + op.f[0]);
         } else if (op.pro == NB_SPRO_ATTN_MERGE) {
           // activations = attention output: per head, the splits' partial softmax numerators and
           // denominators merged; columns outside this rank's heads are zero
-          xs_terms = 2;
           const int Hl = op.i[9], S = op.i[10], hd = op.i[11], col0 = op.i[12];
           const float* part = reinterpret_cast<const float*>(op.p[1]);
           for (int i4 = tid; i4 < K / 4; i4 += kSThreads) {
@@ -573,73 +564,159 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
             }
             stage4<2>(x_s, dst_off, i4, v[0], v[1], v[2], v[3]);
           }
-          if (tid == 0) s_scale[oi & 1] = 1.f;
+          if (tid == 0) s_scale = 1.f;
         }
-      } else {
-        xs_terms = op.i[3] == NB_F32 ? 2 : 1;
-        if (tid == 0) s_scale[oi & 1] = s_scale[(oi & 1) ^ 1];
+        __syncthreads();
+        NB_STRACE(oi, 1);
       }
-      __syncthreads();
-      NB_STRACE(oi, 1);
-      prefetch_op();
 
-      // ---- this warp's units
-      if (xs_terms == 2) run_units<BITS, 2>(ctx, use, fetch, oi, x_s, red, rt_first);
-      else run_units<BITS, 1>(ctx, use, fetch, oi, x_s, red, rt_first);
-      __syncthreads();
-      NB_STRACE(oi, 2);
-
-      // ---- add the warps' partial sums in warp order and write the results
-      const float scale = s_scale[oi & 1];
-      if (op.epi == NB_SEPI_SWIGLU) {
-        // rows 0..7 of a tile are gate channels, rows 8..15 the matching up channels
-        float* out = reinterpret_cast<float*>(op.p[4]);
-        for (int e = tid; e < n_rt * 8; e += kSThreads) {
-          const int tl = e >> 3, r = e & 7;
-          float gsum = 0.f, usum = 0.f;
-#pragma unroll
-          for (int w = 0; w < kSW; ++w) { gsum += red[(tl * kSW + w) * 16 + r]; usum += red[(tl * kSW + w) * 16 + r + 8]; }
-          gsum *= scale; usum *= scale;
-          const int ch = (rt_first + tl) * 8 + r;
-          if (ch < N / 2) out[ch] = gsum / (1.0f + __expf(-gsum)) * usum;
+      // ---- this warp's units.  Warps run ahead of one another by at most kRedBufs - 1 operations (the
+      // partial sums live in a ring of kRedBufs buffers).
+      if (lane == 0) {
+        uint32_t spins = 0;
+        while (s_finished < oi - (kRedBufs - 1)) {
+          __nanosleep(64);
+          if (++spins > kCopySpin) { atomicExch(status, (int)NB_ERR_TIMEOUT); break; }
         }
-      } else {
-        const int units = ((N + 15) >> 4) * bpr;
-        for (int e = tid; e < n_rt * 16; e += kSThreads) {
-          const int tl = e >> 4, r = e & 15;
-          float v = 0.f;
+      }
+      __syncwarp();
+      const int buf = oi & (kRedBufs - 1);
+      float* red = red_base + buf * kRedBufFloats;
+      const int bpr = fi.bpr, cta_a = fi.cta_a, cta_b = fi.cta_b, n_units = cta_b - cta_a;
+      const int rt_first = n_units > 0 ? div_bpr(fi, cta_a) : 0;
+      const int n_rt = n_units > 0 ? div_bpr(fi, cta_b - 1) - rt_first + 1 : 0;
+      // This CTA's part of the matrix is complete: results are published in order (the matrix before this
+      // one may still be in another warp's hands).
+      auto op_complete = [&]() {
+        uint32_t spins = 0;
+        while (s_finished < oi) {
+          __nanosleep(64);
+          if (++spins > kCopySpin) { atomicExch(status, (int)NB_ERR_TIMEOUT); break; }
+        }
+        publish(oi);
+      };
+      if (n_units == 0 && tid == 0) op_complete();
+      if (use.op == oi) {
+        constexpr int kBatch = UnitFmt<BITS>::kBatch;
+        const int sh = (warp + oi) & (kSW - 1);          // this warp's share of the units in this operation
+        float* red_w = red + sh * (kRedSegs * 16);
+        int rt = div_bpr(fi, cta_a + use.u), kb = cta_a + use.u - rt * bpr;
+        int left = use.u_end - use.u;                    // units left in the run
+        int v0 = use.u;                                  // first unit of the segment (inside the CTA's range)
+        // the run, row tile by row tile
+        for (int seg = 0; left > 0; ++seg) {
+          const int seg_len = min(left, bpr - kb);
+          float acc[2][2][4];   // [unit parity][step parity]: four independent MMA chains
 #pragma unroll
-          for (int w = 0; w < kSW; ++w) v += red[(tl * kSW + w) * 16 + r];
-          v *= scale;
-          const int rt = rt_first + tl, row = rt * 16 + r;
-          if (row >= N) continue;
-          if (op.epi == NB_SEPI_STORE) {
-            store_y(op.p[4], op.i[4], row, v);
-          } else {  // NB_SEPI_SLOTS: slot = index of this CTA among the CTAs that share the row tile
-            const int first = cta_of_unit(rt * bpr, units, G), last = cta_of_unit((rt + 1) * bpr - 1, units, G);
-            float* out = reinterpret_cast<float*>(op.p[4]);
-            out[(size_t)(cta - first) * op.i[8] + row] = v;
-            if (cta == first) {
-              // the first CTA of a row tile clears the slots nobody writes: those past the last CTA, and
-              // those of CTAs in between whose share of the units is empty (fewer units than CTAs)
-              for (int sl = 1; sl < op.i[6]; ++sl) {
-                bool unused = sl > last - first;
-                if (!unused) {
-                  int lo, hi;
-                  share(units, G, first + sl, lo, hi);
-                  unused = lo == hi;
+          for (int q = 0; q < 16; ++q) (&acc[0][0][0])[q] = 0.f;
+          for (int done = 0; done < seg_len;) {
+            // up to kBatch consecutive units per iteration: one wait, one round of bookkeeping
+            const int nb = min(kBatch, seg_len - done);
+            cp_async_wait<kStages - 1 - kBatch>();       // this lane's copies of the oldest kBatch units have landed ...
+            __syncwarp();                                // ... and so have the other lanes'
+#pragma unroll
+            for (int b2 = 0; b2 < kBatch; ++b2) {
+              if (b2 < nb) {
+                int sidx = use.stage + b2;
+                if (sidx >= kStages) sidx -= kStages;
+                const uint8_t* st = ctx.ring + sidx * kStageBytes;
+                if (xs_terms == 2) unit_mma<BITS, 2>(st, x_s, kb + b2, lane, acc[b2 & 1]);
+                else unit_mma<BITS, 1>(st, x_s, kb + b2, lane, acc[b2 & 1]);
+              }
+            }
+            use.u += nb;
+            use.stage += nb;
+            if (use.stage >= kStages) use.stage -= kStages;
+            __syncwarp();                                // every lane has consumed the stages before they are overwritten
+#pragma unroll
+            for (int b2 = 0; b2 < kBatch; ++b2)
+              if (b2 < nb) fetch_next<BITS>(ctx, fetch);
+            kb += nb;
+            done += nb;
+          }
+          // ---- the segment's partial sums go to this share's slot; the warp that delivers the last units of
+          // a row tile adds the tile's partial sums in k order and writes the results, while the others carry on
+          if ((lane & 3) == 0) {
+            red_w[seg * 16 + (lane >> 2)] = (acc[0][0][0] + acc[0][1][0]) + (acc[1][0][0] + acc[1][1][0]);
+            red_w[seg * 16 + (lane >> 2) + 8] = (acc[0][0][2] + acc[0][1][2]) + (acc[1][0][2] + acc[1][1][2]);
+          }
+          const int tl = rt - rt_first;
+          const int v_lo = max(rt * bpr, cta_a) - cta_a, v_hi = min((rt + 1) * bpr, cta_b) - cta_a;
+          __syncwarp();
+          int ticket = 0;
+          if (lane == 0) {
+            __threadfence_block();
+            ticket = atomicAdd(&s_tile_cnt[buf][tl], seg_len);
+          }
+          ticket = __shfl_sync(0xffffffffu, ticket, 0);
+          if (ticket + seg_len == v_hi - v_lo) {
+            __threadfence_block();
+            const float scale = s_scale;
+            const int r = lane & 15, half = lane >> 4;
+            // segments of this tile: one per share from sh_lo to sh_hi; lanes 0-15 add the first half of them, lanes 16-31 the rest
+            const int sh_lo = part_of(v_lo, n_units, kSW), sh_hi = part_of(v_hi - 1, n_units, kSW);
+            const int sh_mid = sh_lo + ((sh_hi - sh_lo + 2) >> 1);
+            float y = 0.f;
+            for (int w = half ? sh_mid : sh_lo; w < (half ? sh_hi + 1 : sh_mid); ++w) {
+              const int a_w = n_units * w / kSW, b_w = n_units * (w + 1) / kSW;
+              if (b_w > a_w) {
+                const int first = div_bpr(fi, cta_a + a_w);   // first row tile of that share's run
+                y += red[(w * kRedSegs + (rt - first)) * 16 + r];
+              }
+            }
+            y += __shfl_down_sync(0xffffffffu, y, 16);      // row r: first half + second half
+            y *= scale;
+            if (op.epi == NB_SEPI_SWIGLU) {
+              // rows 0..7 of a tile are gate channels, rows 8..15 the matching up channels
+              const float up = __shfl_down_sync(0xffffffffu, y, 8);
+              const int ch = rt * 8 + r;
+              if (lane < 8 && ch < N / 2) reinterpret_cast<float*>(op.p[4])[ch] = y / (1.0f + __expf(-y)) * up;
+            } else {
+              const int row = rt * 16 + r;
+              if (!half && row < N) {
+                if (op.epi == NB_SEPI_STORE) {
+                  store_y(op.p[4], op.i[4], row, y);
+                } else {  // NB_SEPI_SLOTS: slot = index of this CTA among the CTAs that share the row tile
+                  // only a CTA's first and last row tile can be shared (with earlier / later CTAs)
+                  const bool shared_before = tl == 0 && rt * bpr < cta_a;
+                  const int span_after = (tl == n_rt - 1 && (rt + 1) * bpr > cta_b) ? fi.last_span : 0;
+                  float* out = reinterpret_cast<float*>(op.p[4]);
+                  out[(size_t)(shared_before ? fi.slot_first : 0) * op.i[8] + row] = y;
+                  if (!shared_before) {
+                    // the first CTA of a row tile clears the slots nobody writes: those past the last CTA, and
+                    // those of CTAs in between whose share of the units is empty (fewer units than CTAs)
+                    for (int sl = 1; sl < op.i[6]; ++sl)
+                      if (sl > span_after || ((fi.next_empty >> (sl - 1)) & 1)) out[(size_t)sl * op.i[8] + row] = 0.f;
+                  }
                 }
-                if (unused) out[(size_t)sl * op.i[8] + row] = 0.f;
+              }
+            }
+            __syncwarp();
+            if (lane == 0) {
+              s_tile_cnt[buf][tl] = 0;
+              if (fi.flags & 1) __threadfence();          // someone will wait for this operation: the tile's stores are out
+              if (atomicAdd(&s_tiles_done[buf], 1) == n_rt - 1) {
+                s_tiles_done[buf] = 0;
+                op_complete();
               }
             }
           }
+          left -= seg_len;
+          v0 += seg_len;
+          kb = 0;
+          ++rt;
         }
+        (void)v0;
+        cursor_seek(ctx, use);
       }
-    } else if (op.kind == NB_SOP_ATTN) {
+      continue;
+    }
+
+    // ---- the other kinds run with all warps in step
+    if (waits) wait_flags(flags, G, seq - 1u, spin_limit, status, tid);
+    else __syncthreads();
+    if (op.kind == NB_SOP_ATTN) {
       // ---- single-query attention of one new token: items (head, split) over the CTAs
-      __syncthreads();
-      prefetch_op();
-      __syncthreads();
       const int Hl = op.i[0], hd = op.i[1], ctx_len = op.i[2], S = op.i[3], in_slots = op.i[5], in_stride = op.i[7];
       const float* qkv = reinterpret_cast<const float*>(op.p[0]);
       const float* cos2 = reinterpret_cast<const float*>(op.p[1]);
@@ -654,7 +731,8 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
       const int per = (((n + S - 1) / S) + 7) & ~7;
       float* raw = reinterpret_cast<float*>(x_s);          // q | k | v of the head, raw then rotated: 6 * 128 floats
       float* sc = raw + 6 * 128;                           // scores of this split's keys
-      float* pacc = sc + 2048;                             // [6][hd] partial value sums
+      float* pacc = sc + 2048;                             // [groups][hd] partial value sums
+      const int n_grp = min(kSThreads / hd, 12);
       for (int item = cta; item < Hl * S; item += G) {
         const int h = item / S, s = item - h * S;
         const int k0 = s * per, cnt = max(0, min(n, k0 + per) - k0);
@@ -708,22 +786,21 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
           sum += p;
         }
         sum = block_sum(sum, s16, tid);   // its barriers also publish the probabilities
-        // values: six groups of hd threads, group q takes keys j = q, q + 6, ...
+        // values: groups of hd threads, group q takes keys j = q, q + n_grp, ...
         const int grp = tid / hd, d = tid - grp * hd;
-        if (grp < 6) {
+        if (grp < n_grp) {
           float a = 0.f;
-          for (int j = grp; j < cnt; j += 6) {
+          for (int j = grp; j < cnt; j += n_grp) {
             const int key = k0 + j;
             const float v = key == (int)pos ? vn[d] : __ldg(vc + head_off + (size_t)key * hd + d);
             a += sc[j] * v;
           }
-          pacc[grp * hd + d] = a;
+          pacc[grp * 128 + d] = a;
         }
         __syncthreads();
         if (tid < hd) {
           float a = 0.f;
-#pragma unroll
-          for (int q = 0; q < 6; ++q) a += pacc[q * hd + tid];
+          for (int q = 0; q < n_grp; ++q) a += pacc[q * 128 + tid];
           part[(size_t)item * (hd + 2) + tid] = a;
         }
         if (tid == 0) {
@@ -733,9 +810,6 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
       }
     } else if (op.kind == NB_SOP_HEAD) {
       // ---- final norm + LM head rows of this CTA + soft-cap + the CTA's best candidate
-      __syncthreads();
-      prefetch_op();
-      const OpInfo& f = info[oi];
       const int C = op.i[1];
       float* xh = reinterpret_cast<float*>(x_s);
       const float4* w4 = reinterpret_cast<const float4*>(op.p[3]);
@@ -760,12 +834,15 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
       float* logits = reinterpret_cast<float*>(op.p[4]);
       float best = -FLT_MAX;
       int besti = 0x7fffffff;
+      const int row_bytes = C * 2, pieces = fi.bpr, row0 = fi.cta_a / fi.bpr;
       float acc = 0.f;
+      int row = use.op == oi ? div_bpr(fi, use.u) : 0, piece = use.op == oi ? use.u - row * pieces : 0;
       while (use.op == oi) {
-        const uint8_t* st = wait_chunk(ctx, use);
-        const int row = use.u / f.bpr, piece = use.u - row * f.bpr;
-        const int off = piece * f.ubytes;
-        const int bytes = min((int)f.ubytes, f.row_bytes - off);
+        cp_async_wait<kStages - 2>();
+        __syncwarp();
+        const uint8_t* st = ctx.ring + use.stage * kStageBytes;
+        const int off = piece * fi.ubytes;
+        const int bytes = min((int)fi.ubytes, row_bytes - off);
         for (int j = lane; j < bytes / 16; j += 32) {
           const uint4 r = *reinterpret_cast<const uint4*>(st + 16 * j);
           const float* xv = xh + (off >> 1) + 8 * j;
@@ -775,18 +852,17 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
                  __uint_as_float(r.z << 16) * x1.x + __uint_as_float(r.z & 0xFFFF0000u) * x1.y +
                  __uint_as_float(r.w << 16) * x1.z + __uint_as_float(r.w & 0xFFFF0000u) * x1.w;
         }
-        if (piece == f.bpr - 1) {
+        if (piece == pieces - 1) {
           const float v = cap * tanhf(warp_sum_f(acc) * inv / cap);
           acc = 0.f;
-          if (lane == 0) logits[row] = v;
-          const int gi = op.i[8] + row;      // index in the whole vocabulary
+          if (lane == 0) logits[row0 + row] = v;
+          const int gi = op.i[8] + row0 + row;      // index in the whole vocabulary
           if (v > best || (v == best && gi < besti)) { best = v; besti = gi; }
         }
-        use.u += 1;
-        ++use.count;
-        cursor_seek(ctx, use);
+        if (++piece == pieces) { piece = 0; ++row; }
+        cursor_step(ctx, use);
         __syncwarp();
-        fetch_next(ctx, fetch);
+        fetch_next<BITS>(ctx, fetch);
       }
       if (lane == 0) { s_best[warp] = best; s_besti[warp] = besti; }
       __syncthreads();
@@ -801,9 +877,6 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
       }
     } else if (op.kind == NB_SOP_REDUCE) {
       // ---- y = sum of a projection's partial slots (in slot order), converted to the output type
-      __syncthreads();
-      prefetch_op();
-      __syncthreads();
       const int N = op.i[0];
       for (int i = cta * kSThreads + tid; i < N; i += G * kSThreads) {
         float v = 0.f;
@@ -812,9 +885,6 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
       }
     } else if (op.kind == NB_SOP_ARGMAX) {
       // ---- the best of the CTAs' candidates (lowest index among equals) becomes the next token
-      __syncthreads();
-      prefetch_op();
-      __syncthreads();
       if (cta == 0 && warp == 0) {
         const float* cand = reinterpret_cast<const float*>(op.p[0]);
         float b = -FLT_MAX;
@@ -831,23 +901,17 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
           if (ob > b || (ob == b && obi < bi)) { b = ob; bi = obi; }
         }
         if (lane == 0) {
-          *reinterpret_cast<long long*>(op.p[1]) = (long long)bi;
+          *reinterpret_cast<long long*>(op.p[1]) = (long long)(bi == 0x7fffffff ? 0 : bi);
           if (op.p[2]) *reinterpret_cast<long long*>(op.p[2]) += 1;
         }
       }
     }
-
-    // ---- publish (only when somebody will wait for it): this CTA's results up to operation oi are complete
-    if (info[oi].flags & 1) {
-      __syncthreads();
-      if (tid == 0) {
-        __threadfence();
-        st_release_gpu_u32(flags + cta, seq);
-      }
-    }
-    NB_STRACE(oi, 3);
+    // ---- this CTA's results up to operation oi are complete
+    __syncthreads();
+    if (tid == 0) publish(oi);
   }
 
+  cp_async_wait<0>();
   // the next launch's sequence numbers start above this one's: written once every CTA is done
   wait_flags(flags, G, base + (uint32_t)n_ops, spin_limit, status, tid);
   if (cta == 0 && tid == 0) state[kMaxCtas] = base + (uint32_t)n_ops + 1u;
@@ -878,17 +942,18 @@ __global__ void __launch_bounds__(256) stream_pack_kernel(const uint8_t* __restr
   };
   constexpr int kBlkBytes = 16 * BITS;
   uint8_t* ub = out + u * F::kBytes;
-  uint32_t seq[2 * F::kW];
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int row = src_row(g + 8 * half);
     const bool valid = row < N;
+    // the lane's 32 indices (group t of the block) as packed words, spread to four selector words
     const uint32_t* src = reinterpret_cast<const uint32_t*>(packed + ((size_t)row * bpr + kb) * kBlkBytes) + F::kW * t;
+    uint32_t w[F::kW], U[4];
 #pragma unroll
-    for (int j = 0; j < F::kW; ++j) seq[half * F::kW + j] = valid ? src[j] : 0u;
+    for (int j = 0; j < F::kW; ++j) w[j] = valid ? src[j] : 0u;
+    group_selectors<BITS>(w, 0, U);
+    *reinterpret_cast<uint4*>(ub + half * 512 + lane * 16) = make_uint4(U[0], U[1], U[2], U[3]);
   }
-#pragma unroll
-  for (int j = 0; j < F::kW; ++j) *reinterpret_cast<uint2*>(ub + j * 256 + lane * 8) = make_uint2(seq[2 * j], seq[2 * j + 1]);
   if (lane < 16) {
     const int row = src_row(lane);
     const bool valid = row < N;
@@ -951,25 +1016,27 @@ static int check_op(const nb_stream_op& o, int index, int G, int* bits) {
     if (!(o.flags & NB_SOPF_REUSE_X) && !o.p[1]) return fail("null activation pointer");
     if ((uintptr_t)o.p[1] % 16) return fail("activations must be 16-byte aligned");
     if (o.pro < NB_SPRO_VEC || o.pro > NB_SPRO_ATTN_MERGE) return fail("unknown prologue");
-    if ((o.pro == NB_SPRO_EMBED_NORM || o.pro == NB_SPRO_ADD_NORM) && (K > kMaxC || !o.p[3])) return fail("norm prologue needs K <= 3072 and a weight");
-    if (o.pro == NB_SPRO_EMBED_NORM && !o.p[2]) return fail("embedding prologue needs a token pointer");
+    if ((o.pro == NB_SPRO_EMBED_NORM || o.pro == NB_SPRO_ADD_NORM) && (K > kMaxC || !o.p[3])) return fail("norm prologue needs K <= 2560 and a weight");
+    if (o.pro == NB_SPRO_EMBED_NORM && (!o.p[2] || o.i[13] < 1)) return fail("embedding prologue needs a token pointer and the table's row count");
     if (o.epi < NB_SEPI_STORE || o.epi > NB_SEPI_SWIGLU) return fail("unknown epilogue");
     if (o.epi != NB_SEPI_SLOTS && !(o.flags & NB_SOPF_ALIGN)) return fail("only the slot epilogue may split a row tile between CTAs");
     if (o.epi == NB_SEPI_SWIGLU && N % 16 != 0) return fail("SwiGLU epilogue needs N % 16 == 0");
-    if ((long long)((N + 15) / 16) * (K / kBlock) * (G + 1) >= (1ll << 31)) return fail("matrix too large for the 32-bit work split");
-    const OpGeom g = geom_of(o);
-    // local row tiles of a CTA must fit the reduction buffer, and the slots must cover every CTA of a row tile
-    int worst_rt = 0, worst_slots = 1;
+    if ((long long)((N + 15) / 16) * (K / kBlock) >= 65536) return fail("matrix too large for one launch (more than 65535 units)");
+    const OpGeom g = geom_of(o, b);
+    // a CTA's units of one operation must fit the partial-sum buffer, and the slots must cover every CTA of a row tile
+    int worst_slots = 1;
     for (int c = 0; c < G; ++c) {
       int ca, cb;
       cta_range(g, c, G, ca, cb);
-      if (cb > ca) worst_rt = std::max(worst_rt, (cb - 1) / g.bpr - ca / g.bpr + 1);
+      if (cb - ca > kRedUnits) return fail("too many units per CTA for the partial-sum buffer (N * K too large for one launch)");
+      if (cb > ca && (cb - 1) / g.bpr - ca / g.bpr + 1 > kMaxLocalTiles) return fail("too many row tiles per CTA");
+      if ((cb - ca + kSW - 1) / kSW > (kRedSegs - 1) * g.bpr && (cb - ca + kSW - 1) / kSW > 1)
+        return fail("a warp's run of units would touch too many row tiles (K too small for this N)");
     }
     if (!g.align)
       for (int rt = 0; rt < g.rt; ++rt)
         worst_slots = std::max(worst_slots, cta_of_unit((rt + 1) * g.bpr - 1, g.units, G) - cta_of_unit(rt * g.bpr, g.units, G) + 1);
-    if (worst_rt * kSW * 16 > kRedHalf) return fail("too many row tiles per CTA for the reduction buffer");
-    if (o.epi == NB_SEPI_SLOTS && (o.i[6] < worst_slots || o.i[8] < N)) return fail("too few output slots (see nb_stream_slots) or slot stride < N");
+    if (o.epi == NB_SEPI_SLOTS && (o.i[6] < worst_slots || o.i[6] > 16 || o.i[8] < N)) return fail("output slots: need nb_stream_slots(N, K, CTAs) <= slots <= 16 and slot stride >= N");
     *bits = b;
   } else if (o.kind == NB_SOP_ATTN) {
     const int Hl = o.i[0], hd = o.i[1], ctx = o.i[2], S = o.i[3];
@@ -977,7 +1044,8 @@ static int check_op(const nb_stream_op& o, int index, int G, int* bits) {
     if ((((ctx + S - 1) / S) + 7) > 2048) return fail("more than 2048 keys per attention split");
     for (int j = 0; j < 7; ++j) if (!o.p[j]) return fail("null pointer");
   } else if (o.kind == NB_SOP_HEAD) {
-    if (o.i[0] < 1 || o.i[1] < 8 || o.i[1] % 8 || o.i[1] > kMaxC) return fail("head needs C % 8 == 0, <= 3072");
+    if (o.i[0] < 1 || o.i[1] < 8 || o.i[1] % 8 || o.i[1] > kMaxC) return fail("head needs C % 8 == 0, <= 2560");
+    if (o.i[1] * 2 > 65535) return fail("head row too long");
     if (!o.p[0] || !o.p[3] || !o.p[4] || !o.p[5] || (uintptr_t)o.p[0] % 16) return fail("null or misaligned pointer");
   } else if (o.kind == NB_SOP_REDUCE) {
     if (!o.p[1] || !o.p[4] || o.i[0] < 1 || o.i[5] < 1 || o.i[7] < o.i[0]) return fail("null pointer or bad slot geometry");

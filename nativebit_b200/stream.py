@@ -19,7 +19,7 @@ SOP_GEMV, SOP_ATTN, SOP_HEAD, SOP_ARGMAX, SOP_REDUCE = 1, 2, 3, 4, 5
 SPRO_VEC, SPRO_EMBED_NORM, SPRO_ADD_NORM, SPRO_ATTN_MERGE = 0, 1, 2, 3
 SEPI_STORE, SEPI_SLOTS, SEPI_SWIGLU = 0, 1, 2
 SOPF_WAIT_PREV, SOPF_ALIGN, SOPF_REUSE_X = 1, 2, 4
-STATUS_WORD = 257            # uint32 index of the status word in the state buffer
+STATUS_WORD = 513            # uint32 index of the status word in the state buffer
 
 _DT = {torch.float32: NB_F32, torch.float16: NB_F16, torch.bfloat16: NB_BF16}
 
@@ -147,7 +147,7 @@ def build_decode_program(model, session) -> StreamProgram:
         w = sw[l]
         if l == 0:
             prog.add(_op(SOP_GEMV, 0, SPRO_EMBED_NORM, SEPI_SLOTS, p=(w["qkv"], model.embedding, session.token, blk.ln1, qkv_slots),
-                         i=(n_qkv, C, bits, 0, 0, 0, s_qkv, 0, n_qkv), f=(eps,)), w["qkv"], blk.ln1)
+                         i=(n_qkv, C, bits, 0, 0, 0, s_qkv, 0, n_qkv, 0, 0, 0, 0, model.embedding.shape[0]), f=(eps,)), w["qkv"], blk.ln1)
         else:
             prog.add(_op(SOP_GEMV, SOPF_WAIT_PREV, SPRO_ADD_NORM, SEPI_SLOTS, p=(w["qkv"], d_slots, None, blk.ln1, qkv_slots),
                          i=(n_qkv, C, bits, 0, 0, s_d, s_qkv, C, n_qkv), f=(eps,)), w["qkv"], blk.ln1)
