@@ -105,7 +105,11 @@ template <int BITS> struct UnitFmt {
   static constexpr int kBytes = kIdxBytes + 16 * kTabBytes; // 1280 at 2 and 3 bits, 1536 at 4: one ring stage
   static constexpr int kStages = kRingBytes / (kSW * kBytes) < 16 ? kRingBytes / (kSW * kBytes) : 16;   // per warp: 6, 6, 5 with 16 warps
   // units a warp works on per loop iteration (one wait, one round of bookkeeping for all of them)
+#ifdef NB_STREAM_BATCH
+  static constexpr int kBatch = NB_STREAM_BATCH < kStages ? NB_STREAM_BATCH : kStages - 1;
+#else
   static constexpr int kBatch = kStages >= 6 ? 4 : (kStages >= 4 ? 2 : 1);
+#endif
 };
 
 __host__ __device__ inline int unit_bytes(int bits) { return bits == 3 ? UnitFmt<3>::kBytes : bits == 2 ? UnitFmt<2>::kBytes : UnitFmt<4>::kBytes; }
@@ -352,6 +356,59 @@ __device__ __forceinline__ void unit_mma(const uint8_t* ub, const uint8_t* x_s, 
   }
 }
 
+// Two units at once, their steps interleaved: two independent instruction streams per warp hide the
+// latencies of the shared-memory loads, the byte permutes and the tensor-core MMAs (a warp's own stream is
+// one long dependency chain; four warps per scheduler do not cover it).
+template <int BITS, int XS>
+__device__ __forceinline__ void unit_mma2(const uint8_t* ub0, const uint8_t* ub1, const uint8_t* x_s, int kb0, int kb1, int lane,
+                                          float (&c0)[2][4], float (&c1)[2][4]) {
+  using F = UnitFmt<BITS>;
+  constexpr int kT = BITS == 4 ? 8 : 4;
+  const int g = lane >> 2, t = lane & 3;
+  const uint8_t* ubs[2] = {ub0, ub1};
+  uint32_t UA[2][4], UB[2][4], TA[2][kT], TB[2][kT];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const uint4 a = *reinterpret_cast<const uint4*>(ubs[u] + lane * 16);
+    const uint4 b = *reinterpret_cast<const uint4*>(ubs[u] + 512 + lane * 16);
+    UA[u][0] = a.x; UA[u][1] = a.y; UA[u][2] = a.z; UA[u][3] = a.w;
+    UB[u][0] = b.x; UB[u][1] = b.y; UB[u][2] = b.z; UB[u][3] = b.w;
+    const uint8_t* tab = ubs[u] + F::kIdxBytes;
+#pragma unroll
+    for (int j = 0; j < F::kTabBytes / 16; ++j) {
+      const uint4 ta = *reinterpret_cast<const uint4*>(tab + g * F::kTabBytes + 16 * j);
+      const uint4 tb = *reinterpret_cast<const uint4*>(tab + (g + 8) * F::kTabBytes + 16 * j);
+      TA[u][4 * j] = ta.x; TA[u][4 * j + 1] = ta.y; TA[u][4 * j + 2] = ta.z; TA[u][4 * j + 3] = ta.w;
+      TB[u][4 * j] = tb.x; TB[u][4 * j + 1] = tb.y; TB[u][4 * j + 2] = tb.z; TB[u][4 * j + 3] = tb.w;
+    }
+  }
+  const uint8_t* xseg[2] = {x_s + (kb0 * 4 + t) * kXSegBytes, x_s + (kb1 * 4 + t) * kXSegBytes};
+#pragma unroll
+  for (int uu = 0; uu < 4; ++uu) {
+    uint4 xq[2][XS];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int xs = 0; xs < XS; ++xs) xq[u][xs] = *reinterpret_cast<const uint4*>(xseg[u] + xs * kXTermBytes + uu * 16);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t a0[2], a1[2], a2[2], a3[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const uint32_t sa = h ? (UA[u][uu] >> 16) : UA[u][uu];
+        const uint32_t sb = h ? (UB[u][uu] >> 16) : UB[u][uu];
+        lookup4<BITS>(sa, TA[u], a0[u], a2[u]);
+        lookup4<BITS>(sb, TB[u], a1[u], a3[u]);
+      }
+#pragma unroll
+      for (int xs = 0; xs < XS; ++xs) {
+        mma_16816(c0[h], a0[0], a1[0], a2[0], a3[0], h ? xq[0][xs].z : xq[0][xs].x, h ? xq[0][xs].w : xq[0][xs].y);
+        mma_16816(c1[h], a0[1], a1[1], a2[1], a3[1], h ? xq[1][xs].z : xq[1][xs].x, h ? xq[1][xs].w : xq[1][xs].y);
+      }
+    }
+  }
+}
+
 // Warp that owns local unit v when a CTA's n units are split by warp_part() (packed matrices).
 __device__ __forceinline__ int warp_of_unit(int v, int n) { return part_of(v, n, kSW); }
 
@@ -373,6 +430,7 @@ __device__ __forceinline__ void wait_flags(const uint32_t* flags, int G, uint32_
 
 #ifdef NB_STREAM_TRACE
 __device__ unsigned long long nb_stream_trace_buf[kMaxOps * 8];
+__device__ unsigned long long nb_stream_trace_warp_end[kMaxCtas * kSW];
 #define NB_STRACE(op, i)                                                     \
   do {                                                                       \
     if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {                        \
@@ -475,6 +533,7 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
     const OpInfo& fi = info[oi];
     const uint32_t seq = base + (uint32_t)oi + 1u;     // published after this operation
     const bool waits = oi > 0 && (op.flags & NB_SOPF_WAIT_PREV);
+    if (warp == 0) NB_STRACE(oi, 4);
 
     if (op.kind == NB_SOP_GEMV) {
       const int N = op.i[0], K = op.i[1];
@@ -614,15 +673,22 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
             const int nb = min(kBatch, seg_len - done);
             cp_async_wait<kStages - 1 - kBatch>();       // this lane's copies of the oldest kBatch units have landed ...
             __syncwarp();                                // ... and so have the other lanes'
+            auto stage_of = [&](int b2) {
+              int sidx = use.stage + b2;
+              if (sidx >= kStages) sidx -= kStages;
+              return ctx.ring + sidx * kStageBytes;
+            };
+            // units in pairs (interleaved), then a single one if the count is odd
 #pragma unroll
-            for (int b2 = 0; b2 < kBatch; ++b2) {
-              if (b2 < nb) {
-                int sidx = use.stage + b2;
-                if (sidx >= kStages) sidx -= kStages;
-                const uint8_t* st = ctx.ring + sidx * kStageBytes;
-                if (xs_terms == 2) unit_mma<BITS, 2>(st, x_s, kb + b2, lane, acc[b2 & 1]);
-                else unit_mma<BITS, 1>(st, x_s, kb + b2, lane, acc[b2 & 1]);
+            for (int b2 = 0; b2 + 1 < kBatch; b2 += 2) {
+              if (b2 + 1 < nb) {
+                if (xs_terms == 2) unit_mma2<BITS, 2>(stage_of(b2), stage_of(b2 + 1), x_s, kb + b2, kb + b2 + 1, lane, acc[0], acc[1]);
+                else unit_mma2<BITS, 1>(stage_of(b2), stage_of(b2 + 1), x_s, kb + b2, kb + b2 + 1, lane, acc[0], acc[1]);
               }
+            }
+            if (nb & 1) {
+              if (xs_terms == 2) unit_mma<BITS, 2>(stage_of(nb - 1), x_s, kb + nb - 1, lane, acc[0]);
+              else unit_mma<BITS, 1>(stage_of(nb - 1), x_s, kb + nb - 1, lane, acc[0]);
             }
             use.u += nb;
             use.stage += nb;
@@ -709,6 +775,7 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
         (void)v0;
         cursor_seek(ctx, use);
       }
+      if (warp == 0) NB_STRACE(oi, 6);
       continue;
     }
 
@@ -909,9 +976,17 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
     // ---- this CTA's results up to operation oi are complete
     __syncthreads();
     if (tid == 0) publish(oi);
+    if (warp == 0) NB_STRACE(oi, 5);
   }
 
   cp_async_wait<0>();
+#ifdef NB_STREAM_TRACE
+  if ((threadIdx.x & 31) == 0) {   // per warp of every CTA: when it ran out of work
+    unsigned long long t_;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_));
+    nb_stream_trace_warp_end[blockIdx.x * kSW + (threadIdx.x >> 5)] = t_;
+  }
+#endif
   // the next launch's sequence numbers start above this one's: written once every CTA is done
   wait_flags(flags, G, base + (uint32_t)n_ops, spin_limit, status, tid);
   if (cta == 0 && tid == 0) state[kMaxCtas] = base + (uint32_t)n_ops + 1u;
@@ -920,6 +995,9 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
 #ifdef NB_STREAM_TRACE
 extern "C" int nb_stream_trace_read(unsigned long long* out) {
   return (int)cudaMemcpyFromSymbol(out, nb_stream_trace_buf, sizeof(nb_stream_trace_buf));
+}
+extern "C" int nb_stream_trace_read_ends(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, nb_stream_trace_warp_end, sizeof(nb_stream_trace_warp_end));
 }
 #endif
 

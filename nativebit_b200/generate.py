@@ -279,10 +279,14 @@ class DecodeSession:
                  batch_gemm: bool = False, stream: bool | None = None):
         self.model, self.B = model, batch_size
         self.fused = fused
-        # one sequence on one GPU: the whole step is ONE launch of the persistent kernel (stream.py);
-        # other cases run the step as a chain of fused kernels
-        from . import stream as _stream
-        self.stream_step = fused and _stream.stream_supported(model, batch_size) if stream is None else bool(stream)
+        # stream=True (one sequence on one GPU): the whole step is ONE launch of the persistent kernel
+        # (stream.py).  The default is the chain of fused kernels, which measures faster: inside one launch
+        # every operation pays a device-wide flag wait and the staging of its activations in full.
+        self.stream_step = bool(stream)
+        if self.stream_step:
+            from . import stream as _stream
+            if not _stream.stream_supported(model, batch_size):
+                raise RuntimeError("the one-launch decode step needs batch 1, one rank, bf16 embeddings and block-128 codebooks")
         self.prog = None
         self.batch_gemm = batch_gemm          # batches >= 32: packed linears on the tensor-core GEMM (bf16 operands)
         dev = model.embedding.device
