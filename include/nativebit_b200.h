@@ -123,6 +123,20 @@ int nb_gemm_prefill(const void* x, int x_dtype, int M, const uint8_t* packed, co
                     int block_size, int N, int K, void* y, int y_dtype, void* workspace, size_t workspace_bytes,
                     void* stream);
 
+/* ---- prefill GEMM with the dequantisation fused into the tensor-core kernel: producer warps turn the
+ * packed weights into fp16 tiles in shared memory, tcgen05.mma consumes them; no dense copy of W is ever
+ * written to global memory.  Same contract as nb_gemm_prefill (the reference's M > 1 path,
+ * inference/triton_kernel.py:258-275; tile-wise dequantise-and-contract as in
+ * nativebit_jax/packed_kernel.py:135-178; exact fp16 weights, fp32 accumulation) for any M >= 1, but the
+ * weights are given in the stream layout (nb_stream_pack with row_mode 0) instead of the pack.py bytes.
+ * x: (M, K) NB_F16 or NB_BF16 (bf16 is converted to fp16 into the workspace first), 16-byte aligned;
+ * K % 128 == 0; y: (M, N) NB_BF16 or NB_F32.  workspace: nb_prefill_fused_workspace_bytes(M, K) bytes,
+ * 256-byte aligned; its first 256 bytes carry a status word (zero before the first call; NB_ERR_TIMEOUT
+ * if a bounded wait inside the kernel ran out). */
+size_t nb_prefill_fused_workspace_bytes(int M, int K);
+int nb_gemm_prefill_fused(const void* x, int x_dtype, int M, const uint8_t* w_stream, int bits, int N, int K, void* y,
+                          int y_dtype, void* workspace, size_t workspace_bytes, void* stream);
+
 /* The tensor-core kernel alone: y (M, N) = x (M, K) . w (N, K)^T with x and w bf16 row-major
  * (16-byte aligned, K % 64 == 0), y NB_BF16 or NB_F32, fp32 accumulation in tensor memory.
  * `status` is a device int (zero before the first call) or NULL.  No counterpart in the

@@ -95,9 +95,11 @@ constexpr int kStreamSmem = kOffDst + 256;
 static_assert(sizeof(StreamOp) == 160, "nb_stream_op layout");
 static_assert(kStreamSmem <= 224 * 1024, "shared memory budget");
 
-// A unit in the stream layout: the 32 lanes' selector words (eight 4-bit selectors per word, ready for the
-// byte-permute lookups: the 3- and 2-bit fields are spread to nibbles when the copy is built, so the
-// kernel spends no instructions on it), then the 16 rows' lookup tables.
+// A unit in the stream layout: the 32 lanes' selector words, then the 16 rows' lookup tables.  Lane
+// (g, t) owns weights 32t .. 32t+31 of the block in rows g and g+8: four words per row, word j = the
+// indices of positions 32t + 8j .. + 7, one per nibble in position order, ready for the byte-permute
+// lookups (the 3- and 2-bit fields are spread to nibbles when the copy is built, so the kernels spend
+// no instructions on it, and activations are used in their natural order).
 template <int BITS> struct UnitFmt {
   static constexpr int kW = Fmt<BITS>::kWords / 4;          // packed words of one lane's 32 indices in the source layout
   static constexpr int kIdxBytes = 1024;                    // 32 lanes x 2 rows x 4 selector words
@@ -217,23 +219,20 @@ __device__ __forceinline__ float block_max(float v, float* s16, int tid) {
   return t;
 }
 
-// Four consecutive activations (positions 4*i4 .. 4*i4+3 of the row) -> fp16 hi (+ lo) terms in slot order.
+// Four consecutive activations (positions 4*i4 .. 4*i4+3 of the row) -> fp16 hi (+ lo) terms.  The staged
+// row keeps the natural order; every 32 activations (one lane's share of a k-block) start a new segment of
+// kXSegBytes, which spreads the four lanes t of a warp over different banks.
 template <int XS>
-__device__ __forceinline__ void stage4(uint8_t* x_s, const uint16_t* dst_off, int i4, float u0, float u1, float u2, float u3) {
-  const int kb = i4 >> 5;                       // 32 groups of four per k-block
-  const uint2 o2 = *reinterpret_cast<const uint2*>(dst_off + ((i4 & 31) << 2));
-  uint16_t* blk = reinterpret_cast<uint16_t*>(x_s + kb * 4 * kXSegBytes);
+__device__ __forceinline__ void stage4(uint8_t* x_s, int i4, float u0, float u1, float u2, float u3) {
+  uint8_t* dst = x_s + (i4 >> 3) * kXSegBytes + (i4 & 7) * 8;      // 8 groups of four per segment
   const uint32_t h01 = f32x2_to_f16x2_sat(u0, u1), h23 = f32x2_to_f16x2_sat(u2, u3);
-  blk[o2.x & 0xFFFFu] = (uint16_t)(h01 & 0xFFFFu); blk[o2.x >> 16] = (uint16_t)(h01 >> 16);
-  blk[o2.y & 0xFFFFu] = (uint16_t)(h23 & 0xFFFFu); blk[o2.y >> 16] = (uint16_t)(h23 >> 16);
+  *reinterpret_cast<uint2*>(dst) = make_uint2(h01, h23);
   if (XS == 2) {
     const float2 r01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
     const float2 r23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
     const uint32_t l01 = f32x2_to_f16x2_sat(fminf(fmaxf(u0, -65504.f), 65504.f) - r01.x, fminf(fmaxf(u1, -65504.f), 65504.f) - r01.y);
     const uint32_t l23 = f32x2_to_f16x2_sat(fminf(fmaxf(u2, -65504.f), 65504.f) - r23.x, fminf(fmaxf(u3, -65504.f), 65504.f) - r23.y);
-    uint16_t* lo = blk + kXTermBytes / 2;
-    lo[o2.x & 0xFFFFu] = (uint16_t)(l01 & 0xFFFFu); lo[o2.x >> 16] = (uint16_t)(l01 >> 16);
-    lo[o2.y & 0xFFFFu] = (uint16_t)(l23 & 0xFFFFu); lo[o2.y >> 16] = (uint16_t)(l23 >> 16);
+    *reinterpret_cast<uint2*>(dst + kXTermBytes) = make_uint2(l01, l23);
   }
 }
 
@@ -453,7 +452,6 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
   uint8_t* x_s = smem + kOffX;
   float* h_s = reinterpret_cast<float*>(smem + kOffH);
   float* red_base = reinterpret_cast<float*>(smem + kOffRed);
-  uint16_t* dst_off = reinterpret_cast<uint16_t*>(smem + kOffDst);
   __shared__ float s16[kSW];
   __shared__ float s_scale;
   __shared__ float s_best[kSW];
@@ -495,11 +493,6 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
   if (tid < kRedBufs * kMaxLocalTiles) (&s_tile_cnt[0][0])[tid] = 0;
   if (tid < kRedBufs) s_tiles_done[tid] = 0;
   if (tid == 0) s_finished = 0;
-  if (tid < kBlock) {
-    // position inside a 128-weight block -> offset (in halves) of its activation inside the block's four segments
-    const int slot = tid, pos = slot_to_position<BITS>(slot);
-    dst_off[pos] = (uint16_t)((slot >> 5) * (kXSegBytes / 2) + (slot & 31));
-  }
   __syncthreads();
 
   // every warp's run of every operation: equal shares of the CTA's units, handed out in an order that
@@ -562,8 +555,8 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
                 v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
               }
             }
-            if (dt == NB_F32) stage4<2>(x_s, dst_off, i4, v[0], v[1], v[2], v[3]);
-            else stage4<1>(x_s, dst_off, i4, v[0], v[1], v[2], v[3]);
+            if (dt == NB_F32) stage4<2>(x_s, i4, v[0], v[1], v[2], v[3]);
+            else stage4<1>(x_s, i4, v[0], v[1], v[2], v[3]);
           }
           if (tid == 0) s_scale = 1.f;
         } else if (op.pro == NB_SPRO_EMBED_NORM || op.pro == NB_SPRO_ADD_NORM) {
@@ -591,7 +584,7 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
             reinterpret_cast<float4*>(h_s)[i4] = h;
             ss += h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
             const float4 w = __ldg(w4 + i4);
-            stage4<2>(x_s, dst_off, i4, h.x * w.x, h.y * w.y, h.z * w.z, h.w * w.w);
+            stage4<2>(x_s, i4, h.x * w.x, h.y * w.y, h.z * w.z, h.w * w.w);
           }
           const float tot = block_sum(ss, s16, tid);
           if (tid == 0) s_scale = 1.0f / sqrtf(tot / (float)K + op.f[0]);
@@ -621,7 +614,7 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_kernel(const StreamOp* __
               }
               v[e] = r;
             }
-            stage4<2>(x_s, dst_off, i4, v[0], v[1], v[2], v[3]);
+            stage4<2>(x_s, i4, v[0], v[1], v[2], v[3]);
           }
           if (tid == 0) s_scale = 1.f;
         }
@@ -1026,11 +1019,19 @@ __global__ void __launch_bounds__(256) stream_pack_kernel(const uint8_t* __restr
     const bool valid = row < N;
     // the lane's 32 indices (group t of the block) as packed words, spread to four selector words
     const uint32_t* src = reinterpret_cast<const uint32_t*>(packed + ((size_t)row * bpr + kb) * kBlkBytes) + F::kW * t;
-    uint32_t w[F::kW], U[4];
+    uint32_t w[F::kW], U[4], P[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
     for (int j = 0; j < F::kW; ++j) w[j] = valid ? src[j] : 0u;
     group_selectors<BITS>(w, 0, U);
-    *reinterpret_cast<uint4*>(ub + half * 512 + lane * 16) = make_uint4(U[0], U[1], U[2], U[3]);
+    // nibble k of selector word u holds the index at position slot_position(0, u, k) of the group: put it in position order
+#pragma unroll
+    for (int uu = 0; uu < 4; ++uu)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int pos = slot_position<BITS>(0, uu, k);
+        P[pos >> 3] |= ((U[uu] >> (4 * k)) & 0xFu) << (4 * (pos & 7));
+      }
+    *reinterpret_cast<uint4*>(ub + half * 512 + lane * 16) = make_uint4(P[0], P[1], P[2], P[3]);
   }
   if (lane < 16) {
     const int row = src_row(lane);

@@ -288,7 +288,7 @@ class DecodeSession:
             if not _stream.stream_supported(model, batch_size):
                 raise RuntimeError("the one-launch decode step needs batch 1, one rank, bf16 embeddings and block-128 codebooks")
         self.prog = None
-        self.batch_gemm = batch_gemm          # batches >= 32: packed linears on the tensor-core GEMM (bf16 operands)
+        self.batch_gemm = batch_gemm          # kept for compatibility: batches above 16 rows always take the tensor-core kernel
         dev = model.embedding.device
         self.dev = dev
         self.caches = init_kv_cache(model, batch_size, dev)
@@ -316,11 +316,11 @@ class DecodeSession:
             self.bd = torch.zeros(B, cfg.n_embd, **f32)
 
     def _linear_into(self, lin: PackedLinear, x: torch.Tensor, out: torch.Tensor) -> None:
-        if self.batch_gemm and x.shape[0] >= 32 and lin.in_features % 64 == 0:
-            # large batches, opt-in: dequantise once and multiply on the tcgen05 tensor cores (fp16 operands,
-            # fp32 accumulation) instead of unpacking the weights once per 16 rows
-            ops.gemm_prefill(x, lin.packed_indices, lin.codebook, lin.bits, lin.block_size,
-                             lin.out_features, lin.in_features, out=out)
+        """out = lin(x) for a batch of rows: up to 16 through the fused GEMV, more through the tensor-core
+        kernel that dequantises inside (one pass over the weights, exact fp16 weights, fp32 activations as
+        two fp16 terms)."""
+        if x.shape[0] > 16 and lin.in_features % 128 == 0:
+            ops.gemm_prefill_fused(x, lin.stream_weight(), lin.bits, lin.out_features, lin.in_features, out=out)
             return
         for r in range(0, x.shape[0], 16):
             ops.gemv(x[r:r + 16], lin.packed_indices, lin.codebook, lin.bits, lin.block_size, lin.out_features,

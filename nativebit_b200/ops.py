@@ -276,6 +276,50 @@ def gemm_prefill(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, 
     return out
 
 
+def gemm_prefill_fused(x: torch.Tensor, w_stream: torch.Tensor, bits: int, n: int, k: int,
+                       out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y (M, n) = x (M, k) @ W.T with the dequantisation fused into the tcgen05 kernel; w_stream is the
+    stream-layout copy of the packed weight (stream.stream_pack).  x fp16 or bf16; fp32 activations are
+    carried as the sum of two fp16 terms stacked into one (2M, k) operand (as in gemm_prefill)."""
+    _need_cuda(x, w_stream)
+    if x.dim() != 2 or x.shape[1] != k:
+        raise RuntimeError(f"x must be an (M, {k}) tensor; got {tuple(x.shape)}")
+    if x.dtype == torch.float32:
+        xc = x.clamp(-65504.0, 65504.0)
+        hi = xc.half()
+        lo = (xc - hi.float()).half()
+        m = x.shape[0]
+        y2 = gemm_prefill_fused(torch.cat((hi, lo)), w_stream, bits, n, k, out_dtype=torch.float32)
+        y = y2[:m].add_(y2[m:])
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y if out_dtype in (torch.float32, None) else y.to(out_dtype)
+    if x.dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError(f"unsupported activation dtype {x.dtype}")
+    if out_dtype is None:
+        out_dtype = out.dtype if out is not None else x.dtype
+    if out is None and out_dtype == torch.float16:     # the kernel writes bf16 or fp32
+        return gemm_prefill_fused(x, w_stream, bits, n, k, out_dtype=torch.float32).half()
+    m = x.shape[0]
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=x.device)
+    l = _lib.lib()
+    with torch.cuda.device(x.device):
+        need = int(l.nb_prefill_fused_workspace_bytes(m, k))
+        ws = prefill_workspace(x.device, need)
+        _lib.check(l.nb_gemm_prefill_fused(x.data_ptr(), _DTYPE[x.dtype], m, w_stream.data_ptr(), bits, n, k, out.data_ptr(),
+                                           _DTYPE[out.dtype], ws.data_ptr(), ws.numel(), _stream()), "nb_gemm_prefill_fused")
+    return out
+
+
+def prefill_status(device) -> int:
+    """Status word of the prefill workspace of the current stream (0, or NB_ERR_TIMEOUT); synchronises."""
+    key = (torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device(), _stream())
+    ws = _prefill_ws.get(key)
+    return 0 if ws is None else int(ws[:4].view(torch.int32).item())
+
+
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """y = x @ w.T for bf16 x (M, K) and w (N, K) with the hand-written tcgen05 kernel."""
     _need_cuda(x, w)

@@ -87,20 +87,22 @@ class PackedLinear(torch.nn.Module):
             y = self._forward_many(x_flat)
         return y.reshape(*shape[:-1], self.out_features)
 
+    def stream_weight(self):
+        """Tile-major copy of the packed weight for the fused tensor-core kernel and the persistent
+        kernel (built on first use, kept with the module)."""
+        w = getattr(self, "_wstream", None)
+        if w is None:
+            from .stream import stream_pack
+            w = self._wstream = stream_pack(self.packed_indices, self.codebook, self.bits, self.out_features, self.in_features)
+        return w
+
     def _forward_many(self, x_flat):
-        """M > 16 rows."""
-        m = x_flat.shape[0]
-        if m <= 4 * GEMV_MAX_M:
-            y = torch.empty(m, self.out_features, dtype=x_flat.dtype, device=x_flat.device)
-            for r in range(0, m, GEMV_MAX_M):
-                ops.gemv(x_flat[r:r + GEMV_MAX_M], self.packed_indices, self.codebook, self.bits, self.block_size,
-                         self.out_features, self.in_features, out=y[r:r + GEMV_MAX_M])
-            return y
-        if self.in_features % 64 == 0 and self.bits in (2, 3, 4):
-            # prefill: the tcgen05 GEMM with exact fp16 weights and 16-bit activations (bf16 and fp16 as
-            # given, fp32 carried as fp16), fp32 accumulation, result in x's dtype
-            return ops.gemm_prefill(x_flat, self.packed_indices, self.codebook, self.bits, self.block_size,
-                                    self.out_features, self.in_features, out_dtype=x_flat.dtype)
+        """M > 16 rows: one pass over the weights, dequantised inside the tcgen05 kernel (exact fp16 weights;
+        bf16 and fp16 activations as given, fp32 carried as two fp16 terms; fp32 accumulation; result in
+        x's dtype)."""
+        if self.in_features % BS == 0 and self.bits in (2, 3, 4):
+            return ops.gemm_prefill_fused(x_flat, self.stream_weight(), self.bits, self.out_features, self.in_features,
+                                          out_dtype=x_flat.dtype)
         wdt = x_flat.dtype if x_flat.dtype in (torch.float16, torch.bfloat16) else torch.float32
         w = ops.dequant(self.packed_indices, self.codebook, self.bits, self.block_size,
                         (self.out_features, self.in_features), dtype=wdt)

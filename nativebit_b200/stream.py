@@ -175,10 +175,9 @@ def stream_weights(model) -> list[dict]:
         return cached
     out = []
     for blk in model.blocks:
-        d = {}
-        for name, mode in (("qkv", 0), ("out_proj", 0), ("gate_up", 1), ("down", 0)):
-            lin = getattr(blk, name)
-            d[name] = stream_pack(lin.packed_indices, lin.codebook, lin.bits, lin.out_features, lin.in_features, mode)
+        d = {name: getattr(blk, name).stream_weight() for name in ("qkv", "out_proj", "down")}   # shared with the prefill kernel
+        lin = blk.gate_up
+        d["gate_up"] = stream_pack(lin.packed_indices, lin.codebook, lin.bits, lin.out_features, lin.in_features, 1)
         out.append(d)
     torch.cuda.synchronize(model.embedding.device)
     model._stream_weights = out

@@ -60,3 +60,30 @@ def test_packed_linear_uses_tensor_core_path_for_long_inputs(built_lib):
     assert y.dtype == torch.bfloat16 and y.shape == (m, n)
     ref = o.packed_linear_forward(x.float().cpu().numpy(), packed, cb.astype(np.float32), n, k, 3, acc_dtype=np.float64)
     assert np.abs(y.double().cpu().numpy() - ref).max() <= 2.0 ** -8 * np.abs(ref).max()     # bf16 output: half an ulp
+
+
+@pytest.mark.parametrize("bits,m,n,k", [(3, 128, 256, 384), (3, 300, 640, 1280), (2, 256, 256, 512), (4, 130, 200, 256), (3, 17, 1000, 640),
+                                        (3, 64, 2560, 2560), (3, 1, 128, 128), (3, 2048, 6912, 2560), (3, 2048, 2560, 6912)])
+@pytest.mark.parametrize("xdt", [torch.bfloat16, torch.float16, torch.float32])
+def test_fused_dequant_gemm(built_lib, bits, m, n, k, xdt):
+    """The kernel that dequantises inside the tensor-core pipeline, against the fp64 product with the
+    reference's dense weights: ragged M and N, every packed format, all activation types."""
+    from nativebit_b200 import ops, stream as S
+    dev = _dev()
+    if xdt != torch.bfloat16 and m == 2048 and k == 6912:
+        pytest.skip("one activation type is enough at the largest shape")
+    packed, cb, _ = o.make_packed_linear(n, k, bits, seed=m + 1)
+    x = o.make_activation(m, k, seed=m)                                  # bf16-representable
+    if xdt == torch.float32:
+        x = (x.astype(np.float64) * (1.0 + 1e-4 * np.arange(k))).astype(np.float32)   # needs both fp16 terms
+    w = S.stream_pack(torch.from_numpy(packed).to(dev), torch.from_numpy(cb).to(dev), bits, n, k)
+    xt = torch.from_numpy(x).to(dev).to(xdt)
+    y = ops.gemm_prefill_fused(xt, w, bits, n, k, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert ops.prefill_status(dev) == 0
+    W = torch.from_numpy(o.dequant_packed(packed, cb.astype(np.float32), n, k, bits)).to(dev)
+    ref = xt.double() @ W.double().T
+    assert (y.double() - ref).abs().max() <= 2e-5 * ref.abs().max()
+    yb = ops.gemm_prefill_fused(xt, w, bits, n, k, out_dtype=torch.bfloat16) if xdt != torch.float32 else None
+    if yb is not None:
+        assert (yb.double() - ref).abs().max() <= 2.0 ** -8 * ref.abs().max()     # bf16 output: half an ulp
