@@ -6,12 +6,16 @@
 Workload (one "step"): the FFN decode matvecs of the 2.2B configuration — per layer gate and
 up (6912 x 2560) and down (2560 x 6912), 3-bit indices, block 128, fp16 K=8 codebooks, bf16
 activations at batch M — over 26 layers of distinct synthetic weights (691 MB, larger than L2, so
-every launch streams its weights from HBM).  The 78 launches of a step are replayed from one
-CUDA graph.  Metric: achieved HBM GB/s = algorithmic bytes / time.
+every matrix streams from HBM).  At batch 1 the 78 matvecs of a step are ONE launch of the
+persistent multi-matrix kernel (nativebit_b200.MatvecGroup); at larger batches, and for the
+per-layer all-reduce chain reported beside it, one CUDA graph of 78 single-matrix launches.
+Metric: achieved HBM GB/s = algorithmic bytes / time.
 
-With N > 1 ranks (torchrun) the same stack is tensor-parallel: gate/up split by rows, down by
-input blocks, one NCCL all-reduce of the down output per layer; `value` is the whole job's
-algorithmic bytes over the slowest rank's time ("strong" scaling: total work fixed).
+With N > 1 ranks (torchrun) the same stack is tensor-parallel: every rank generates the same global
+weights and keeps its shard (gate/up rows, down input blocks); the partial down outputs of all
+layers are summed across ranks after the launch.  `value` is the whole job's algorithmic bytes over
+the slowest rank's time ("strong" scaling: total work fixed).  Every N > 1 run checks its summed
+outputs against the unsharded matvecs computed on the same GPU and exits non-zero on a mismatch.
 
 `--impl reference` times the reference's CPU PyTorch path (restated in oracle/nb_oracle.py) on
 the host cores over a bounded sample of the same workload.
@@ -36,6 +40,8 @@ METRIC, UNIT = "dequant_matvec_hbm_gbs", "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one 6912 x 2560 batch-1 launch, from one ncu capture
 # (algorithmic bytes: 8 866 304)
 NCU_TRAFFIC_B1 = 8912128
+# the same sum for one launch of the persistent kernel over a step's 78 matrices (see roofline.traffic_source)
+NCU_TRAFFIC_STEP = None
 
 
 def alg_bytes(m, n, k, bits=BITS):
@@ -189,6 +195,9 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------- GPU arm
+N_BLOCKS, MIN_TIMED_S = 20, 0.5
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -203,19 +212,32 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     m = args.batch
+    use_group = m == 1 and not args.chain          # one launch of the persistent kernel per step
 
-    # ---- weights: this rank's shard of every layer
+    # ---- weights: every rank generates the same global matrices (seed 10 * layer + j) and keeps its shard
     ch0, ch_n = tp.ffn_shard_plan(FFN, world, rank)            # hidden channels of this rank
     shapes = [("gate", ch_n, HIDDEN), ("up", ch_n, HIDDEN), ("down", HIDDEN, ch_n)]
-    layers = []
+    check_layers = (0, LAYERS - 1) if world > 1 else ()
+    layers, full_layers = [], {}
     for l in range(LAYERS):
-        mods = {}
-        for j, (name, n, k) in enumerate(shapes):
-            p, c = synthetic.synthetic_packed(n, k, BITS, seed=1000 * rank + 10 * l + j, device=dev)
-            mods[name] = nbt.PackedLinear(p, c, n, k, bits=BITS)
+        mods, full = {}, {}
+        for j, name in enumerate(("gate", "up", "down")):
+            n, k = (FFN, HIDDEN) if name != "down" else (HIDDEN, FFN)
+            p, c = synthetic.synthetic_packed(n, k, BITS, seed=10 * l + j, device=dev)
+            if l in check_layers:
+                full[name] = (p, c)
+            if world > 1:
+                if name != "down":
+                    p, c = tp.slice_rows(p, c, n, k, BITS, ch0, ch_n, BLOCK)
+                else:
+                    p, c = tp.slice_cols(p, c, n, k, BITS, ch0 // BLOCK, ch_n // BLOCK, BLOCK)
+            mods[name] = nbt.PackedLinear(p, c, *(((ch_n, HIDDEN) if name != "down" else (HIDDEN, ch_n))), bits=BITS)
         layers.append(mods)
+        if full:
+            full_layers[l] = full
     x = synthetic.synthetic_activation(m, HIDDEN, 1, dev)
-    h = synthetic.synthetic_activation(m, ch_n, 2, dev)
+    h_full = synthetic.synthetic_activation(m, FFN, 2, dev)
+    h = h_full[:, ch0:ch0 + ch_n].contiguous()
     y_gate = torch.empty(LAYERS, m, ch_n, dtype=torch.bfloat16, device=dev)
     y_up = torch.empty_like(y_gate)
     # with more than one rank the partial down outputs are summed in fp32
@@ -224,7 +246,7 @@ def run_ours(args):
     oneshot = None
     if world > 1 and args.allreduce in ("oneshot", "fused"):
         from nativebit_b200.comm import OneShotAllReduce
-        oneshot = OneShotAllReduce(m * HIDDEN, dev)
+        oneshot = OneShotAllReduce(LAYERS * m * HIDDEN, dev)
 
     def all_reduce(t):
         if oneshot is not None:
@@ -232,8 +254,6 @@ def run_ours(args):
         else:
             dist.all_reduce(t)
 
-    # gate and up read the same x and are independent: they run on two streams, as in the model;
-    # down follows both.  Each stream has its own split-K workspace.
     stream = torch.cuda.Stream(device=dev)
     side = torch.cuda.Stream(device=dev)
     ws_side = torch.zeros(8 << 20, dtype=torch.uint8, device=dev)
@@ -241,7 +261,21 @@ def run_ours(args):
     def run_lin(lin, src, dst, wsp):
         ops.gemv(src, lin.packed_indices, lin.codebook, BITS, BLOCK, lin.out_features, lin.in_features, out=dst, ws=wsp)
 
-    def launch_all(xin, hin):
+    # ---- path A: the whole step as one launch of the persistent kernel (+ one sum over the ranks)
+    group = None
+    if use_group:
+        items = [(mods[nm], x, out[l]) for l, mods in enumerate(layers) for nm, out in (("gate", y_gate), ("up", y_up))]
+        items += [(mods["down"], h, y_down[l]) for l, mods in enumerate(layers)]
+        group = nbt.MatvecGroup(items)
+
+    def group_step():
+        group.run()
+        if world > 1:
+            all_reduce(y_down)
+
+    # ---- path B: one launch per matrix, gate || up on two streams, down after both, the down output of a
+    # layer summed over the ranks before the next layer (the order a decoder imposes); one CUDA graph
+    def launch_chain(xin, hin):
         cur = torch.cuda.current_stream()
         for l, mods in enumerate(layers):
             side.wait_stream(cur)
@@ -255,11 +289,12 @@ def run_ours(args):
 
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(stream):
-        launch_all(x, h)                     # warm the kernels / NCCL before capture
+        launch_chain(x, h)                     # warm the kernels / NCCL before capture
         stream.synchronize()
         with torch.cuda.graph(graph, stream=stream):
-            launch_all(x, h)
-    launches_per_step = 3 * LAYERS
+            launch_chain(x, h)
+    step_fn = group_step if use_group else graph.replay
+    launches_per_step = (1 + (1 if world > 1 else 0)) if use_group else 3 * LAYERS + (LAYERS if world > 1 else 0)
     step_bytes_rank = sum(alg_bytes(m, n, k) for _, n, k in shapes) * LAYERS
 
     def barrier():
@@ -267,69 +302,120 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    def timed_blocks(fn, steps, blocks):
+        """`blocks` back-to-back blocks of `steps` calls, each block timed with CUDA events on the launching
+        stream, a barrier + synchronize on both sides of the whole region; per block the max over ranks."""
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(blocks + 1)]
         barrier()
         with torch.cuda.stream(stream):
-            e0.record(stream)
-            for _ in range(steps):
-                fn()
-            e1.record(stream)
+            ev[0].record(stream)
+            for b in range(blocks):
+                for _ in range(steps):
+                    fn()
+                ev[b + 1].record(stream)
         barrier()
-        ms = e0.elapsed_time(e1)
+        t = torch.tensor([ev[b].elapsed_time(ev[b + 1]) for b in range(blocks)], device=dev)
         if world > 1:
-            t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t)
-        return ms
+        return [float(v) for v in t]
 
-    # ---- device-resident throughput (the `value`)
+    def timed(fn, steps):
+        return sum(timed_blocks(fn, steps, 1))
+
+    # ---- device-resident throughput (the `value`): at least N_BLOCKS blocks of `steps` steps and MIN_TIMED_S seconds
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
-            graph.replay()
+            step_fn()
+    probe = timed(step_fn, args.steps)
+    blocks = max(N_BLOCKS, int(MIN_TIMED_S * 1e3 / max(probe, 1e-3)) + 1)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms = timed(graph.replay, args.steps)
+    block_ms = timed_blocks(step_fn, args.steps, blocks)
     clocks = sampler.stop() if rank == 0 else None
+    if group is not None:
+        group.check()
     total_bytes = torch.tensor([float(step_bytes_rank)], device=dev)
     if world > 1:
         dist.all_reduce(total_bytes)
     step_bytes = float(total_bytes)
-    ms_per_step = ms / args.steps
+    ms_per_step = statistics.median(block_ms) / args.steps
     value = step_bytes / (ms_per_step * 1e-3) / 1e9
+    timing = {"blocks": blocks, "steps_per_block": args.steps, "timed_region_ms": sum(block_ms),
+              "ms_per_step_median_block": ms_per_step, "ms_per_step_mean": sum(block_ms) / (blocks * args.steps),
+              "ms_per_step_min_block": min(block_ms) / args.steps, "ms_per_step_max_block": max(block_ms) / args.steps}
+    # the other way of issuing the same step, for the record
+    other = None
+    if m == 1 and not args.chain:
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                graph.replay()
+        t_chain = statistics.median(timed_blocks(graph.replay, args.steps, 5)) / args.steps
+        other = {"graph_of_78_launches_ms_per_step": t_chain, "graph_of_78_launches_GBps": step_bytes / (t_chain * 1e-3) / 1e9,
+                 "exchange": "per-layer all-reduce inside the graph" if world > 1 else "none"}
 
-    # ---- end to end through the module API with host buffers
+    # ---- N > 1: the sharded, summed outputs against the unsharded matvecs computed on this GPU
+    tp_check = None
+    if world > 1:
+        with torch.cuda.stream(stream):
+            step_fn()
+        stream.synchronize()
+        worst = {"gate_up": 0.0, "down": 0.0}
+        for l, full in full_layers.items():
+            for nm, ysh in (("gate", y_gate), ("up", y_up)):
+                ref = ops.gemv(x, full[nm][0], full[nm][1], BITS, BLOCK, FFN, HIDDEN, out_dtype=torch.float32, ordered=True)
+                err = (ysh[l].float() - ref[:, ch0:ch0 + ch_n]).abs().max() / ref.abs().max()
+                worst["gate_up"] = max(worst["gate_up"], float(err))
+            ref = ops.gemv(h_full, full["down"][0], full["down"][1], BITS, BLOCK, HIDDEN, FFN, out_dtype=torch.float32, ordered=True)
+            worst["down"] = max(worst["down"], float((y_down[l].float() - ref).abs().max() / ref.abs().max()))
+        ok = worst["gate_up"] <= 2.0 ** -7 and worst["down"] <= 2e-5          # bf16 outputs / fp32 sums
+        flag = torch.tensor([int(ok)], device=dev)
+        errs = torch.tensor([worst["gate_up"], worst["down"]], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+        if oneshot is not None:
+            oneshot.check()
+        tp_check = {"ok": bool(flag.item() == 1), "layers_checked": list(full_layers), "gate_up_rel_err_bf16_out": float(errs[0]),
+                    "down_sum_rel_err": float(errs[1]), "against": "unsharded matvecs of the same global weights on every rank's GPU"}
+        full_layers.clear()
+
+    # ---- end to end through the public API with host buffers: inputs from pinned host memory, results back to it
     x_host = x.cpu().pin_memory()
     h_host = h.cpu().pin_memory()
     out_host = torch.empty(LAYERS, m, HIDDEN, dtype=y_down.dtype).pin_memory()
-    xd, hd = torch.empty_like(x), torch.empty_like(h)
+    gu_host = torch.empty(2, LAYERS, m, ch_n, dtype=torch.bfloat16).pin_memory()
 
     def e2e_step():
-        xd.copy_(x_host, non_blocking=True)
-        hd.copy_(h_host, non_blocking=True)
-        for l, mods in enumerate(layers):
-            g = mods["gate"](xd)
-            u = mods["up"](xd)
-            y_down[l] = mods["down"](hd)
-            if world > 1:
-                all_reduce(y_down[l])
-            del g, u
+        x.copy_(x_host, non_blocking=True)
+        h.copy_(h_host, non_blocking=True)
+        if use_group:
+            group_step()
+        else:
+            for l, mods in enumerate(layers):
+                y_gate[l] = mods["gate"](x)
+                y_up[l] = mods["up"](x)
+                y_down[l] = mods["down"](h).to(y_down.dtype)
+                if world > 1:
+                    all_reduce(y_down[l])
+        gu_host[0].copy_(y_gate, non_blocking=True)
+        gu_host[1].copy_(y_up, non_blocking=True)
         out_host.copy_(y_down, non_blocking=True)
+        torch.cuda.current_stream().synchronize()          # the caller reads the results of every step
 
     with torch.cuda.stream(stream):
-        for _ in range(max(1, args.warmup // 2)):
+        for _ in range(3):
             e2e_step()
     e2e_steps = max(1, min(args.steps, 20))
-    ms_e2e = timed(e2e_step, e2e_steps) / e2e_steps
+    ms_e2e = statistics.median(timed_blocks(e2e_step, e2e_steps, 5)) / e2e_steps
     e2e_value = step_bytes / (ms_e2e * 1e-3) / 1e9
     h2d = x_host.numel() * 2 + h_host.numel() * 2
-    d2h = out_host.numel() * out_host.element_size()
+    d2h = out_host.numel() * out_host.element_size() + gu_host.numel() * 2
 
-    # ---- roofline of the dominant kernel: the 6912 x 2560 matvec, timed alone (1 GPU only)
+    # ---- roofline of the dominant kernel and the per-kernel figures (1 GPU only)
     roofline, extra = None, {}
     if world == 1:
         peak, peak_src = measured_peak()
+        kb = alg_bytes(m, FFN, HIDDEN)
         gate_up = [(mods[nm]) for mods in layers for nm in ("gate", "up")]          # 52 copies, 461 MB > L2
         yb = torch.empty(m, FFN, dtype=torch.bfloat16, device=dev)
         yb2 = torch.empty_like(yb)
@@ -357,16 +443,39 @@ def run_ours(args):
         reps = max(5, args.steps)
         ms_k = timed(g2.replay, reps) / (reps * len(gate_up))
         ms_k1 = timed(g1.replay, reps) / (reps * len(gate_up))
-        kb = alg_bytes(m, FFN, HIDDEN)
-        ach = kb / (ms_k * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": NCU_TRAFFIC_B1 if m == 1 else None,
-                    "kernel": "nb::gemv_kernel<3,%d,%d> 6912x2560 batch %d" % (2 if m > 8 else 1, 1 if m == 1 else 8, m),
-                    "us_per_launch": ms_k * 1e3, "algorithmic_bytes": kb, "peak_source": peak_src,
-                    "method": "52 launches over 52 distinct weight copies (461 MB), issued as the two independent "
-                              "chains gate || up of the model; one dependent chain: %.3f us/launch = %.1f GB/s"
-                              % (ms_k1 * 1e3, kb / (ms_k1 * 1e-3) / 1e9),
-                    "frac_of_nominal_8TBs": ach / 8000.0}
-        # other batch sizes of configs[1], same kernel, for the record
+        single = {"kernel": "nb::gemv_kernel<3,%d,%d> 6912x2560 batch %d, one launch per matrix" % (2 if m > 8 else 1, 1 if m == 1 else 8, m),
+                  "algorithmic_bytes": kb,
+                  "one_chain_us": ms_k1 * 1e3, "one_chain_GBps": kb / (ms_k1 * 1e-3) / 1e9, "one_chain_frac": kb / (ms_k1 * 1e-3) / 1e9 / peak,
+                  "two_chains_us": ms_k * 1e3, "two_chains_GBps": kb / (ms_k * 1e-3) / 1e9, "two_chains_frac": kb / (ms_k * 1e-3) / 1e9 / peak}
+        if use_group:
+            # the persistent kernel on the two FFN shapes alone: 52 gate/up matrices, 26 down matrices per launch
+            per = {}
+            for tag, its, n, k in (("6912x2560", [(lin, x, y_gate[i // 2] if i % 2 == 0 else y_up[i // 2]) for i, lin in enumerate(gate_up)], FFN, HIDDEN),
+                                   ("2560x6912", [(mods["down"], h, y_down[l]) for l, mods in enumerate(layers)], HIDDEN, FFN)):
+                g = nbt.MatvecGroup(its)
+                with torch.cuda.stream(stream):
+                    for _ in range(3):
+                        g.run()
+                t = statistics.median(timed_blocks(g.run, 10, 5)) / 10 / len(its)
+                per[tag] = {"us_per_matrix": t * 1e3, "GBps": alg_bytes(1, n, k) / (t * 1e-3) / 1e9,
+                            "frac": alg_bytes(1, n, k) / (t * 1e-3) / 1e9 / peak, "matrices_per_launch": len(its)}
+                g.check()
+                del g
+            roofline = {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
+                        "traffic": NCU_TRAFFIC_STEP,
+                        "kernel": "nb::stream_kernel<3>, one launch = the 78 matrices of a step",
+                        "us_per_launch": ms_per_step * 1e3, "algorithmic_bytes": int(step_bytes), "peak_source": peak_src,
+                        "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch over 20 matrices of 6912x2560 "
+                                          "(one ncu capture), scaled by algorithmic bytes to the 78 matrices of a step",
+                        "per_shape_within_one_launch": per, "single_matrix_kernel": single,
+                        "frac_of_nominal_8TBs": value / 8000.0}
+        else:
+            ach = kb / (ms_k * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                        "traffic": NCU_TRAFFIC_B1 if m == 1 else None, "kernel": single["kernel"], "us_per_launch": ms_k * 1e3,
+                        "algorithmic_bytes": kb, "peak_source": peak_src, "single_matrix_kernel": single,
+                        "frac_of_nominal_8TBs": ach / 8000.0}
+        # other batch sizes of configs[1], the single-matrix kernel, for the record
         for mb in (1, 4, 16):
             xb = synthetic.synthetic_activation(mb, HIDDEN, 3, dev)
             hb = synthetic.synthetic_activation(mb, FFN, 4, dev)
@@ -385,7 +494,9 @@ def run_ours(args):
                     for _ in range(3):
                         gk.replay()
                 t = timed(gk.replay, 5) / (5 * len(lins))
-                extra[f"{tag}_b{mb}"] = {"us": round(t * 1e3, 3), "GB/s": round(alg_bytes(mb, n, k) / (t * 1e-3) / 1e9, 1)}
+                gbs = alg_bytes(mb, n, k) / (t * 1e-3) / 1e9
+                extra[f"{tag}_b{mb}"] = {"us": round(t * 1e3, 3), "GB/s": round(gbs, 1), "frac": round(gbs / peak, 4)}
+    del group
 
     # ---- CPU baseline on the host cores (rank 0, N=1 only)
     cpu = None
@@ -396,7 +507,7 @@ def run_ours(args):
                "sample": "gate+up+down matvec of one layer (3 of the step's 78 matvecs), best of 3 after 1 warm-up; "
                          "reference CPU PyTorch path: unpack + gather + matmul per call"}
 
-    # ---- prefill dequant-GEMM (configs[2]): 2048 tokens against both FFN shapes, tcgen05 path
+    # ---- prefill dequant-GEMM (configs[2]): 2048 tokens against both FFN shapes on the tensor cores
     prefill = None
     if world == 1 and not args.no_prefill:
         prefill = {}
@@ -407,20 +518,29 @@ def run_ours(args):
             xp = synthetic.synthetic_activation(2048, k, 5, dev)
             yp = torch.empty(2048, n, dtype=torch.bfloat16, device=dev)
             wbf = ops.dequant(lin.packed_indices, lin.codebook, BITS, BLOCK, (n, k), torch.bfloat16)
+            wst = lin.stream_weight()
+            calls = {"fused": lambda: ops.gemm_prefill_fused(xp, wst, BITS, n, k, out=yp),
+                     "dequant_then_gemm": lambda: ops.gemm_prefill(xp, lin.packed_indices, lin.codebook, BITS, BLOCK, n, k, out=yp),
+                     "gemm_only": lambda: ops.gemm_bf16(xp, wbf),
+                     "library_gemm_on_dense": lambda: torch.matmul(xp, wbf.T)}
+            t = {}
             with torch.cuda.stream(stream):
-                for _ in range(3):
-                    ops.gemm_prefill(xp, lin.packed_indices, lin.codebook, BITS, BLOCK, n, k, out=yp)
-                    ops.gemm_bf16(xp, wbf)
-                    torch.matmul(xp, wbf.T)
-            t_full = timed(lambda: ops.gemm_prefill(xp, lin.packed_indices, lin.codebook, BITS, BLOCK, n, k, out=yp), 20) / 20
-            t_mma = timed(lambda: ops.gemm_bf16(xp, wbf), 20) / 20
-            t_lib = timed(lambda: torch.matmul(xp, wbf.T), 20) / 20
+                for fn in calls.values():
+                    for _ in range(3):
+                        fn()
+            for name, fn in calls.items():
+                t[name] = timed(fn, 20) / 20
             fl = 2.0 * 2048 * n * k
-            prefill[f"2048x{n}x{k}"] = {"dequant_plus_gemm_us": round(t_full * 1e3, 1), "gemm_only_us": round(t_mma * 1e3, 1),
-                                        "library_gemm_us": round(t_lib * 1e3, 1),
-                                        "TFLOPs_fused_call": round(fl / (t_full * 1e-3) / 1e12, 1),
-                                        "TFLOPs_gemm_only": round(fl / (t_mma * 1e-3) / 1e12, 1),
-                                        "frac_of_measured_bf16_peak_gemm_only": round(fl / (t_mma * 1e-3) / 1e12 / pk_bf16, 3)}
+            prefill[f"2048x{n}x{k}"] = {
+                "fused_dequant_in_kernel_us": round(t["fused"] * 1e3, 1), "dequant_then_gemm_us": round(t["dequant_then_gemm"] * 1e3, 1),
+                "gemm_only_us": round(t["gemm_only"] * 1e3, 1), "library_gemm_on_dense_us": round(t["library_gemm_on_dense"] * 1e3, 1),
+                "TFLOPs_fused": round(fl / (t["fused"] * 1e-3) / 1e12, 1),
+                "frac_of_measured_bf16_peak_fused": round(fl / (t["fused"] * 1e-3) / 1e12 / pk_bf16, 3),
+                "TFLOPs_gemm_only": round(fl / (t["gemm_only"] * 1e-3) / 1e12, 1),
+                "frac_of_measured_bf16_peak_gemm_only": round(fl / (t["gemm_only"] * 1e-3) / 1e12 / pk_bf16, 3),
+                "weight_operand": "exact fp16 codebook entries; bf16 activations converted to fp16 (exact in range)"}
+            if ops.prefill_status(dev) != 0:
+                raise RuntimeError("a bounded wait of the prefill kernel ran out")
             del wbf, xp, yp
 
     # ---- the full 2.2B packed decoder (configs[3]): 128-token prompt, 256 greedy tokens, batch 1
@@ -437,6 +557,44 @@ def run_ours(args):
             model.enable_fused_allreduce(max_batch=1)
         gen = torch.Generator().manual_seed(0)
         prompt = torch.randint(0, cfg.vocab_size, (128,), generator=gen)
+        # self-check before timing: the logits of the prompt's last token from the batched (tensor-core) prefill
+        # against the same token reached by single-token decode steps (the GEMV kernels); with N > 1 also
+        # against the unsharded model built on this GPU from the same seed
+        pr = prompt.to(dev).reshape(1, -1)
+        sess = G.DecodeSession(model, 1)
+        sess.prefill(pr)
+        lg_prefill = sess.logits.float().clone()
+        sess2 = G.DecodeSession(model, 1, use_graph=False)
+        sess2.prefill(pr[:, :96])
+        for j in range(96, 128):
+            sess2.token.copy_(pr[:, j].reshape(sess2.token.shape))     # teacher forcing: the prompt's token
+            sess2.step()
+        torch.cuda.synchronize()
+        scale = float(lg_prefill.abs().max())
+        errs = [float((sess2.logits.float() - lg_prefill).abs().max()) / scale]
+        names = ["prefill_vs_stepwise_rel_err"]
+        same_token = True
+        del sess2
+        if world > 1:
+            full = G.PackedGPT.random_init(cfg, seed=0, device=dev)
+            s1 = G.DecodeSession(full, 1, use_graph=False)
+            s1.prefill(pr)
+            errs.append(float((s1.logits.float() - lg_prefill).abs().max()) / float(s1.logits.abs().max()))
+            names.append("tp_vs_single_gpu_rel_err")
+            same_token = bool(torch.equal(s1.logits.argmax(-1), lg_prefill.argmax(-1)))
+            del s1, full
+            torch.cuda.empty_cache()
+        errs_t = torch.tensor(errs, device=dev)
+        flag = torch.tensor([int(same_token)], device=dev)
+        if world > 1:
+            dist.all_reduce(errs_t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        checks = {nm: float(errs_t[i]) for i, nm in enumerate(names)}
+        if world > 1:
+            checks["tp_vs_single_gpu_next_token_equal"] = bool(flag.item() == 1)
+        checks["gate"] = "2e-3 of max |logit|"
+        checks["ok"] = bool(float(errs_t.max()) <= 2e-3 and flag.item() == 1)
+        del sess
         res = G.benchmark(model, prompt, n_generate=256, n_runs=2)
         t = torch.tensor([res["per_token_ms"], res["prefill_ms"]], device=dev)
         if world > 1:
@@ -450,7 +608,8 @@ def run_ours(args):
                   "allreduce": ("none" if world == 1 else args.allreduce),
                   "packed_linear_bytes_per_token": lin_bytes, "lm_head_bytes_per_token": head_bytes,
                   "weight_GBps": (lin_bytes + head_bytes) / (per_tok_ms * 1e-3) / 1e9,
-                  "model": "26 layers, hidden 2560, 32 heads, FFN 6912, vocab 32000, random-init 3-bit packed linears"}
+                  "model": "26 layers, hidden 2560, 32 heads, FFN 6912, vocab 32000, random-init 3-bit packed linears",
+                  "self_check": checks}
         del model
 
     # ---- serving sweep (configs[4]): batch 1/8/32/64 decode after a 512-token prompt, 3-bit and 2-bit
@@ -482,16 +641,29 @@ def run_ours(args):
             del model
             torch.cuda.empty_cache()
 
+    failed = (tp_check is not None and not tp_check["ok"]) or (decode is not None and not decode["self_check"]["ok"])
     if rank == 0:
+        cfgd = workload_config(m, world)
+        cfgd["launch"] = ("one launch of the persistent multi-matrix kernel per step (nativebit_b200.MatvecGroup)" if use_group else
+                          "one CUDA graph of 78 kernels per step; gate and up of a layer on two streams, down after both")
+        if world > 1:
+            cfgd["exchange"] = ("one sum over the ranks of all layers' partial down outputs per step (the layers of this workload are "
+                                "independent); the per-layer exchange of a decoder is the `other_issue_order` and `decode` figures"
+                                if use_group else "all-reduce of the down output after every layer") + f"; {args.allreduce}"
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-                "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16xf16->f32",
-                "data": "synthetic",
-                "config": workload_config(m, world),
+                "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32",
+                "data": "synthetic", "config": cfgd, "timing": timing,
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": ms_e2e, "api": "PackedLinear.forward per matvec, pinned host in/out"},
-                "gpu_launches": launches_per_step * args.steps,
+                        "ms_per_step": ms_e2e,
+                        "api": ("nativebit_b200.MatvecGroup.run()" if use_group else "PackedLinear.forward per matrix") +
+                               ", inputs copied from pinned host memory and every output copied back to it, stream synchronised, each step"},
+                "gpu_launches": launches_per_step * args.steps * blocks,
                 "clocks": clocks}
+        if other is not None:
+            line["other_issue_order"] = other
+        if tp_check is not None:
+            line["tp_check"] = tp_check
         if roofline is not None:
             line["roofline"] = roofline
             line["per_shape"] = extra
@@ -510,7 +682,9 @@ def run_ours(args):
         dist.barrier()
         torch.cuda.synchronize()
         sys.stdout.flush()
-        os._exit(0)
+        os._exit(1 if failed else 0)
+    if failed:
+        sys.exit(1)
 
 
 def run_kernel_only(args):
@@ -536,9 +710,37 @@ def run_kernel_only(args):
     print(json.dumps({"kernel_only": [n, k, m], "copies": copies, "us_per_launch_stream": e0.elapsed_time(e1) * 1e3 / copies}))
 
 
+def run_group_only(args):
+    """A few launches of the persistent kernel over N_MATS matrices of 6912 x 2560 (distinct weights, more than
+    L2 from 10 matrices up) — the small case that profiler captures are taken on
+    (python bench.py --group-only N_MATS)."""
+    import torch
+    import nativebit_b200 as nbt
+    from nativebit_b200 import synthetic
+    dev = torch.device("cuda", 0)
+    x = synthetic.synthetic_activation(1, HIDDEN, 1, dev)
+    y = torch.empty(args.group_only, 1, FFN, dtype=torch.bfloat16, device=dev)
+    items = []
+    for i in range(args.group_only):
+        p, c = synthetic.synthetic_packed(FFN, HIDDEN, BITS, seed=i, device=dev)
+        items.append((nbt.PackedLinear(p, c, FFN, HIDDEN, bits=BITS), x, y[i]))
+    grp = nbt.MatvecGroup(items)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for rep in range(3):
+        e0.record()
+        grp.run()
+        e1.record()
+        torch.cuda.synchronize()
+    grp.check()
+    us = e0.elapsed_time(e1) * 1e3
+    print(json.dumps({"group_only": args.group_only, "us_per_launch": us, "us_per_matrix": us / args.group_only,
+                      "GBps": args.group_only * alg_bytes(1, FFN, HIDDEN) / us / 1e3}))
+
+
 def run_gemm_only(args):
-    """A few plain launches of the prefill GEMM (dequant + tcgen05 kernel) on one shape — the small
-    case that profiler captures are taken on (python bench.py --gemm-only M N K)."""
+    """A few plain launches of the prefill GEMM on one shape, first the dequant kernel + tcgen05 GEMM, then the
+    kernel that dequantises inside the tensor-core pipeline — the small case that profiler captures are taken
+    on (python bench.py --gemm-only M N K)."""
     import torch
     from nativebit_b200 import ops, synthetic
     m, n, k = args.gemm_only
@@ -553,7 +755,17 @@ def run_gemm_only(args):
             ops.gemm_prefill(x, p, c, BITS, BLOCK, n, k, out=y)
         e1.record()
         torch.cuda.synchronize()
-    print(json.dumps({"gemm_only": [m, n, k], "us_per_call_dequant_plus_gemm": e0.elapsed_time(e1) * 1e3 / 4}))
+    two = e0.elapsed_time(e1) * 1e3 / 4
+    from nativebit_b200 import stream as S
+    w = S.stream_pack(p, c, BITS, n, k)
+    for rep in range(3):
+        e0.record()
+        for _ in range(4):
+            ops.gemm_prefill_fused(x, w, BITS, n, k, out=y)
+        e1.record()
+        torch.cuda.synchronize()
+    print(json.dumps({"gemm_only": [m, n, k], "us_per_call_dequant_plus_gemm": two, "us_per_call_fused": e0.elapsed_time(e1) * 1e3 / 4,
+                      "status": ops.prefill_status(dev)}))
 
 
 def run_decode_only(args):
@@ -593,6 +805,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--chain", action="store_true", help="time the graph of one launch per matrix instead of the persistent kernel")
     ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "fused", "nccl"],
                     help="tensor-parallel all-reduce of the decoder: the one-shot peer-memory kernel (default, the fastest "
                          "measured), folded into the packed GEMVs (peer-memory push + gather; the one-shot kernel where that "
@@ -602,6 +815,8 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="skip the 2.2B decoder leg")
     ap.add_argument("--decode-only", type=int, default=0, metavar="STEPS",
                     help="time STEPS decode steps of the 2.2B decoder at batch 1 and exit (profiling case)")
+    ap.add_argument("--group-only", type=int, default=0, metavar="N_MATS",
+                    help="launch the persistent kernel over N_MATS 6912x2560 matrices a few times and exit (profiling case)")
     ap.add_argument("--gemm-only", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
                     help="launch the prefill GEMM on one shape a few times and exit (profiling case)")
     ap.add_argument("--kernel-only", type=int, nargs=3, metavar=("N", "K", "M"), default=None,
@@ -610,6 +825,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.decode_only:
         run_decode_only(args)
+    elif args.group_only:
+        run_group_only(args)
     elif args.gemm_only:
         run_gemm_only(args)
     elif args.kernel_only:

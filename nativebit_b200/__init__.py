@@ -9,4 +9,6 @@ from . import ops  # noqa: F401
 from .packed_linear import (BS, NE, TILE_N, PackedLinear, dequant_matvec, dequant_matvec_3bit,  # noqa: F401
                             dequant_matvec_3bit_cuda, pack_indices_to_3bit)
 
+from .stream import MatvecGroup  # noqa: F401,E402
+
 __version__ = "0.1.0"

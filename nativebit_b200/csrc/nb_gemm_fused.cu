@@ -13,7 +13,7 @@
 //
 // Weights are read in the stream layout (nb_stream_pack: per 16 rows x 128 weights, every lane-group's
 // indices as nibbles in position order + the rows' byte-plane lookup tables), straight from L2 into
-// registers.  Persistent kernel, one CTA per SM, 448 threads:
+// registers.  Persistent kernel, one CTA per SM, 704 threads:
 //   warp 0       one lane issues the TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast)
 //                of the BN x 64 activation slab of every k-step into a ring of stages;
 //   warp 1       allocates tensor memory; one lane waits for a stage's activations AND weights and issues
@@ -22,9 +22,11 @@
 //   warps 2-5    epilogue: each warp owns one 32-lane quadrant of tensor memory (32 output features),
 //                reads a finished accumulator with tcgen05.ld and stores Y (transposed: lanes run along
 //                N, so a warp's store of one token covers 32 consecutive outputs);
-//   warps 6-13   dequant producers: thread (row, half) of the 128 x 64 weight tile loads four selector
-//                words and the row's table (prefetched one k-step ahead), looks 32 weights up with
-//                byte permutes and writes them as four 16-byte chunks into the 128-byte-swizzled stage.
+//   warps 6-21   dequant producers, two groups of 8 warps that take turns at the k-steps (filling a stage is
+//                a chain of dependent steps, so two stages are filled at a time): thread (row, half) of the
+//                128 x 64 weight tile loads four selector words and the row's table (prefetched one of its
+//                k-steps ahead), looks 32 weights up with byte permutes and writes them as four 16-byte
+//                chunks into the 128-byte-swizzled stage.
 // Two accumulators in tensor memory let the epilogue of one tile overlap the MMAs of the next.  Every
 // mbarrier wait is bounded; on a timeout the waiter raises a shared abort flag, writes NB_ERR_TIMEOUT
 // to the status word and all roles fall through to the exit, where tensor memory is freed.
@@ -45,8 +47,9 @@ namespace nb {
 
 constexpr int kFM = 128;                  // output features per tile (the MMA's M)
 constexpr int kFK = 64;                   // k per stage
-constexpr int kFThreads = 448;
-constexpr int kFProducerWarp0 = 6, kFProducerWarps = 8;
+constexpr int kFProducerWarp0 = 6, kFProducerWarps = 8;   // warps per producer group
+constexpr int kFGroups = 2;                                // groups take turns at the k-steps
+constexpr int kFThreads = (kFProducerWarp0 + kFGroups * kFProducerWarps) * 32;
 constexpr int kFABytes = kFM * kFK * 2;   // 16 KB of weights per stage
 constexpr int kFRing = 192 * 1024;
 constexpr int kFMaxStages = 8;
@@ -55,6 +58,13 @@ constexpr int kFSmem = kFRing + 1024 + 512;
 __host__ __device__ constexpr int fused_stages(int bn) {
   return kFRing / (kFABytes + bn * kFK * 2) < kFMaxStages ? kFRing / (kFABytes + bn * kFK * 2) : kFMaxStages;
 }
+
+#ifdef NB_FUSED_TRACE
+__device__ long long g_ftrace[8][512];
+#define FTRACE(role, kt) do { if (blockIdx.x == 0 && (kt) < 512) g_ftrace[role][kt] = clock64(); } while (0)
+#else
+#define FTRACE(role, kt) do {} while (0)
+#endif
 
 template <int BITS> struct FusedFmt {
   static constexpr int kTabBytes = BITS == 4 ? 32 : 16;
@@ -112,6 +122,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         for (int kt = 0; kt < KT; ++kt) {
           ok = bar_wait(&empty[s], phase ^ 1, abort_flag, status);
           if (!ok) break;
+          FTRACE(0, kt);
           bar_expect_tx(&full_b[s], (uint32_t)b_bytes);
           tma_load_2d(sB + s * b_bytes, &map_x, &full_b[s], kt * kFK, m0);
           if (++s == S) { s = 0; phase ^= 1; }
@@ -132,8 +143,11 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * 256);
         for (int kt = 0; kt < KT && ok; ++kt) {
-          ok = bar_wait(&full_a[s], phase, abort_flag, status) && bar_wait(&full_b[s], phase, abort_flag, status);
+          ok = bar_wait(&full_a[s], phase, abort_flag, status);
+          FTRACE(1, kt);
+          ok = ok && bar_wait(&full_b[s], phase, abort_flag, status);
           if (!ok) break;
+          FTRACE(2, kt);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t da = smem_desc_sw128(sA + s * kFABytes), db = smem_desc_sw128(sB + s * b_bytes);
 #pragma unroll
@@ -190,12 +204,12 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
   } else {
     // ---- dequant producers: thread (row, half) writes 32 weights = 64 bytes of row `row` of the stage
     const int p = threadIdx.x - kFProducerWarp0 * 32;
-    const int row = p & 127, q2 = p >> 7;
+    const int grp = p >> 8, pp = p & 255;                // group `grp` fills the k-steps kt with kt % kFGroups == grp
+    const int row = pp & 127, q2 = pp >> 7;
     const int r16 = row & 15, g = r16 & 7, hrow = r16 >> 3;
-    int s = 0;
-    uint32_t phase = 0;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-    for (int t = blockIdx.x; t < n_total; t += gridDim.x) {
+    uint32_t step0 = 0;                                  // k-steps of all earlier tiles: stage = step % S, phase = (step / S) & 1
+    for (int t = blockIdx.x; t < n_total; t += gridDim.x, step0 += (uint32_t)KT) {
       const int n0 = (t / m_tiles) * kFM;
       const int grow = n0 + row;
       const bool valid = grow < rows_padded;
@@ -214,13 +228,18 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         }
       };
       uint4 sel, tab[kT / 4];
-      load(0, sel, tab);
+      load(grp, sel, tab);
       bool ok = true;
-      for (int kt = 0; kt < KT; ++kt) {
+      for (int kt = grp; kt < KT; kt += kFGroups) {
         uint4 sel_n, tab_n[kT / 4];
-        load(kt + 1, sel_n, tab_n);                      // next k-step's words, in flight while this one is unpacked
+        load(kt + kFGroups, sel_n, tab_n);               // this group's next k-step, in flight while this one is unpacked
+        const uint32_t step = step0 + (uint32_t)kt;
+        const int s = (int)(step % (uint32_t)S);
+        const uint32_t phase = (step / (uint32_t)S) & 1u;
+        if (pp == 0) FTRACE(3, kt);
         ok = bar_wait<20>(&empty[s], phase ^ 1, abort_flag, status);
         if (!ok) break;
+        if (pp == 0) FTRACE(4, kt);
         uint32_t T[kT];
 #pragma unroll
         for (int j = 0; j < kT / 4; ++j) { T[4 * j] = tab[j].x; T[4 * j + 1] = tab[j].y; T[4 * j + 2] = tab[j].z; T[4 * j + 3] = tab[j].w; }
@@ -238,10 +257,10 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s2u(&full_a[s])) : "memory");
+        if (pp == 0) FTRACE(5, kt);
         sel = sel_n;
 #pragma unroll
         for (int j = 0; j < kT / 4; ++j) tab[j] = tab_n[j];
-        if (++s == S) { s = 0; phase ^= 1; }
       }
       if (!ok) break;
     }
@@ -266,18 +285,21 @@ __global__ void __launch_bounds__(256) bf16_to_f16_kernel2(const uint4* __restri
   out[i] = make_uint4(r[0], r[1], r[2], r[3]);
 }
 
-// Token-tile width: the multiple of 16 in [16, 256] that wastes the least of the last wave of CTAs; ties go
-// to the wider tile, which dequantises every weight tile fewer times.  Short inputs take one tile.
+// Token-tile width (a multiple of 16 up to 256).  A k-step costs the longer of the tensor-core time, 2 * BN
+// clocks, and the time the producers need to fill a stage, which does not depend on BN (measured: about
+// kProducerClocks); the tile width that minimises waves * max(2 * BN, kProducerClocks) is chosen, the
+// wider one on ties (every weight tile is then dequantised fewer times).  Short inputs take one tile.
+constexpr int kProducerClocks = 340;
 static int pick_token_tile(int M, int N, int sms) {
   if (M <= 256) return std::min(256, (M + 15) / 16 * 16);
   const int w_tiles = (N + kFM - 1) / kFM;
   int best = 256;
-  double best_eff = -1.0;
+  double best_cost = 1e30;
   for (int bn = 256; bn >= 96; bn -= 16) {
     const long tiles = (long)w_tiles * ((M + bn - 1) / bn);
     const long waves = (tiles + sms - 1) / sms;
-    const double eff = (double)M * N / ((double)waves * sms * kFM * bn);
-    if (eff > best_eff + 0.02) { best_eff = eff; best = bn; }     // a narrower tile must buy at least 2 % to be chosen
+    const double cost = (double)waves * std::max(2 * bn, kProducerClocks);
+    if (cost < best_cost * 0.98) { best_cost = cost; best = bn; }
   }
   return best;
 }
@@ -290,6 +312,10 @@ static int make_map_f16(CUtensorMap* map, const void* base, int rows, int cols, 
 }  // namespace nb
 
 using namespace nb;
+
+#ifdef NB_FUSED_TRACE
+extern "C" int nb_fused_trace_read(long long* host) { return (int)cudaMemcpyFromSymbol(host, g_ftrace, sizeof(g_ftrace)); }
+#endif
 
 extern "C" size_t nb_prefill_fused_workspace_bytes(int M, int K) {
   if (M < 1 || K < 1) return 0;

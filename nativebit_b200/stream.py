@@ -192,3 +192,53 @@ def stream_supported(model, batch_size: int) -> bool:
             and cfg.head_dim % 4 == 0 and cfg.head_dim <= 128 and blk.gate_up.out_features % 16 == 0
             and max(blk.down.in_features, blk.out_proj.in_features, cfg.n_embd) <= 8192
             and 5 * cfg.n_layers + 2 <= int(_lib.lib().nb_stream_max_ops()))
+
+
+class MatvecGroup:
+    """Independent packed matvecs y_i = W_i x_i at batch 1, executed by ONE launch of the persistent kernel:
+    the weights of all matrices stream through the SMs back to back, with no launch boundary between
+    matrices.  items: (PackedLinear, x (k,) or (1, k), out (n,) or (1, n)) triples; consecutive items that
+    read the same x share its staged copy.  The reference runs one library launch per matrix
+    (inference/triton_kernel.py:240-256)."""
+
+    def __init__(self, items, device=None):
+        items = list(items)
+        if not items:
+            raise RuntimeError("MatvecGroup needs at least one matvec")
+        dev = torch.device(device) if device is not None else items[0][1].device
+        if len(items) > int(_lib.lib().nb_stream_max_ops()):
+            raise RuntimeError(f"at most {int(_lib.lib().nb_stream_max_ops())} matvecs per launch")
+        self.prog = StreamProgram(dev)
+        G = n_ctas()
+        prev_x = None
+        split = []                       # (partial-sum slots, n, out) of the matvecs whose row tiles are shared between CTAs
+        for lin, x, out in items:
+            n, k = lin.out_features, lin.in_features
+            if lin.block_size != 128 or n % 16:
+                raise RuntimeError("MatvecGroup needs block size 128 and a multiple of 16 output rows")
+            if x.numel() != k or out.numel() != n:
+                raise RuntimeError("MatvecGroup runs one activation vector per matrix")
+            same = prev_x is not None and prev_x.data_ptr() == x.data_ptr() and prev_x.numel() == x.numel()
+            tiles = n // 16
+            if tiles >= 0.9 * (-(-tiles // G) * G):
+                # whole 16-row tiles per CTA keep the CTAs evenly loaded: every CTA stores its own outputs
+                self.prog.gemv_vec(lin.stream_weight(), n, k, lin.bits, x, out, reuse_x=same)
+            else:
+                # few row tiles: the units are dealt out evenly, CTAs that share a row tile write partial sums
+                sl = n_slots(n, k)
+                part = torch.empty(sl, n, dtype=torch.float32, device=dev)
+                self.prog.gemv_vec(lin.stream_weight(), n, k, lin.bits, x, part, reuse_x=same, slots=sl)
+                split.append((part, n, out))
+            prev_x = x
+        for j, (part, n, out) in enumerate(split):
+            self.prog.reduce(part, n, out.reshape(-1), wait=(j == 0))
+        self.n_matvecs = len(items)
+        if len(self.prog.ops) > int(_lib.lib().nb_stream_max_ops()):
+            raise RuntimeError(f"at most {int(_lib.lib().nb_stream_max_ops())} operations per launch")
+
+    def run(self) -> None:
+        self.prog.run()
+
+    def check(self) -> None:
+        if self.prog.status():
+            raise RuntimeError("a bounded wait of the persistent kernel ran out (status %d)" % self.prog.status())

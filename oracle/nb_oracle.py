@@ -104,6 +104,18 @@ def pack_indices_to_3bit(indices_uint8: np.ndarray) -> np.ndarray:
     return pack_3bit(indices_uint8)
 
 
+# --------------------------------------------------------------------------- quantise
+def quantize_weight(weight: np.ndarray, codebook: np.ndarray, block_size: int) -> np.ndarray:
+    """Nearest codebook entry per weight, first minimum on ties, the zero-padded tail included
+    (nativebit/pack.py:176-199; the same argmin as nativebit/layers.py:84-86 and
+    nativebit/inference.py:60-67).  Returns (num_blocks * block_size,) uint8."""
+    nb = codebook.shape[0]
+    w = np.zeros(nb * block_size, np.float32)
+    w[:weight.size] = np.asarray(weight, np.float32).reshape(-1)
+    d = np.abs(w.reshape(nb, block_size, 1) - np.asarray(codebook, np.float32)[:, None, :])
+    return d.argmin(-1).astype(np.uint8).reshape(-1)
+
+
 # --------------------------------------------------------------------------- dequant
 def reconstruct_weight(indices: np.ndarray, codebook: np.ndarray, shape, block_size: int,
                        total_weights: int) -> np.ndarray:

@@ -8,7 +8,9 @@ exporters, plus what the reference itself computes from them.
    params/embedding, RMSNorm weights); golden logits come from the reference's own
    inference/generate_torch.py:load_packed_model + PackedGPT run on CPU (prompt of 8 tokens, batched path).
 2. tiny.nbpack      — nativebit/pack.py:export_packed on a tiny NativeBitGPT training checkpoint
-   (block_size 128) and, for the generic path, one with block_size 8 as in the reference's tests.
+   (block_size 128) and, for the generic path, one with block_size 8 as in the reference's tests; beside each
+   the checkpoint it was exported from (*_ckpt.pt) and *_nbpack_expected.npz: logits of the reference's training
+   forward and of its load_packed model on one seeded input, verify_packed's max_diff and the exporter's statistics.
 """
 import os
 import sys
@@ -26,7 +28,7 @@ def main(ref_root):
     from inference.generate_torch import load_packed_model, init_kv_cache
     from nativebit.codebook_utils import init_codebook_percentile
     from nativebit.model import NativeBitGPT
-    from nativebit.pack import export_packed
+    from nativebit.pack import export_packed, load_packed, verify_packed
 
     # ---------------------------------------------------------------- 1. .nbpack.npz
     V, L, C, H, Fh, ctx = 128, 2, 256, 4, 512, 32
@@ -84,7 +86,21 @@ def main(ref_root):
                         "config": {"vocab_size": 256, "n_layers": 2, "n_embd": n_embd, "n_head": 2, "ffn_hidden": ffn,
                                    "context_len": 32, "block_size": bs, "n_codebook": 8}}, ckp)
             stats = export_packed(ckp, os.path.join(HERE, f"{tag}.nbpack"))
-        print(tag, ".nbpack", stats["file_size_bytes"], "bytes,", stats["n_quantized_layers"], "layers")
+            # the checkpoint itself (for the device exporter, which must write the same file) and what the
+            # reference computes from both sides: the training forward and its load_packed model
+            import shutil
+            shutil.copy(ckp, os.path.join(HERE, f"{tag}_ckpt.pt"))
+            idx = torch.randint(0, 256, (1, 16), generator=torch.Generator().manual_seed(5))
+            m.train(False)
+            with torch.no_grad():
+                lo = m(idx).float()
+                lp = load_packed(os.path.join(HERE, f"{tag}.nbpack"), "cpu")(idx).float()
+            ver = verify_packed(ckp, os.path.join(HERE, f"{tag}.nbpack"), "cpu")
+            np.savez_compressed(os.path.join(HERE, f"{tag}_nbpack_expected.npz"), idx=idx.numpy(), logits_checkpoint=lo.numpy(),
+                                logits_packed=lp.numpy(), verify_max_diff=np.float64(ver["max_diff"]),
+                                stats=np.array([stats[k] for k in ("packed_indices_bytes", "codebook_bytes", "float_param_bytes",
+                                                                   "n_quantized_layers", "bits")]))
+        print(tag, ".nbpack", stats["file_size_bytes"], "bytes,", stats["n_quantized_layers"], "layers; verify", ver)
 
 
 if __name__ == "__main__":

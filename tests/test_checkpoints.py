@@ -80,3 +80,111 @@ def test_torch_nbpack_layers_bit_exact_and_forward(built_lib, name):
         y = lin(torch.from_numpy(x).to(dev)).double().cpu().numpy()
         yr = x.astype(np.float64) @ ref.T.astype(np.float64)
         assert np.abs(y - yr).max() <= 2e-5 * max(np.abs(yr).max(), 1e-6), lname
+
+
+# ----------------------------------------------------------------------------------------------------------
+# Whole-checkpoint exporter with the reference's names (export_packed / load_packed / verify_packed,
+# convert_to_inference), against files and logits the reference itself produced from the same checkpoint.
+
+@pytest.mark.parametrize("tag,bs", [("tiny", 128), ("tiny_bs8", 8)])
+def test_checkpoint_layout_is_read_like_the_reference_on_cpu(tag, bs):
+    from nativebit_b200 import pack as P
+    cfg, sd, names = P._read_checkpoint(os.path.join(GOLD, f"{tag}_ckpt.pt"))
+    blob = torch.load(os.path.join(GOLD, f"{tag}.nbpack"), map_location="cpu", weights_only=False)
+    assert names == list(blob["quantized_layers"].keys())
+    assert P._full_config(cfg, sd, names) == blob["config"]
+
+
+def test_export_packed_refuses_cpu_and_float_checkpoints(tmp_path):
+    from nativebit_b200 import pack as P
+    with pytest.raises(RuntimeError):
+        P.export_packed(os.path.join(GOLD, "tiny_ckpt.pt"), str(tmp_path / "x.nbpack"), device="cpu")
+    p = tmp_path / "float.pt"
+    torch.save({"model_state_dict": {"tok_emb.weight": torch.zeros(4, 4)}, "config": {}}, p)
+    with pytest.raises(ValueError):
+        P._read_checkpoint(str(p))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tag", ["tiny", "tiny_bs8"])
+def test_export_packed_writes_the_reference_file(built_lib, tmp_path, tag):
+    """tests/test_pack.py:187-211 of the reference, plus equality with the file its exporter wrote."""
+    from nativebit_b200.pack import export_packed
+    out = tmp_path / "sub" / f"{tag}.nbpack"
+    stats = export_packed(os.path.join(GOLD, f"{tag}_ckpt.pt"), str(out), device="cuda:0")
+    exp = np.load(os.path.join(GOLD, f"{tag}_nbpack_expected.npz"))
+    assert out.exists() and stats["file_size_bytes"] < stats["original_size_bytes"] and stats["bits"] == 3
+    got = [stats[k] for k in ("packed_indices_bytes", "codebook_bytes", "float_param_bytes", "n_quantized_layers", "bits")]
+    assert got == list(exp["stats"])
+    mine = torch.load(out, map_location="cpu", weights_only=False)
+    ref = torch.load(os.path.join(GOLD, f"{tag}.nbpack"), map_location="cpu", weights_only=False)
+    assert {k: mine[k] for k in ("format_version", "config", "bits", "n_entries")} == \
+           {k: ref[k] for k in ("format_version", "config", "bits", "n_entries")}
+    assert list(mine["quantized_layers"]) == list(ref["quantized_layers"]) and list(mine["float_params"]) == list(ref["float_params"])
+    for name, d in ref["quantized_layers"].items():
+        m = mine["quantized_layers"][name]
+        assert set(m) == set(d)
+        for key, v in d.items():
+            if torch.is_tensor(v):
+                assert m[key].dtype == v.dtype and torch.equal(m[key], v), (name, key)      # index bytes and fp16 codebooks
+            else:
+                assert m[key] == v, (name, key)
+    for name, v in ref["float_params"].items():
+        assert mine["float_params"][name].dtype == torch.float16 and torch.equal(mine["float_params"][name], v)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tag", ["tiny", "tiny_bs8"])
+def test_load_and_verify_packed_match_the_reference(built_lib, tag):
+    """Logits of load_packed against the reference's own load_packed model, and verify_packed's gate
+    (tests/test_pack.py:213-235 of the reference)."""
+    from nativebit_b200.pack import load_packed, verify_packed
+    exp = np.load(os.path.join(GOLD, f"{tag}_nbpack_expected.npz"))
+    model = load_packed(os.path.join(GOLD, f"{tag}.nbpack"), device="cuda:0")
+    logits = model(torch.from_numpy(exp["idx"]).cuda())
+    assert logits.shape == (1, 16, 256)
+    ref = exp["logits_packed"]
+    assert np.abs(logits.cpu().numpy() - ref).max() <= 2e-3 * np.abs(ref).max()
+    res = verify_packed(os.path.join(GOLD, f"{tag}_ckpt.pt"), os.path.join(GOLD, f"{tag}.nbpack"), device="cuda:0")
+    assert res["passed"] and res["max_diff"] < 0.1
+    assert res["max_diff"] <= 4 * float(exp["verify_max_diff"]) + 1e-4          # fp16 codebook rounding only, like the reference's
+
+
+@pytest.mark.gpu
+def test_convert_to_inference_replaces_trainable_layers(built_lib):
+    """A stand-in with the attributes of the reference's NativeBitLinear (nativebit/layers.py:28-62): after the
+    conversion each layer computes x @ codebook[argmin].T like the reference's converted layer."""
+    from nativebit_b200.inference import NativeBitInferenceLinear, convert_to_inference
+
+    class Trainable(torch.nn.Module):
+        def __init__(self, i, n, k, bs=128):
+            super().__init__()
+            g = torch.Generator().manual_seed(i)
+            self.in_features, self.out_features, self.block_size = k, n, bs
+            self.weight = torch.nn.Parameter(torch.randn(n, k, generator=g) * 0.05)
+            self.bias = torch.nn.Parameter(torch.randn(n, generator=g)) if i == 1 else None
+            self.codebook = torch.nn.Parameter(torch.sort(torch.randn(n * k // bs, 8, generator=g) * 0.05, dim=1).values)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.inner = Trainable(0, 256, 384), torch.nn.ModuleList([Trainable(1, 128, 256), Trainable(2, 64, 128, bs=8)])
+            self.norm = torch.nn.LayerNorm(8)
+
+    net = Net().cuda()
+    layers = {"a": net.a, "inner.0": net.inner[0], "inner.1": net.inner[1]}
+    want = {}
+    for name, m in layers.items():
+        w, cb = m.weight.data.cpu().numpy(), m.codebook.data.cpu().numpy()
+        idx = o.quantize_weight(w, cb, m.block_size)
+        want[name] = o.reconstruct_weight(idx.reshape(-1), cb, w.shape, m.block_size, w.size)
+    out = convert_to_inference(net)
+    assert out is net and isinstance(net.norm, torch.nn.LayerNorm)
+    for name in layers:
+        m = net.get_submodule(name)
+        assert isinstance(m, NativeBitInferenceLinear) and not any(p.requires_grad for p in m.parameters())
+        x = torch.from_numpy(o.make_activation(2, m.in_features, seed=3)).cuda()
+        ref = x.double().cpu().numpy() @ want[name].astype(np.float64).T
+        if m.bias is not None:
+            ref = ref + m.bias.double().cpu().numpy()
+        assert np.abs(m(x).double().cpu().numpy() - ref).max() <= 2e-5 * np.abs(ref).max(), name

@@ -123,3 +123,32 @@ def test_one_launch_decode_step_equals_kernel_chain(built_lib):
             assert torch.equal(a.token, b.token)
             assert (a.logits - b.logits).abs().max() <= 1e-4 * b.logits.abs().max()
         a.check()
+
+
+def test_matvec_group_api(built_lib):
+    """The user-facing group: FFN-shaped matvecs of two layers in one launch, evenly loaded (store) and
+    shared-tile (partial sums + reduce) layouts chosen per matrix, bf16 and fp32 outputs."""
+    import nativebit_b200 as nbt
+    dev = _dev()
+    H, F = 2560, 6912
+    x = _cu(o.make_activation(1, H, seed=1), dev).bfloat16()
+    h = _cu(o.make_activation(1, F, seed=2), dev).bfloat16()
+    items, refs = [], []
+    for l in range(2):
+        for j, (n, k, src) in enumerate(((F, H, x), (F, H, x), (H, F, h))):
+            packed, cb, _ = o.make_packed_linear(n, k, 3, seed=10 * l + j)
+            lin = nbt.PackedLinear(_cu(packed, dev), _cu(cb, dev), n, k)
+            out = torch.full((1, n), float("nan"), dtype=torch.float32 if j == 2 else torch.bfloat16, device=dev)
+            items.append((lin, src, out))
+            refs.append(o.packed_linear_forward(src.float().cpu().numpy(), packed, cb.astype(np.float32), n, k, 3, acc_dtype=np.float64)[0])
+    grp = nbt.MatvecGroup(items)
+    grp.run()
+    torch.cuda.synchronize()
+    grp.check()
+    assert any(op.epi == 1 for op in grp.prog.ops) and any(op.epi == 0 and op.kind == 1 for op in grp.prog.ops)   # both layouts used
+    for (lin, _, out), ref in zip(items, refs):
+        tol = 2e-5 if out.dtype == torch.float32 else 2.0 ** -8
+        assert np.abs(out.double().cpu().numpy()[0] - ref).max() <= tol * np.abs(ref).max()
+        # and equal to the single-matrix kernel's answer up to the output rounding
+        y1 = lin(items[0][1] if lin.in_features == H else h)
+        assert np.abs(y1.double().cpu().numpy()[0] - ref).max() <= 2.0 ** -8 * np.abs(ref).max()

@@ -1,7 +1,10 @@
 """The CPU oracle against golden vectors produced by the reference's own functions
 (tests/golden/make_golden.py), plus the round-trip cases of the reference's tests/test_pack.py."""
+import os
+
 import numpy as np
 import pytest
+import torch
 
 from oracle import nb_oracle as o
 
@@ -103,3 +106,16 @@ def test_synthetic_inputs_are_deterministic_and_sorted():
     assert o.algorithmic_bytes(16, 6912, 2560, 3) == 9_150_464
     assert o.algorithmic_bytes(1, 2560, 2560, 3) == 3_287_040
     assert o.algorithmic_bytes(1, 6912, 2560, 2) == 5_548_544
+
+
+def test_quantiser_restatement_matches_the_reference_argmin(golden):
+    """quantize_weight against the indices the reference's quantiser produced for the same weight, and
+    against the index bytes its exporter stored for a whole training checkpoint."""
+    idx = o.quantize_weight(golden["quant_w"], golden["lin3_cb16"].astype(np.float32), 128)
+    assert np.array_equal(idx.reshape(-1, 128), golden["quant_idx"])
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    ck = torch.load(os.path.join(here, "tiny_bs8_ckpt.pt"), map_location="cpu", weights_only=False)["model_state_dict"]
+    blob = torch.load(os.path.join(here, "tiny_bs8.nbpack"), map_location="cpu", weights_only=False)
+    for name, d in blob["quantized_layers"].items():
+        idx = o.quantize_weight(ck[name + ".weight"].numpy(), ck[name + ".codebook"].numpy(), 8)
+        assert np.array_equal(o.pack_3bit(idx), d["packed_indices"].numpy()), name
