@@ -272,7 +272,7 @@ int nb_gemv_static_status(int* host_out, int clear);
  * codebooks are stored as fp16 (an fp32 codebook is rounded, as in nb_gemv).
  *
  * An operation is an nb_stream_op (160 bytes; unused fields zero).  Pointers are device pointers.
- *  NB_SOP_GEMV   y = W x.  p[0] stream-layout weights; i[0] N, i[1] K (multiple of 128, <= 8192), i[2] bits.
+ *  NB_SOP_GEMV   y = W x.  p[0] stream-layout weights; i[0] N, i[1] K (multiple of 128, <= 7168), i[2] bits.
  *     prologue (how x is formed; i[3] = dtype of p[1] for NB_SPRO_VEC):
  *       NB_SPRO_VEC         x = p[1][0..K) (NB_F32 carried as two fp16 terms, NB_F16 / NB_BF16 as one)
  *       NB_SPRO_EMBED_NORM  h = table p[1] (bf16, i[13] rows; row *p[2] (int64), clamped to the table);
@@ -308,7 +308,8 @@ int nb_gemv_static_status(int* host_out, int clear);
  * status word (uint32 index 513) set to NB_ERR_TIMEOUT if a bounded wait ran out (the launch then finishes
  * without hanging; results are invalid).  One launch at a time per state buffer.  The launch is cooperative
  * (all nb_stream_ctas() CTAs resident).  All packed matrices of a program share one `bits`.
- * Limits: at most nb_stream_max_ops() operations; one activation row (batch 1). */
+ * Limits: at most nb_stream_max_ops() operations; one activation row (batch 1); K <= 7168; the norm prologues and
+ * the head need a model width <= 2560; fewer than 65536 (16-row x 128-weight) units per matrix. */
 typedef enum { NB_SOP_GEMV = 1, NB_SOP_ATTN = 2, NB_SOP_HEAD = 3, NB_SOP_ARGMAX = 4, NB_SOP_REDUCE = 5 } nb_stream_kind;
 typedef enum { NB_SPRO_VEC = 0, NB_SPRO_EMBED_NORM = 1, NB_SPRO_ADD_NORM = 2, NB_SPRO_ATTN_MERGE = 3 } nb_stream_prologue;
 typedef enum { NB_SEPI_STORE = 0, NB_SEPI_SLOTS = 1, NB_SEPI_SWIGLU = 2 } nb_stream_epilogue;

@@ -30,15 +30,19 @@ class OneShotAllReduce:
         torch.cuda.synchronize(device)
         dist.barrier(self.group)          # every rank's buffer is zeroed before anyone pushes into it
 
-    def __call__(self, t: torch.Tensor) -> torch.Tensor:
+    def __call__(self, t: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Sum of t over the ranks, in place or into `out` (same shape and type; t is left as it was)."""
         if t.dtype != torch.float32 or not t.is_contiguous() or t.numel() % 4 or t.numel() > self.max_count:
             raise RuntimeError("one-shot all-reduce needs a contiguous fp32 tensor whose numel is a multiple of 4 "
                                f"and at most {self.max_count}")
-        rc = _lib.lib().nb_allreduce(t.data_ptr(), t.data_ptr(), t.numel(), self.peer_array, self.world, self.rank,
+        dst = t if out is None else out
+        if dst.dtype != torch.float32 or not dst.is_contiguous() or dst.numel() != t.numel():
+            raise RuntimeError("one-shot all-reduce: `out` must be a contiguous fp32 tensor of the input's size")
+        rc = _lib.lib().nb_allreduce(t.data_ptr(), dst.data_ptr(), t.numel(), self.peer_array, self.world, self.rank,
                                      self.max_count, 0, self.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
         if rc:
             _lib.check(rc, "nb_allreduce")
-        return t
+        return dst
 
     def check(self) -> None:
         """Raises if a wait for the peers ever ran out (reads the device status word: synchronises)."""

@@ -14,7 +14,7 @@
 namespace nb {
 
 constexpr int kBM = 128, kBK = 64;
-constexpr uint32_t kGemmSpinLimit = 1u << 22;
+constexpr uint32_t kGemmSpinLimit = 1u << 21;
 
 __device__ __forceinline__ uint32_t s2u(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -24,21 +24,27 @@ __device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void bar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s2u(bar)), "r"(bytes) : "memory");
 }
+// One probe of a barrier phase that may suspend the thread in hardware for up to about kBarSuspendNs
+// before it answers: a waiting thread takes no issue slots and no shared-memory bandwidth from the threads
+// that issue the copies and the MMAs.  (Probing with test_wait in a loop was measured to slow the single
+// TMA and MMA lanes of a 704-thread CTA by a factor of five.)
+constexpr uint32_t kBarSuspendNs = 1000;
 __device__ __forceinline__ bool bar_test(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok) : "r"(s2u(bar)), "r"(parity) : "memory");
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(s2u(bar)), "r"(parity), "r"(kBarSuspendNs) : "memory");
   return ok != 0;
 }
-// Bounded wait; returns false (and raises the abort flag) when it gives up or someone else did.
-// kSleep > 0 backs off between probes (used by the 128 epilogue threads, whose wait spans a whole
-// main loop and must not take issue slots from the TMA and MMA threads).
+
+// Bounded wait; returns false (and raises the abort flag) when it gives up or someone else did.  The bound is
+// kGemmSpinLimit probes: between 0.1 s (every probe answers at once) and a few seconds (every probe suspends
+// for its full time), far beyond any kernel of this library.  kSleep > 0 adds a back-off between probes.
 template <int kSleep = 0>
 __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
   for (uint32_t i = 0; i < kGemmSpinLimit; ++i) {
     if (bar_test(bar, parity)) return true;
     if (kSleep > 0) __nanosleep(kSleep);
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+    if ((i & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1;
   if (status) atomicExch(status, (int)NB_ERR_TIMEOUT);

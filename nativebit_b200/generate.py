@@ -107,6 +107,15 @@ class PackedGPT(torch.nn.Module):
         if self.tp_size > 1:
             from .comm import OneShotAllReduce
             self.oneshot = OneShotAllReduce(max_batch * self.n_embd, self.embedding.device, self.group)
+            # decode steps of up to 8 sequences also shard the tied LM head by vocabulary rows: every rank multiplies
+            # its rows of the table only and the ranks' slices of the logits are put together by one more sum
+            # (all other ranks contribute zeros to a slice, so the sum is exact)
+            V = self.embedding.shape[0]
+            if V % 8 == 0 and self.embedding.dtype == torch.bfloat16:
+                self.head_batch = min(8, max_batch)
+                self.head_ar = OneShotAllReduce(self.head_batch * V, self.embedding.device, self.group)
+                v0, vn = tp.share(V // 8, self.tp_size, self.tp_rank)
+                self.head_rows = (8 * v0, 8 * vn)
 
     def enable_fused_allreduce(self, max_batch: int = 8) -> None:
         """Fold the decode step's all-reduces into the packed GEMVs on both sides of them (nb_gemv_tp):
@@ -152,11 +161,12 @@ class PackedGPT(torch.nn.Module):
         gate, up = gu.split(gu.shape[-1] // 2, dim=-1)
         return x + self._all_reduce(blk.down(F.silu(gate) * up).float())
 
-    def _head(self, x: torch.Tensor) -> torch.Tensor:
+    def _head(self, x: torch.Tensor, rows: tuple[int, int] | None = None) -> torch.Tensor:
         """x (..., C) fp32 @ embedding.T with fp32 accumulation and an fp32 result.  A bf16 table is
         multiplied by the activations split into two bf16 terms (16 significant bits) stacked into one
-        operand, so the table is read once and neither the activations nor the logits are rounded to 8 bits."""
-        emb = self.embedding
+        operand, so the table is read once and neither the activations nor the logits are rounded to 8 bits.
+        rows = (first, count): only those rows of the table (a vocabulary shard)."""
+        emb = self.embedding if rows is None else self.embedding[rows[0]:rows[0] + rows[1]]
         shape = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1]).float()
         if emb.dtype != torch.bfloat16:
@@ -384,7 +394,15 @@ class DecodeSession:
             ops.exchange_gather(self.bd, xch, xch.status)
             delta = self.bd
         ops.add_rmsnorm(xa, delta, m.ln_f, eps, self.bh)
-        logits = m._head(self.bh)                                # the LM head is a plain library GEMM (bf16 table, 164 MB)
+        if getattr(m, "head_ar", None) is not None and self.B <= m.head_batch:
+            if getattr(self, "blog_in", None) is None:
+                self.blog_in = torch.zeros(self.B, m.embedding.shape[0], dtype=torch.float32, device=self.bh.device)
+                self.blog_sum = torch.empty_like(self.blog_in)
+            r0, rn = m.head_rows
+            self.blog_in[:, r0:r0 + rn].copy_(m._head(self.bh, m.head_rows))   # the rest of blog_in stays zero
+            logits = m.head_ar(self.blog_in, out=self.blog_sum)
+        else:
+            logits = m._head(self.bh)                            # the LM head is a plain library GEMM (bf16 table, 164 MB)
         ops.softcap_argmax(logits, cfg.logit_cap, self.logits, self.token, self.pos)
 
     @torch.no_grad()
@@ -435,7 +453,7 @@ class DecodeSession:
                 ws = ops.workspace(self.model.embedding.device, 0)
             if ops.workspace_status(ws) != 0:
                 raise RuntimeError("nb_gemv: a bounded wait ran out (status NB_ERR_TIMEOUT in the workspace)")
-        for name in ("oneshot", "exchange"):
+        for name in ("oneshot", "head_ar", "exchange"):
             obj = getattr(self.model, name, None)
             if obj is not None and int(obj.status.item()) != 0:
                 raise RuntimeError(f"{name}: a peer did not arrive within the bounded wait")

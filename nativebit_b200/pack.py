@@ -177,10 +177,13 @@ def export_packed(ckpt_path: str, output_path: str, device: str = "cuda") -> dic
         q_bytes += packed.numel()
         cb_bytes += cb.numel() * 2
     owned = tuple(n + "." for n in names)
+    seen = set()
     for key, v in sd.items():
-        # parameters only: buffers (utilisation counters) and the tied lm_head stay out (nativebit/pack.py:300-311)
-        if key.startswith(owned) or key == "lm_head.weight" or not v.is_floating_point():
+        # parameters only, each once: buffers (utilisation counters), the tied lm_head and the other names of the
+        # token table (value embeddings share it) stay out, as with named_parameters (nativebit/pack.py:300-311)
+        if key.startswith(owned) or key == "lm_head.weight" or not v.is_floating_point() or v.data_ptr() in seen:
             continue
+        seen.add(v.data_ptr())
         state["float_params"][key] = v.half()
         f_bytes += v.numel() * 2
     out = Path(output_path)

@@ -188,9 +188,9 @@ def stream_supported(model, batch_size: int) -> bool:
     cfg = model.config
     blk = model.blocks[0] if len(model.blocks) else None
     return (blk is not None and batch_size == 1 and model.tp_size == 1 and cfg.block_size == 128 and cfg.bits in (2, 3, 4)
-            and model.embedding.dtype == torch.bfloat16 and cfg.n_embd % 128 == 0 and cfg.n_embd <= 4096
+            and model.embedding.dtype == torch.bfloat16 and cfg.n_embd % 128 == 0
             and cfg.head_dim % 4 == 0 and cfg.head_dim <= 128 and blk.gate_up.out_features % 16 == 0
-            and max(blk.down.in_features, blk.out_proj.in_features, cfg.n_embd) <= 8192
+            and max(blk.down.in_features, blk.out_proj.in_features, cfg.n_embd) <= 7168 and cfg.n_embd <= 2560
             and 5 * cfg.n_layers + 2 <= int(_lib.lib().nb_stream_max_ops()))
 
 

@@ -188,3 +188,13 @@ def test_convert_to_inference_replaces_trainable_layers(built_lib):
         if m.bias is not None:
             ref = ref + m.bias.double().cpu().numpy()
         assert np.abs(m(x).double().cpu().numpy() - ref).max() <= 2e-5 * np.abs(ref).max(), name
+
+
+@pytest.mark.gpu
+def test_export_command_line(built_lib, tmp_path, capsys):
+    """The exporter's command line (flags and exit status of the reference's export.py:15-61)."""
+    from nativebit_b200 import export
+    out = tmp_path / "cli.nbpack"
+    rc = export.main(["--checkpoint", os.path.join(GOLD, "tiny_ckpt.pt"), "--output", str(out), "--verify", "--device", "cuda:0"])
+    text = capsys.readouterr().out
+    assert rc == 0 and out.exists() and "Status:           PASS" in text and "Bit width:            3-bit" in text
