@@ -326,7 +326,7 @@ def run_ours(args):
         for _ in range(args.warmup):
             step_fn()
     probe = timed(step_fn, args.steps)
-    blocks = max(N_BLOCKS, int(MIN_TIMED_S * 1e3 / max(probe, 1e-3)) + 1)
+    blocks = max(args.blocks, int(args.min_timed_s * 1e3 / max(probe, 1e-3)) + 1)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -462,7 +462,7 @@ def run_ours(args):
                 del g
             roofline = {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
                         "traffic": NCU_TRAFFIC_STEP,
-                        "kernel": "nb::stream_kernel<3>, one launch = the 78 matrices of a step",
+                        "kernel": "nb::group_kernel<3>, one launch = the 78 matrices of a step",
                         "us_per_launch": ms_per_step * 1e3, "algorithmic_bytes": int(step_bytes), "peak_source": peak_src,
                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch over 20 matrices of 6912x2560 "
                                           "(one ncu capture), scaled by algorithmic bytes to the 78 matrices of a step",
@@ -613,9 +613,11 @@ def run_ours(args):
 
     # ---- serving sweep (configs[4]): batch 1/8/32/64 decode after a 512-token prompt, 3-bit and 2-bit
     serving = None
-    if args.serving:
+    compact = world == 8 and not args.serving and not args.no_decode      # the 8-GPU line always carries batch 8 and 64
+    if args.serving or compact:
         from nativebit_b200 import generate as G
-        serving = {}
+        serving = {"prompt_tokens": 512, "n_generate": 64, "tp": world,
+                   "linears": "up to 16 sequences: fused GEMV; more: the tensor-core kernel that dequantises inside (exact fp16 weights)"}
         for bits in (3, 2):
             cfg = G.ModelConfig(bits=bits)
             model = G.PackedGPT.random_init(cfg, seed=0, device=dev, tp_rank=rank, tp_size=world)
@@ -624,19 +626,12 @@ def run_ours(args):
             if world > 1 and args.allreduce == "fused":
                 model.enable_fused_allreduce(max_batch=8)
             prompt = torch.randint(0, cfg.vocab_size, (512,), generator=torch.Generator().manual_seed(1))
-            for b in (1, 8, 32, 64):
+            for b in ((8, 64) if compact else (1, 8, 32, 64)):
                 res = G.benchmark(model, prompt, n_generate=64, n_runs=1, batch_size=b)
                 t = torch.tensor([res["per_token_ms"]], device=dev)
                 if world > 1:
                     dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 serving[f"{bits}bit_b{b}"] = {"ms_per_step": round(float(t), 3), "tokens_per_s": round(b * 1e3 / float(t), 1)}
-                if b >= 32:   # the same batch with the packed linears on the tcgen05 GEMM (bf16 operands)
-                    res = G.benchmark(model, prompt, n_generate=64, n_runs=1, batch_size=b, batch_gemm=True)
-                    t = torch.tensor([res["per_token_ms"]], device=dev)
-                    if world > 1:
-                        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                    serving[f"{bits}bit_b{b}_bf16_gemm"] = {"ms_per_step": round(float(t), 3),
-                                                            "tokens_per_s": round(b * 1e3 / float(t), 1)}
             del model
             torch.cuda.empty_cache()
 
@@ -804,6 +799,9 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--blocks", type=int, default=N_BLOCKS, help="timed blocks of --steps steps each (the median block is reported)")
+    ap.add_argument("--min-timed-s", type=float, default=MIN_TIMED_S,
+                    help="lower bound of the timed region in seconds (more blocks are added to reach it; 0 for short profiling runs)")
     ap.add_argument("--chain", action="store_true", help="time the graph of one launch per matrix instead of the persistent kernel")
     ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "fused", "nccl"],
                     help="tensor-parallel all-reduce of the decoder: the one-shot peer-memory kernel (default, the fastest "

@@ -129,7 +129,9 @@ int nb_gemm_prefill(const void* x, int x_dtype, int M, const uint8_t* packed, co
  * inference/triton_kernel.py:258-275; tile-wise dequantise-and-contract as in
  * nativebit_jax/packed_kernel.py:135-178; exact fp16 weights, fp32 accumulation) for any M >= 1, but the
  * weights are given in the stream layout (nb_stream_pack with row_mode 0) instead of the pack.py bytes.
- * x: (M, K) NB_F16 or NB_BF16 (bf16 is converted to fp16 into the workspace first), 16-byte aligned;
+ * x: (M, K) NB_F16, NB_BF16 (converted to fp16 into the workspace first) or NB_F32 (carried as two fp16 terms per
+ * element, hi = fp16(x) and lo = fp16(x - hi), as two operand rows whose results the kernel adds: about 22
+ * significant bits, as in nb_gemv), 16-byte aligned;
  * K % 128 == 0; y: (M, N) NB_BF16 or NB_F32.  workspace: nb_prefill_fused_workspace_bytes(M, K) bytes,
  * 256-byte aligned; its first 256 bytes carry a status word (zero before the first call; NB_ERR_TIMEOUT
  * if a bounded wait inside the kernel ran out). */
@@ -329,6 +331,29 @@ int nb_stream_ctas(void);
 int nb_stream_slots(int N, int K, int ctas);
 int nb_stream_run(const nb_stream_op* ops_host, const nb_stream_op* ops_device, int n_ops, void* state, uint32_t spin_limit,
                   void* stream);
+
+/* ---- a group of INDEPENDENT packed matvecs in one launch (none reads another's output): y_i = W_i x_i for one
+ * activation vector each.  The reference runs one launch per matrix (inference/triton_kernel.py:240-256,
+ * inference/cuda_kernel.py:84-104); here the row tiles of all matrices form one sequence that the CTAs share
+ * by weight bytes, a warp computes a whole 16-row tile from the first k-block to the last with the sums in
+ * registers, and nothing waits on anything but its own copies (no flags, no status word needed).
+ * Weights are nb_stream_pack copies (row_mode 0), all of one `bits`; x: k values of x_dtype (NB_F32 carried as
+ * two fp16 terms), 16-byte aligned, K % 128 == 0 and K <= 7168; y: n values of y_dtype.  At most
+ * nb_group_max_items() matvecs and 6 distinct activation vectors whose staged copies fit 96 KB of shared
+ * memory (a K-element vector takes K * 2.5 bytes per fp16 term, the first term of an fp32 vector 17920 bytes).
+ * nb_group_build validates the list and writes the launch plan (nb_group_plan_bytes() bytes) into host
+ * memory; the caller copies it to device memory once and passes both copies to nb_group_run (the host
+ * copy for the launch geometry).  Results are bit-identical from run to run. */
+typedef struct {
+  const void* w;
+  const void* x;
+  void* y;
+  int32_t n, k, x_dtype, y_dtype;
+} nb_group_item;
+size_t nb_group_plan_bytes(void);
+int nb_group_max_items(void);
+int nb_group_build(const nb_group_item* items, int n_items, int bits, void* plan_out, size_t plan_bytes);
+int nb_group_run(const void* plan_device, const void* plan_host, void* stream);
 
 /* Launch geometry nb_gemv will use for a shape on the current device (no launch; works without
  * a GPU, assuming 148 SMs): out6 = {grid.x, grid.y (k partitions), threads per CTA, dynamic

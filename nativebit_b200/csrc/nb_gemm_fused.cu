@@ -74,7 +74,7 @@ template <int BITS> struct FusedFmt {
 template <int BITS>
 __global__ void __launch_bounds__(kFThreads, 1)
 gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_stream, void* __restrict__ y, int y_dtype,
-                  int M, int N, int K, int BN, int m_tiles, int w_tiles, int* status) {
+                  int M, int N, int K, int BN, int m_tiles, int w_tiles, int pair, int* status) {
   using F = FusedFmt<BITS>;
   constexpr int kT = BITS == 4 ? 8 : 4;
   const int S = fused_stages(BN);
@@ -182,7 +182,19 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
               "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (n < N) {
+        if (n < N && pair) {
+          // rows 2i and 2i+1 of the operand are the two fp16 terms of activation row i: their results are added
+          const int mb = (m0 + c * 16) >> 1;
+          const int m_out = M >> 1;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (mb + j < m_out) {
+              const float v = __uint_as_float(r[2 * j]) + __uint_as_float(r[2 * j + 1]);
+              if (y_dtype == NB_BF16) reinterpret_cast<__nv_bfloat16*>(y)[(size_t)(mb + j) * N + n] = __float2bfloat16_rn(v);
+              else reinterpret_cast<float*>(y)[(size_t)(mb + j) * N + n] = v;
+            }
+          }
+        } else if (n < N) {
           const int mb = m0 + c * 16;
           if (y_dtype == NB_BF16) {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(y) + (size_t)mb * N + n;
@@ -285,6 +297,26 @@ __global__ void __launch_bounds__(256) bf16_to_f16_kernel2(const uint4* __restri
   out[i] = make_uint4(r[0], r[1], r[2], r[3]);
 }
 
+// fp32 -> two fp16 terms per element, hi = fp16(x) (saturating) and lo = fp16(x - hi), written as rows 2i and
+// 2i+1 of a (2M, K) fp16 matrix: x = hi + lo to about 22 significant bits.  Eight elements per thread.
+__global__ void __launch_bounds__(256) f32_to_f16_pair_kernel(const float4* __restrict__ in, uint4* __restrict__ out, int M, int K) {
+  const int k8 = K >> 3;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)M * k8) return;
+  const int row = (int)(i / k8), c = (int)(i - (size_t)row * k8);
+  const float4 a = in[2 * i], b = in[2 * i + 1];
+  const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  uint32_t hi[4], lo[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    hi[j] = f32x2_to_f16x2_sat(v[2 * j], v[2 * j + 1]);
+    const float2 h = __half22float2(*reinterpret_cast<const __half2*>(&hi[j]));
+    lo[j] = f32x2_to_f16x2_sat(v[2 * j] - h.x, v[2 * j + 1] - h.y);
+  }
+  out[(size_t)(2 * row) * k8 + c] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+  out[(size_t)(2 * row + 1) * k8 + c] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+}
+
 // Token-tile width (a multiple of 16 up to 256).  A k-step costs the longer of the tensor-core time, 2 * BN
 // clocks, and the time the producers need to fill a stage, which does not depend on BN (measured: about
 // kProducerClocks); the tile width that minimises waves * max(2 * BN, kProducerClocks) is chosen, the
@@ -319,13 +351,13 @@ extern "C" int nb_fused_trace_read(long long* host) { return (int)cudaMemcpyFrom
 
 extern "C" size_t nb_prefill_fused_workspace_bytes(int M, int K) {
   if (M < 1 || K < 1) return 0;
-  return 256 + (size_t)M * K * 2;   // status word (first 256 bytes) + fp16 copy of bf16 activations
+  return 256 + (size_t)2 * M * K * 2;   // status word (first 256 bytes) + fp16 copy of the activations (two terms for fp32)
 }
 
 extern "C" int nb_gemm_prefill_fused(const void* x, int x_dtype, int M, const uint8_t* w_stream, int bits, int N, int K, void* y,
                                      int y_dtype, void* workspace, size_t workspace_bytes, void* stream) {
   if (!x || !w_stream || !y || M < 1 || N < 1 || K < 1) return NB_ERR_ARG;
-  if (x_dtype != NB_BF16 && x_dtype != NB_F16) return NB_ERR_ARG;
+  if (x_dtype != NB_BF16 && x_dtype != NB_F16 && x_dtype != NB_F32) return NB_ERR_ARG;
   if (y_dtype != NB_BF16 && y_dtype != NB_F32) return NB_ERR_ARG;
   if (bits != 2 && bits != 3 && bits != 4) return NB_ERR_SHAPE;
   if (K % kBlock != 0) return NB_ERR_SHAPE;
@@ -334,17 +366,24 @@ extern "C" int nb_gemm_prefill_fused(const void* x, int x_dtype, int M, const ui
   if (int rc = check_device()) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   const void* xh = x;
+  const int pair = x_dtype == NB_F32 ? 1 : 0;
+  const int rows = pair ? 2 * M : M;              // rows of the fp16 operand
+  uint8_t* dst = reinterpret_cast<uint8_t*>(workspace) + 256;
   if (x_dtype == NB_BF16) {
-    uint8_t* dst = reinterpret_cast<uint8_t*>(workspace) + 256;
     const size_t n8 = (size_t)M * K / 8;
     bf16_to_f16_kernel2<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(dst), n8);
     if (int rc = check_launch()) return rc;
     xh = dst;
+  } else if (x_dtype == NB_F32) {
+    const size_t n8 = (size_t)M * K / 8;
+    f32_to_f16_pair_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(reinterpret_cast<const float4*>(x), reinterpret_cast<uint4*>(dst), M, K);
+    if (int rc = check_launch()) return rc;
+    xh = dst;
   }
-  const int bn = pick_token_tile(M, N, sm_count());
+  const int bn = pick_token_tile(rows, N, sm_count());
   CUtensorMap mx;
-  if (int rc = make_map_f16(&mx, xh, M, K, bn)) return rc;
-  const int m_tiles = (M + bn - 1) / bn, w_tiles = (N + kFM - 1) / kFM;
+  if (int rc = make_map_f16(&mx, xh, rows, K, bn)) return rc;
+  const int m_tiles = (rows + bn - 1) / bn, w_tiles = (N + kFM - 1) / kFM;
   const int grid = std::min(sm_count(), m_tiles * w_tiles);
   int* status = reinterpret_cast<int*>(workspace);
   static bool attr_done[64][5] = {};
@@ -355,8 +394,8 @@ extern "C" int nb_gemm_prefill_fused(const void* x, int x_dtype, int M, const ui
     if (cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kFSmem)) return record_cuda_error(e);
     attr_done[dev & 63][bits] = true;
   }
-  if (bits == 3) gemm_fused_kernel<3><<<grid, kFThreads, kFSmem, st>>>(mx, w_stream, y, y_dtype, M, N, K, bn, m_tiles, w_tiles, status);
-  else if (bits == 2) gemm_fused_kernel<2><<<grid, kFThreads, kFSmem, st>>>(mx, w_stream, y, y_dtype, M, N, K, bn, m_tiles, w_tiles, status);
-  else gemm_fused_kernel<4><<<grid, kFThreads, kFSmem, st>>>(mx, w_stream, y, y_dtype, M, N, K, bn, m_tiles, w_tiles, status);
+  if (bits == 3) gemm_fused_kernel<3><<<grid, kFThreads, kFSmem, st>>>(mx, w_stream, y, y_dtype, rows, N, K, bn, m_tiles, w_tiles, pair, status);
+  else if (bits == 2) gemm_fused_kernel<2><<<grid, kFThreads, kFSmem, st>>>(mx, w_stream, y, y_dtype, rows, N, K, bn, m_tiles, w_tiles, pair, status);
+  else gemm_fused_kernel<4><<<grid, kFThreads, kFSmem, st>>>(mx, w_stream, y, y_dtype, rows, N, K, bn, m_tiles, w_tiles, pair, status);
   return check_launch();
 }

@@ -1045,6 +1045,191 @@ __global__ void __launch_bounds__(256) stream_pack_kernel(const uint8_t* __restr
   }
 }
 
+
+// ====================================================================================================
+// Independent matvecs: one warp per row tile
+// ====================================================================================================
+// A group of packed matvecs none of which reads another's result (the gate, up and down matrices of many
+// layers against given activations; the reference runs each as its own launch,
+// inference/triton_kernel.py:240-256).  Without dependencies no operation boundary is needed at all: the
+// row tiles (16 rows x K) of ALL matrices form one sequence, every CTA owns a contiguous stretch of it
+// (equal shares of the weight bytes), and its warps take row tiles from that stretch one at a time.  A warp
+// streams the units of its tile through its own ring of asynchronous copies and keeps the tile's 16 sums in
+// its accumulator registers from the first unit to the last: no partial sums in shared memory, no tickets,
+// no flags, no barrier after the activations are staged, and no wait that could fail to end.  Every output
+// is the sum of its units in index order whichever warp computes it: bit-identical from run to run.
+constexpr int kGroupMaxItems = 256;
+constexpr int kGroupMaxX = 6;
+constexpr int kGroupXBytes = 96 * 1024;                   // shared memory for the staged activation vectors
+constexpr int kGroupFifo = 8;                             // row tiles a warp may have taken ahead of its arithmetic
+constexpr int kGroupSmem = kRingBytes + kGroupXBytes;
+
+struct GroupItem {            // 48 bytes
+  const uint8_t* w;           // stream-layout weights
+  void* y;                    // outputs
+  int n, bpr;                 // rows, k-blocks per row
+  int tile0;                  // index of the matrix' first row tile in the sequence of all row tiles
+  int x_off;                  // byte offset of its staged activations in shared memory
+  int xs;                     // fp16 terms per activation (2: fp32 activations)
+  int y_dtype;
+  int pad[2];
+};
+struct GroupX {               // 24 bytes: one distinct activation vector
+  const void* ptr;
+  int k, dtype, off, xs;
+};
+struct GroupPlan {
+  int n_items, n_x, total_tiles, ctas, bits, pad[3];
+  GroupX xv[kGroupMaxX];
+  int cta_lo[kMaxCtas + 1];   // CTA c owns row tiles [cta_lo[c], cta_lo[c + 1])
+  GroupItem items[kGroupMaxItems];
+};
+
+template <int BITS>
+__global__ void __launch_bounds__(kSThreads, 1) group_kernel(const GroupPlan* __restrict__ plan) {
+  using F = UnitFmt<BITS>;
+  constexpr int D = F::kStages;                           // ring stages per warp
+  static_assert(D >= 4, "the per-warp ring needs at least four stages");
+  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ int s_next;
+  __shared__ int s_tile0[kGroupMaxItems + 1];
+  __shared__ int s_fifo[kSW][kGroupFifo];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* ring = smem + warp * (D * F::kBytes);
+  uint8_t* x_all = smem + kRingBytes;
+  const int n_items = plan->n_items;
+  const int t_lo = plan->cta_lo[blockIdx.x], t_hi = plan->cta_lo[blockIdx.x + 1];
+
+  // ---- the activation vectors, staged once for the whole launch (fp16 terms in k order, one segment per
+  // lane share of a k-block)
+  for (int v = 0; v < plan->n_x; ++v) {
+    const GroupX xv = plan->xv[v];
+    uint8_t* x_s = x_all + xv.off;
+    for (int i4 = tid; i4 < xv.k / 4; i4 += kSThreads) {
+      float u[4];
+      if (xv.dtype == NB_F32) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(xv.ptr) + i4);
+        u[0] = a.x; u[1] = a.y; u[2] = a.z; u[3] = a.w;
+        stage4<2>(x_s, i4, u[0], u[1], u[2], u[3]);
+      } else {
+        const uint2 r = __ldg(reinterpret_cast<const uint2*>(xv.ptr) + i4);
+        if (xv.dtype == NB_BF16) {
+          u[0] = __uint_as_float(r.x << 16); u[1] = __uint_as_float(r.x & 0xFFFF0000u);
+          u[2] = __uint_as_float(r.y << 16); u[3] = __uint_as_float(r.y & 0xFFFF0000u);
+        } else {
+          const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&r.x));
+          const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+          u[0] = f0.x; u[1] = f0.y; u[2] = f1.x; u[3] = f1.y;
+        }
+        stage4<1>(x_s, i4, u[0], u[1], u[2], u[3]);
+      }
+    }
+  }
+  for (int i = tid; i <= n_items; i += kSThreads) s_tile0[i] = i < n_items ? plan->items[i].tile0 : plan->total_tiles;
+  if (tid == 0) s_next = t_lo;
+  __syncthreads();
+
+  // matrix that holds row tile t: the last item whose first tile is <= t
+  auto item_of = [&](int t) {
+    int lo = 0, hi = n_items - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_tile0[mid] <= t) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+  };
+  // the warp takes the CTA's next row tile (or learns that none is left); all lanes get the same answer
+  auto take = [&]() {
+    int t = 0;
+    if (lane == 0) t = atomicAdd(&s_next, 1);
+    t = __shfl_sync(0xffffffffu, t, 0);
+    return t < t_hi ? t : -1;
+  };
+
+  // ---- the copy side: requests run D - 2 units ahead of the arithmetic
+  int fifo_w = 0, fifo_r = 0;                              // tiles taken / tiles started (uniform in the warp)
+  const uint8_t* f_src = nullptr;                          // next unit to request
+  int f_left = 0;                                          // units of the current copy-side tile still to request
+  bool f_done = false;
+  int requested = 0, consumed = 0;                         // units requested / used so far (ring positions)
+  auto request_one = [&]() {
+    if (f_left == 0 && !f_done) {
+      const int t = take();
+      if (t < 0) {
+        f_done = true;
+      } else {
+        if (lane == 0) s_fifo[warp][fifo_w & (kGroupFifo - 1)] = t;
+        ++fifo_w;
+        const GroupItem& it = plan->items[item_of(t)];
+        f_left = it.bpr;
+        f_src = it.w + (size_t)(t - it.tile0) * it.bpr * F::kBytes;
+      }
+    }
+    if (f_left > 0) {
+      uint8_t* dst = ring + (requested % D) * F::kBytes;
+      constexpr int kChunks = F::kBytes / 16;
+#pragma unroll
+      for (int i = 0; i < (kChunks + 31) / 32; ++i)
+        if (i * 32 + 32 <= kChunks || lane + i * 32 < kChunks) cp_async16(dst + 16 * (lane + i * 32), f_src + 16 * (lane + i * 32));
+      f_src += F::kBytes;
+      --f_left;
+    }
+    ++requested;                                           // a group is closed even when nothing was left to request
+    cp_async_commit();
+  };
+#pragma unroll 1
+  for (int i = 0; i < D - 2; ++i) request_one();
+
+  // ---- the arithmetic side
+#pragma unroll 1
+  while (true) {
+    // The copy side is D - 2 >= 2 requests ahead, and the first request after a tile's last unit takes the next
+    // tile: when no taken tile is waiting here, the CTA's stretch is exhausted.
+    if (fifo_r == fifo_w) break;
+    __syncwarp();
+    const int t = s_fifo[warp][fifo_r & (kGroupFifo - 1)];
+    ++fifo_r;
+    const GroupItem it = plan->items[item_of(t)];
+    const int rt = t - it.tile0;
+    const uint8_t* x_s = x_all + it.x_off;
+    float c0[2][4], c1[2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { c0[h][e] = 0.f; c1[h][e] = 0.f; }
+#pragma unroll 1
+    for (int j = 0; j < it.bpr;) {
+      const int nb = it.bpr - j >= 2 ? 2 : 1;
+      request_one();
+      if (nb == 2) request_one();
+      cp_async_wait<D - 2>();                              // all but the newest D - 2 requests have landed: units `consumed` (+1)
+      __syncwarp();
+      const uint8_t* u0 = ring + (consumed % D) * F::kBytes;
+      const uint8_t* u1 = ring + ((consumed + 1) % D) * F::kBytes;
+      if (it.xs == 2) {
+        if (nb == 2) unit_mma2<BITS, 2>(u0, u1, x_s, j, j + 1, lane, c0, c1);
+        else unit_mma<BITS, 2>(u0, x_s, j, lane, c0);
+      } else {
+        if (nb == 2) unit_mma2<BITS, 1>(u0, u1, x_s, j, j + 1, lane, c0, c1);
+        else unit_mma<BITS, 1>(u0, x_s, j, lane, c0);
+      }
+      consumed += nb;
+      j += nb;
+      __syncwarp();                                        // every lane is done with these stages before they are requested again
+    }
+    // all eight columns of the accumulator tile hold the same sums; lanes t == 0 write rows g and g + 8
+    if ((lane & 3) == 0) {
+      const int g = lane >> 2;
+      const int ra = rt * 16 + g, rb = ra + 8;
+      const float ya = (c0[0][0] + c0[1][0]) + (c1[0][0] + c1[1][0]);
+      const float yb = (c0[0][2] + c0[1][2]) + (c1[0][2] + c1[1][2]);
+      if (ra < it.n) store_y(it.y, it.y_dtype, (size_t)ra, ya);
+      if (rb < it.n) store_y(it.y, it.y_dtype, (size_t)rb, yb);
+    }
+  }
+  cp_async_wait<0>();
+}
+
 }  // namespace nb
 
 using namespace nb;
@@ -1190,4 +1375,101 @@ extern "C" int nb_stream_run(const nb_stream_op* ops_host, const nb_stream_op* o
   if (bits == 3) return record_cuda_error(cudaLaunchKernelEx(&cfg, stream_kernel<3>, ops_device, n_ops, st, spin));
   if (bits == 2) return record_cuda_error(cudaLaunchKernelEx(&cfg, stream_kernel<2>, ops_device, n_ops, st, spin));
   return record_cuda_error(cudaLaunchKernelEx(&cfg, stream_kernel<4>, ops_device, n_ops, st, spin));
+}
+
+// ---- independent matvecs: plan on the host, run from device memory ----------------------------------
+extern "C" size_t nb_group_plan_bytes(void) { return sizeof(GroupPlan); }
+
+extern "C" int nb_group_max_items(void) { return kGroupMaxItems; }
+
+extern "C" int nb_group_build(const nb_group_item* items, int n_items, int bits, void* plan_out, size_t plan_bytes) {
+  auto fail = [&](int index, const char* why) {
+    char msg[200];
+    std::snprintf(msg, sizeof(msg), "nb_group_build: matvec %d: %s", index, why);
+    set_last_error(msg);
+    return (int)NB_ERR_SHAPE;
+  };
+  if (!items || !plan_out || n_items < 1) return NB_ERR_ARG;
+  if (n_items > kGroupMaxItems) return fail(n_items, "too many matvecs for one launch");
+  if (bits != 2 && bits != 3 && bits != 4) return NB_ERR_SHAPE;
+  if (plan_bytes < sizeof(GroupPlan)) return NB_ERR_WORKSPACE;
+  GroupPlan* pl = reinterpret_cast<GroupPlan*>(plan_out);
+  std::memset(pl, 0, sizeof(GroupPlan));
+  const int G = nb_stream_ctas();
+  pl->n_items = n_items; pl->bits = bits; pl->ctas = G;
+  long long tiles = 0, units = 0;
+  int x_bytes = 0;
+  for (int i = 0; i < n_items; ++i) {
+    const nb_group_item& in = items[i];
+    if (!in.w || !in.x || !in.y) return fail(i, "null pointer");
+    if ((uintptr_t)in.w % 16 || (uintptr_t)in.x % 16) return fail(i, "weights and activations must be 16-byte aligned");
+    if (in.n < 1 || in.k < kBlock || in.k % kBlock || in.k / kBlock > kMaxKBlocks) return fail(i, "needs N >= 1 and K a multiple of 128 up to 7168");
+    if (in.x_dtype != NB_F32 && in.x_dtype != NB_F16 && in.x_dtype != NB_BF16) return fail(i, "unknown activation type");
+    if (in.y_dtype != NB_F32 && in.y_dtype != NB_F16 && in.y_dtype != NB_BF16) return fail(i, "unknown output type");
+    int v = 0;
+    for (; v < pl->n_x; ++v)
+      if (pl->xv[v].ptr == in.x && pl->xv[v].k == in.k && pl->xv[v].dtype == in.x_dtype) break;
+    if (v == pl->n_x) {
+      if (v == kGroupMaxX) return fail(i, "too many distinct activation vectors for one launch");
+      const int xs = in.x_dtype == NB_F32 ? 2 : 1;
+      // a vector's terms are kXTermBytes apart (the lookup code's fixed stride); the last term is cut to its length
+      const int need = (xs - 1) * kXTermBytes + (in.k / kBlock) * 4 * kXSegBytes;
+      if (x_bytes + need > kGroupXBytes) return fail(i, "the activation vectors of the group do not fit in shared memory");
+      pl->xv[v].ptr = in.x; pl->xv[v].k = in.k; pl->xv[v].dtype = in.x_dtype; pl->xv[v].off = x_bytes; pl->xv[v].xs = xs;
+      x_bytes += (need + 127) / 128 * 128;
+      pl->n_x = v + 1;
+    }
+    GroupItem& it = pl->items[i];
+    it.w = reinterpret_cast<const uint8_t*>(in.w); it.y = in.y; it.n = in.n; it.bpr = in.k / kBlock;
+    it.tile0 = (int)tiles; it.x_off = pl->xv[v].off; it.xs = pl->xv[v].xs; it.y_dtype = in.y_dtype;
+    tiles += (in.n + 15) / 16;
+    units += (long long)((in.n + 15) / 16) * it.bpr;
+    if (tiles > (1ll << 30)) return fail(i, "too many row tiles");
+  }
+  pl->total_tiles = (int)tiles;
+  // equal shares of the units (= weight bytes), cut at the nearest row-tile boundary
+  pl->cta_lo[0] = 0;
+  int item = 0;
+  long long unit0 = 0;   // units before `item`
+  for (int c = 1; c < G; ++c) {
+    const long long target = units * c / G;
+    while (item < n_items - 1) {
+      const long long item_units = (long long)((pl->items[item].n + 15) / 16) * pl->items[item].bpr;
+      if (unit0 + item_units > target) break;
+      unit0 += item_units;
+      ++item;
+    }
+    const GroupItem& it = pl->items[item];
+    const int rt = (it.n + 15) / 16;
+    long long k = (target - unit0 + it.bpr / 2) / it.bpr;
+    if (k < 0) k = 0;
+    if (k > rt) k = rt;
+    pl->cta_lo[c] = std::max(pl->cta_lo[c - 1], it.tile0 + (int)k);
+  }
+  for (int c = G; c <= kMaxCtas; ++c) pl->cta_lo[c] = (int)tiles;
+  return NB_OK;
+}
+
+extern "C" int nb_group_run(const void* plan_device, const void* plan_host, void* stream) {
+  if (!plan_device || !plan_host) return NB_ERR_ARG;
+  if ((uintptr_t)plan_device % 16) return NB_ERR_ALIGN;
+  if (int rc = check_device()) return rc;
+  const GroupPlan* pl = reinterpret_cast<const GroupPlan*>(plan_host);
+  const int bits = pl->bits, G = pl->ctas;
+  if ((bits != 2 && bits != 3 && bits != 4) || G < 1 || G > kMaxCtas || pl->n_items < 1 || pl->n_items > kGroupMaxItems) return NB_ERR_ARG;
+  if (G != nb_stream_ctas()) { set_last_error("nb_group_run: the plan was built for another device"); return NB_ERR_ARG; }
+  static bool attr_done[64][5] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const void* fn = bits == 3 ? (const void*)group_kernel<3> : bits == 2 ? (const void*)group_kernel<2> : (const void*)group_kernel<4>;
+  if (!attr_done[dev & 63][bits]) {
+    if (cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kGroupSmem)) return record_cuda_error(e);
+    attr_done[dev & 63][bits] = true;
+  }
+  const GroupPlan* pd = reinterpret_cast<const GroupPlan*>(plan_device);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bits == 3) group_kernel<3><<<G, kSThreads, kGroupSmem, st>>>(pd);
+  else if (bits == 2) group_kernel<2><<<G, kSThreads, kGroupSmem, st>>>(pd);
+  else group_kernel<4><<<G, kSThreads, kGroupSmem, st>>>(pd);
+  return check_launch();
 }

@@ -50,6 +50,10 @@ class ModelConfig:
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    if x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and x.shape[-1] <= 4096 and weight.dtype == torch.float32:
+        out = torch.empty_like(x)                      # one kernel instead of five element-wise launches
+        ops.add_rmsnorm(x.view(-1, x.shape[-1]), None, weight, eps, out.view(-1, x.shape[-1]))
+        return out
     xf = x.float()
     return xf / torch.sqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * weight
 
@@ -158,8 +162,13 @@ class PackedGPT(torch.nn.Module):
             attn_out = padded
         x = x + self._all_reduce(blk.out_proj(attn_out).float())
         gu = blk.gate_up(rms_norm(x, blk.ln2, self.config.norm_eps)).float()
-        gate, up = gu.split(gu.shape[-1] // 2, dim=-1)
-        return x + self._all_reduce(blk.down(F.silu(gate) * up).float())
+        if gu.is_cuda and gu.is_contiguous():
+            act = torch.empty(*gu.shape[:-1], gu.shape[-1] // 2, dtype=torch.float32, device=gu.device)
+            ops.silu_mul(gu.view(-1, gu.shape[-1]), act.view(-1, act.shape[-1]))
+        else:
+            gate, up = gu.split(gu.shape[-1] // 2, dim=-1)
+            act = F.silu(gate) * up
+        return x + self._all_reduce(blk.down(act).float())
 
     def _head(self, x: torch.Tensor, rows: tuple[int, int] | None = None) -> torch.Tensor:
         """x (..., C) fp32 @ embedding.T with fp32 accumulation and an fp32 result.  A bf16 table is
@@ -184,9 +193,10 @@ class PackedGPT(torch.nn.Module):
 
     # ------------------------------------------------------------------ eager forward (prefill, tests)
     @torch.no_grad()
-    def forward(self, idx: torch.Tensor, kv_caches=None):
+    def forward(self, idx: torch.Tensor, kv_caches=None, last_only: bool = False):
         """idx (B, T) int64 -> logits (B, T, V) fp32 [, new caches].  kv_caches: list of
-        (k_buf, v_buf, cache_len) as returned by init_kv_cache."""
+        (k_buf, v_buf, cache_len) as returned by init_kv_cache.  last_only: logits of the last position
+        only, (B, 1, V) (what a decode loop needs from its prompt)."""
         B, T = idx.shape
         x = self.embedding[idx].float()
         new_caches = []
@@ -206,7 +216,7 @@ class PackedGPT(torch.nn.Module):
                 q, k, v = self._attn_inputs(x, blk, 0, T)
                 out = F.scaled_dot_product_attention(q, k, v, is_causal=True)
             x = self._finish_block(x, blk, out.transpose(1, 2).reshape(B, T, -1))
-        logits = self._logits(x)
+        logits = self._logits(x[:, -1:, :].contiguous() if last_only else x)
         return (logits, new_caches) if kv_caches is not None else logits
 
     # ------------------------------------------------------------------ construction
@@ -411,7 +421,7 @@ class DecodeSession:
         if prompt.shape[1] > self.model.context_len:
             raise RuntimeError(f"prompt of {prompt.shape[1]} tokens exceeds the context of {self.model.context_len}")
         caches = [(k, v, 0) for k, v, _ in self.caches]
-        logits, caches = self.model(prompt, kv_caches=caches)
+        logits, caches = self.model(prompt, kv_caches=caches, last_only=True)
         self.caches = caches
         self.pos.fill_(prompt.shape[1])
         self.pos_host = int(prompt.shape[1])

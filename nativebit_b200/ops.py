@@ -279,24 +279,15 @@ def gemm_prefill(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, 
 def gemm_prefill_fused(x: torch.Tensor, w_stream: torch.Tensor, bits: int, n: int, k: int,
                        out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """y (M, n) = x (M, k) @ W.T with the dequantisation fused into the tcgen05 kernel; w_stream is the
-    stream-layout copy of the packed weight (stream.stream_pack).  x fp16 or bf16; fp32 activations are
-    carried as the sum of two fp16 terms stacked into one (2M, k) operand (as in gemm_prefill)."""
+    stream-layout copy of the packed weight (stream.stream_pack).  x fp16, bf16 or fp32; the library carries
+    fp32 activations as two fp16 terms per element (rows 2i, 2i+1 of the operand) and adds their results."""
     _need_cuda(x, w_stream)
     if x.dim() != 2 or x.shape[1] != k:
         raise RuntimeError(f"x must be an (M, {k}) tensor; got {tuple(x.shape)}")
-    if x.dtype == torch.float32:
-        xc = x.clamp(-65504.0, 65504.0)
-        hi = xc.half()
-        lo = (xc - hi.float()).half()
-        m = x.shape[0]
-        y2 = gemm_prefill_fused(torch.cat((hi, lo)), w_stream, bits, n, k, out_dtype=torch.float32)
-        y = y2[:m].add_(y2[m:])
-        if out is not None:
-            out.copy_(y)
-            return out
-        return y if out_dtype in (torch.float32, None) else y.to(out_dtype)
-    if x.dtype not in (torch.bfloat16, torch.float16):
+    if x.dtype not in (torch.bfloat16, torch.float16, torch.float32):
         raise RuntimeError(f"unsupported activation dtype {x.dtype}")
+    if not x.is_contiguous():
+        x = x.contiguous()
     if out_dtype is None:
         out_dtype = out.dtype if out is not None else x.dtype
     if out is None and out_dtype == torch.float16:     # the kernel writes bf16 or fp32

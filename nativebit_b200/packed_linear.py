@@ -18,6 +18,7 @@ BS = 128      # weights per codebook block
 NE = 8        # codebook entries per block at 3 bits
 TILE_N = 32   # kept for signature compatibility; the B200 kernels pick their own tiling
 GEMV_MAX_M = 16
+FUSED_MAX_ROWS = 1024   # up to this many activation rows the weights are dequantised inside the GEMM kernel
 
 
 def pack_indices_to_3bit(indices_uint8: torch.Tensor) -> torch.Tensor:
@@ -97,10 +98,16 @@ class PackedLinear(torch.nn.Module):
         return w
 
     def _forward_many(self, x_flat):
-        """M > 16 rows: one pass over the weights, dequantised inside the tcgen05 kernel (exact fp16 weights;
-        bf16 and fp16 activations as given, fp32 carried as two fp16 terms; fp32 accumulation; result in
-        x's dtype)."""
+        """M > 16 rows on the tcgen05 kernels (exact fp16 weights; bf16 and fp16 activations as given, fp32
+        carried as two fp16 terms; fp32 accumulation; result in x's dtype): one pass over the packed weights,
+        dequantised inside the kernel, up to FUSED_MAX_ROWS rows; dequantise-once + GEMM beyond."""
         if self.in_features % BS == 0 and self.bits in (2, 3, 4):
+            rows = x_flat.shape[0] * (2 if x_flat.dtype == torch.float32 else 1)
+            if rows > FUSED_MAX_ROWS:
+                # long inputs: dequantising W once into a scratch copy (12 us for 6912 x 2560) and running the plain
+                # tensor-core kernel measures faster than dequantising every weight tile once per 256 rows
+                return ops.gemm_prefill(x_flat, self.packed_indices, self.codebook, self.bits, self.block_size,
+                                        self.out_features, self.in_features, out_dtype=x_flat.dtype)
             return ops.gemm_prefill_fused(x_flat, self.stream_weight(), self.bits, self.out_features, self.in_features,
                                           out_dtype=x_flat.dtype)
         wdt = x_flat.dtype if x_flat.dtype in (torch.float16, torch.bfloat16) else torch.float32

@@ -194,11 +194,18 @@ def stream_supported(model, batch_size: int) -> bool:
             and 5 * cfg.n_layers + 2 <= int(_lib.lib().nb_stream_max_ops()))
 
 
+class GroupItem(ctypes.Structure):
+    """Mirror of nb_group_item (include/nativebit_b200.h)."""
+    _fields_ = [("w", ctypes.c_void_p), ("x", ctypes.c_void_p), ("y", ctypes.c_void_p),
+                ("n", ctypes.c_int32), ("k", ctypes.c_int32), ("x_dtype", ctypes.c_int32), ("y_dtype", ctypes.c_int32)]
+
+
 class MatvecGroup:
-    """Independent packed matvecs y_i = W_i x_i at batch 1, executed by ONE launch of the persistent kernel:
-    the weights of all matrices stream through the SMs back to back, with no launch boundary between
-    matrices.  items: (PackedLinear, x (k,) or (1, k), out (n,) or (1, n)) triples; consecutive items that
-    read the same x share its staged copy.  The reference runs one library launch per matrix
+    """Independent packed matvecs y_i = W_i x_i at batch 1, executed by ONE launch (nb_group_run): the row
+    tiles of all matrices are dealt out to the CTAs by weight bytes and every warp computes whole 16-row tiles,
+    so the weights of all matrices stream through the SMs back to back with no launch or operation boundary
+    between them.  items: (PackedLinear, x (k,) or (1, k), out (n,) or (1, n)) triples; matrices that read the
+    same x share its staged copy.  The reference runs one library launch per matrix
     (inference/triton_kernel.py:240-256)."""
 
     def __init__(self, items, device=None):
@@ -206,39 +213,35 @@ class MatvecGroup:
         if not items:
             raise RuntimeError("MatvecGroup needs at least one matvec")
         dev = torch.device(device) if device is not None else items[0][1].device
-        if len(items) > int(_lib.lib().nb_stream_max_ops()):
-            raise RuntimeError(f"at most {int(_lib.lib().nb_stream_max_ops())} matvecs per launch")
-        self.prog = StreamProgram(dev)
-        G = n_ctas()
-        prev_x = None
-        split = []                       # (partial-sum slots, n, out) of the matvecs whose row tiles are shared between CTAs
-        for lin, x, out in items:
-            n, k = lin.out_features, lin.in_features
-            if lin.block_size != 128 or n % 16:
-                raise RuntimeError("MatvecGroup needs block size 128 and a multiple of 16 output rows")
-            if x.numel() != k or out.numel() != n:
-                raise RuntimeError("MatvecGroup runs one activation vector per matrix")
-            same = prev_x is not None and prev_x.data_ptr() == x.data_ptr() and prev_x.numel() == x.numel()
-            tiles = n // 16
-            if tiles >= 0.9 * (-(-tiles // G) * G):
-                # whole 16-row tiles per CTA keep the CTAs evenly loaded: every CTA stores its own outputs
-                self.prog.gemv_vec(lin.stream_weight(), n, k, lin.bits, x, out, reuse_x=same)
-            else:
-                # few row tiles: the units are dealt out evenly, CTAs that share a row tile write partial sums
-                sl = n_slots(n, k)
-                part = torch.empty(sl, n, dtype=torch.float32, device=dev)
-                self.prog.gemv_vec(lin.stream_weight(), n, k, lin.bits, x, part, reuse_x=same, slots=sl)
-                split.append((part, n, out))
-            prev_x = x
-        for j, (part, n, out) in enumerate(split):
-            self.prog.reduce(part, n, out.reshape(-1), wait=(j == 0))
+        l = _lib.lib()
+        if len(items) > int(l.nb_group_max_items()):
+            raise RuntimeError(f"at most {int(l.nb_group_max_items())} matvecs per launch")
+        bits = items[0][0].bits
+        arr = (GroupItem * len(items))()
+        self.keep = []
+        for i, (lin, x, out) in enumerate(items):
+            if lin.block_size != 128 or lin.bits != bits:
+                raise RuntimeError("MatvecGroup needs block size 128 and one index width for all matrices")
+            if x.numel() != lin.in_features or out.numel() != lin.out_features or not x.is_contiguous() or not out.is_contiguous():
+                raise RuntimeError("MatvecGroup runs one contiguous activation vector per matrix")
+            w = lin.stream_weight()
+            arr[i].w, arr[i].x, arr[i].y = w.data_ptr(), x.data_ptr(), out.data_ptr()
+            arr[i].n, arr[i].k, arr[i].x_dtype, arr[i].y_dtype = lin.out_features, lin.in_features, _DT[x.dtype], _DT[out.dtype]
+            self.keep.extend((w, x, out))
+        nbytes = int(l.nb_group_plan_bytes())
+        self._plan_host = ctypes.create_string_buffer(nbytes)
+        _lib.check(l.nb_group_build(arr, len(items), bits, self._plan_host, nbytes), "nb_group_build")
+        self._plan_dev = torch.frombuffer(bytearray(self._plan_host.raw), dtype=torch.uint8).to(dev)
+        self.device = dev
         self.n_matvecs = len(items)
-        if len(self.prog.ops) > int(_lib.lib().nb_stream_max_ops()):
-            raise RuntimeError(f"at most {int(_lib.lib().nb_stream_max_ops())} operations per launch")
 
     def run(self) -> None:
-        self.prog.run()
+        with torch.cuda.device(self.device):
+            rc = _lib.lib().nb_group_run(self._plan_dev.data_ptr(), self._plan_host, ops._stream())
+        if rc:
+            _lib.check(rc, "nb_group_run")
 
     def check(self) -> None:
-        if self.prog.status():
-            raise RuntimeError("a bounded wait of the persistent kernel ran out (status %d)" % self.prog.status())
+        """Nothing in this launch can time out (no flags, no barriers between CTAs): kept for symmetry with
+        StreamProgram."""
+        return None

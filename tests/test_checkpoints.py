@@ -187,7 +187,10 @@ def test_convert_to_inference_replaces_trainable_layers(built_lib):
         ref = x.double().cpu().numpy() @ want[name].astype(np.float64).T
         if m.bias is not None:
             ref = ref + m.bias.double().cpu().numpy()
-        assert np.abs(m(x).double().cpu().numpy() - ref).max() <= 2e-5 * np.abs(ref).max(), name
+        # trained codebooks are fp32; the fused kernels hold them as fp16 (relative rounding 2^-11 per weight), so the
+        # gate here is the path's stated 2e-3, not the 2e-5 of fp16-representable codebooks
+        tol = 2e-5 if m.block_size != 128 else 2e-3          # block sizes other than 128 run the exact gather + matmul
+        assert np.abs(m(x).double().cpu().numpy() - ref).max() <= tol * np.abs(ref).max(), name
 
 
 @pytest.mark.gpu
