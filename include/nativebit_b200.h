@@ -339,7 +339,7 @@ int nb_stream_run(const nb_stream_op* ops_host, const nb_stream_op* ops_device, 
  * registers, and nothing waits on anything but its own copies (no flags, no status word needed).
  * Weights are nb_stream_pack copies (row_mode 0), all of one `bits`; x: k values of x_dtype (NB_F32 carried as
  * two fp16 terms), 16-byte aligned, K % 128 == 0 and K <= 7168; y: n values of y_dtype.  At most
- * nb_group_max_items() matvecs and 6 distinct activation vectors whose staged copies fit 96 KB of shared
+ * nb_group_max_items() matvecs and 6 distinct activation vectors whose staged copies fit 64 KB of shared
  * memory (a K-element vector takes K * 2.5 bytes per fp16 term, the first term of an fp32 vector 17920 bytes).
  * nb_group_build validates the list and writes the launch plan (nb_group_plan_bytes() bytes) into host
  * memory; the caller copies it to device memory once and passes both copies to nb_group_run (the host

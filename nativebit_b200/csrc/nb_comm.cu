@@ -48,10 +48,6 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 
 __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const ArParams p) {
   const int c = blockIdx.x, tid = threadIdx.x;
-  // Launched with programmatic stream serialisation: the CTAs may become resident while the kernel before
-  // is still running and wait here for its results; the kernel after may do the same behind this one.
-  asm volatile("griddepcontrol.launch_dependents;");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   uint8_t* self = p.peers[p.rank];
   uint32_t* seq_ptr = reinterpret_cast<uint32_t*>(self + ar_slots_bytes(p.world, p.max_count) + ar_flags_bytes(p.world)) + c;
   const uint32_t seq = *seq_ptr + 1;
@@ -133,14 +129,9 @@ extern "C" int nb_allreduce(const float* in, float* out, int count, const uint64
   p.in = in; p.out = out; p.count = count; p.max_count = max_count; p.world = world; p.rank = rank;
   p.spin_limit = spin_limit ? spin_limit : kArSpinLimit;
   p.status = status;
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(kArChunks);
-  cfg.blockDim = dim3(256);
-  cfg.stream = (cudaStream_t)stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return record_cuda_error(cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel, p));
+  // A plain, fully stream-ordered launch.  Programmatic dependent launch was measured on two GPUs (2.2B decoder,
+  // batch 1): releasing the next kernel at this kernel's start 1.94 ms/token, after its dependency wait 1.66 ms,
+  // plain launch 1.56 ms — the kernels that start early crowd out the GEMV that is still computing.
+  allreduce_oneshot_kernel<<<kArChunks, 256, 0, (cudaStream_t)stream>>>(p);
+  return check_launch();
 }

@@ -36,6 +36,7 @@
 #include <algorithm>
 #include <cfloat>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "nb_common.cuh"
@@ -1053,16 +1054,19 @@ __global__ void __launch_bounds__(256) stream_pack_kernel(const uint8_t* __restr
 // layers against given activations; the reference runs each as its own launch,
 // inference/triton_kernel.py:240-256).  Without dependencies no operation boundary is needed at all: the
 // row tiles (16 rows x K) of ALL matrices form one sequence, every CTA owns a contiguous stretch of it
-// (equal shares of the weight bytes), and its warps take row tiles from that stretch one at a time.  A warp
+// (equal shares of the weight bytes), and its 24 warps take row tiles from that stretch one at a time.  A warp
 // streams the units of its tile through its own ring of asynchronous copies and keeps the tile's 16 sums in
 // its accumulator registers from the first unit to the last: no partial sums in shared memory, no tickets,
 // no flags, no barrier after the activations are staged, and no wait that could fail to end.  Every output
 // is the sum of its units in index order whichever warp computes it: bit-identical from run to run.
 constexpr int kGroupMaxItems = 256;
 constexpr int kGroupMaxX = 6;
-constexpr int kGroupXBytes = 96 * 1024;                   // shared memory for the staged activation vectors
+constexpr int kGW = 24;                                   // warps per CTA: measured 0.174 ms per 691 MB step against 0.187 with 16 warps
+                                                          // working on two units at a time; 20, 28 and 32 warps within 2 % of 24
+constexpr int kGroupRing = 160 * 1024;                    // the warps' copy rings (5 stages of one unit per warp at 2 and 3 bits)
+constexpr int kGroupXBytes = 64 * 1024;                   // shared memory for the staged activation vectors
 constexpr int kGroupFifo = 8;                             // row tiles a warp may have taken ahead of its arithmetic
-constexpr int kGroupSmem = kRingBytes + kGroupXBytes;
+constexpr int kGroupSmem = kGroupRing + kGroupXBytes;
 
 struct GroupItem {            // 48 bytes
   const uint8_t* w;           // stream-layout weights
@@ -1085,18 +1089,19 @@ struct GroupPlan {
   GroupItem items[kGroupMaxItems];
 };
 
-template <int BITS>
-__global__ void __launch_bounds__(kSThreads, 1) group_kernel(const GroupPlan* __restrict__ plan) {
+template <int BITS, int GW, bool PAIR>
+__global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __restrict__ plan) {
   using F = UnitFmt<BITS>;
-  constexpr int D = F::kStages;                           // ring stages per warp
+  constexpr int D = kGroupRing / (GW * F::kBytes) < 8 ? kGroupRing / (GW * F::kBytes) : 8;   // ring stages per warp
+  constexpr int kThreads = GW * 32;
   static_assert(D >= 4, "the per-warp ring needs at least four stages");
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ int s_next;
   __shared__ int s_tile0[kGroupMaxItems + 1];
-  __shared__ int s_fifo[kSW][kGroupFifo];
+  __shared__ int s_fifo[GW][kGroupFifo];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* ring = smem + warp * (D * F::kBytes);
-  uint8_t* x_all = smem + kRingBytes;
+  uint8_t* x_all = smem + kGroupRing;
   const int n_items = plan->n_items;
   const int t_lo = plan->cta_lo[blockIdx.x], t_hi = plan->cta_lo[blockIdx.x + 1];
 
@@ -1105,7 +1110,7 @@ __global__ void __launch_bounds__(kSThreads, 1) group_kernel(const GroupPlan* __
   for (int v = 0; v < plan->n_x; ++v) {
     const GroupX xv = plan->xv[v];
     uint8_t* x_s = x_all + xv.off;
-    for (int i4 = tid; i4 < xv.k / 4; i4 += kSThreads) {
+    for (int i4 = tid; i4 < xv.k / 4; i4 += kThreads) {
       float u[4];
       if (xv.dtype == NB_F32) {
         const float4 a = __ldg(reinterpret_cast<const float4*>(xv.ptr) + i4);
@@ -1125,7 +1130,7 @@ __global__ void __launch_bounds__(kSThreads, 1) group_kernel(const GroupPlan* __
       }
     }
   }
-  for (int i = tid; i <= n_items; i += kSThreads) s_tile0[i] = i < n_items ? plan->items[i].tile0 : plan->total_tiles;
+  for (int i = tid; i <= n_items; i += kThreads) s_tile0[i] = i < n_items ? plan->items[i].tile0 : plan->total_tiles;
   if (tid == 0) s_next = t_lo;
   __syncthreads();
 
@@ -1199,7 +1204,7 @@ __global__ void __launch_bounds__(kSThreads, 1) group_kernel(const GroupPlan* __
       for (int e = 0; e < 4; ++e) { c0[h][e] = 0.f; c1[h][e] = 0.f; }
 #pragma unroll 1
     for (int j = 0; j < it.bpr;) {
-      const int nb = it.bpr - j >= 2 ? 2 : 1;
+      const int nb = (PAIR && it.bpr - j >= 2) ? 2 : 1;
       request_one();
       if (nb == 2) request_one();
       cp_async_wait<D - 2>();                              // all but the newest D - 2 requests have landed: units `consumed` (+1)
@@ -1461,15 +1466,16 @@ extern "C" int nb_group_run(const void* plan_device, const void* plan_host, void
   static bool attr_done[64][5] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  const void* fn = bits == 3 ? (const void*)group_kernel<3> : bits == 2 ? (const void*)group_kernel<2> : (const void*)group_kernel<4>;
+  const GroupPlan* pd = reinterpret_cast<const GroupPlan*>(plan_device);
+  cudaStream_t st = (cudaStream_t)stream;
+  const void* fn = bits == 3 ? (const void*)group_kernel<3, kGW, false> : bits == 2 ? (const void*)group_kernel<2, kGW, false>
+                             : (const void*)group_kernel<4, kGW, false>;
   if (!attr_done[dev & 63][bits]) {
     if (cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kGroupSmem)) return record_cuda_error(e);
     attr_done[dev & 63][bits] = true;
   }
-  const GroupPlan* pd = reinterpret_cast<const GroupPlan*>(plan_device);
-  cudaStream_t st = (cudaStream_t)stream;
-  if (bits == 3) group_kernel<3><<<G, kSThreads, kGroupSmem, st>>>(pd);
-  else if (bits == 2) group_kernel<2><<<G, kSThreads, kGroupSmem, st>>>(pd);
-  else group_kernel<4><<<G, kSThreads, kGroupSmem, st>>>(pd);
+  if (bits == 3) group_kernel<3, kGW, false><<<G, kGW * 32, kGroupSmem, st>>>(pd);
+  else if (bits == 2) group_kernel<2, kGW, false><<<G, kGW * 32, kGroupSmem, st>>>(pd);
+  else group_kernel<4, kGW, false><<<G, kGW * 32, kGroupSmem, st>>>(pd);
   return check_launch();
 }
