@@ -40,8 +40,9 @@ METRIC, UNIT = "dequant_matvec_hbm_gbs", "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one 6912 x 2560 batch-1 launch, from one ncu capture
 # (algorithmic bytes: 8 866 304)
 NCU_TRAFFIC_B1 = 8912128
-# the same sum for one launch of the persistent kernel over a step's 78 matrices (see roofline.traffic_source)
-NCU_TRAFFIC_STEP = None
+# the same sum for one launch of the group kernel over a step's 78 matrices: 225 787 392 B captured on a launch over
+# 20 matrices of 6912 x 2560 (algorithmic 177 326 080 B), scaled by algorithmic bytes to the step's 691 571 712 B
+NCU_TRAFFIC_STEP = 880570829
 
 
 def alg_bytes(m, n, k, bits=BITS):
@@ -331,6 +332,9 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     block_ms = timed_blocks(step_fn, args.steps, blocks)
+    if sum(block_ms) < args.min_timed_s * 1e3:      # the probe ran slower than the steady state: take the region again, longer
+        blocks = int(blocks * args.min_timed_s * 1e3 / max(sum(block_ms), 1e-3) * 1.1) + 1
+        block_ms = timed_blocks(step_fn, args.steps, blocks)
     clocks = sampler.stop() if rank == 0 else None
     if group is not None:
         group.check()

@@ -93,3 +93,44 @@ def test_fused_and_exchange_argument_checks(built_lib):
     assert l.nb_softcap_argmax(fake, 2, 1, 32000, 0.0, fake, fake, None, None) == 1      # cap must be positive
     assert l.nb_embed_rows(None, fake, 1, 10, 8, fake, None) == 1
     assert l.nb_decode_attention(fake, fake, fake, fake, 1, 4, 82, 64, fake, 328, 0, None) == 3   # head_dim % 4
+
+
+def test_group_plan_shares_the_weight_bytes_evenly():
+    """nb_group_build is host code: the plan of the benchmark's 78 matrices (no GPU needed; 148 CTAs are assumed
+    without a device).  Every CTA's stretch of row tiles must be contiguous, cover the sequence exactly once and
+    hold the mean share of units to within one row tile; bad lists are refused with a message."""
+    import ctypes
+    import struct
+    from nativebit_b200 import _lib
+    from nativebit_b200.stream import GroupItem
+    l = _lib.lib()
+    shapes = [(6912, 2560), (6912, 2560), (2560, 6912)] * 26
+    arr = (GroupItem * len(shapes))()
+    for i, (n, k) in enumerate(shapes):
+        arr[i].w, arr[i].x, arr[i].y = 0x10000 * (i + 1), 0x1000 if k == 2560 else 0x2000, 0x7000000 + 0x10000 * i
+        arr[i].n, arr[i].k, arr[i].x_dtype, arr[i].y_dtype = n, k, _lib.NB_BF16, _lib.NB_BF16
+    nbytes = l.nb_group_plan_bytes()
+    buf = ctypes.create_string_buffer(nbytes)
+    assert l.nb_group_build(arr, len(shapes), 3, buf, nbytes) == 0
+    n_items, n_x, total_tiles, ctas, bits = struct.unpack_from("5i", buf.raw, 0)
+    assert (n_items, n_x, bits) == (78, 2, 3) and total_tiles == 52 * 432 + 26 * 160 and ctas >= 1
+    off = 32 + 6 * 24                                     # header, then six activation-vector records
+    cta_lo = struct.unpack_from(f"{ctas + 1}i", buf.raw, off)
+    assert cta_lo[0] == 0 and cta_lo[ctas] == total_tiles and all(a <= b for a, b in zip(cta_lo, cta_lo[1:]))
+    tile_units = [20] * 432 * 2 + [54] * 160              # one layer: gate, up, down
+    units = [tile_units[t % len(tile_units)] for t in range(total_tiles)]
+    # the sequence is op-major, not layer-interleaved: rebuild it in the plan's order
+    units = []
+    for n, k in shapes:
+        units += [k // 128] * ((n + 15) // 16)
+    share = sum(units) / ctas
+    for c in range(ctas):
+        got = sum(units[cta_lo[c]:cta_lo[c + 1]])
+        assert abs(got - share) <= 54, (c, got, share)
+    # refusals
+    arr[3].k = 100
+    assert l.nb_group_build(arr, len(shapes), 3, buf, nbytes) != 0 and b"matvec 3" in l.nb_last_cuda_error()
+    arr[3].k = 2560
+    for i in range(7):
+        arr[i].x = 0x100000 + 0x10000 * i                 # seven distinct activation vectors
+    assert l.nb_group_build(arr, len(shapes), 3, buf, nbytes) != 0
