@@ -319,8 +319,9 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.b
     m, k = x.shape
     n = w.shape[0]
     out = torch.empty(m, n, dtype=out_dtype, device=x.device)
-    status = torch.zeros(1, dtype=torch.int32, device=x.device)
     with torch.cuda.device(x.device):
+        # the status word is the head of this stream's persistent prefill workspace: prefill_status() reads it
+        status = prefill_workspace(x.device, 256)
         _lib.check(_lib.lib().nb_gemm_bf16(x.data_ptr(), w.data_ptr(), m, n, k, out.data_ptr(), _DTYPE[out_dtype],
                                            status.data_ptr(), _stream()), "nb_gemm_bf16")
     return out
