@@ -1156,7 +1156,7 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
   const uint8_t* f_src = nullptr;                          // next unit to request
   int f_left = 0;                                          // units of the current copy-side tile still to request
   bool f_done = false;
-  int requested = 0, consumed = 0;                         // units requested / used so far (ring positions)
+  int rq_stage = 0, use_stage = 0;                         // ring stage of the next request / of the next unit to use
   auto request_one = [&]() {
     if (f_left == 0 && !f_done) {
       const int t = take();
@@ -1171,7 +1171,7 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
       }
     }
     if (f_left > 0) {
-      uint8_t* dst = ring + (requested % D) * F::kBytes;
+      uint8_t* dst = ring + rq_stage * F::kBytes;
       constexpr int kChunks = F::kBytes / 16;
 #pragma unroll
       for (int i = 0; i < (kChunks + 31) / 32; ++i)
@@ -1179,7 +1179,7 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
       f_src += F::kBytes;
       --f_left;
     }
-    ++requested;                                           // a group is closed even when nothing was left to request
+    if (++rq_stage == D) rq_stage = 0;                     // a group is closed (and a stage passed over) even when nothing was left to request
     cp_async_commit();
   };
 #pragma unroll 1
@@ -1209,8 +1209,8 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
       if (nb == 2) request_one();
       cp_async_wait<D - 2>();                              // all but the newest D - 2 requests have landed: units `consumed` (+1)
       __syncwarp();
-      const uint8_t* u0 = ring + (consumed % D) * F::kBytes;
-      const uint8_t* u1 = ring + ((consumed + 1) % D) * F::kBytes;
+      const uint8_t* u0 = ring + use_stage * F::kBytes;
+      const uint8_t* u1 = ring + (use_stage + 1 == D ? 0 : use_stage + 1) * F::kBytes;
       if (it.xs == 2) {
         if (nb == 2) unit_mma2<BITS, 2>(u0, u1, x_s, j, j + 1, lane, c0, c1);
         else unit_mma<BITS, 2>(u0, x_s, j, lane, c0);
@@ -1218,7 +1218,8 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
         if (nb == 2) unit_mma2<BITS, 1>(u0, u1, x_s, j, j + 1, lane, c0, c1);
         else unit_mma<BITS, 1>(u0, x_s, j, lane, c0);
       }
-      consumed += nb;
+      use_stage += nb;
+      if (use_stage >= D) use_stage -= D;
       j += nb;
       __syncwarp();                                        // every lane is done with these stages before they are requested again
     }

@@ -319,6 +319,7 @@ class DecodeSession:
         self.k_idx = torch.arange(model.context_len, device=dev)
         self.use_graph = use_graph
         self.graph = None
+        self._prefill_graphs = {}             # prompt length -> (captured prefill, its static input)
         self.stream = torch.cuda.Stream(device=dev)
         if fused:  # static activation buffers of the fused step
             cfg, B = model.config, batch_size
@@ -420,14 +421,39 @@ class DecodeSession:
         """prompt (B, T): fills the caches, sets the position and the first generated token."""
         if prompt.shape[1] > self.model.context_len:
             raise RuntimeError(f"prompt of {prompt.shape[1]} tokens exceeds the context of {self.model.context_len}")
+        T = int(prompt.shape[1])
+        if not self.use_graph or self.model.tp_size > 1 or not prompt.is_cuda:
+            self._prefill_body(prompt)
+        else:
+            # one CUDA graph per prompt length: the eager forward is about thirty small launches per layer and
+            # is bound by the host; replayed from a graph only the device time remains
+            entry = self._prefill_graphs.get(T)
+            cur = torch.cuda.current_stream(self.dev)
+            if entry is None:
+                static_in = prompt.clone()
+                self.stream.wait_stream(cur)
+                with torch.cuda.stream(self.stream):
+                    self._prefill_body(static_in)            # warms every kernel up and IS this call's result
+                    self.stream.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=self.stream):
+                        self._prefill_body(static_in)
+                cur.wait_stream(self.stream)
+                self._prefill_graphs[T] = (g, static_in)
+            else:
+                g, static_in = entry
+                static_in.copy_(prompt)
+                g.replay()
+        self.caches = [(k, v, T) for k, v, _ in self.caches]
+        self.pos_host = T
+        return self.logits
+
+    def _prefill_body(self, prompt: torch.Tensor) -> None:
         caches = [(k, v, 0) for k, v, _ in self.caches]
-        logits, caches = self.model(prompt, kv_caches=caches, last_only=True)
-        self.caches = caches
+        logits, _ = self.model(prompt, kv_caches=caches, last_only=True)      # the caches are written in place
         self.pos.fill_(prompt.shape[1])
-        self.pos_host = int(prompt.shape[1])
         self.logits.copy_(logits[:, -1, :])
         self.token.copy_(self.logits.argmax(-1, keepdim=True))
-        return self.logits
 
     @torch.no_grad()
     def _step_body(self):
