@@ -341,16 +341,18 @@ int nb_stream_run(const nb_stream_op* ops_host, const nb_stream_op* ops_device, 
  * two fp16 terms), 16-byte aligned, K % 128 == 0 and K <= 7168; y: n values of y_dtype.  At most
  * nb_group_max_items() matvecs and 6 distinct activation vectors whose staged copies fit 64 KB of shared
  * memory (a K-element vector takes K * 2.5 bytes per fp16 term, the first term of an fp32 vector 17920 bytes).
- * nb_group_build validates the list and writes the launch plan (nb_group_plan_bytes() bytes) into host
- * memory; the caller copies it to device memory once and passes both copies to nb_group_run (the host
- * copy for the launch geometry).  Results are bit-identical from run to run. */
+ * nb_group_build validates the list and writes the launch plan (nb_group_plan_bytes(items, n) bytes: a header
+ * and one word per 16-row tile) into host memory: the row tiles are dealt out to the CTAs longest first, each
+ * to the CTA with the least work so far, so that all CTAs finish within one short tile of one another.  The
+ * caller copies the plan to device memory once and passes both copies to nb_group_run (the host copy for the
+ * launch geometry).  Results are bit-identical from run to run. */
 typedef struct {
   const void* w;
   const void* x;
   void* y;
   int32_t n, k, x_dtype, y_dtype;
 } nb_group_item;
-size_t nb_group_plan_bytes(void);
+size_t nb_group_plan_bytes(const nb_group_item* items, int n_items);
 int nb_group_max_items(void);
 int nb_group_build(const nb_group_item* items, int n_items, int bits, void* plan_out, size_t plan_bytes);
 int nb_group_run(const void* plan_device, const void* plan_host, void* stream);

@@ -38,6 +38,10 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
+#include <queue>
+#include <utility>
+#include <vector>
 
 #include "nb_common.cuh"
 #include "nb_device.cuh"
@@ -1053,8 +1057,9 @@ __global__ void __launch_bounds__(256) stream_pack_kernel(const uint8_t* __restr
 // A group of packed matvecs none of which reads another's result (the gate, up and down matrices of many
 // layers against given activations; the reference runs each as its own launch,
 // inference/triton_kernel.py:240-256).  Without dependencies no operation boundary is needed at all: the
-// row tiles (16 rows x K) of ALL matrices form one sequence, every CTA owns a contiguous stretch of it
-// (equal shares of the weight bytes), and its 24 warps take row tiles from that stretch one at a time.  A warp
+// row tiles (16 rows x K) of ALL matrices are dealt out to the CTAs on the host (equal shares of the weight
+// bytes, every CTA a mix of all tile lengths), and a CTA's 24 warps take its tiles one at a time, the longest
+// first, so that the last warps to finish are at most one short tile apart.  A warp
 // streams the units of its tile through its own ring of asynchronous copies and keeps the tile's 16 sums in
 // its accumulator registers from the first unit to the last: no partial sums in shared memory, no tickets,
 // no flags, no barrier after the activations are staged, and no wait that could fail to end.  Every output
@@ -1085,8 +1090,9 @@ struct GroupX {               // 24 bytes: one distinct activation vector
 struct GroupPlan {
   int n_items, n_x, total_tiles, ctas, bits, pad[3];
   GroupX xv[kGroupMaxX];
-  int cta_lo[kMaxCtas + 1];   // CTA c owns row tiles [cta_lo[c], cta_lo[c + 1])
+  int cta_lo[kMaxCtas + 1];   // CTA c owns entries [cta_lo[c], cta_lo[c + 1]) of the tile list
   GroupItem items[kGroupMaxItems];
+  int tile_list[1];           // total_tiles row-tile indices: every CTA's tiles, the longest first (the plan is allocated with the list's real length)
 };
 
 template <int BITS, int GW, bool PAIR>
@@ -1145,10 +1151,12 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
   };
   // the warp takes the CTA's next row tile (or learns that none is left); all lanes get the same answer
   auto take = [&]() {
-    int t = 0;
-    if (lane == 0) t = atomicAdd(&s_next, 1);
-    t = __shfl_sync(0xffffffffu, t, 0);
-    return t < t_hi ? t : -1;
+    int t = -1;
+    if (lane == 0) {
+      const int p = atomicAdd(&s_next, 1);
+      if (p < t_hi) t = __ldg(plan->tile_list + p);
+    }
+    return __shfl_sync(0xffffffffu, t, 0);
   };
 
   // ---- the copy side: requests run D - 2 units ahead of the arithmetic
@@ -1384,7 +1392,12 @@ extern "C" int nb_stream_run(const nb_stream_op* ops_host, const nb_stream_op* o
 }
 
 // ---- independent matvecs: plan on the host, run from device memory ----------------------------------
-extern "C" size_t nb_group_plan_bytes(void) { return sizeof(GroupPlan); }
+extern "C" size_t nb_group_plan_bytes(const nb_group_item* items, int n_items) {
+  if (!items || n_items < 1) return 0;
+  long long tiles = 0;
+  for (int i = 0; i < n_items; ++i) tiles += items[i].n > 0 ? (items[i].n + 15) / 16 : 0;
+  return sizeof(GroupPlan) + (size_t)tiles * sizeof(int);
+}
 
 extern "C" int nb_group_max_items(void) { return kGroupMaxItems; }
 
@@ -1398,7 +1411,7 @@ extern "C" int nb_group_build(const nb_group_item* items, int n_items, int bits,
   if (!items || !plan_out || n_items < 1) return NB_ERR_ARG;
   if (n_items > kGroupMaxItems) return fail(n_items, "too many matvecs for one launch");
   if (bits != 2 && bits != 3 && bits != 4) return NB_ERR_SHAPE;
-  if (plan_bytes < sizeof(GroupPlan)) return NB_ERR_WORKSPACE;
+  if (plan_bytes < nb_group_plan_bytes(items, n_items)) return NB_ERR_WORKSPACE;
   GroupPlan* pl = reinterpret_cast<GroupPlan*>(plan_out);
   std::memset(pl, 0, sizeof(GroupPlan));
   const int G = nb_stream_ctas();
@@ -1433,26 +1446,34 @@ extern "C" int nb_group_build(const nb_group_item* items, int n_items, int bits,
     if (tiles > (1ll << 30)) return fail(i, "too many row tiles");
   }
   pl->total_tiles = (int)tiles;
-  // equal shares of the units (= weight bytes), cut at the nearest row-tile boundary
-  pl->cta_lo[0] = 0;
-  int item = 0;
-  long long unit0 = 0;   // units before `item`
-  for (int c = 1; c < G; ++c) {
-    const long long target = units * c / G;
-    while (item < n_items - 1) {
-      const long long item_units = (long long)((pl->items[item].n + 15) / 16) * pl->items[item].bpr;
-      if (unit0 + item_units > target) break;
-      unit0 += item_units;
-      ++item;
+  // Deal the row tiles out: longest tiles first, to the CTA that holds the fewest units so far (ties: lowest
+  // CTA).  Every CTA's list is then in descending tile length, its share within one short tile of the mean.
+  {
+    std::vector<int> order(n_items);
+    for (int i = 0; i < n_items; ++i) order[i] = i;
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return pl->items[a].bpr > pl->items[b].bpr; });
+    std::vector<long long> load(G, 0);
+    std::vector<std::vector<int>> lists(G);
+    // a min-heap of (units, CTA): all tiles of one matrix have the same length, so they go round the CTAs in turn
+    std::priority_queue<std::pair<long long, int>, std::vector<std::pair<long long, int>>, std::greater<>> heap;
+    for (int c = 0; c < G; ++c) heap.push({0, c});
+    for (int oi = 0; oi < n_items; ++oi) {
+      const GroupItem& it = pl->items[order[oi]];
+      const int rt = (it.n + 15) / 16;
+      for (int t = 0; t < rt; ++t) {
+        auto top = heap.top();
+        heap.pop();
+        lists[top.second].push_back(it.tile0 + t);
+        heap.push({top.first + it.bpr, top.second});
+      }
     }
-    const GroupItem& it = pl->items[item];
-    const int rt = (it.n + 15) / 16;
-    long long k = (target - unit0 + it.bpr / 2) / it.bpr;
-    if (k < 0) k = 0;
-    if (k > rt) k = rt;
-    pl->cta_lo[c] = std::max(pl->cta_lo[c - 1], it.tile0 + (int)k);
+    int pos = 0;
+    for (int c = 0; c < G; ++c) {
+      pl->cta_lo[c] = pos;
+      for (int t : lists[c]) pl->tile_list[pos++] = t;
+    }
+    for (int c = G; c <= kMaxCtas; ++c) pl->cta_lo[c] = pos;
   }
-  for (int c = G; c <= kMaxCtas; ++c) pl->cta_lo[c] = (int)tiles;
   return NB_OK;
 }
 

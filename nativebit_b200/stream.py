@@ -228,7 +228,7 @@ class MatvecGroup:
             arr[i].w, arr[i].x, arr[i].y = w.data_ptr(), x.data_ptr(), out.data_ptr()
             arr[i].n, arr[i].k, arr[i].x_dtype, arr[i].y_dtype = lin.out_features, lin.in_features, _DT[x.dtype], _DT[out.dtype]
             self.keep.extend((w, x, out))
-        nbytes = int(l.nb_group_plan_bytes())
+        nbytes = int(l.nb_group_plan_bytes(arr, len(items)))
         self._plan_host = ctypes.create_string_buffer(nbytes)
         _lib.check(l.nb_group_build(arr, len(items), bits, self._plan_host, nbytes), "nb_group_build")
         self._plan_dev = torch.frombuffer(bytearray(self._plan_host.raw), dtype=torch.uint8).to(dev)

@@ -109,24 +109,25 @@ def test_group_plan_shares_the_weight_bytes_evenly():
     for i, (n, k) in enumerate(shapes):
         arr[i].w, arr[i].x, arr[i].y = 0x10000 * (i + 1), 0x1000 if k == 2560 else 0x2000, 0x7000000 + 0x10000 * i
         arr[i].n, arr[i].k, arr[i].x_dtype, arr[i].y_dtype = n, k, _lib.NB_BF16, _lib.NB_BF16
-    nbytes = l.nb_group_plan_bytes()
+    nbytes = l.nb_group_plan_bytes(arr, len(shapes))
     buf = ctypes.create_string_buffer(nbytes)
     assert l.nb_group_build(arr, len(shapes), 3, buf, nbytes) == 0
     n_items, n_x, total_tiles, ctas, bits = struct.unpack_from("5i", buf.raw, 0)
     assert (n_items, n_x, bits) == (78, 2, 3) and total_tiles == 52 * 432 + 26 * 160 and ctas >= 1
     off = 32 + 6 * 24                                     # header, then six activation-vector records
-    cta_lo = struct.unpack_from(f"{ctas + 1}i", buf.raw, off)
+    cta_lo = struct.unpack_from("513i", buf.raw, off)
     assert cta_lo[0] == 0 and cta_lo[ctas] == total_tiles and all(a <= b for a, b in zip(cta_lo, cta_lo[1:]))
-    tile_units = [20] * 432 * 2 + [54] * 160              # one layer: gate, up, down
-    units = [tile_units[t % len(tile_units)] for t in range(total_tiles)]
-    # the sequence is op-major, not layer-interleaved: rebuild it in the plan's order
-    units = []
+    off_items = (off + 513 * 4 + 7) // 8 * 8              # 256 records of 48 bytes, 8-byte aligned; the tile list follows them
+    tile_list = struct.unpack_from(f"{total_tiles}i", buf.raw, off_items + 256 * 48)
+    assert sorted(tile_list) == list(range(total_tiles))  # every row tile exactly once
+    units = []                                            # units of every row tile, in the order of the matrices
     for n, k in shapes:
         units += [k // 128] * ((n + 15) // 16)
     share = sum(units) / ctas
     for c in range(ctas):
-        got = sum(units[cta_lo[c]:cta_lo[c + 1]])
-        assert abs(got - share) <= 54, (c, got, share)
+        mine = [units[t] for t in tile_list[cta_lo[c]:cta_lo[c + 1]]]
+        assert mine == sorted(mine, reverse=True)         # the longest tiles first
+        assert abs(sum(mine) - share) <= 20, (c, sum(mine), share)     # within one short tile of the mean
     # refusals
     arr[3].k = 100
     assert l.nb_group_build(arr, len(shapes), 3, buf, nbytes) != 0 and b"matvec 3" in l.nb_last_cuda_error()
