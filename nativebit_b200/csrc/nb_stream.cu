@@ -325,10 +325,12 @@ __device__ __forceinline__ void fetch_next(const StreamCtx& c, Cursor& f) {
 }
 
 // ---- one unit: 16 rows x 128 weights against the staged activations -----------------------------
+// `xseg`: this lane's 32 activations of the unit's k-block (fp16, 64 bytes), the second fp16 term `term_stride`
+// bytes further on.
 template <int BITS, int XS>
-__device__ __forceinline__ void unit_mma(const uint8_t* ub, const uint8_t* x_s, int kb, int lane, float (&c)[2][4]) {
+__device__ __forceinline__ void unit_mma_x(const uint8_t* ub, const uint8_t* xseg, int term_stride, int lane, float (&c)[2][4]) {
   using F = UnitFmt<BITS>;
-  const int g = lane >> 2, t = lane & 3;
+  const int g = lane >> 2;
   const uint4 ua = *reinterpret_cast<const uint4*>(ub + lane * 16);
   const uint4 ub4 = *reinterpret_cast<const uint4*>(ub + 512 + lane * 16);
   const uint32_t UA[4] = {ua.x, ua.y, ua.z, ua.w}, UB[4] = {ub4.x, ub4.y, ub4.z, ub4.w};
@@ -341,12 +343,11 @@ __device__ __forceinline__ void unit_mma(const uint8_t* ub, const uint8_t* x_s, 
     TA[4 * j] = a.x; TA[4 * j + 1] = a.y; TA[4 * j + 2] = a.z; TA[4 * j + 3] = a.w;
     TB[4 * j] = b.x; TB[4 * j + 1] = b.y; TB[4 * j + 2] = b.z; TB[4 * j + 3] = b.w;
   }
-  const uint8_t* xseg = x_s + (kb * 4 + t) * kXSegBytes;
 #pragma unroll
   for (int uu = 0; uu < 4; ++uu) {
     uint4 xq[XS];    // the activations of steps 2*uu and 2*uu + 1
 #pragma unroll
-    for (int xs = 0; xs < XS; ++xs) xq[xs] = *reinterpret_cast<const uint4*>(xseg + xs * kXTermBytes + uu * 16);
+    for (int xs = 0; xs < XS; ++xs) xq[xs] = *reinterpret_cast<const uint4*>(xseg + xs * term_stride + uu * 16);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const uint32_t sa = h ? (UA[uu] >> 16) : UA[uu];
@@ -358,6 +359,11 @@ __device__ __forceinline__ void unit_mma(const uint8_t* ub, const uint8_t* x_s, 
       for (int xs = 0; xs < XS; ++xs) mma_16816(c[h], a0, a1, a2, a3, h ? xq[xs].z : xq[xs].x, h ? xq[xs].w : xq[xs].y);
     }
   }
+}
+
+template <int BITS, int XS>
+__device__ __forceinline__ void unit_mma(const uint8_t* ub, const uint8_t* x_s, int kb, int lane, float (&c)[2][4]) {
+  unit_mma_x<BITS, XS>(ub, x_s + (kb * 4 + (lane & 3)) * kXSegBytes, kXTermBytes, lane, c);
 }
 
 // Two units at once, their steps interleaved: two independent instruction streams per warp hide the
@@ -1136,6 +1142,10 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
       }
     }
   }
+  // 128 zero bytes: the activations of the seven MMA columns that a single activation vector does not use
+  // (all eight columns would otherwise carry the same vector; zeros cost the tensor cores less power)
+  uint8_t* x_zero = x_all + kGroupXBytes - 128;
+  if (tid < 32) reinterpret_cast<uint32_t*>(x_zero)[tid] = 0u;
   for (int i = tid; i <= n_items; i += kThreads) s_tile0[i] = i < n_items ? plan->items[i].tile0 : plan->total_tiles;
   if (tid == 0) s_next = t_lo;
   __syncthreads();
@@ -1219,19 +1229,22 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
       __syncwarp();
       const uint8_t* u0 = ring + use_stage * F::kBytes;
       const uint8_t* u1 = ring + (use_stage + 1 == D ? 0 : use_stage + 1) * F::kBytes;
-      if (it.xs == 2) {
-        if (nb == 2) unit_mma2<BITS, 2>(u0, u1, x_s, j, j + 1, lane, c0, c1);
-        else unit_mma<BITS, 2>(u0, x_s, j, lane, c0);
+      if (PAIR && nb == 2) {
+        if (it.xs == 2) unit_mma2<BITS, 2>(u0, u1, x_s, j, j + 1, lane, c0, c1);
+        else unit_mma2<BITS, 1>(u0, u1, x_s, j, j + 1, lane, c0, c1);
       } else {
-        if (nb == 2) unit_mma2<BITS, 1>(u0, u1, x_s, j, j + 1, lane, c0, c1);
-        else unit_mma<BITS, 1>(u0, x_s, j, lane, c0);
+        // column 0 of the MMA carries the activation vector (lanes g == 0 supply it), the other columns zeros
+        const bool col0 = lane < 4;
+        const uint8_t* xseg = col0 ? x_s + (j * 4 + (lane & 3)) * kXSegBytes : x_zero;
+        if (it.xs == 2) unit_mma_x<BITS, 2>(u0, xseg, col0 ? kXTermBytes : 0, lane, c0);
+        else unit_mma_x<BITS, 1>(u0, xseg, 0, lane, c0);
       }
       use_stage += nb;
       if (use_stage >= D) use_stage -= D;
       j += nb;
       __syncwarp();                                        // every lane is done with these stages before they are requested again
     }
-    // all eight columns of the accumulator tile hold the same sums; lanes t == 0 write rows g and g + 8
+    // column 0 of the accumulator tile holds the sums (the paired path fills all eight alike); lanes t == 0 write rows g and g + 8
     if ((lane & 3) == 0) {
       const int g = lane >> 2;
       const int ra = rt * 16 + g, rb = ra + 8;
@@ -1433,7 +1446,7 @@ extern "C" int nb_group_build(const nb_group_item* items, int n_items, int bits,
       const int xs = in.x_dtype == NB_F32 ? 2 : 1;
       // a vector's terms are kXTermBytes apart (the lookup code's fixed stride); the last term is cut to its length
       const int need = (xs - 1) * kXTermBytes + (in.k / kBlock) * 4 * kXSegBytes;
-      if (x_bytes + need > kGroupXBytes) return fail(i, "the activation vectors of the group do not fit in shared memory");
+      if (x_bytes + need > kGroupXBytes - 128) return fail(i, "the activation vectors of the group do not fit in shared memory");
       pl->xv[v].ptr = in.x; pl->xv[v].k = in.k; pl->xv[v].dtype = in.x_dtype; pl->xv[v].off = x_bytes; pl->xv[v].xs = xs;
       x_bytes += (need + 127) / 128 * 128;
       pl->n_x = v + 1;
