@@ -40,9 +40,9 @@ METRIC, UNIT = "dequant_matvec_hbm_gbs", "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one 6912 x 2560 batch-1 launch, from one ncu capture
 # (algorithmic bytes: 8 866 304)
 NCU_TRAFFIC_B1 = 8912128
-# the same sum for one launch of the group kernel over a step's 78 matrices: 225 787 392 B captured on a launch over
-# 20 matrices of 6912 x 2560 (algorithmic 177 326 080 B), scaled by algorithmic bytes to the step's 691 571 712 B
-NCU_TRAFFIC_STEP = 880570829
+# the same sum for one launch of the group kernel over a step's 78 matrices: 225,413,376 B captured on a launch over
+# 20 matrices of 6912 x 2560 (algorithmic 177,326,080 B), scaled by algorithmic bytes to the step's 691,571,712 B
+NCU_TRAFFIC_STEP = 879112166
 
 
 def alg_bytes(m, n, k, bits=BITS):
