@@ -132,10 +132,13 @@ int nb_gemm_prefill(const void* x, int x_dtype, int M, const uint8_t* packed, co
  * x: (M, K) NB_F16, NB_BF16 (converted to fp16 into the workspace first) or NB_F32 (carried as two fp16 terms per
  * element, hi = fp16(x) and lo = fp16(x - hi), as two operand rows whose results the kernel adds: about 22
  * significant bits, as in nb_gemv), 16-byte aligned;
- * K % 128 == 0; y: (M, N) NB_BF16 or NB_F32.  workspace: nb_prefill_fused_workspace_bytes(M, K) bytes,
+ * K % 128 == 0; y: (M, N) NB_BF16 or NB_F32.  workspace: nb_prefill_fused_workspace_bytes(M, N, K) bytes,
  * 256-byte aligned; its first 256 bytes carry a status word (zero before the first call; NB_ERR_TIMEOUT
- * if a bounded wait inside the kernel ran out). */
-size_t nb_prefill_fused_workspace_bytes(int M, int K);
+ * if a bounded wait inside the kernel ran out), then the fp16 copy of the activations and, for short
+ * inputs, fp32 slabs: when the output has fewer 128 x BN tiles than half the SMs, the k range is cut
+ * into up to 8 parts that run on different SMs and a second kernel adds their results in k order (still
+ * bit-identical from run to run). */
+size_t nb_prefill_fused_workspace_bytes(int M, int N, int K);
 int nb_gemm_prefill_fused(const void* x, int x_dtype, int M, const uint8_t* w_stream, int bits, int N, int K, void* y,
                           int y_dtype, void* workspace, size_t workspace_bytes, void* stream);
 

@@ -74,7 +74,7 @@ template <int BITS> struct FusedFmt {
 template <int BITS>
 __global__ void __launch_bounds__(kFThreads, 1)
 gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_stream, void* __restrict__ y, int y_dtype,
-                  int M, int N, int K, int BN, int m_tiles, int w_tiles, int pair, int* status) {
+                  int M, int N, int K, int BN, int m_tiles, int w_tiles, int pair, int ks, float* __restrict__ partial, int* status) {
   using F = FusedFmt<BITS>;
   constexpr int kT = BITS == 4 ? 8 : 4;
   const int S = fused_stages(BN);
@@ -93,7 +93,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KT = K / kFK, bpr = K / kBlock;
-  const int n_total = m_tiles * w_tiles;
+  const int KTs = (KT + ks - 1) / ks;           // k-steps per k split (the last split may be shorter, never empty)
+  const int n_total = m_tiles * w_tiles * ks;   // work item t: k split t % ks of output tile t / ks
   const int rows_padded = ((N + 15) >> 4) << 4;   // rows the stream layout holds (zero rows past N)
 
   if (threadIdx.x == 0) {
@@ -111,15 +112,19 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  // tile t: features 128 * (t / m_tiles), tokens BN * (t % m_tiles): CTAs running together share a weight tile
+  // output tile o = t / ks: features 128 * (o / m_tiles), tokens BN * (o % m_tiles): CTAs running together share a
+  // weight tile; with ks > 1 the k range of an output tile is cut into ks parts whose fp32 results go to
+  // `partial` and are added in k order by a second kernel (short inputs would otherwise leave most SMs idle
+  // behind a long serial chain of k-steps)
   if (warp == 0) {
     if (lane == 0) {  // ---- TMA producer of the activation slabs
       int s = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < n_total; t += gridDim.x) {
-        const int m0 = (t % m_tiles) * BN;
+        const int m0 = ((t / ks) % m_tiles) * BN;
+        const int k_lo = (t % ks) * KTs, k_hi = min(KT, k_lo + KTs);
         bool ok = true;
-        for (int kt = 0; kt < KT; ++kt) {
+        for (int kt = k_lo; kt < k_hi; ++kt) {
           ok = bar_wait(&empty[s], phase ^ 1, abort_flag, status);
           if (!ok) break;
           FTRACE(0, kt);
@@ -142,7 +147,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         bool ok = bar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag, status);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * 256);
-        for (int kt = 0; kt < KT && ok; ++kt) {
+        const int k_lo = (t % ks) * KTs, k_hi = min(KT, k_lo + KTs);
+        for (int kt = k_lo; kt < k_hi && ok; ++kt) {
           ok = bar_wait(&full_a[s], phase, abort_flag, status);
           FTRACE(1, kt);
           ok = ok && bar_wait(&full_b[s], phase, abort_flag, status);
@@ -152,7 +158,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
           const uint64_t da = smem_desc_sw128(sA + s * kFABytes), db = smem_desc_sw128(sB + s * b_bytes);
 #pragma unroll
           for (int k4 = 0; k4 < kFK / 16; ++k4)  // 16 fp16 = 32 bytes = 2 descriptor address units per step
-            umma_f16(tmem_d, da + 2 * k4, db + 2 * k4, idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
+            umma_f16(tmem_d, da + 2 * k4, db + 2 * k4, idesc, (kt > k_lo || k4 > 0) ? 1u : 0u);
           umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
           if (++s == S) { s = 0; phase ^= 1; }
         }
@@ -166,7 +172,11 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
     int local = 0;
     for (int t = blockIdx.x; t < n_total; t += gridDim.x, ++local) {
       const int buf = local & 1;
-      const int m0 = (t % m_tiles) * BN, n0 = (t / m_tiles) * kFM;
+      const int o = t / ks;
+      const int m0 = (o % m_tiles) * BN, n0 = (o / m_tiles) * kFM;
+      // with k splits the tile's fp32 sums go to this split's slab of `partial` ((M >> pair) x N floats each)
+      void* const y_t = ks > 1 ? (void*)(partial + (size_t)(t % ks) * (size_t)(M >> pair) * N) : y;
+      const int y_dt = ks > 1 ? (int)NB_F32 : y_dtype;
       const bool ok = bar_wait<200>(&acc_full[buf], (local >> 1) & 1, abort_flag, status) && !*abort_flag;
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -190,19 +200,19 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
           for (int j = 0; j < 8; ++j) {
             if (mb + j < m_out) {
               const float v = __uint_as_float(r[2 * j]) + __uint_as_float(r[2 * j + 1]);
-              if (y_dtype == NB_BF16) reinterpret_cast<__nv_bfloat16*>(y)[(size_t)(mb + j) * N + n] = __float2bfloat16_rn(v);
-              else reinterpret_cast<float*>(y)[(size_t)(mb + j) * N + n] = v;
+              if (y_dt == NB_BF16) reinterpret_cast<__nv_bfloat16*>(y_t)[(size_t)(mb + j) * N + n] = __float2bfloat16_rn(v);
+              else reinterpret_cast<float*>(y_t)[(size_t)(mb + j) * N + n] = v;
             }
           }
         } else if (n < N) {
           const int mb = m0 + c * 16;
-          if (y_dtype == NB_BF16) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(y) + (size_t)mb * N + n;
+          if (y_dt == NB_BF16) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(y_t) + (size_t)mb * N + n;
 #pragma unroll
             for (int j = 0; j < 16; ++j)
               if (mb + j < M) dst[(size_t)j * N] = __float2bfloat16_rn(__uint_as_float(r[j]));
           } else {
-            float* dst = reinterpret_cast<float*>(y) + (size_t)mb * N + n;
+            float* dst = reinterpret_cast<float*>(y_t) + (size_t)mb * N + n;
 #pragma unroll
             for (int j = 0; j < 16; ++j)
               if (mb + j < M) dst[(size_t)j * N] = __uint_as_float(r[j]);
@@ -220,9 +230,10 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
     const int row = pp & 127, q2 = pp >> 7;
     const int r16 = row & 15, g = r16 & 7, hrow = r16 >> 3;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-    uint32_t step0 = 0;                                  // k-steps of all earlier tiles: stage = step % S, phase = (step / S) & 1
-    for (int t = blockIdx.x; t < n_total; t += gridDim.x, step0 += (uint32_t)KT) {
-      const int n0 = (t / m_tiles) * kFM;
+    uint32_t step0 = 0;                                  // k-steps of all earlier work items: stage = step % S, phase = (step / S) & 1
+    for (int t = blockIdx.x; t < n_total; t += gridDim.x) {
+      const int n0 = ((t / ks) / m_tiles) * kFM;
+      const int k_lo = (t % ks) * KTs, k_hi = min(KT, k_lo + KTs);
       const int grow = n0 + row;
       const bool valid = grow < rows_padded;
       const uint8_t* urow = w_stream + (size_t)(grow >> 4) * bpr * F::kUnitBytes;   // the row tile's units
@@ -231,7 +242,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         sel = zero4;
 #pragma unroll
         for (int j = 0; j < kT / 4; ++j) tab[j] = zero4;
-        if (valid && kt < KT) {
+        if (valid && kt < k_hi) {
           const uint8_t* u = urow + (size_t)(kt >> 1) * F::kUnitBytes;
           const int lane_u = g * 4 + 2 * (kt & 1) + q2;
           sel = __ldg(reinterpret_cast<const uint4*>(u + hrow * 512 + lane_u * 16));
@@ -240,12 +251,12 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         }
       };
       uint4 sel, tab[kT / 4];
-      load(grp, sel, tab);
+      load(k_lo + grp, sel, tab);
       bool ok = true;
-      for (int kt = grp; kt < KT; kt += kFGroups) {
+      for (int kt = k_lo + grp; kt < k_hi; kt += kFGroups) {
         uint4 sel_n, tab_n[kT / 4];
         load(kt + kFGroups, sel_n, tab_n);               // this group's next k-step, in flight while this one is unpacked
-        const uint32_t step = step0 + (uint32_t)kt;
+        const uint32_t step = step0 + (uint32_t)(kt - k_lo);
         const int s = (int)(step % (uint32_t)S);
         const uint32_t phase = (step / (uint32_t)S) & 1u;
         if (pp == 0) FTRACE(3, kt);
@@ -275,6 +286,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         for (int j = 0; j < kT / 4; ++j) tab[j] = tab_n[j];
       }
       if (!ok) break;
+      step0 += (uint32_t)(k_hi - k_lo);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -336,6 +348,35 @@ static int pick_token_tile(int M, int N, int sms) {
   return best;
 }
 
+// Number of k splits for `tiles` output tiles of KT k-steps: short inputs (fewer output tiles than half the
+// SMs) cut the k range so that one wave of work items covers the SMs; every split keeps at least four k-steps
+// and none is empty.
+static int pick_k_splits(long tiles, int KT, int sms) {
+  if (tiles * 2 > sms || KT < 8) return 1;
+  int ks = (int)std::min<long>(std::min<long>(8, sms / tiles), KT / 4);
+  while (ks > 1 && (long)(ks - 1) * ((KT + ks - 1) / ks) >= KT) --ks;
+  return std::max(ks, 1);
+}
+
+// y (rows x N) = sum over the k splits' fp32 slabs, in split order; four outputs per thread.
+__global__ void __launch_bounds__(256) splitk_sum_kernel(const float* __restrict__ partial, int ks, size_t slab, void* __restrict__ y,
+                                                         int y_dtype, size_t n4) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 acc = reinterpret_cast<const float4*>(partial)[i];
+  for (int z = 1; z < ks; ++z) {
+    const float4 v = reinterpret_cast<const float4*>(partial + (size_t)z * slab)[i];
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  if (y_dtype == NB_BF16) {
+    __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(y) + 2 * i;
+    dst[0] = __floats2bfloat162_rn(acc.x, acc.y);
+    dst[1] = __floats2bfloat162_rn(acc.z, acc.w);
+  } else {
+    reinterpret_cast<float4*>(y)[i] = acc;
+  }
+}
+
 // (rows, cols) row-major 16-bit matrix -> tensor map with a (box_rows x 64) box and 128-byte swizzle.
 static int make_map_f16(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
   return make_map(map, base, rows, cols, box_rows);   // element size and swizzle are those of the bf16 maps
@@ -349,9 +390,20 @@ using namespace nb;
 extern "C" int nb_fused_trace_read(long long* host) { return (int)cudaMemcpyFromSymbol(host, g_ftrace, sizeof(g_ftrace)); }
 #endif
 
-extern "C" size_t nb_prefill_fused_workspace_bytes(int M, int K) {
-  if (M < 1 || K < 1) return 0;
-  return 256 + (size_t)2 * M * K * 2;   // status word (first 256 bytes) + fp16 copy of the activations (two terms for fp32)
+// Workspace: [256 B status][fp16 operand rows x K][k-split slabs: ks x (M x N) floats]; sized for the worse of the
+// one-term (bf16 / fp16) and two-term (fp32) forms of M activation rows.
+static size_t fused_partial_bytes(int rows, int M, int N, int K) {
+  const int sms = sm_count();
+  const int bn = pick_token_tile(rows, N, sms);
+  const long tiles = (long)((rows + bn - 1) / bn) * ((N + kFM - 1) / kFM);
+  const int ks = pick_k_splits(tiles, K / kFK, sms);
+  return ks > 1 ? (size_t)ks * M * N * sizeof(float) : 0;
+}
+
+extern "C" size_t nb_prefill_fused_workspace_bytes(int M, int N, int K) {
+  if (M < 1 || N < 1 || K < kFK) return 0;
+  const size_t x_bytes = ((size_t)2 * M * K * 2 + 255) / 256 * 256;
+  return 256 + x_bytes + std::max(fused_partial_bytes(M, M, N, K), fused_partial_bytes(2 * M, M, N, K));
 }
 
 extern "C" int nb_gemm_prefill_fused(const void* x, int x_dtype, int M, const uint8_t* w_stream, int bits, int N, int K, void* y,
@@ -361,7 +413,7 @@ extern "C" int nb_gemm_prefill_fused(const void* x, int x_dtype, int M, const ui
   if (y_dtype != NB_BF16 && y_dtype != NB_F32) return NB_ERR_ARG;
   if (bits != 2 && bits != 3 && bits != 4) return NB_ERR_SHAPE;
   if (K % kBlock != 0) return NB_ERR_SHAPE;
-  if (!workspace || workspace_bytes < nb_prefill_fused_workspace_bytes(M, K)) return NB_ERR_WORKSPACE;
+  if (!workspace || workspace_bytes < nb_prefill_fused_workspace_bytes(M, N, K)) return NB_ERR_WORKSPACE;
   if ((uintptr_t)workspace % 256 || (uintptr_t)x % 16 || (uintptr_t)w_stream % 16) return NB_ERR_ALIGN;
   if (int rc = check_device()) return rc;
   cudaStream_t st = (cudaStream_t)stream;
@@ -380,11 +432,15 @@ extern "C" int nb_gemm_prefill_fused(const void* x, int x_dtype, int M, const ui
     if (int rc = check_launch()) return rc;
     xh = dst;
   }
-  const int bn = pick_token_tile(rows, N, sm_count());
+  const int sms = sm_count();
+  const int bn = pick_token_tile(rows, N, sms);
   CUtensorMap mx;
   if (int rc = make_map_f16(&mx, xh, rows, K, bn)) return rc;
   const int m_tiles = (rows + bn - 1) / bn, w_tiles = (N + kFM - 1) / kFM;
-  const int grid = std::min(sm_count(), m_tiles * w_tiles);
+  int ks = pick_k_splits((long)m_tiles * w_tiles, K / kFK, sms);
+  if (ks > 1 && (N % 4 != 0 || (uintptr_t)y % 16)) ks = 1;       // the summing kernel writes four outputs at a time
+  float* partial = reinterpret_cast<float*>(dst + ((size_t)2 * M * K * 2 + 255) / 256 * 256);
+  const int grid = std::min(sms, m_tiles * w_tiles * ks);
   int* status = reinterpret_cast<int*>(workspace);
   static bool attr_done[64][5] = {};
   int dev = 0;
@@ -394,8 +450,14 @@ extern "C" int nb_gemm_prefill_fused(const void* x, int x_dtype, int M, const ui
     if (cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kFSmem)) return record_cuda_error(e);
     attr_done[dev & 63][bits] = true;
   }
-  if (bits == 3) gemm_fused_kernel<3><<<grid, kFThreads, kFSmem, st>>>(mx, w_stream, y, y_dtype, rows, N, K, bn, m_tiles, w_tiles, pair, status);
-  else if (bits == 2) gemm_fused_kernel<2><<<grid, kFThreads, kFSmem, st>>>(mx, w_stream, y, y_dtype, rows, N, K, bn, m_tiles, w_tiles, pair, status);
-  else gemm_fused_kernel<4><<<grid, kFThreads, kFSmem, st>>>(mx, w_stream, y, y_dtype, rows, N, K, bn, m_tiles, w_tiles, pair, status);
-  return check_launch();
+  if (bits == 3) gemm_fused_kernel<3><<<grid, kFThreads, kFSmem, st>>>(mx, w_stream, y, y_dtype, rows, N, K, bn, m_tiles, w_tiles, pair, ks, partial, status);
+  else if (bits == 2) gemm_fused_kernel<2><<<grid, kFThreads, kFSmem, st>>>(mx, w_stream, y, y_dtype, rows, N, K, bn, m_tiles, w_tiles, pair, ks, partial, status);
+  else gemm_fused_kernel<4><<<grid, kFThreads, kFSmem, st>>>(mx, w_stream, y, y_dtype, rows, N, K, bn, m_tiles, w_tiles, pair, ks, partial, status);
+  if (int rc = check_launch()) return rc;
+  if (ks > 1) {
+    const size_t n4 = (size_t)M * N / 4;
+    splitk_sum_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(partial, ks, (size_t)M * N, y, y_dtype, n4);
+    return check_launch();
+  }
+  return NB_OK;
 }

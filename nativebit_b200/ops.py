@@ -297,7 +297,7 @@ def gemm_prefill_fused(x: torch.Tensor, w_stream: torch.Tensor, bits: int, n: in
         out = torch.empty(m, n, dtype=out_dtype, device=x.device)
     l = _lib.lib()
     with torch.cuda.device(x.device):
-        need = int(l.nb_prefill_fused_workspace_bytes(m, k))
+        need = int(l.nb_prefill_fused_workspace_bytes(m, n, k))
         ws = prefill_workspace(x.device, need)
         _lib.check(l.nb_gemm_prefill_fused(x.data_ptr(), _DTYPE[x.dtype], m, w_stream.data_ptr(), bits, n, k, out.data_ptr(),
                                            _DTYPE[out.dtype], ws.data_ptr(), ws.numel(), _stream()), "nb_gemm_prefill_fused")

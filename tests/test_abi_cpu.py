@@ -135,3 +135,22 @@ def test_group_plan_shares_the_weight_bytes_evenly():
     for i in range(7):
         arr[i].x = 0x100000 + 0x10000 * i                 # seven distinct activation vectors
     assert l.nb_group_build(arr, len(shapes), 3, buf, nbytes) != 0
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` runs on the host cores alone (the oracle's mirror of the reference CPU path) and
+    prints one JSON line with the keys the benchmark contract names."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
+                       stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "dequant_matvec_hbm_gbs" and line["unit"] == "GB/s"
+    assert line["higher_is_better"] is True and line["scaling"] == "strong" and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1 and line["cpu_baseline"]["value"] == line["value"]
+    assert line["e2e"] == {"value": line["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in line["config"]
