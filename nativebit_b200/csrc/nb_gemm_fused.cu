@@ -329,33 +329,35 @@ __global__ void __launch_bounds__(256) f32_to_f16_pair_kernel(const float4* __re
   out[(size_t)(2 * row + 1) * k8 + c] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
 }
 
-// Token-tile width (a multiple of 16 up to 256).  A k-step costs the longer of the tensor-core time, 2 * BN
-// clocks, and the time the producers need to fill a stage, which does not depend on BN (measured: about
-// kProducerClocks); the tile width that minimises waves * max(2 * BN, kProducerClocks) is chosen, the
-// wider one on ties (every weight tile is then dequantised fewer times).  Short inputs take one tile.
+// Tile plan of one call: token-tile width BN (a multiple of 16 up to 256) and number of k splits.  A k-step of a work
+// item costs the longer of the tensor-core time, 2 * BN clocks, and the time the producers need to fill a stage, which
+// does not depend on BN (measured: about kProducerClocks); a work item is one k split of one 128 x BN output tile, the
+// items run in waves of one per SM.  The plan with the fewest estimated clocks wins: waves * k-steps per item * clocks
+// per k-step, plus a charge for the second kernel that adds the splits' results (fixed part + its reads).  Splits keep at least four
+// k-steps each and none is empty; inputs of up to 256 operand rows take one token tile.
 constexpr int kProducerClocks = 340;
-static int pick_token_tile(int M, int N, int sms) {
-  if (M <= 256) return std::min(256, (M + 15) / 16 * 16);
+constexpr int kSplitCharge = 3000;
+struct FusedPlan { int bn, ks; };
+static FusedPlan plan_fused(int rows, int N, int K, int sms) {
+  const int KT = K / kFK;
   const int w_tiles = (N + kFM - 1) / kFM;
-  int best = 256;
+  FusedPlan best{256, 1};
   double best_cost = 1e30;
-  for (int bn = 256; bn >= 96; bn -= 16) {
-    const long tiles = (long)w_tiles * ((M + bn - 1) / bn);
-    const long waves = (tiles + sms - 1) / sms;
-    const double cost = (double)waves * std::max(2 * bn, kProducerClocks);
-    if (cost < best_cost * 0.98) { best_cost = cost; best = bn; }
+  const int bn_hi = rows <= 256 ? std::min(256, (rows + 15) / 16 * 16) : 256;
+  const int bn_lo = rows <= 256 ? bn_hi : 96;
+  for (int bn = bn_hi; bn >= bn_lo; bn -= 16) {
+    const long tiles = (long)w_tiles * ((rows + bn - 1) / bn);
+    for (int ks = 1; ks <= 8; ++ks) {
+      const int kts = (KT + ks - 1) / ks;
+      if (ks > 1 && (kts < 4 || (long)(ks - 1) * kts >= KT)) continue;
+      const long waves = (tiles * ks + sms - 1) / sms;
+      // the second kernel reads ks slabs of rows x N floats at roughly 3 KB per clock
+      const double sum_cost = ks > 1 ? kSplitCharge + (double)ks * rows * N * 4.0 / 3000.0 : 0.0;
+      const double cost = (double)waves * kts * std::max(2 * bn, kProducerClocks) + sum_cost;
+      if (cost < best_cost * 0.98) { best_cost = cost; best = FusedPlan{bn, ks}; }
+    }
   }
   return best;
-}
-
-// Number of k splits for `tiles` output tiles of KT k-steps: short inputs (fewer output tiles than half the
-// SMs) cut the k range so that one wave of work items covers the SMs; every split keeps at least four k-steps
-// and none is empty.
-static int pick_k_splits(long tiles, int KT, int sms) {
-  if (tiles * 2 > sms || KT < 8) return 1;
-  int ks = (int)std::min<long>(std::min<long>(8, sms / tiles), KT / 4);
-  while (ks > 1 && (long)(ks - 1) * ((KT + ks - 1) / ks) >= KT) --ks;
-  return std::max(ks, 1);
 }
 
 // y (rows x N) = sum over the k splits' fp32 slabs, in split order; four outputs per thread.
@@ -393,10 +395,7 @@ extern "C" int nb_fused_trace_read(long long* host) { return (int)cudaMemcpyFrom
 // Workspace: [256 B status][fp16 operand rows x K][k-split slabs: ks x (M x N) floats]; sized for the worse of the
 // one-term (bf16 / fp16) and two-term (fp32) forms of M activation rows.
 static size_t fused_partial_bytes(int rows, int M, int N, int K) {
-  const int sms = sm_count();
-  const int bn = pick_token_tile(rows, N, sms);
-  const long tiles = (long)((rows + bn - 1) / bn) * ((N + kFM - 1) / kFM);
-  const int ks = pick_k_splits(tiles, K / kFK, sms);
+  const int ks = plan_fused(rows, N, K, sm_count()).ks;
   return ks > 1 ? (size_t)ks * M * N * sizeof(float) : 0;
 }
 
@@ -433,11 +432,12 @@ extern "C" int nb_gemm_prefill_fused(const void* x, int x_dtype, int M, const ui
     xh = dst;
   }
   const int sms = sm_count();
-  const int bn = pick_token_tile(rows, N, sms);
+  const FusedPlan plan = plan_fused(rows, N, K, sms);
+  const int bn = plan.bn;
   CUtensorMap mx;
   if (int rc = make_map_f16(&mx, xh, rows, K, bn)) return rc;
   const int m_tiles = (rows + bn - 1) / bn, w_tiles = (N + kFM - 1) / kFM;
-  int ks = pick_k_splits((long)m_tiles * w_tiles, K / kFK, sms);
+  int ks = plan.ks;
   if (ks > 1 && (N % 4 != 0 || (uintptr_t)y % 16)) ks = 1;       // the summing kernel writes four outputs at a time
   float* partial = reinterpret_cast<float*>(dst + ((size_t)2 * M * K * 2 + 255) / 256 * 256);
   const int grid = std::min(sms, m_tiles * w_tiles * ks);
