@@ -560,6 +560,28 @@ def run_ours(args):
             if ops.prefill_status(dev) != 0:
                 raise RuntimeError("a bounded wait of the prefill kernel ran out")
             del wbf, xp, yp
+        # a decoder layer's four packed linears at 128 fp32 activation rows (the prefill of a 128-token prompt: the
+        # residual stream is fp32 and enters the tensor cores as two fp16 terms), replayed from a CUDA graph
+        per128 = {}
+        for j, (nm, n, k) in enumerate((("qkv", 3 * HIDDEN, HIDDEN), ("out_proj", HIDDEN, HIDDEN), ("gate_up", 2 * FFN, HIDDEN),
+                                        ("down", HIDDEN, FFN))):
+            p2, c2 = synthetic.synthetic_packed(n, k, BITS, seed=900 + j, device=dev)
+            lin = nbt.PackedLinear(p2, c2, n, k, bits=BITS)
+            xr = synthetic.synthetic_activation(128, k, 6, dev).float()
+            with torch.cuda.stream(stream):
+                for _ in range(2):
+                    lin(xr)
+                stream.synchronize()
+                gq = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gq, stream=stream):
+                    for _ in range(10):
+                        lin(xr)
+                for _ in range(2):
+                    gq.replay()
+            per128[nm] = round(timed(gq.replay, 5) / 50 * 1e3, 2)
+            del gq, lin, p2, c2
+        per128["layer_total_us"] = round(sum(per128.values()), 1)
+        prefill["128_rows_fp32_us"] = per128
 
     # ---- the full 2.2B packed decoder (configs[3]): 128-token prompt, 256 greedy tokens, batch 1
     decode = None

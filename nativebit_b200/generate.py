@@ -422,7 +422,7 @@ class DecodeSession:
         if prompt.shape[1] > self.model.context_len:
             raise RuntimeError(f"prompt of {prompt.shape[1]} tokens exceeds the context of {self.model.context_len}")
         T = int(prompt.shape[1])
-        if not self.use_graph or self.model.tp_size > 1 or not prompt.is_cuda:
+        if not self.use_graph or not prompt.is_cuda:
             self._prefill_body(prompt)
         else:
             # one CUDA graph per prompt length: the eager forward is about thirty small launches per layer and

@@ -87,3 +87,29 @@ def test_fused_dequant_gemm(built_lib, bits, m, n, k, xdt):
     yb = ops.gemm_prefill_fused(xt, w, bits, n, k, out_dtype=torch.bfloat16) if xdt != torch.float32 else None
     if yb is not None:
         assert (yb.double() - ref).abs().max() <= 2.0 ** -8 * ref.abs().max()     # bf16 output: half an ulp
+
+
+@pytest.mark.parametrize("bits,m,n,k,xdt", [(3, 64, 2560, 6912, torch.float32), (3, 128, 2560, 2560, torch.bfloat16), (2, 32, 1000, 1280, torch.float16),
+                                            (4, 40, 1002, 640, torch.float32), (3, 512, 2560, 6912, torch.bfloat16), (3, 18, 384, 7168, torch.float32)])
+def test_fused_dequant_gemm_with_k_splits(built_lib, bits, m, n, k, xdt):
+    """Short inputs: the k range of an output tile is cut into parts that run on different SMs and a second kernel adds
+    their fp32 results in k order (1002 outputs per row cannot use the four-wide summing kernel and stay unsplit).  Against
+    the fp64 product with the reference's dense weights, for both output types, and twice: bit-identical."""
+    from nativebit_b200 import ops, stream as S
+    dev = _dev()
+    packed, cb, _ = o.make_packed_linear(n, k, bits, seed=n + 7)
+    x = o.make_activation(m, k, seed=m + 3)
+    if xdt == torch.float32:
+        x = (x.astype(np.float64) * (1.0 + 1e-4 * np.arange(k))).astype(np.float32)   # needs both fp16 terms
+    w = S.stream_pack(torch.from_numpy(packed).to(dev), torch.from_numpy(cb).to(dev), bits, n, k)
+    xt = torch.from_numpy(x).to(dev).to(xdt)
+    W = torch.from_numpy(o.dequant_packed(packed, cb.astype(np.float32), n, k, bits)).to(dev)
+    ref = xt.double() @ W.double().T
+    y1 = ops.gemm_prefill_fused(xt, w, bits, n, k, out_dtype=torch.float32)
+    y2 = ops.gemm_prefill_fused(xt, w, bits, n, k, out_dtype=torch.float32)
+    yb = ops.gemm_prefill_fused(xt, w, bits, n, k, out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    assert ops.prefill_status(dev) == 0
+    assert (y1.double() - ref).abs().max() <= 2e-5 * ref.abs().max()
+    assert torch.equal(y1, y2)
+    assert (yb.double() - ref).abs().max() <= 2.0 ** -8 * ref.abs().max()
