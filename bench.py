@@ -651,6 +651,20 @@ def run_ours(args):
                   "model": "26 layers, hidden 2560, 32 heads, FFN 6912, vocab 32000, random-init 3-bit packed linears",
                   "self_check": checks}
         del model
+        torch.cuda.empty_cache()
+        # the 2-bit (K=4) model of the same shape, decode speed only
+        cfg2 = G.ModelConfig(bits=2)
+        model2 = G.PackedGPT.random_init(cfg2, seed=0, device=dev, tp_rank=rank, tp_size=world)
+        if world > 1 and args.allreduce in ("oneshot", "fused"):
+            model2.enable_oneshot_allreduce(max_batch=1)
+        if world > 1 and args.allreduce == "fused":
+            model2.enable_fused_allreduce(max_batch=1)
+        res2 = G.benchmark(model2, prompt, n_generate=128, n_runs=1)
+        t2 = torch.tensor([res2["per_token_ms"]], device=dev)
+        if world > 1:
+            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        decode["two_bit"] = {"tokens_per_s": 1e3 / float(t2), "per_token_ms": float(t2), "n_generate": 128}
+        del model2
 
     # ---- serving sweep (configs[4]): batch 1/8/32/64 decode after a 512-token prompt, 3-bit and 2-bit
     serving = None
