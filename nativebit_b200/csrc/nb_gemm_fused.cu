@@ -16,9 +16,9 @@
 // registers.  Persistent kernel, one CTA per SM, 704 threads:
 //   warp 0       one lane issues the TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast)
 //                of the BN x 64 activation slab of every k-step into a ring of stages;
-//   warp 1       allocates tensor memory; one lane waits for a stage's activations AND weights and issues
-//                four tcgen05.mma (128 x BN x 16, fp16 x fp16 -> fp32) per stage, then tcgen05.commit on
-//                the stage's "empty" barrier;
+//   warp 1       allocates tensor memory; one lane waits on the stage's "full" barrier (eight producer warps'
+//                arrivals + the TMA bytes) and issues four tcgen05.mma (128 x BN x 16, fp16 x fp16 -> fp32)
+//                per stage, then tcgen05.commit on the stage's "empty" barrier;
 //   warps 2-5    epilogue: each warp owns one 32-lane quadrant of tensor memory (32 output features),
 //                reads a finished accumulator with tcgen05.ld and stores Y (transposed: lanes run along
 //                N, so a warp's store of one token covers 32 consecutive outputs);
@@ -83,9 +83,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;                         // weights
   uint8_t* sB = smem + S * kFABytes;          // activations
-  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + kFRing);
-  uint64_t* full_b = full_a + kFMaxStages;
-  uint64_t* empty = full_b + kFMaxStages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kFRing);   // a stage's weights (8 producer warps) AND activations (TMA bytes)
+  uint64_t* empty = full + kFMaxStages;
   uint64_t* acc_full = empty + kFMaxStages;   // [2] MMA -> epilogue
   uint64_t* acc_empty = acc_full + 2;         // [2] epilogue -> MMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
@@ -98,7 +97,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
   const int rows_padded = ((N + 15) >> 4) << 4;   // rows the stream layout holds (zero rows past N)
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) { bar_init(&full_a[s], kFProducerWarps); bar_init(&full_b[s], 1); bar_init(&empty[s], 1); }
+    for (int s = 0; s < S; ++s) { bar_init(&full[s], kFProducerWarps + 1); bar_init(&empty[s], 1); }
     for (int b = 0; b < 2; ++b) { bar_init(&acc_full[b], 1); bar_init(&acc_empty[b], 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -128,8 +127,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
           ok = bar_wait(&empty[s], phase ^ 1, abort_flag, status);
           if (!ok) break;
           FTRACE(0, kt);
-          bar_expect_tx(&full_b[s], (uint32_t)b_bytes);
-          tma_load_2d(sB + s * b_bytes, &map_x, &full_b[s], kt * kFK, m0);
+          bar_expect_tx(&full[s], (uint32_t)b_bytes);
+          tma_load_2d(sB + s * b_bytes, &map_x, &full[s], kt * kFK, m0);
           if (++s == S) { s = 0; phase ^= 1; }
         }
         if (!ok) break;
@@ -140,6 +139,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
       // instruction descriptor: fp32 accumulate (bit 4), A and B fp16 (format 0 at bits 7 and 10), both K-major,
       // N = BN (tokens), M = 128 (features)
       const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kFM >> 4) << 24);
+      const uint64_t desc_a0 = smem_desc_sw128(sA), desc_b0 = smem_desc_sw128(sB);
       int s = 0, local = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < n_total; t += gridDim.x, ++local) {
@@ -149,16 +149,16 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * 256);
         const int k_lo = (t % ks) * KTs, k_hi = min(KT, k_lo + KTs);
         for (int kt = k_lo; kt < k_hi && ok; ++kt) {
-          ok = bar_wait(&full_a[s], phase, abort_flag, status);
-          FTRACE(1, kt);
-          ok = ok && bar_wait(&full_b[s], phase, abort_flag, status);
+          ok = bar_wait(&full[s], phase, abort_flag, status);
           if (!ok) break;
           FTRACE(2, kt);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint64_t da = smem_desc_sw128(sA + s * kFABytes), db = smem_desc_sw128(sB + s * b_bytes);
+          // the stage's descriptors: the start-address field counts 16-byte units, so a stage further on is an add
+          const uint64_t da = desc_a0 + (uint64_t)(s * (kFABytes >> 4)), db = desc_b0 + (uint64_t)(s * (b_bytes >> 4));
+          umma_f16(tmem_d, da, db, idesc, kt > k_lo ? 1u : 0u);
 #pragma unroll
-          for (int k4 = 0; k4 < kFK / 16; ++k4)  // 16 fp16 = 32 bytes = 2 descriptor address units per step
-            umma_f16(tmem_d, da + 2 * k4, db + 2 * k4, idesc, (kt > k_lo || k4 > 0) ? 1u : 0u);
+          for (int k4 = 1; k4 < kFK / 16; ++k4)  // 16 fp16 = 32 bytes = 2 descriptor address units per step
+            umma_f16(tmem_d, da + 2 * k4, db + 2 * k4, idesc, 1u);
           umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
           if (++s == S) { s = 0; phase ^= 1; }
         }
@@ -279,7 +279,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
         __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s2u(&full_a[s])) : "memory");
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s2u(&full[s])) : "memory");
         if (pp == 0) FTRACE(5, kt);
         sel = sel_n;
 #pragma unroll
