@@ -115,6 +115,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       // fp16 (format 0) at bits 7 and 10, both K-major, N = BN, M = 128
       const uint32_t fmt = f16 ? 0u : 1u;
       const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      const uint64_t desc_a0 = smem_desc_sw128(sA), desc_b0 = smem_desc_sw128(sB);
       int s = 0, local = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < n_total; t += gridDim.x, ++local) {
@@ -127,10 +128,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           ok = bar_wait(&full[s], phase, abort_flag, status);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint64_t da = smem_desc_sw128(sA + s * Cfg::kABytes), db = smem_desc_sw128(sB + s * b_bytes);
+          // the stage's descriptors: the start-address field counts 16-byte units, so a stage further on is an add
+          const uint64_t da = desc_a0 + (uint64_t)(s * (Cfg::kABytes >> 4)), db = desc_b0 + (uint64_t)(s * (b_bytes >> 4));
+          umma_f16(tmem_d, da, db, idesc, kt > 0 ? 1u : 0u);
 #pragma unroll
-          for (int k4 = 0; k4 < kBK / 16; ++k4)  // 16 bf16 = 32 bytes = 2 descriptor address units per step
-            umma_f16(tmem_d, da + 2 * k4, db + 2 * k4, idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
+          for (int k4 = 1; k4 < kBK / 16; ++k4)  // 16 bf16 = 32 bytes = 2 descriptor address units per step
+            umma_f16(tmem_d, da + 2 * k4, db + 2 * k4, idesc, 1u);
           umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
           if (++s == S) { s = 0; phase ^= 1; }
         }
