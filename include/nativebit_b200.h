@@ -113,7 +113,8 @@ int nb_gemv_ordered(const void* x, int x_dtype, int M, const uint8_t* packed, co
  * nativebit_jax/packed_kernel.py:86-97, 151-178 (16-bit operands, fp32 accumulation) with one
  * difference: the weights enter as the fp16 codebook entries themselves (exact), not rounded to bf16,
  * and the bf16 activations are converted to fp16 (exact for magnitudes 6.1e-5..65504, clamped above).
- * x: (M, K) NB_BF16 or NB_F16 row-major, 16-byte aligned; y: (M, N) NB_BF16 or NB_F32; K % 64 == 0 and
+ * x: (M, K) NB_BF16, NB_F16 or NB_F32 (two fp16 terms per element in adjacent operand rows, their results added
+ * in the epilogue) row-major, 16-byte aligned; y: (M, N) NB_BF16 or NB_F32; K % 64 == 0 and
  * K % block_size == 0; bits in {2,3,4}.  `workspace` must be 256-byte aligned and hold
  * nb_prefill_workspace_bytes(M, N, K) bytes: its first 256 bytes carry a status word that must be
  * zero before the first call and is set to NB_ERR_TIMEOUT if a bounded wait inside the kernel ran

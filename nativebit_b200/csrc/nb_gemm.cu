@@ -56,7 +56,7 @@ struct GemmCfg {
 // Two accumulator buffers in tensor memory let the epilogue of one tile overlap the MMAs of the next.
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* __restrict__ y,
-                 int y_dtype, int M, int N, int K, int BN, int m_tiles, int n_tiles, int f16, int* status) {
+                 int y_dtype, int M, int N, int K, int BN, int m_tiles, int n_tiles, int f16, int pair, int* status) {
   using Cfg = GemmCfg;
   const int S = Cfg::stages(BN);
   const int b_bytes = BN * kBK * 2;   // multiple of 1024 because BN is a multiple of 16
@@ -164,10 +164,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int n = n0 + c * 16;
-        if (m < M && n < N) {
+        int m_st = m, rows_st = M;
+        if (pair) {
+          // operand rows 2i and 2i+1 are the two fp16 terms of activation row i: adjacent lanes add their results
+          // (every lane takes part in the shuffles), the even lane stores output row i
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            r[j] = __float_as_uint(__uint_as_float(r[j]) + __shfl_xor_sync(0xffffffffu, __uint_as_float(r[j]), 1));
+          m_st = m >> 1;
+          rows_st = M >> 1;
+        }
+        if ((!pair || !(lane & 1)) && m_st < rows_st && n < N) {
           const bool whole = n + 16 <= N;
           if (y_dtype == NB_BF16) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(y) + (size_t)m * N + n;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(y) + (size_t)m_st * N + n;
             if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
               uint32_t pk[8];
 #pragma unroll
@@ -183,7 +193,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 if (n + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
             }
           } else {
-            float* dst = reinterpret_cast<float*>(y) + (size_t)m * N + n;
+            float* dst = reinterpret_cast<float*>(y) + (size_t)m_st * N + n;
             if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
@@ -226,7 +236,7 @@ static int pick_bn(int M, int N, int sms) {
 }
 
 static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, void* y, int y_dtype, int M, int N, int K, int bn,
-                       int f16, int* status, cudaStream_t st) {
+                       int f16, int pair, int* status, cudaStream_t st) {
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -237,7 +247,7 @@ static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, void* y, in
   }
   const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + bn - 1) / bn;
   const int grid = std::min(sm_count(), m_tiles * n_tiles);
-  gemm_bf16_kernel<<<grid, 192, GemmCfg::kSmem, st>>>(mx, mw, y, y_dtype, M, N, K, bn, m_tiles, n_tiles, f16, status);
+  gemm_bf16_kernel<<<grid, 192, GemmCfg::kSmem, st>>>(mx, mw, y, y_dtype, M, N, K, bn, m_tiles, n_tiles, f16, pair, status);
   return check_launch();
 }
 
@@ -247,8 +257,8 @@ using namespace nb;
 
 extern "C" size_t nb_prefill_workspace_bytes(int M, int N, int K) {
   if (M < 1 || N < 1 || K < 1) return 0;
-  // status word (first 256 bytes) + fp16 weight + fp16 copy of the activations
-  return 256 + (((size_t)N * K * 2 + 255) & ~(size_t)255) + (size_t)M * K * 2;
+  // status word (first 256 bytes) + fp16 weight + fp16 copy of the activations (two terms per element for fp32)
+  return 256 + (((size_t)N * K * 2 + 255) & ~(size_t)255) + (size_t)2 * M * K * 2;
 }
 
 namespace nb {
@@ -268,8 +278,10 @@ __global__ void __launch_bounds__(256) bf16_to_f16_kernel(const uint4* __restric
 }
 }  // namespace nb
 
-// x (M, K) times w (N, K), both bf16 or both fp16 (f16).  The tensor maps copy 2-byte elements either way.
-static int gemm_16bit(const void* x, const void* w, int f16, int M, int N, int K, void* y, int y_dtype, int* status, void* stream) {
+// x (M, K) times w (N, K), both bf16 or both fp16 (f16).  The tensor maps copy 2-byte elements either way.  pair: rows
+// 2i and 2i+1 of x are the two fp16 terms of one activation row; y then has M / 2 rows.
+static int gemm_16bit(const void* x, const void* w, int f16, int M, int N, int K, void* y, int y_dtype, int* status, void* stream,
+                      int pair = 0) {
   if (!x || !w || !y || M < 1 || N < 1 || K < 1) return NB_ERR_ARG;
   if (y_dtype != NB_BF16 && y_dtype != NB_F32) return NB_ERR_ARG;
   if (K % kBK != 0) return NB_ERR_SHAPE;
@@ -280,7 +292,7 @@ static int gemm_16bit(const void* x, const void* w, int f16, int M, int N, int K
   if (int rc = make_map(&mx, x, M, K, kBM)) return rc;
   if (int rc = make_map(&mw, w, N, K, bn)) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  return launch_gemm(mx, mw, y, y_dtype, M, N, K, bn, f16, status, st);
+  return launch_gemm(mx, mw, y, y_dtype, M, N, K, bn, f16, pair, status, st);
 }
 
 extern "C" int nb_gemm_bf16(const void* x, const void* w, int M, int N, int K, void* y, int y_dtype, int* status, void* stream) {
@@ -291,7 +303,7 @@ extern "C" int nb_gemm_prefill(const void* x, int x_dtype, int M, const uint8_t*
                                int block_size, int N, int K, void* y, int y_dtype, void* workspace, size_t workspace_bytes,
                                void* stream) {
   if (!x || !packed || !codebook || !y) return NB_ERR_ARG;
-  if (x_dtype != NB_BF16 && x_dtype != NB_F16) return NB_ERR_ARG;
+  if (x_dtype != NB_BF16 && x_dtype != NB_F16 && x_dtype != NB_F32) return NB_ERR_ARG;
   if (!workspace || workspace_bytes < nb_prefill_workspace_bytes(M, N, K)) return NB_ERR_WORKSPACE;
   if ((uintptr_t)workspace % 256) return NB_ERR_ALIGN;
   if (K % kBK != 0 || K % block_size != 0) return NB_ERR_SHAPE;
@@ -301,6 +313,12 @@ extern "C" int nb_gemm_prefill(const void* x, int x_dtype, int M, const uint8_t*
   if (int rc = nb_dequant(packed, codebook, cb_dtype, bits, block_size, N, K, w, NB_F16, stream)) return rc;
   if (x_dtype == NB_F16) return gemm_16bit(x, w, 1, M, N, K, y, y_dtype, reinterpret_cast<int*>(workspace), stream);
   const size_t n8 = (size_t)M * K / 8;  // K % 64 == 0
+  if (x_dtype == NB_F32) {  // two fp16 terms per element as operand rows 2i, 2i+1; the epilogue adds their results
+    f32_to_f16_pair_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const float4*>(x),
+                                                                                          reinterpret_cast<uint4*>(xh), M, K);
+    if (int rc = check_launch()) return rc;
+    return gemm_16bit(xh, w, 1, 2 * M, N, K, y, y_dtype, reinterpret_cast<int*>(workspace), stream, 1);
+  }
   bf16_to_f16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const uint4*>(x),
                                                                                     reinterpret_cast<uint4*>(xh), n8);
   if (int rc = check_launch()) return rc;

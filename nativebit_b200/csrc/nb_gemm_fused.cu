@@ -309,26 +309,6 @@ __global__ void __launch_bounds__(256) bf16_to_f16_kernel2(const uint4* __restri
   out[i] = make_uint4(r[0], r[1], r[2], r[3]);
 }
 
-// fp32 -> two fp16 terms per element, hi = fp16(x) (saturating) and lo = fp16(x - hi), written as rows 2i and
-// 2i+1 of a (2M, K) fp16 matrix: x = hi + lo to about 22 significant bits.  Eight elements per thread.
-__global__ void __launch_bounds__(256) f32_to_f16_pair_kernel(const float4* __restrict__ in, uint4* __restrict__ out, int M, int K) {
-  const int k8 = K >> 3;
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (size_t)M * k8) return;
-  const int row = (int)(i / k8), c = (int)(i - (size_t)row * k8);
-  const float4 a = in[2 * i], b = in[2 * i + 1];
-  const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-  uint32_t hi[4], lo[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    hi[j] = f32x2_to_f16x2_sat(v[2 * j], v[2 * j + 1]);
-    const float2 h = __half22float2(*reinterpret_cast<const __half2*>(&hi[j]));
-    lo[j] = f32x2_to_f16x2_sat(v[2 * j] - h.x, v[2 * j + 1] - h.y);
-  }
-  out[(size_t)(2 * row) * k8 + c] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-  out[(size_t)(2 * row + 1) * k8 + c] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-}
-
 // Tile plan of one call: token-tile width BN (a multiple of 16 up to 256) and number of k splits.  A k-step of a work
 // item costs the longer of the tensor-core time, 2 * BN clocks, and the time the producers need to fill a stage, which
 // does not depend on BN (measured: about kProducerClocks); a work item is one k split of one 128 x BN output tile, the

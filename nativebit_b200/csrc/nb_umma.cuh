@@ -4,11 +4,13 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <cuda_fp16.h>
 
 #include <cstdio>
 #include <mutex>
 
 #include "nb_common.cuh"
+#include "nb_device.cuh"
 #include "nb_host.h"
 
 namespace nb {
@@ -107,5 +109,26 @@ inline int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
   }
   return NB_OK;
 }
+
+// fp32 -> two fp16 terms per element, hi = fp16(x) (saturating) and lo = fp16(x - hi), written as rows 2i and
+// 2i+1 of a (2M, K) fp16 matrix: x = hi + lo to about 22 significant bits.  Eight elements per thread.
+static __global__ void __launch_bounds__(256) f32_to_f16_pair_kernel(const float4* __restrict__ in, uint4* __restrict__ out, int M, int K) {
+  const int k8 = K >> 3;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)M * k8) return;
+  const int row = (int)(i / k8), c = (int)(i - (size_t)row * k8);
+  const float4 a = in[2 * i], b = in[2 * i + 1];
+  const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  uint32_t hi[4], lo[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    hi[j] = f32x2_to_f16x2_sat(v[2 * j], v[2 * j + 1]);
+    const float2 h = __half22float2(*reinterpret_cast<const __half2*>(&hi[j]));
+    lo[j] = f32x2_to_f16x2_sat(v[2 * j] - h.x, v[2 * j + 1] - h.y);
+  }
+  out[(size_t)(2 * row) * k8 + c] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+  out[(size_t)(2 * row + 1) * k8 + c] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+}
+
 
 }  // namespace nb

@@ -243,25 +243,18 @@ def prefill_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def gemm_prefill(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size: int,
                  n: int, k: int, out_dtype: torch.dtype = torch.bfloat16, out: torch.Tensor | None = None) -> torch.Tensor:
-    """y (M, n) = x (M, k) @ W.T on the tcgen05 tensor cores.  x bf16 or fp16.  fp32 activations are
-    carried as the sum of two fp16 terms (about 22 significant bits, as in the GEMV): the terms are
-    stacked into one (2M, k) operand, so the weights are dequantised once, and the two halves of the
-    fp32 result are added."""
+    """y (M, n) = x (M, k) @ W.T on the tcgen05 tensor cores: W is dequantised once into the workspace, then
+    the plain tensor-core kernel multiplies.  x bf16, fp16 or fp32; the library carries fp32 activations as two
+    fp16 terms per element (about 22 significant bits, as in the GEMV) in adjacent operand rows and adds their
+    results in the epilogue."""
     _need_cuda(x, packed, codebook)
-    if x.dtype == torch.float32:
-        xc = x.clamp(-65504.0, 65504.0)
-        hi = xc.half()
-        lo = (xc - hi.float()).half()
-        m = x.shape[0]
-        y2 = gemm_prefill(torch.cat((hi, lo)), packed, codebook, bits, block_size, n, k, out_dtype=torch.float32)
-        y = y2[:m].add_(y2[m:])
-        if out is not None:
-            out.copy_(y)
-            return out
-        return y if out_dtype in (torch.float32, None) else y.to(out_dtype)
-    if x.dtype not in (torch.bfloat16, torch.float16) or x.dim() != 2 or x.shape[1] != k:
-        raise RuntimeError(f"x must be a 16-bit (M, {k}) tensor; got {x.dtype} {tuple(x.shape)}")
+    if x.dtype not in (torch.bfloat16, torch.float16, torch.float32) or x.dim() != 2 or x.shape[1] != k:
+        raise RuntimeError(f"x must be a bf16, fp16 or fp32 (M, {k}) tensor; got {x.dtype} {tuple(x.shape)}")
+    if not x.is_contiguous():
+        x = x.contiguous()
     m = x.shape[0]
+    if out_dtype is None:
+        out_dtype = out.dtype if out is not None else x.dtype
     if out is None and out_dtype == torch.float16:     # the kernel writes bf16 or fp32
         return gemm_prefill(x, packed, codebook, bits, block_size, n, k, out_dtype=torch.float32).half()
     if out is None:

@@ -113,3 +113,24 @@ def test_fused_dequant_gemm_with_k_splits(built_lib, bits, m, n, k, xdt):
     assert (y1.double() - ref).abs().max() <= 2e-5 * ref.abs().max()
     assert torch.equal(y1, y2)
     assert (yb.double() - ref).abs().max() <= 2.0 ** -8 * ref.abs().max()
+
+
+@pytest.mark.parametrize("m,n,k", [(130, 200, 256), (1100, 640, 1280)])
+def test_dequant_then_gemm_with_fp32_activations(built_lib, m, n, k):
+    """The two-kernel form with fp32 activations: the library splits them into two fp16 terms in adjacent operand rows
+    and the epilogue adds the pair's results; 1100 rows is also what PackedLinear sends this way."""
+    import nativebit_b200 as nbt
+    from nativebit_b200 import ops
+    dev = _dev()
+    packed, cb, _ = o.make_packed_linear(n, k, 3, seed=m)
+    x = (o.make_activation(m, k, seed=m).astype(np.float64) * (1.0 + 1e-4 * np.arange(k))).astype(np.float32)
+    xt = torch.from_numpy(x).to(dev)
+    p, c = torch.from_numpy(packed).to(dev), torch.from_numpy(cb).to(dev)
+    W = torch.from_numpy(o.dequant_packed(packed, cb.astype(np.float32), n, k, 3)).to(dev)
+    ref = xt.double() @ W.double().T
+    y = ops.gemm_prefill(xt, p, c, 3, 128, n, k, out_dtype=torch.float32)
+    yl = nbt.PackedLinear(p, c, n, k)(xt)
+    torch.cuda.synchronize()
+    assert ops.prefill_status(dev) == 0
+    assert (y.double() - ref).abs().max() <= 2e-5 * ref.abs().max()
+    assert yl.dtype == torch.float32 and (yl.double() - ref).abs().max() <= 2e-5 * ref.abs().max()
