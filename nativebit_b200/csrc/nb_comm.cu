@@ -16,12 +16,14 @@
 // status word and returns with whatever has arrived.
 #include <cuda_runtime.h>
 
+#include <algorithm>
+
 #include "nb_common.cuh"
 #include "nb_host.h"
 
 namespace nb {
 
-constexpr int kArChunks = 8;             // CTAs per all-reduce
+constexpr int kArChunks = 32;            // most CTAs per all-reduce (8 for decode-sized vectors, more for long ones)
 constexpr int kArMaxWorld = 8;
 constexpr uint32_t kArSpinLimit = 1u << 24;
 
@@ -54,7 +56,7 @@ __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const ArParams p
   const int set = seq & 1;
   // this CTA's share of the vector, in float4 units
   const int n4 = p.count >> 2;
-  const int per = (n4 + kArChunks - 1) / kArChunks;
+  const int per = (n4 + (int)gridDim.x - 1) / (int)gridDim.x;
   const int i0 = c * per, i1 = min(n4, i0 + per);
   const size_t slot_off = ((size_t)set * p.world + p.rank) * p.max_count;
 
@@ -132,6 +134,8 @@ extern "C" int nb_allreduce(const float* in, float* out, int count, const uint64
   // A plain, fully stream-ordered launch.  Programmatic dependent launch was measured on two GPUs (2.2B decoder,
   // batch 1): releasing the next kernel at this kernel's start 1.94 ms/token, after its dependency wait 1.66 ms,
   // plain launch 1.56 ms — the kernels that start early crowd out the GEMV that is still computing.
-  allreduce_oneshot_kernel<<<kArChunks, 256, 0, (cudaStream_t)stream>>>(p);
+  // every rank derives the same number of CTAs from the count: 8 up to 4096 floats per CTA, then more, up to kArChunks
+  const int ctas = std::min(kArChunks, std::max(8, count / 2048));
+  allreduce_oneshot_kernel<<<ctas, 256, 0, (cudaStream_t)stream>>>(p);
   return check_launch();
 }
