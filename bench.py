@@ -212,7 +212,7 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     m = args.batch
-    use_group = m == 1 and not args.chain          # one launch of the persistent kernel per step
+    use_group = m <= 8 and not args.chain          # one launch per step, if the activations fit its shared memory (1..4 rows here)
 
     # ---- weights: every rank generates the same global matrices (seed 10 * layer + j) and keeps its shard
     ch0, ch_n = tp.ffn_shard_plan(FFN, world, rank)            # hidden channels of this rank
@@ -266,7 +266,10 @@ def run_ours(args):
     if use_group:
         items = [(mods[nm], x, out[l]) for l, mods in enumerate(layers) for nm, out in (("gate", y_gate), ("up", y_up))]
         items += [(mods["down"], h, y_down[l]) for l, mods in enumerate(layers)]
-        group = nbt.MatvecGroup(items)
+        try:
+            group = nbt.MatvecGroup(items)
+        except RuntimeError:                       # too many activation rows for the kernel's shared memory: the graph of launches
+            use_group = False
 
     def group_step():
         group.run()
@@ -349,7 +352,7 @@ def run_ours(args):
               "ms_per_step_min_block": min(block_ms) / args.steps, "ms_per_step_max_block": max(block_ms) / args.steps}
     # the other way of issuing the same step, for the record
     other = None
-    if m == 1 and not args.chain:
+    if use_group:
         with torch.cuda.stream(stream):
             for _ in range(3):
                 graph.replay()
@@ -464,6 +467,23 @@ def run_ours(args):
                             "frac": alg_bytes(1, n, k) / (t * 1e-3) / 1e9 / peak, "matrices_per_launch": len(its)}
                 g.check()
                 del g
+            # four activation rows per matrix (configs[1] at batch 4): rows ride in the MMA's columns
+            if m == 1:
+                x4 = synthetic.synthetic_activation(4, HIDDEN, 7, dev)
+                h4 = synthetic.synthetic_activation(4, FFN, 8, dev)
+                yg4 = torch.empty(len(gate_up), 4, FFN, dtype=torch.bfloat16, device=dev)
+                yd4 = torch.empty(LAYERS, 4, HIDDEN, dtype=torch.bfloat16, device=dev)
+                for tag, its, n, k in (("6912x2560_b4", [(lin, x4, yg4[i]) for i, lin in enumerate(gate_up)], FFN, HIDDEN),
+                                       ("2560x6912_b4", [(mods["down"], h4, yd4[l]) for l, mods in enumerate(layers)], HIDDEN, FFN)):
+                    g = nbt.MatvecGroup(its)
+                    with torch.cuda.stream(stream):
+                        for _ in range(3):
+                            g.run()
+                    t = statistics.median(timed_blocks(g.run, 10, 5)) / 10 / len(its)
+                    per[tag] = {"us_per_matrix": t * 1e3, "GBps": alg_bytes(4, n, k) / (t * 1e-3) / 1e9,
+                                "frac": alg_bytes(4, n, k) / (t * 1e-3) / 1e9 / peak, "matrices_per_launch": len(its)}
+                    del g
+                del x4, h4, yg4, yd4
             # the other index widths of the format (2-bit K=4, 4-bit K=16), 26 matrices of 6912 x 2560 per launch
             for wb in (2, 4):
                 its = []
@@ -480,7 +500,7 @@ def run_ours(args):
                                              "matrices_per_launch": len(its), "algorithmic_bytes": ab}
                 del g, its
             roofline = {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
-                        "traffic": NCU_TRAFFIC_STEP,
+                        "traffic": NCU_TRAFFIC_STEP if m == 1 else None,
                         "kernel": "nb::group_kernel<3>, one launch = the 78 matrices of a step",
                         "us_per_launch": ms_per_step * 1e3, "algorithmic_bytes": int(step_bytes), "peak_source": peak_src,
                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch over 20 matrices of 6912x2560 "

@@ -341,10 +341,12 @@ int nb_stream_run(const nb_stream_op* ops_host, const nb_stream_op* ops_device, 
  * inference/cuda_kernel.py:84-104); here the row tiles of all matrices form one sequence that the CTAs share
  * by weight bytes, a warp computes a whole 16-row tile from the first k-block to the last with the sums in
  * registers, and nothing waits on anything but its own copies (no flags, no status word needed).
- * Weights are nb_stream_pack copies (row_mode 0), all of one `bits`; x: k values of x_dtype (NB_F32 carried as
- * two fp16 terms), 16-byte aligned, K % 128 == 0 and K <= 7168; y: n values of y_dtype.  At most
- * nb_group_max_items() matvecs and 6 distinct activation vectors whose staged copies fit 64 KB of shared
- * memory (a K-element vector takes K * 2.5 bytes per fp16 term, the first term of an fp32 vector 17920 bytes).
+ * Weights are nb_stream_pack copies (row_mode 0), all of one `bits`; x: m rows of k values of x_dtype, 16-byte
+ * aligned, K % 128 == 0 and K <= 7168 (one row: NB_F32 is carried as two fp16 terms; 2..8 rows: NB_F16 or
+ * NB_BF16 only, each row one column of the MMA); y: m rows of n values of y_dtype.  At most
+ * nb_group_max_items() matvecs and 6 distinct activation matrices whose staged copies fit 104 KB of shared
+ * memory (64 KB at 4 bits; a row takes K * 2.5 bytes per fp16 term, the first term of an fp32 vector 17920
+ * bytes; beyond 64 KB the copy rings are one stage shorter).
  * nb_group_build validates the list and writes the launch plan (nb_group_plan_bytes(items, n) bytes: a header
  * and one word per 16-row tile) into host memory: the row tiles are dealt out to the CTAs longest first, each
  * to the CTA with the least work so far, so that all CTAs finish within one short tile of one another.  The
@@ -355,6 +357,8 @@ typedef struct {
   const void* x;
   void* y;
   int32_t n, k, x_dtype, y_dtype;
+  int32_t m;          /* activation rows, 1..8 (0 means 1): x is (m, k), y is (m, n), both row-major */
+  int32_t reserved;   /* zero */
 } nb_group_item;
 size_t nb_group_plan_bytes(const nb_group_item* items, int n_items);
 int nb_group_max_items(void);

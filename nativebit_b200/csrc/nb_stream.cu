@@ -1075,7 +1075,8 @@ constexpr int kGroupMaxX = 6;
 constexpr int kGW = 24;                                   // warps per CTA: measured 0.174 ms per 691 MB step against 0.187 with 16 warps
                                                           // working on two units at a time; 20, 28 and 32 warps within 2 % of 24
 constexpr int kGroupRing = 160 * 1024;                    // the warps' copy rings (5 stages of one unit per warp at 2 and 3 bits)
-constexpr int kGroupXBytes = 64 * 1024;                   // shared memory for the staged activation vectors
+constexpr int kGroupRingSmall = 120 * 1024;               // ... 4 stages, when the staged activations need the room (2 and 3 bits)
+constexpr int kGroupXBytes = 64 * 1024;                   // shared memory for the staged activations beside the large ring
 constexpr int kGroupFifo = 8;                             // row tiles a warp may have taken ahead of its arithmetic
 constexpr int kGroupSmem = kGroupRing + kGroupXBytes;
 
@@ -1087,24 +1088,25 @@ struct GroupItem {            // 48 bytes
   int x_off;                  // byte offset of its staged activations in shared memory
   int xs;                     // fp16 terms per activation (2: fp32 activations)
   int y_dtype;
-  int pad[2];
+  int m;                      // activation rows (1..8): column g of the MMA carries row g
+  int x_row;                  // bytes between the staged rows
 };
-struct GroupX {               // 24 bytes: one distinct activation vector
+struct GroupX {               // 32 bytes: one distinct activation matrix (m rows of k values)
   const void* ptr;
-  int k, dtype, off, xs;
+  int k, dtype, off, xs, m, row;
 };
 struct GroupPlan {
-  int n_items, n_x, total_tiles, ctas, bits, pad[3];
+  int n_items, n_x, total_tiles, ctas, bits, ring_bytes, pad[2];
   GroupX xv[kGroupMaxX];
   int cta_lo[kMaxCtas + 1];   // CTA c owns entries [cta_lo[c], cta_lo[c + 1]) of the tile list
   GroupItem items[kGroupMaxItems];
   int tile_list[1];           // total_tiles row-tile indices: every CTA's tiles, the longest first (the plan is allocated with the list's real length)
 };
 
-template <int BITS, int GW, bool PAIR>
+template <int BITS, int GW, bool PAIR, int RING>
 __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __restrict__ plan) {
   using F = UnitFmt<BITS>;
-  constexpr int D = kGroupRing / (GW * F::kBytes) < 8 ? kGroupRing / (GW * F::kBytes) : 8;   // ring stages per warp
+  constexpr int D = RING / (GW * F::kBytes) < 8 ? RING / (GW * F::kBytes) : 8;   // ring stages per warp
   constexpr int kThreads = GW * 32;
   static_assert(D >= 4, "the per-warp ring needs at least four stages");
   extern __shared__ __align__(16) uint8_t smem[];
@@ -1113,7 +1115,7 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
   __shared__ int s_fifo[GW][kGroupFifo];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* ring = smem + warp * (D * F::kBytes);
-  uint8_t* x_all = smem + kGroupRing;
+  uint8_t* x_all = smem + RING;
   const int n_items = plan->n_items;
   const int t_lo = plan->cta_lo[blockIdx.x], t_hi = plan->cta_lo[blockIdx.x + 1];
 
@@ -1121,30 +1123,32 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
   // lane share of a k-block)
   for (int v = 0; v < plan->n_x; ++v) {
     const GroupX xv = plan->xv[v];
-    uint8_t* x_s = x_all + xv.off;
-    for (int i4 = tid; i4 < xv.k / 4; i4 += kThreads) {
+    const int k4 = xv.k / 4;
+    for (int e = tid; e < xv.m * k4; e += kThreads) {
+      const int r = e / k4, i4 = e - r * k4;
+      uint8_t* x_s = x_all + xv.off + r * xv.row;
       float u[4];
       if (xv.dtype == NB_F32) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(xv.ptr) + i4);
+        const float4 a = __ldg(reinterpret_cast<const float4*>(xv.ptr) + e);
         u[0] = a.x; u[1] = a.y; u[2] = a.z; u[3] = a.w;
         stage4<2>(x_s, i4, u[0], u[1], u[2], u[3]);
       } else {
-        const uint2 r = __ldg(reinterpret_cast<const uint2*>(xv.ptr) + i4);
+        const uint2 q = __ldg(reinterpret_cast<const uint2*>(xv.ptr) + e);
         if (xv.dtype == NB_BF16) {
-          u[0] = __uint_as_float(r.x << 16); u[1] = __uint_as_float(r.x & 0xFFFF0000u);
-          u[2] = __uint_as_float(r.y << 16); u[3] = __uint_as_float(r.y & 0xFFFF0000u);
+          u[0] = __uint_as_float(q.x << 16); u[1] = __uint_as_float(q.x & 0xFFFF0000u);
+          u[2] = __uint_as_float(q.y << 16); u[3] = __uint_as_float(q.y & 0xFFFF0000u);
         } else {
-          const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&r.x));
-          const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+          const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&q.x));
+          const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&q.y));
           u[0] = f0.x; u[1] = f0.y; u[2] = f1.x; u[3] = f1.y;
         }
         stage4<1>(x_s, i4, u[0], u[1], u[2], u[3]);
       }
     }
   }
-  // 128 zero bytes: the activations of the seven MMA columns that a single activation vector does not use
-  // (all eight columns would otherwise carry the same vector; zeros cost the tensor cores less power)
-  uint8_t* x_zero = x_all + kGroupXBytes - 128;
+  // 128 zero bytes: the activations of the MMA columns that carry no activation row (with one row, seven of the
+  // eight; all columns would otherwise carry the same vector, and zeros cost the tensor cores less power)
+  uint8_t* x_zero = smem + kGroupSmem - 128;
   if (tid < 32) reinterpret_cast<uint32_t*>(x_zero)[tid] = 0u;
   for (int i = tid; i <= n_items; i += kThreads) s_tile0[i] = i < n_items ? plan->items[i].tile0 : plan->total_tiles;
   if (tid == 0) s_next = t_lo;
@@ -1233,10 +1237,10 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
         if (it.xs == 2) unit_mma2<BITS, 2>(u0, u1, x_s, j, j + 1, lane, c0, c1);
         else unit_mma2<BITS, 1>(u0, u1, x_s, j, j + 1, lane, c0, c1);
       } else {
-        // column 0 of the MMA carries the activation vector (lanes g == 0 supply it), the other columns zeros
-        const bool col0 = lane < 4;
-        const uint8_t* xseg = col0 ? x_s + (j * 4 + (lane & 3)) * kXSegBytes : x_zero;
-        if (it.xs == 2) unit_mma_x<BITS, 2>(u0, xseg, col0 ? kXTermBytes : 0, lane, c0);
+        // column g of the MMA carries activation row g (the lanes of group g supply it), columns without a row zeros
+        const bool have = (lane >> 2) < it.m;
+        const uint8_t* xseg = have ? x_s + (lane >> 2) * it.x_row + (j * 4 + (lane & 3)) * kXSegBytes : x_zero;
+        if (it.xs == 2) unit_mma_x<BITS, 2>(u0, xseg, have ? kXTermBytes : 0, lane, c0);
         else unit_mma_x<BITS, 1>(u0, xseg, 0, lane, c0);
       }
       use_stage += nb;
@@ -1244,14 +1248,19 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
       j += nb;
       __syncwarp();                                        // every lane is done with these stages before they are requested again
     }
-    // column 0 of the accumulator tile holds the sums (the paired path fills all eight alike); lanes t == 0 write rows g and g + 8
-    if ((lane & 3) == 0) {
-      const int g = lane >> 2;
+    // lane (g, t) holds rows g and g + 8 of columns 2t and 2t + 1 = activation rows 2t, 2t + 1
+    {
+      const int g = lane >> 2, b0 = 2 * (lane & 3);
       const int ra = rt * 16 + g, rb = ra + 8;
-      const float ya = (c0[0][0] + c0[1][0]) + (c1[0][0] + c1[1][0]);
-      const float yb = (c0[0][2] + c0[1][2]) + (c1[0][2] + c1[1][2]);
-      if (ra < it.n) store_y(it.y, it.y_dtype, (size_t)ra, ya);
-      if (rb < it.n) store_y(it.y, it.y_dtype, (size_t)rb, yb);
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        if (b0 + e < it.m) {
+          const float ya = (c0[0][e] + c0[1][e]) + (c1[0][e] + c1[1][e]);
+          const float yb = (c0[0][2 + e] + c0[1][2 + e]) + (c1[0][2 + e] + c1[1][2 + e]);
+          if (ra < it.n) store_y(it.y, it.y_dtype, (size_t)(b0 + e) * it.n + ra, ya);
+          if (rb < it.n) store_y(it.y, it.y_dtype, (size_t)(b0 + e) * it.n + rb, yb);
+        }
+      }
     }
   }
   cp_async_wait<0>();
@@ -1438,27 +1447,38 @@ extern "C" int nb_group_build(const nb_group_item* items, int n_items, int bits,
     if (in.n < 1 || in.k < kBlock || in.k % kBlock || in.k / kBlock > kMaxKBlocks) return fail(i, "needs N >= 1 and K a multiple of 128 up to 7168");
     if (in.x_dtype != NB_F32 && in.x_dtype != NB_F16 && in.x_dtype != NB_BF16) return fail(i, "unknown activation type");
     if (in.y_dtype != NB_F32 && in.y_dtype != NB_F16 && in.y_dtype != NB_BF16) return fail(i, "unknown output type");
+    const int m = in.m < 1 ? 1 : in.m;
+    if (m > 8) return fail(i, "at most 8 activation rows per matvec");
+    if (m > 1 && in.x_dtype == NB_F32) return fail(i, "several activation rows need 16-bit activations");
     int v = 0;
     for (; v < pl->n_x; ++v)
-      if (pl->xv[v].ptr == in.x && pl->xv[v].k == in.k && pl->xv[v].dtype == in.x_dtype) break;
+      if (pl->xv[v].ptr == in.x && pl->xv[v].k == in.k && pl->xv[v].dtype == in.x_dtype && pl->xv[v].m == m) break;
     if (v == pl->n_x) {
       if (v == kGroupMaxX) return fail(i, "too many distinct activation vectors for one launch");
       const int xs = in.x_dtype == NB_F32 ? 2 : 1;
-      // a vector's terms are kXTermBytes apart (the lookup code's fixed stride); the last term is cut to its length
-      const int need = (xs - 1) * kXTermBytes + (in.k / kBlock) * 4 * kXSegBytes;
-      if (x_bytes + need > kGroupXBytes - 128) return fail(i, "the activation vectors of the group do not fit in shared memory");
+      // a vector's terms are kXTermBytes apart (the lookup code's fixed stride); the last term is cut to its length.
+      // Rows are one 16-byte chunk more than a row's segments apart: an odd number of chunks, so that the eight
+      // lane groups of a warp (one row each) read from different banks.
+      const int row = (in.k / kBlock) * 4 * kXSegBytes + 16;
+      const int need = m > 1 ? m * row : (xs - 1) * kXTermBytes + (in.k / kBlock) * 4 * kXSegBytes;
+      if (x_bytes + need > kGroupSmem - kGroupRingSmall - 128) return fail(i, "the activations of the group do not fit in shared memory");
       pl->xv[v].ptr = in.x; pl->xv[v].k = in.k; pl->xv[v].dtype = in.x_dtype; pl->xv[v].off = x_bytes; pl->xv[v].xs = xs;
+      pl->xv[v].m = m; pl->xv[v].row = row;
       x_bytes += (need + 127) / 128 * 128;
       pl->n_x = v + 1;
     }
     GroupItem& it = pl->items[i];
     it.w = reinterpret_cast<const uint8_t*>(in.w); it.y = in.y; it.n = in.n; it.bpr = in.k / kBlock;
     it.tile0 = (int)tiles; it.x_off = pl->xv[v].off; it.xs = pl->xv[v].xs; it.y_dtype = in.y_dtype;
+    it.m = m; it.x_row = pl->xv[v].row;
     tiles += (in.n + 15) / 16;
     units += (long long)((in.n + 15) / 16) * it.bpr;
     if (tiles > (1ll << 30)) return fail(i, "too many row tiles");
   }
   pl->total_tiles = (int)tiles;
+  // the large ring when the activations leave room for it; 4-bit units are longer and always need it
+  pl->ring_bytes = x_bytes <= kGroupXBytes - 128 ? kGroupRing : kGroupRingSmall;
+  if (bits == 4 && pl->ring_bytes != kGroupRing) return fail(n_items - 1, "the activations of a 4-bit group must fit 64 KB of shared memory");
   // Deal the row tiles out: longest tiles first, to the CTA that holds the fewest units so far (ties: lowest
   // CTA).  Every CTA's list is then in descending tile length, its share within one short tile of the mean.
   {
@@ -1498,19 +1518,26 @@ extern "C" int nb_group_run(const void* plan_device, const void* plan_host, void
   const int bits = pl->bits, G = pl->ctas;
   if ((bits != 2 && bits != 3 && bits != 4) || G < 1 || G > kMaxCtas || pl->n_items < 1 || pl->n_items > kGroupMaxItems) return NB_ERR_ARG;
   if (G != nb_stream_ctas()) { set_last_error("nb_group_run: the plan was built for another device"); return NB_ERR_ARG; }
-  static bool attr_done[64][5] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   const GroupPlan* pd = reinterpret_cast<const GroupPlan*>(plan_device);
   cudaStream_t st = (cudaStream_t)stream;
-  const void* fn = bits == 3 ? (const void*)group_kernel<3, kGW, false> : bits == 2 ? (const void*)group_kernel<2, kGW, false>
-                             : (const void*)group_kernel<4, kGW, false>;
-  if (!attr_done[dev & 63][bits]) {
+  const bool big = pl->ring_bytes == kGroupRing;
+  if (!big && pl->ring_bytes != kGroupRingSmall) return NB_ERR_ARG;
+  const void* fn = bits == 3 ? (big ? (const void*)group_kernel<3, kGW, false, kGroupRing> : (const void*)group_kernel<3, kGW, false, kGroupRingSmall>)
+                 : bits == 2 ? (big ? (const void*)group_kernel<2, kGW, false, kGroupRing> : (const void*)group_kernel<2, kGW, false, kGroupRingSmall>)
+                             : (const void*)group_kernel<4, kGW, false, kGroupRing>;
+  if (bits == 4 && !big) return NB_ERR_ARG;
+  const int slot = bits * 2 + (big ? 1 : 0);
+  static bool attr_done[64][10] = {};
+  if (!attr_done[dev & 63][slot]) {
     if (cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kGroupSmem)) return record_cuda_error(e);
-    attr_done[dev & 63][bits] = true;
+    attr_done[dev & 63][slot] = true;
   }
-  if (bits == 3) group_kernel<3, kGW, false><<<G, kGW * 32, kGroupSmem, st>>>(pd);
-  else if (bits == 2) group_kernel<2, kGW, false><<<G, kGW * 32, kGroupSmem, st>>>(pd);
-  else group_kernel<4, kGW, false><<<G, kGW * 32, kGroupSmem, st>>>(pd);
+  if (bits == 3 && big) group_kernel<3, kGW, false, kGroupRing><<<G, kGW * 32, kGroupSmem, st>>>(pd);
+  else if (bits == 3) group_kernel<3, kGW, false, kGroupRingSmall><<<G, kGW * 32, kGroupSmem, st>>>(pd);
+  else if (bits == 2 && big) group_kernel<2, kGW, false, kGroupRing><<<G, kGW * 32, kGroupSmem, st>>>(pd);
+  else if (bits == 2) group_kernel<2, kGW, false, kGroupRingSmall><<<G, kGW * 32, kGroupSmem, st>>>(pd);
+  else group_kernel<4, kGW, false, kGroupRing><<<G, kGW * 32, kGroupSmem, st>>>(pd);
   return check_launch();
 }

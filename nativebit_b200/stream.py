@@ -197,15 +197,16 @@ def stream_supported(model, batch_size: int) -> bool:
 class GroupItem(ctypes.Structure):
     """Mirror of nb_group_item (include/nativebit_b200.h)."""
     _fields_ = [("w", ctypes.c_void_p), ("x", ctypes.c_void_p), ("y", ctypes.c_void_p),
-                ("n", ctypes.c_int32), ("k", ctypes.c_int32), ("x_dtype", ctypes.c_int32), ("y_dtype", ctypes.c_int32)]
+                ("n", ctypes.c_int32), ("k", ctypes.c_int32), ("x_dtype", ctypes.c_int32), ("y_dtype", ctypes.c_int32),
+                ("m", ctypes.c_int32), ("reserved", ctypes.c_int32)]
 
 
 class MatvecGroup:
     """Independent packed matvecs y_i = W_i x_i at batch 1, executed by ONE launch (nb_group_run): the row
     tiles of all matrices are dealt out to the CTAs by weight bytes and every warp computes whole 16-row tiles,
     so the weights of all matrices stream through the SMs back to back with no launch or operation boundary
-    between them.  items: (PackedLinear, x (k,) or (1, k), out (n,) or (1, n)) triples; matrices that read the
-    same x share its staged copy.  The reference runs one library launch per matrix
+    between them.  items: (PackedLinear, x (k,) or (m, k), out (n,) or (m, n)) triples with up to 8 activation rows
+    (16-bit activations for more than one); matrices that read the same x share its staged copy.  The reference runs one library launch per matrix
     (inference/triton_kernel.py:240-256)."""
 
     def __init__(self, items, device=None):
@@ -222,11 +223,14 @@ class MatvecGroup:
         for i, (lin, x, out) in enumerate(items):
             if lin.block_size != 128 or lin.bits != bits:
                 raise RuntimeError("MatvecGroup needs block size 128 and one index width for all matrices")
-            if x.numel() != lin.in_features or out.numel() != lin.out_features or not x.is_contiguous() or not out.is_contiguous():
-                raise RuntimeError("MatvecGroup runs one contiguous activation vector per matrix")
+            m = x.numel() // lin.in_features
+            if (x.numel() != m * lin.in_features or out.numel() != m * lin.out_features or m < 1 or not x.is_contiguous()
+                    or not out.is_contiguous()):
+                raise RuntimeError("MatvecGroup needs contiguous (m, k) activations and (m, n) outputs per matrix")
             w = lin.stream_weight()
             arr[i].w, arr[i].x, arr[i].y = w.data_ptr(), x.data_ptr(), out.data_ptr()
             arr[i].n, arr[i].k, arr[i].x_dtype, arr[i].y_dtype = lin.out_features, lin.in_features, _DT[x.dtype], _DT[out.dtype]
+            arr[i].m = m
             self.keep.extend((w, x, out))
         nbytes = int(l.nb_group_plan_bytes(arr, len(items)))
         self._plan_host = ctypes.create_string_buffer(nbytes)

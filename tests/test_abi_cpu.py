@@ -114,7 +114,7 @@ def test_group_plan_shares_the_weight_bytes_evenly():
     assert l.nb_group_build(arr, len(shapes), 3, buf, nbytes) == 0
     n_items, n_x, total_tiles, ctas, bits = struct.unpack_from("5i", buf.raw, 0)
     assert (n_items, n_x, bits) == (78, 2, 3) and total_tiles == 52 * 432 + 26 * 160 and ctas >= 1
-    off = 32 + 6 * 24                                     # header, then six activation-vector records
+    off = 32 + 6 * 32                                     # header, then six activation records
     cta_lo = struct.unpack_from("513i", buf.raw, off)
     assert cta_lo[0] == 0 and cta_lo[ctas] == total_tiles and all(a <= b for a, b in zip(cta_lo, cta_lo[1:]))
     off_items = (off + 513 * 4 + 7) // 8 * 8              # 256 records of 48 bytes, 8-byte aligned; the tile list follows them

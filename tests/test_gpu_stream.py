@@ -199,3 +199,52 @@ def test_matvec_group_refuses_what_it_cannot_run(built_lib):
         nbt.MatvecGroup([(lin, x, out) for x in xs])                    # seven distinct activation vectors
     with pytest.raises(RuntimeError):
         nbt.MatvecGroup([(lin, torch.zeros(128, device=dev), out)])     # wrong length
+
+
+@pytest.mark.parametrize("bits,m", [(3, 2), (3, 4), (3, 8), (2, 5), (4, 3)])
+def test_matvec_group_with_several_activation_rows(built_lib, bits, m):
+    """Up to eight activation rows per matrix ride in the eight columns of the MMA: FFN-shaped matrices against (m, k)
+    activations, against the fp64 oracle; twice, bit-identical.  The 3-bit case at 4 rows needs the shorter copy rings."""
+    import nativebit_b200 as nbt
+    dev = _dev()
+    H, F = 2560, 6912
+    # the staged activations must fit the kernel's shared memory: 6912-wide rows only up to four of them
+    shapes = [(1000, H), (320, 1280)] if bits == 4 else [(F, H), (1000, H)] + ([(H, F)] if m <= 4 else [(640, 1280)])
+    xs = {}
+    items, refs = [], []
+    for j, (n, k) in enumerate(shapes):
+        packed, cb, _ = o.make_packed_linear(n, k, bits, seed=40 + j)
+        if k not in xs:
+            x = o.make_activation(m, k, seed=100 + k)
+            xs[k] = (x, _cu(x, dev).to(torch.bfloat16 if j % 2 == 0 else torch.float16))
+        x, xt = xs[k]
+        lin = nbt.PackedLinear(_cu(packed, dev), _cu(cb, dev), n, k, bits=bits)
+        out = torch.full((m, n), float("nan"), dtype=torch.float32 if j != 1 else torch.bfloat16, device=dev)
+        items.append((lin, xt, out))
+        refs.append(o.packed_linear_forward(xt.double().cpu().numpy(), packed, cb.astype(np.float32), n, k, bits, acc_dtype=np.float64))
+    grp = nbt.MatvecGroup(items)
+    grp.run()
+    torch.cuda.synchronize()
+    first = [out.clone() for _, _, out in items]
+    for (_, _, out), ref in zip(items, refs):
+        tol = 2e-5 if out.dtype == torch.float32 else 2.0 ** -8
+        assert np.abs(out.double().cpu().numpy() - ref).max() <= tol * np.abs(ref).max()
+    for _, _, out in items:
+        out.fill_(float("nan"))
+    grp.run()
+    torch.cuda.synchronize()
+    for (_, _, out), f in zip(items, first):
+        assert torch.equal(out, f)
+
+
+def test_matvec_group_refuses_rows_it_cannot_stage(built_lib):
+    import nativebit_b200 as nbt
+    dev = _dev()
+    packed, cb, _ = o.make_packed_linear(64, 6912, 3, seed=1)
+    lin = nbt.PackedLinear(_cu(packed, dev), _cu(cb, dev), 64, 6912)
+    with pytest.raises(RuntimeError):                                   # 8 rows of 6912 activations: 138 KB of shared memory
+        nbt.MatvecGroup([(lin, torch.zeros(8, 6912, dtype=torch.bfloat16, device=dev), torch.zeros(8, 64, device=dev))])
+    with pytest.raises(RuntimeError):                                   # several rows need 16-bit activations
+        nbt.MatvecGroup([(lin, torch.zeros(2, 6912, dtype=torch.float32, device=dev), torch.zeros(2, 64, device=dev))])
+    with pytest.raises(RuntimeError):                                   # nine rows
+        nbt.MatvecGroup([(lin, torch.zeros(9, 6912, dtype=torch.bfloat16, device=dev), torch.zeros(9, 64, device=dev))])
