@@ -365,6 +365,19 @@ int nb_group_max_items(void);
 int nb_group_build(const nb_group_item* items, int n_items, int bits, void* plan_out, size_t plan_bytes);
 int nb_group_run(const void* plan_device, const void* plan_host, void* stream);
 
+/* ---- one packed matvec of a chain of dependent launches (the decode step at one sequence), over the
+ * nb_stream_pack copy of the weights: y (N fp32) = W . act(x).  Same contract as nb_gemv_fused at M = 1
+ * (inference/triton_kernel.py:240-256 with the element-wise step of inference/generate_torch.py:109-117 in front):
+ * prologue NB_PRO_NONE: act = x (K values of x_dtype; NB_F32 carried as two fp16 terms);
+ * NB_PRO_ADD_RMSNORM: x fp32 residual, delta (K, may be NULL) added first, act = rmsnorm(x + delta) * norm_weight,
+ * x + delta written to x_out (may be NULL; must not alias x); NB_PRO_SILU_MUL: x = [gate | up] (2K fp32),
+ * act = silu(gate) * up.  One CTA per SM; the k-blocks of a 16-row tile are shared by a team of warps of one CTA, so
+ * there is no workspace and nothing to wait for but the launch's own copies; weights are requested before the
+ * launch waits for the one before it (programmatic dependent launch).  K % 128 == 0, K <= 7168; 16-byte aligned
+ * pointers.  Bit-identical from run to run. */
+int nb_gemv_stream(int prologue, const void* x, int x_dtype, const float* delta, const float* norm_weight, float eps,
+                   float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, void* stream);
+
 /* Launch geometry nb_gemv will use for a shape on the current device (no launch; works without
  * a GPU, assuming 148 SMs): out6 = {grid.x, grid.y (k partitions), threads per CTA, dynamic
  * shared memory bytes, row tiles per CTA, k-groups per partition}.  No counterpart in the

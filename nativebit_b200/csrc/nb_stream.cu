@@ -1266,6 +1266,178 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
   cp_async_wait<0>();
 }
 
+
+// ====================================================================================================
+// One matrix, one activation row, inside a chain of dependent launches (the decode step)
+// ====================================================================================================
+// y (N) = W x for ONE packed matrix in the stream layout, with the element-wise step in front of the packed
+// linear computed while x is staged (inference/generate_torch.py:109-117): residual add + RMSNorm, or SwiGLU.
+// The reference launches its fused matvec once per linear (inference/triton_kernel.py:240-256); so does this,
+// but built like the group kernel above: one CTA per SM, 24 warps, every warp streams its own units through its
+// own ring of asynchronous copies.  A matrix has far fewer 16-row tiles than the GPU has warps, so the k range of a
+// tile is shared by a team of warps of ONE CTA (24, 12, 6 or 3 warps, as many as the row has k-blocks), whose
+// partial sums meet in shared memory: no workspace, no tickets, nothing shared between CTAs.  The weights do not
+// depend on the launch before: every warp requests its first units, then executes griddepcontrol.wait, then x is
+// staged, so the dependent part of the launch is staging + a few units per warp + one block-wide sum per round.
+constexpr int kTileRing = 160 * 1024;
+constexpr int kTileSmem = kTileRing + 2 * kXTermBytes + 2 * kGW * 16 * 4 + 64;
+
+struct TileGemvParams {
+  const uint8_t* w;          // stream-layout weights
+  const void* x;             // activations: K values (prologue 0, 1) or 2K values [gate | up] (prologue 2)
+  const float* delta;        // prologue 1: added to x before the norm (may be null)
+  const float* weight;       // prologue 1: RMSNorm weight
+  float* x_out;              // prologue 1: receives x + delta (may be null; must not alias x)
+  float* y;                  // N outputs, fp32
+  int N, bpr, x_dtype, prologue;
+  float eps;
+};
+
+template <int BITS, int XS>
+__global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvParams p) {
+  using F = UnitFmt<BITS>;
+  constexpr int D = kTileRing / (kGW * F::kBytes) < 8 ? kTileRing / (kGW * F::kBytes) : 8;
+  constexpr int kThreads = kGW * 32;
+  static_assert(D >= 4, "the per-warp ring needs at least four stages");
+  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ float s16[32];
+  __shared__ float s_scale;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* ring = smem + warp * (D * F::kBytes);
+  uint8_t* x_s = smem + kTileRing;
+  float* s_part = reinterpret_cast<float*>(smem + kTileRing + 2 * kXTermBytes);      // [2][kGW][16]
+  const int bpr = p.bpr, K = bpr * kBlock;
+  // the warps of a CTA form teams of wpt warps; a team shares the k-blocks of one row tile
+  const int wpt = bpr >= 24 ? 24 : (bpr >= 12 ? 12 : (bpr >= 6 ? 6 : 3));
+  const int tpr = kGW / wpt;                              // row tiles per CTA per round
+  const int team = warp / wpt, wi = warp - team * wpt;
+  const int u_lo = bpr * wi / wpt, u_hi = bpr * (wi + 1) / wpt;        // this warp's units of its team's tile
+  const int n_tiles = (p.N + 15) >> 4;
+  const int per_round = (int)gridDim.x * tpr;
+  const int rounds = (n_tiles + per_round - 1) / per_round;
+  auto tile_of = [&](int r) { return (r * (int)gridDim.x + (int)blockIdx.x) * tpr + team; };
+
+  // ---- copies: requests run D - 2 units ahead of the arithmetic; the first ones go out before the launch this one
+  // depends on has finished
+  int rq_round = 0, rq_u = u_lo, rq_stage = 0, use_stage = 0;
+  auto request_one = [&]() {
+    while (rq_round < rounds && (rq_u >= u_hi || tile_of(rq_round) >= n_tiles)) { ++rq_round; rq_u = u_lo; }
+    if (rq_round < rounds) {
+      const uint8_t* src = p.w + ((size_t)tile_of(rq_round) * bpr + rq_u) * F::kBytes;
+      uint8_t* dst = ring + rq_stage * F::kBytes;
+      constexpr int kChunks = F::kBytes / 16;
+#pragma unroll
+      for (int i = 0; i < (kChunks + 31) / 32; ++i)
+        if (i * 32 + 32 <= kChunks || lane + i * 32 < kChunks) cp_async16(dst + 16 * (lane + i * 32), src + 16 * (lane + i * 32));
+      ++rq_u;
+    }
+    if (++rq_stage == D) rq_stage = 0;
+    cp_async_commit();
+  };
+#pragma unroll 1
+  for (int i = 0; i < D - 2; ++i) request_one();
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- the activations (and the element-wise step in front of this linear)
+  if (p.prologue == 1) {
+    const float4* xr = reinterpret_cast<const float4*>(p.x);
+    const float4* dr = reinterpret_cast<const float4*>(p.delta);
+    const float4* w4 = reinterpret_cast<const float4*>(p.weight);
+    const bool writer = blockIdx.x == 0 && p.x_out != nullptr;
+    float ss = 0.f;
+    for (int i4 = tid; i4 < K / 4; i4 += kThreads) {
+      float4 v = __ldcg(xr + i4);
+      if (dr) { const float4 d = __ldcg(dr + i4); v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+      if (writer) reinterpret_cast<float4*>(p.x_out)[i4] = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      const float4 w = __ldg(w4 + i4);
+      stage4<2>(x_s, i4, v.x * w.x, v.y * w.y, v.z * w.z, v.w * w.w);
+    }
+    ss = warp_sum_f(ss);                                   // the warps' sums, then in warp order: the same bits in every CTA
+    if (lane == 0) s16[warp] = ss;
+    __syncthreads();
+    if (tid == 0) {
+      float tot = 0.f;
+      for (int i = 0; i < kGW; ++i) tot += s16[i];
+      s_scale = 1.0f / sqrtf(tot / (float)K + p.eps);
+    }
+  } else if (p.prologue == 2) {
+    const float4* g4 = reinterpret_cast<const float4*>(p.x);
+    const float4* u4 = g4 + K / 4;
+    for (int i4 = tid; i4 < K / 4; i4 += kThreads) {
+      const float4 g = __ldcg(g4 + i4), u = __ldcg(u4 + i4);
+      stage4<2>(x_s, i4, g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y, g.z / (1.f + __expf(-g.z)) * u.z,
+                g.w / (1.f + __expf(-g.w)) * u.w);
+    }
+    if (tid == 0) s_scale = 1.f;
+  } else {
+    for (int i4 = tid; i4 < K / 4; i4 += kThreads) {
+      float v[4];
+      if (p.x_dtype == NB_F32) {
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(p.x) + i4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+      } else {
+        const uint2 q = __ldcg(reinterpret_cast<const uint2*>(p.x) + i4);
+        if (p.x_dtype == NB_BF16) {
+          v[0] = __uint_as_float(q.x << 16); v[1] = __uint_as_float(q.x & 0xFFFF0000u);
+          v[2] = __uint_as_float(q.y << 16); v[3] = __uint_as_float(q.y & 0xFFFF0000u);
+        } else {
+          const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&q.x));
+          const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&q.y));
+          v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
+        }
+      }
+      stage4<XS>(x_s, i4, v[0], v[1], v[2], v[3]);
+    }
+    if (tid == 0) s_scale = 1.f;
+  }
+  // zeros for the MMA columns that carry no activation row (seven of the eight)
+  uint8_t* x_zero = reinterpret_cast<uint8_t*>(s_part + 2 * kGW * 16);
+  if (tid < 16) reinterpret_cast<uint32_t*>(x_zero)[tid] = 0u;
+  __syncthreads();
+  const float scale = s_scale;
+
+  // ---- rounds: every team one row tile; a warp adds its units, the team's sums meet in shared memory
+  const bool col0 = lane < 4;
+#pragma unroll 1
+  for (int r = 0; r < rounds; ++r) {
+    const int tile = tile_of(r);
+    float c[2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) c[h][e] = 0.f;
+    if (tile < n_tiles) {
+#pragma unroll 1
+      for (int u = u_lo; u < u_hi; ++u) {
+        request_one();
+        cp_async_wait<D - 2>();
+        __syncwarp();
+        const uint8_t* xseg = col0 ? x_s + (u * 4 + (lane & 3)) * kXSegBytes : x_zero;
+        unit_mma_x<BITS, XS>(ring + use_stage * F::kBytes, xseg, col0 ? kXTermBytes : 0, lane, c);
+        if (++use_stage == D) use_stage = 0;
+        __syncwarp();
+      }
+    }
+    float* part = s_part + (r & 1) * (kGW * 16);
+    if ((lane & 3) == 0) {
+      part[warp * 16 + (lane >> 2)] = c[0][0] + c[1][0];
+      part[warp * 16 + 8 + (lane >> 2)] = c[0][2] + c[1][2];
+    }
+    __syncthreads();                                       // one barrier per round: the buffers alternate
+    if (tid < tpr * 16) {
+      const int tm = tid >> 4, row = tid & 15;
+      const int t_out = (r * (int)gridDim.x + (int)blockIdx.x) * tpr + tm;
+      float acc = 0.f;
+      for (int j = 0; j < wpt; ++j) acc += part[(tm * wpt + j) * 16 + row];     // the team's warps in k order
+      const int n = t_out * 16 + row;
+      if (t_out < n_tiles && n < p.N) p.y[n] = acc * scale;
+    }
+  }
+  cp_async_wait<0>();
+}
+
 }  // namespace nb
 
 using namespace nb;
@@ -1540,4 +1712,48 @@ extern "C" int nb_group_run(const void* plan_device, const void* plan_host, void
   else if (bits == 2) group_kernel<2, kGW, false, kGroupRingSmall><<<G, kGW * 32, kGroupSmem, st>>>(pd);
   else group_kernel<4, kGW, false, kGroupRing><<<G, kGW * 32, kGroupSmem, st>>>(pd);
   return check_launch();
+}
+
+// ---- one matrix in a chain of dependent launches --------------------------------------------------
+extern "C" int nb_gemv_stream(int prologue, const void* x, int x_dtype, const float* delta, const float* norm_weight, float eps,
+                              float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, void* stream) {
+  if (!x || !w_stream || !y || N < 1) return NB_ERR_ARG;
+  if (prologue < 0 || prologue > 2) return NB_ERR_ARG;
+  if (bits != 2 && bits != 3 && bits != 4) return NB_ERR_SHAPE;
+  if (K < kBlock || K % kBlock != 0 || K / kBlock > kMaxKBlocks) return NB_ERR_SHAPE;
+  if (prologue == 1 && !norm_weight) return NB_ERR_ARG;
+  if (prologue != 0 && x_dtype != NB_F32) return NB_ERR_ARG;
+  if (x_dtype != NB_F32 && x_dtype != NB_F16 && x_dtype != NB_BF16) return NB_ERR_ARG;
+  if ((uintptr_t)w_stream % 16 || (uintptr_t)x % 16 || (uintptr_t)delta % 16 || (uintptr_t)norm_weight % 16 || (uintptr_t)x_out % 16)
+    return NB_ERR_ALIGN;
+  if (x_out && x_out == x) return NB_ERR_ARG;
+  if (int rc = check_device()) return rc;
+  TileGemvParams p{};
+  p.w = w_stream; p.x = x; p.delta = delta; p.weight = norm_weight; p.x_out = x_out; p.y = y;
+  p.N = N; p.bpr = K / kBlock; p.x_dtype = x_dtype; p.prologue = prologue; p.eps = eps;
+  const int xs = x_dtype == NB_F32 ? 2 : 1;
+  const void* fn = nullptr;
+  if (bits == 3) fn = xs == 2 ? (const void*)tile_gemv_kernel<3, 2> : (const void*)tile_gemv_kernel<3, 1>;
+  else if (bits == 2) fn = xs == 2 ? (const void*)tile_gemv_kernel<2, 2> : (const void*)tile_gemv_kernel<2, 1>;
+  else fn = xs == 2 ? (const void*)tile_gemv_kernel<4, 2> : (const void*)tile_gemv_kernel<4, 1>;
+  static bool attr_done[64][12] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int slot = bits * 2 + xs - 1;
+  if (!attr_done[dev & 63][slot]) {
+    if (cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmem)) return record_cuda_error(e);
+    attr_done[dev & 63][slot] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nb_stream_ctas());
+  cfg.blockDim = dim3(kGW * 32);
+  cfg.dynamicSmemBytes = kTileSmem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  void* args[] = {&p};
+  return record_cuda_error(cudaLaunchKernelExC(&cfg, fn, args));
 }

@@ -296,9 +296,15 @@ class DecodeSession:
     (inference/generate_torch.py:91-97)."""
 
     def __init__(self, model: PackedGPT, batch_size: int = 1, use_graph: bool = True, fused: bool = True,
-                 batch_gemm: bool = False, stream: bool | None = None):
+                 batch_gemm: bool = False, stream: bool | None = None, tile_gemv: bool | None = None):
         self.model, self.B = model, batch_size
         self.fused = fused
+        # one sequence: the packed linears of the step run on the kernel that reads the tile-major copy of the weights
+        # (nb_gemv_stream: teams of warps per row tile, no workspace); tile_gemv=False keeps nb_gemv_fused
+        blk0 = model.blocks[0] if len(model.blocks) else None
+        fits = (blk0 is not None and model.config.block_size == 128 and model.config.bits in (2, 3, 4)
+                and all(l.in_features % 128 == 0 and l.in_features <= 7168 for l in (blk0.qkv, blk0.out_proj, blk0.gate_up, blk0.down)))
+        self.tile_gemv = bool(fits and batch_size == 1 and fused) if tile_gemv is None else bool(tile_gemv and fits and batch_size == 1)
         # stream=True (one sequence on one GPU): the whole step is ONE launch of the persistent kernel
         # (stream.py).  The default is the chain of fused kernels, which measures faster: inside one launch
         # every operation pays a device-wide flag wait and the staging of its activations in full.
@@ -370,6 +376,10 @@ class DecodeSession:
                 ops.gemv_tp(ops.PRO_ADD_RMSNORM, xa, *args, xch, out=out, gather=True, norm_weight=w, eps=eps, x_out=xb)
                 xa, xb = xb, xa
                 pending = False
+            elif self.tile_gemv:
+                ops.gemv_stream(ops.PRO_ADD_RMSNORM, xa, lin.stream_weight(), lin.bits, lin.out_features, lin.in_features, out,
+                                delta=delta, norm_weight=w, eps=eps, x_out=xb)
+                xa, xb = xb, xa
             elif fold:
                 ops.gemv_fused(ops.PRO_ADD_RMSNORM, xa, *args, out, delta=delta, norm_weight=w, eps=eps, x_out=xb)
                 xa, xb = xb, xa
@@ -385,7 +395,9 @@ class DecodeSession:
                 ops.gemv_tp(prologue, x, *args, xch, push=True)
                 pending = True
                 return None
-            if prologue == ops.PRO_SILU_MUL and fold:
+            if self.tile_gemv:
+                ops.gemv_stream(prologue, x, lin.stream_weight(), lin.bits, lin.out_features, lin.in_features, out)
+            elif prologue == ops.PRO_SILU_MUL and fold:
                 ops.gemv_fused(prologue, x, *args, out)
             elif prologue == ops.PRO_SILU_MUL:
                 ops.silu_mul(x, self.bhm)

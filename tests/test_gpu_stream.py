@@ -248,3 +248,77 @@ def test_matvec_group_refuses_rows_it_cannot_stage(built_lib):
         nbt.MatvecGroup([(lin, torch.zeros(2, 6912, dtype=torch.float32, device=dev), torch.zeros(2, 64, device=dev))])
     with pytest.raises(RuntimeError):                                   # nine rows
         nbt.MatvecGroup([(lin, torch.zeros(9, 6912, dtype=torch.bfloat16, device=dev), torch.zeros(9, 64, device=dev))])
+
+
+@pytest.mark.parametrize("bits,n,k", [(3, 7680, 2560), (3, 2560, 6912), (3, 1000, 640), (3, 24, 128), (2, 2560, 2560), (4, 512, 1280),
+                                      (3, 13824, 2560), (3, 320, 384), (3, 40, 7168)])
+def test_chain_gemv_over_the_stream_layout(built_lib, bits, n, k):
+    """nb_gemv_stream, the decode step's matvec: plain activations of every type, residual add + RMSNorm in front
+    (with the updated residual written out), SwiGLU in front; against the fp64 oracle, and twice bit-identical."""
+    from nativebit_b200 import ops, stream as S
+    dev = _dev()
+    packed, cb, _ = o.make_packed_linear(n, k, bits, seed=n % 97 + bits)
+    w = S.stream_pack(_cu(packed, dev), _cu(cb, dev), bits, n, k)
+    cbf = cb.astype(np.float32)
+    rng = np.random.default_rng(n + k)
+
+    def check(y, act):
+        ref = o.packed_linear_forward(act.reshape(1, k), packed, cbf, n, k, bits, acc_dtype=np.float64)[0]
+        assert np.abs(y.double().cpu().numpy() - ref).max() <= 2e-5 * np.abs(ref).max()
+
+    for xdt in (torch.float32, torch.bfloat16, torch.float16):
+        x = o.make_activation(1, k, seed=3)[0]
+        if xdt == torch.float32:
+            x = (x.astype(np.float64) * (1.0 + 1e-4 * np.arange(k))).astype(np.float32)
+        xt = _cu(x, dev).to(xdt)
+        y = torch.full((n,), float("nan"), device=dev)
+        ops.gemv_stream(ops.PRO_NONE, xt, w, bits, n, k, y)
+        y2 = torch.full((n,), float("nan"), device=dev)
+        ops.gemv_stream(ops.PRO_NONE, xt, w, bits, n, k, y2)
+        torch.cuda.synchronize()
+        check(y, xt.double().cpu().numpy())
+        assert torch.equal(y, y2)
+    # residual add + RMSNorm
+    h = rng.standard_normal(k).astype(np.float32)
+    d = rng.standard_normal(k).astype(np.float32)
+    g = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    for delta in (d, None):
+        v = h.astype(np.float64) + (0 if delta is None else delta.astype(np.float64))
+        act = v / np.sqrt((v * v).mean() + 1e-6) * g
+        y = torch.full((n,), float("nan"), device=dev)
+        x_out = torch.full((k,), float("nan"), device=dev)
+        ops.gemv_stream(ops.PRO_ADD_RMSNORM, _cu(h, dev), w, bits, n, k, y, delta=None if delta is None else _cu(delta, dev),
+                        norm_weight=_cu(g, dev), eps=1e-6, x_out=x_out)
+        torch.cuda.synchronize()
+        check(y, act)
+        assert np.array_equal(x_out.cpu().numpy(), (h + delta).astype(np.float32) if delta is not None else h)
+    # SwiGLU
+    gu = rng.standard_normal(2 * k).astype(np.float32)
+    gate, up = gu[:k].astype(np.float64), gu[k:].astype(np.float64)
+    y = torch.full((n,), float("nan"), device=dev)
+    ops.gemv_stream(ops.PRO_SILU_MUL, _cu(gu, dev), w, bits, n, k, y)
+    torch.cuda.synchronize()
+    ref = o.packed_linear_forward((gate / (1 + np.exp(-gate)) * up).reshape(1, k), packed, cbf, n, k, bits, acc_dtype=np.float64)[0]
+    assert np.abs(y.double().cpu().numpy() - ref).max() <= 5e-5 * np.abs(ref).max()     # __expf in the activation
+
+
+def test_decode_step_on_the_stream_layout_equals_the_workspace_kernels(built_lib):
+    """The decode session with its packed linears on nb_gemv_stream against the same session on nb_gemv_fused:
+    identical greedy tokens, logits within fp32 summation-order differences."""
+    from nativebit_b200 import generate as G
+    dev = _dev()
+    cfg = G.ModelConfig(vocab_size=512, n_layers=3, n_embd=512, n_head=4, ffn_hidden=1408, context_len=64)
+    model = G.PackedGPT.random_init(cfg, seed=5, device=dev)
+    prompt = torch.randint(0, cfg.vocab_size, (1, 7), generator=torch.Generator().manual_seed(1)).to(dev)
+    a = G.DecodeSession(model, 1, use_graph=False, tile_gemv=True)
+    b = G.DecodeSession(model, 1, use_graph=False, tile_gemv=False)
+    assert a.tile_gemv and not b.tile_gemv
+    a.prefill(prompt); b.prefill(prompt)
+    for _ in range(12):
+        a.step(); b.step()
+        assert torch.equal(a.token, b.token)
+        assert (a.logits - b.logits).abs().max() <= 1e-4 * b.logits.abs().max()
+    g = G.DecodeSession(model, 1, use_graph=True, tile_gemv=True)
+    toks_g = g.generate(prompt, 12)
+    toks_e = G.DecodeSession(model, 1, use_graph=False, tile_gemv=True).generate(prompt, 12)
+    assert torch.equal(toks_g, toks_e)
