@@ -374,9 +374,11 @@ int nb_group_run(const void* plan_device, const void* plan_host, void* stream);
  * act = silu(gate) * up.  One CTA per SM; the k-blocks of a 16-row tile are shared by a team of warps of one CTA, so
  * there is no workspace and nothing to wait for but the launch's own copies; weights are requested before the
  * launch waits for the one before it (programmatic dependent launch).  K % 128 == 0, K <= 7168; 16-byte aligned
- * pointers.  Bit-identical from run to run. */
+ * pointers.  swiglu != 0: W is a fused [gate | up] matrix packed with nb_stream_pack row_mode 1 (N % 16 == 0) and y
+ * receives the N / 2 values silu(gate_c) * up_c (the SwiGLU of generate_torch.py:116-117 in the epilogue).
+ * Bit-identical from run to run. */
 int nb_gemv_stream(int prologue, const void* x, int x_dtype, const float* delta, const float* norm_weight, float eps,
-                   float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, void* stream);
+                   float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, int swiglu, void* stream);
 
 /* Launch geometry nb_gemv will use for a shape on the current device (no launch; works without
  * a GPU, assuming 148 SMs): out6 = {grid.x, grid.y (k partitions), threads per CTA, dynamic

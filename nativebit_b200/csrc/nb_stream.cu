@@ -1291,6 +1291,9 @@ struct TileGemvParams {
   float* y;                  // N outputs, fp32
   int N, bpr, x_dtype, prologue;
   float eps;
+  int wpt;                   // warps per team (24, 12, 6 or 3): chosen on the host
+  int swiglu;                // epilogue: rows 0..7 of a tile are gate channels, rows 8..15 the matching up channels
+                             // (nb_stream_pack row_mode 1); y receives N / 2 values silu(gate) * up
 };
 
 template <int BITS, int XS>
@@ -1307,15 +1310,17 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
   uint8_t* x_s = smem + kTileRing;
   float* s_part = reinterpret_cast<float*>(smem + kTileRing + 2 * kXTermBytes);      // [2][kGW][16]
   const int bpr = p.bpr, K = bpr * kBlock;
-  // the warps of a CTA form teams of wpt warps; a team shares the k-blocks of one row tile
-  const int wpt = bpr >= 24 ? 24 : (bpr >= 12 ? 12 : (bpr >= 6 ? 6 : 3));
+  // the warps of a CTA form teams of wpt warps; a team shares the k-blocks of one row tile.  Tiles go round the CTAs
+  // first and the teams second, so that a last, partly filled round still has work on every SM.
+  const int wpt = p.wpt;
   const int tpr = kGW / wpt;                              // row tiles per CTA per round
   const int team = warp / wpt, wi = warp - team * wpt;
   const int u_lo = bpr * wi / wpt, u_hi = bpr * (wi + 1) / wpt;        // this warp's units of its team's tile
   const int n_tiles = (p.N + 15) >> 4;
   const int per_round = (int)gridDim.x * tpr;
   const int rounds = (n_tiles + per_round - 1) / per_round;
-  auto tile_of = [&](int r) { return (r * (int)gridDim.x + (int)blockIdx.x) * tpr + team; };
+  auto tile_at = [&](int r, int tm) { return r * per_round + tm * (int)gridDim.x + (int)blockIdx.x; };
+  auto tile_of = [&](int r) { return tile_at(r, team); };
 
   // ---- copies: requests run D - 2 units ahead of the arithmetic; the first ones go out before the launch this one
   // depends on has finished
@@ -1346,13 +1351,28 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
     const float4* w4 = reinterpret_cast<const float4*>(p.weight);
     const bool writer = blockIdx.x == 0 && p.x_out != nullptr;
     float ss = 0.f;
-    for (int i4 = tid; i4 < K / 4; i4 += kThreads) {
-      float4 v = __ldcg(xr + i4);
-      if (dr) { const float4 d = __ldcg(dr + i4); v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
-      if (writer) reinterpret_cast<float4*>(p.x_out)[i4] = v;
-      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-      const float4 w = __ldg(w4 + i4);
-      stage4<2>(x_s, i4, v.x * w.x, v.y * w.y, v.z * w.z, v.w * w.w);
+    // K <= 7168: at most three float4 per thread; all loads are issued before the first use (one memory round trip)
+    constexpr int kIt = (kMaxKBlocks * kBlock / 4 + kThreads - 1) / kThreads;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 vx[kIt], vd[kIt], vw[kIt];
+#pragma unroll
+    for (int j = 0; j < kIt; ++j) {
+      const int i4 = tid + j * kThreads;
+      const bool in = i4 < K / 4;
+      vx[j] = in ? __ldcg(xr + i4) : zero4;
+      vd[j] = (in && dr) ? __ldcg(dr + i4) : zero4;
+      vw[j] = in ? __ldg(w4 + i4) : zero4;
+    }
+#pragma unroll
+    for (int j = 0; j < kIt; ++j) {
+      const int i4 = tid + j * kThreads;
+      if (i4 < K / 4) {
+        float4 v = vx[j];
+        v.x += vd[j].x; v.y += vd[j].y; v.z += vd[j].z; v.w += vd[j].w;
+        if (writer) reinterpret_cast<float4*>(p.x_out)[i4] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        stage4<2>(x_s, i4, v.x * vw[j].x, v.y * vw[j].y, v.z * vw[j].z, v.w * vw[j].w);
+      }
     }
     ss = warp_sum_f(ss);                                   // the warps' sums, then in warp order: the same bits in every CTA
     if (lane == 0) s16[warp] = ss;
@@ -1365,13 +1385,26 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
   } else if (p.prologue == 2) {
     const float4* g4 = reinterpret_cast<const float4*>(p.x);
     const float4* u4 = g4 + K / 4;
-    for (int i4 = tid; i4 < K / 4; i4 += kThreads) {
-      const float4 g = __ldcg(g4 + i4), u = __ldcg(u4 + i4);
-      stage4<2>(x_s, i4, g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y, g.z / (1.f + __expf(-g.z)) * u.z,
-                g.w / (1.f + __expf(-g.w)) * u.w);
+    constexpr int kIt = (kMaxKBlocks * kBlock / 4 + kThreads - 1) / kThreads;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 vg[kIt], vu[kIt];
+#pragma unroll
+    for (int j = 0; j < kIt; ++j) {      // all loads first: one memory round trip
+      const int i4 = tid + j * kThreads;
+      vg[j] = i4 < K / 4 ? __ldcg(g4 + i4) : zero4;
+      vu[j] = i4 < K / 4 ? __ldcg(u4 + i4) : zero4;
+    }
+#pragma unroll
+    for (int j = 0; j < kIt; ++j) {
+      const int i4 = tid + j * kThreads;
+      const float4 g = vg[j], u = vu[j];
+      if (i4 < K / 4)
+        stage4<2>(x_s, i4, g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y, g.z / (1.f + __expf(-g.z)) * u.z,
+                  g.w / (1.f + __expf(-g.w)) * u.w);
     }
     if (tid == 0) s_scale = 1.f;
   } else {
+#pragma unroll 3
     for (int i4 = tid; i4 < K / 4; i4 += kThreads) {
       float v[4];
       if (p.x_dtype == NB_F32) {
@@ -1426,9 +1459,22 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
       part[warp * 16 + 8 + (lane >> 2)] = c[0][2] + c[1][2];
     }
     __syncthreads();                                       // one barrier per round: the buffers alternate
-    if (tid < tpr * 16) {
+    if (p.swiglu) {
+      if (tid < tpr * 8) {
+        const int tm = tid >> 3, ch = tid & 7;
+        const int t_out = tile_at(r, tm);
+        float gate = 0.f, up = 0.f;
+        for (int j = 0; j < wpt; ++j) {                                          // the team's warps in k order
+          gate += part[(tm * wpt + j) * 16 + ch];
+          up += part[(tm * wpt + j) * 16 + 8 + ch];
+        }
+        gate *= scale; up *= scale;
+        const int c_out = t_out * 8 + ch;
+        if (t_out < n_tiles && c_out < (p.N >> 1)) p.y[c_out] = gate / (1.f + __expf(-gate)) * up;
+      }
+    } else if (tid < tpr * 16) {
       const int tm = tid >> 4, row = tid & 15;
-      const int t_out = (r * (int)gridDim.x + (int)blockIdx.x) * tpr + tm;
+      const int t_out = tile_at(r, tm);
       float acc = 0.f;
       for (int j = 0; j < wpt; ++j) acc += part[(tm * wpt + j) * 16 + row];     // the team's warps in k order
       const int n = t_out * 16 + row;
@@ -1716,9 +1762,10 @@ extern "C" int nb_group_run(const void* plan_device, const void* plan_host, void
 
 // ---- one matrix in a chain of dependent launches --------------------------------------------------
 extern "C" int nb_gemv_stream(int prologue, const void* x, int x_dtype, const float* delta, const float* norm_weight, float eps,
-                              float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, void* stream) {
+                              float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, int swiglu, void* stream) {
   if (!x || !w_stream || !y || N < 1) return NB_ERR_ARG;
   if (prologue < 0 || prologue > 2) return NB_ERR_ARG;
+  if (swiglu && N % 16 != 0) return NB_ERR_SHAPE;
   if (bits != 2 && bits != 3 && bits != 4) return NB_ERR_SHAPE;
   if (K < kBlock || K % kBlock != 0 || K / kBlock > kMaxKBlocks) return NB_ERR_SHAPE;
   if (prologue == 1 && !norm_weight) return NB_ERR_ARG;
@@ -1730,7 +1777,17 @@ extern "C" int nb_gemv_stream(int prologue, const void* x, int x_dtype, const fl
   if (int rc = check_device()) return rc;
   TileGemvParams p{};
   p.w = w_stream; p.x = x; p.delta = delta; p.weight = norm_weight; p.x_out = x_out; p.y = y;
-  p.N = N; p.bpr = K / kBlock; p.x_dtype = x_dtype; p.prologue = prologue; p.eps = eps;
+  p.N = N; p.bpr = K / kBlock; p.x_dtype = x_dtype; p.prologue = prologue; p.eps = eps; p.swiglu = swiglu ? 1 : 0;
+  {  // team size: rounds x (units per warp + the round's barrier and sum, about two thirds of a unit)
+    const int G = nb_stream_ctas(), n_tiles = (N + 15) / 16;
+    double best = 1e30;
+    for (int wpt : {24, 12, 6, 3}) {
+      const int per_round = G * (kGW / wpt);
+      const int rounds = (n_tiles + per_round - 1) / per_round;
+      const double cost = rounds * ((p.bpr + wpt - 1) / wpt + 0.67);
+      if (cost < best) { best = cost; p.wpt = wpt; }
+    }
+  }
   const int xs = x_dtype == NB_F32 ? 2 : 1;
   const void* fn = nullptr;
   if (bits == 3) fn = xs == 2 ? (const void*)tile_gemv_kernel<3, 2> : (const void*)tile_gemv_kernel<3, 1>;

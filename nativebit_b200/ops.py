@@ -200,20 +200,22 @@ def gemv_fused(prologue: int, x: torch.Tensor, packed: torch.Tensor, codebook: t
 
 def gemv_stream(prologue: int, x: torch.Tensor, w_stream: torch.Tensor, bits: int, n: int, k: int, out: torch.Tensor,
                 delta: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None, eps: float = 0.0,
-                x_out: torch.Tensor | None = None) -> torch.Tensor:
+                x_out: torch.Tensor | None = None, swiglu: bool = False) -> torch.Tensor:
     """One packed matvec of a dependent chain over the stream-layout copy of the weights (nb_gemv_stream): out (n) fp32
-    = W . act(x), act as in gemv_fused (PRO_NONE: x of any float type; PRO_ADD_RMSNORM / PRO_SILU_MUL: fp32)."""
+    = W . act(x), act as in gemv_fused (PRO_NONE: x of any float type; PRO_ADD_RMSNORM / PRO_SILU_MUL: fp32).
+    swiglu: W is a [gate | up] matrix packed with row_mode 1 and out receives the n / 2 values silu(gate) * up."""
     _need_cuda(x, w_stream, out)
     cols = 2 * k if prologue == PRO_SILU_MUL else k
-    if x.numel() != cols or not x.is_contiguous() or out.dtype != torch.float32 or out.numel() != n or not out.is_contiguous():
-        raise RuntimeError(f"gemv_stream needs one contiguous activation row of {cols} values and an fp32 output of {n}")
+    n_out = n // 2 if swiglu else n
+    if x.numel() != cols or not x.is_contiguous() or out.dtype != torch.float32 or out.numel() != n_out or not out.is_contiguous():
+        raise RuntimeError(f"gemv_stream needs one contiguous activation row of {cols} values and an fp32 output of {n_out}")
     if prologue != PRO_NONE and x.dtype != torch.float32:
         raise RuntimeError("the fused prologues take fp32 activations")
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().nb_gemv_stream(prologue, x.data_ptr(), _DTYPE[x.dtype], 0 if delta is None else delta.data_ptr(),
                                              0 if norm_weight is None else norm_weight.data_ptr(), float(eps),
                                              0 if x_out is None else x_out.data_ptr(), w_stream.data_ptr(), bits, n, k,
-                                             out.data_ptr(), _stream()), "nb_gemv_stream")
+                                             out.data_ptr(), 1 if swiglu else 0, _stream()), "nb_gemv_stream")
     return out
 
 

@@ -88,13 +88,16 @@ class PackedLinear(torch.nn.Module):
             y = self._forward_many(x_flat)
         return y.reshape(*shape[:-1], self.out_features)
 
-    def stream_weight(self):
-        """Tile-major copy of the packed weight for the fused tensor-core kernel and the persistent
-        kernel (built on first use, kept with the module)."""
-        w = getattr(self, "_wstream", None)
+    def stream_weight(self, row_mode: int = 0):
+        """Tile-major copy of the packed weight for the fused tensor-core kernel and the many-matrix / decode-chain
+        kernels (built on first use, kept with the module).  row_mode 1: this is a fused [gate | up] matrix and every
+        16-row tile holds 8 gate channels and the matching 8 up channels (for a SwiGLU epilogue)."""
+        attr = "_wstream" if row_mode == 0 else "_wstream_rm1"
+        w = getattr(self, attr, None)
         if w is None:
             from .stream import stream_pack
-            w = self._wstream = stream_pack(self.packed_indices, self.codebook, self.bits, self.out_features, self.in_features)
+            w = stream_pack(self.packed_indices, self.codebook, self.bits, self.out_features, self.in_features, row_mode)
+            setattr(self, attr, w)
         return w
 
     def _forward_many(self, x_flat):

@@ -176,8 +176,7 @@ def stream_weights(model) -> list[dict]:
     out = []
     for blk in model.blocks:
         d = {name: getattr(blk, name).stream_weight() for name in ("qkv", "out_proj", "down")}   # shared with the prefill kernel
-        lin = blk.gate_up
-        d["gate_up"] = stream_pack(lin.packed_indices, lin.codebook, lin.bits, lin.out_features, lin.in_features, 1)
+        d["gate_up"] = blk.gate_up.stream_weight(1)
         out.append(d)
     torch.cuda.synchronize(model.embedding.device)
     model._stream_weights = out

@@ -322,3 +322,27 @@ def test_decode_step_on_the_stream_layout_equals_the_workspace_kernels(built_lib
     toks_g = g.generate(prompt, 12)
     toks_e = G.DecodeSession(model, 1, use_graph=False, tile_gemv=True).generate(prompt, 12)
     assert torch.equal(toks_g, toks_e)
+
+
+@pytest.mark.parametrize("bits,f,k", [(3, 6912, 2560), (3, 704, 640), (2, 1408, 1280)])
+def test_chain_gemv_swiglu_epilogue(built_lib, bits, f, k):
+    """A fused [gate | up] matrix packed with 8 gate and the 8 matching up channels per tile: the matvec's epilogue
+    writes silu(gate) * up, with the residual add + RMSNorm in front as in the decoder."""
+    from nativebit_b200 import ops, stream as S
+    dev = _dev()
+    n = 2 * f
+    packed, cb, _ = o.make_packed_linear(n, k, bits, seed=f % 89)
+    w = S.stream_pack(_cu(packed, dev), _cu(cb, dev), bits, n, k, row_mode=1)
+    rng = np.random.default_rng(f)
+    h = rng.standard_normal(k).astype(np.float32)
+    d = rng.standard_normal(k).astype(np.float32)
+    g = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    v = h.astype(np.float64) + d.astype(np.float64)
+    act = v / np.sqrt((v * v).mean() + 1e-6) * g
+    gu = o.packed_linear_forward(act.reshape(1, k), packed, cb.astype(np.float32), n, k, bits, acc_dtype=np.float64)[0]
+    ref = gu[:f] / (1 + np.exp(-gu[:f])) * gu[f:]
+    y = torch.full((f,), float("nan"), device=dev)
+    ops.gemv_stream(ops.PRO_ADD_RMSNORM, _cu(h, dev), w, bits, n, k, y, delta=_cu(d, dev), norm_weight=_cu(g, dev), eps=1e-6,
+                    x_out=torch.empty(k, device=dev), swiglu=True)
+    torch.cuda.synchronize()
+    assert np.abs(y.double().cpu().numpy() - ref).max() <= 5e-5 * np.abs(ref).max()
