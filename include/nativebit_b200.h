@@ -167,6 +167,14 @@ int nb_rope_kv_write(const float* qkv, int B, int H, int hd, const float* cos2, 
 int nb_decode_attention(const float* q, const float* k_cache, const float* v_cache, const int64_t* pos, int B, int H,
                         int hd, int ctx, float* out, int out_stride, int out_offset, void* stream);
 int nb_silu_mul(const float* gu, int B, int F, float* hmid, void* stream);
+/* Causal attention of a prompt of T tokens per sequence that continues a cache of pos0 keys (pos0 = 0 for a fresh
+ * prompt), one launch per layer: rotates q and k of qkv (B*T, 3*H*hd) with rows pos0 .. pos0+T-1 of cos2/sin2, writes
+ * the rotated k and v to the caches (B, H, ctx, hd) at those positions and
+ * out[(b*T + t)*out_stride + out_offset + h*hd + d] = softmax(q_t . K[0..pos0+t] / sqrt(hd)) . V[0..pos0+t]
+ * (inference/generate_torch.py:41-60, :86-97 for T > 1).  fp32 throughout; hd a multiple of 4, <= 128; pos0 + T <= ctx;
+ * qkv, caches and out 16-byte aligned, out_stride and out_offset multiples of 4. */
+int nb_prefill_attention(const float* qkv, int B, int T, int H, int hd, const float* cos2, const float* sin2, int pos0,
+                         float* k_cache, float* v_cache, int ctx, float* out, int out_stride, int out_offset, void* stream);
 /* nb_rope_kv_write and nb_decode_attention in one launch: rotates q and k of qkv (B, 3*H*hd), writes
  * k and v to the caches at *pos and attends with the rotated q (same limits as nb_decode_attention). */
 int nb_decode_attention_rope(const float* qkv, const float* cos2, const float* sin2, const int64_t* pos, float* k_cache,

@@ -302,6 +302,152 @@ static int launch_attention(int B, int H, int hd, int ctx, cudaStream_t st, Args
   return record_cuda_error(cudaLaunchKernelEx(&cfg, decode_attention_kernel, args...));
 }
 
+// Causal attention of a prompt (or a chunk of one that continues a cache of pos0 keys) in ONE launch per layer:
+// RoPE on q and k, cache write, softmax(q k^T / sqrt(hd)) v over keys 0 .. pos0 + t for query t
+// (inference/generate_torch.py:41-60 RoPE, :86-97 cache write and masked attention).  grid (ceil(T / 16), H, B):
+// a CTA owns 16 queries of one head; it walks the keys in chunks of 32, staging a chunk of K and V in shared
+// memory — from the cache below pos0, from qkv (rotating k on the way) from pos0 on, so no CTA reads what
+// another one writes in this launch — and keeps a running maximum, denominator and numerator per query.  The
+// CTA whose queries sit at positions [q0, q0 + 16) is the one that writes those positions' k and v to the cache.
+// Eight threads share a query: for the scores each takes every eighth key of the chunk, for the values four head
+// dimensions out of every 32.  Everything is fp32.  head_dim a multiple of 4, <= 128.
+constexpr int kPQ = 16, kPK = 32, kPThreads = 128;
+
+__global__ void __launch_bounds__(kPThreads) prefill_attention_kernel(
+    const float* __restrict__ qkv, const float* __restrict__ cos2, const float* __restrict__ sin2, float* __restrict__ k_cache,
+    float* __restrict__ v_cache, float* __restrict__ out, int T, int H, int hd, int ctx, int pos0, int out_stride, int out_offset,
+    float scale) {
+  extern __shared__ __align__(16) float psm[];
+  const int hdp = hd + 4;                       // row stride: 16-byte aligned, eight consecutive rows on different banks
+  float* q_s = psm;                             // [kPQ][hdp]
+  float* k_s = q_s + kPQ * hdp;                 // [kPK][hdp]
+  float* v_s = k_s + kPK * hdp;                 // [kPK][hdp]
+  float* p_s = v_s + kPK * hdp;                 // [kPQ][kPK + 1]
+  const int tid = threadIdx.x, q0 = blockIdx.x * kPQ, h = blockIdx.y, b = blockIdx.z;
+  const int row3 = 3 * H * hd, half = hd >> 1, quarter = hd >> 2;
+  const size_t cbase = ((size_t)b * H + h) * (size_t)ctx * hd;
+
+  // this tile's queries, rotated (rows past the prompt's end repeat its last query and are not written)
+  for (int i = tid; i < kPQ * half; i += kPThreads) {
+    const int r = i / half, d = (i - r * half) * 2;
+    const int t = min(q0 + r, T - 1);
+    const float2 x = *reinterpret_cast<const float2*>(qkv + (size_t)(b * T + t) * row3 + h * hd + d);
+    const size_t ri = (size_t)(pos0 + t) * hd + d;
+    const float c = cos2[ri], s = sin2[ri];
+    q_s[r * hdp + d] = x.x * c - x.y * s;
+    q_s[r * hdp + d + 1] = x.y * c + x.x * s;
+  }
+
+  const int qi = tid >> 3, sub = tid & 7;
+  const int my_pos = pos0 + min(q0 + qi, T - 1);
+  const int kmax = pos0 + min(q0 + kPQ - 1, T - 1);      // last key any query of this tile may see
+  float m = -INFINITY, l = 0.f;
+  float4 acc[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  for (int kc = 0; kc <= kmax; kc += kPK) {
+    for (int i = tid; i < kPK * half; i += kPThreads) {
+      const int j = i / half, d = (i - j * half) * 2, p = kc + j;
+      float2 r = make_float2(0.f, 0.f);
+      if (p <= kmax) {
+        if (p < pos0) {
+          r = *reinterpret_cast<const float2*>(k_cache + cbase + (size_t)p * hd + d);
+        } else {
+          const int t = p - pos0;
+          const float2 x = *reinterpret_cast<const float2*>(qkv + (size_t)(b * T + t) * row3 + (H + h) * hd + d);
+          const size_t ri = (size_t)p * hd + d;
+          const float c = cos2[ri], s = sin2[ri];
+          r.x = x.x * c - x.y * s;
+          r.y = x.y * c + x.x * s;
+          if (t >= q0) *reinterpret_cast<float2*>(k_cache + cbase + (size_t)p * hd + d) = r;
+        }
+      }
+      k_s[j * hdp + d] = r.x;
+      k_s[j * hdp + d + 1] = r.y;
+    }
+    for (int i = tid; i < kPK * quarter; i += kPThreads) {
+      const int j = i / quarter, d = (i - j * quarter) * 4, p = kc + j;
+      float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p <= kmax) {
+        if (p < pos0) {
+          r = *reinterpret_cast<const float4*>(v_cache + cbase + (size_t)p * hd + d);
+        } else {
+          const int t = p - pos0;
+          r = *reinterpret_cast<const float4*>(qkv + (size_t)(b * T + t) * row3 + (2 * H + h) * hd + d);
+          if (t >= q0) *reinterpret_cast<float4*>(v_cache + cbase + (size_t)p * hd + d) = r;
+        }
+      }
+      *reinterpret_cast<float4*>(v_s + j * hdp + d) = r;
+    }
+    __syncthreads();
+
+    // scores of keys sub, sub + 8, sub + 16, sub + 24 of the chunk against query qi
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      const float4* qr = reinterpret_cast<const float4*>(q_s + qi * hdp);
+      const float4* kr = reinterpret_cast<const float4*>(k_s + sub * hdp);
+      const int kstep = 8 * hdp / 4;
+      for (int d4 = 0; d4 < quarter; ++d4) {
+        const float4 x = qr[d4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 y = kr[i * kstep + d4];
+          sc[i] += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
+        }
+      }
+    }
+    float cm = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      sc[i] = (kc + sub + 8 * i <= my_pos) ? sc[i] * scale : -INFINITY;
+      cm = fmaxf(cm, sc[i]);
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, o));
+    const float m_new = fmaxf(m, cm);           // finite from the first chunk on: key 0 is visible to every query
+    const float corr = expf(m - m_new);
+    float ps = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float pr = expf(sc[i] - m_new);
+      p_s[qi * (kPK + 1) + sub + 8 * i] = pr;
+      ps += pr;
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+    l = l * corr + ps;
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { acc[i].x *= corr; acc[i].y *= corr; acc[i].z *= corr; acc[i].w *= corr; }
+    __syncwarp();                               // the eight threads of a query are lanes of one warp
+
+    // numerator: head dimensions sub*4 + 32*i of query qi
+    const float* pr = p_s + qi * (kPK + 1);
+#pragma unroll 4
+    for (int j = 0; j < kPK; ++j) {
+      const float w = pr[j];
+      const float* vr = v_s + j * hdp + sub * 4;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (sub * 4 + 32 * i < hd) {
+          const float4 v = *reinterpret_cast<const float4*>(vr + 32 * i);
+          acc[i].x += w * v.x; acc[i].y += w * v.y; acc[i].z += w * v.z; acc[i].w += w * v.w;
+        }
+      }
+    }
+    __syncthreads();                            // before the next chunk overwrites K, V and the weights
+  }
+  if (q0 + qi < T) {
+    const float inv = 1.f / l;
+    float* o = out + (size_t)(b * T + q0 + qi) * out_stride + out_offset + h * hd + sub * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (sub * 4 + 32 * i < hd)
+        *reinterpret_cast<float4*>(o + 32 * i) = make_float4(acc[i].x * inv, acc[i].y * inv, acc[i].z * inv, acc[i].w * inv);
+  }
+}
+
 // h[b, i] = silu(gu[b, i]) * gu[b, F + i]
 __global__ void silu_mul_kernel(const float* __restrict__ gu, float* __restrict__ hmid, int F, int total) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -436,6 +582,25 @@ extern "C" int nb_decode_attention(const float* q, const float* k_cache, const f
   return launch_attention(B, H, hd, ctx, (cudaStream_t)stream, q, const_cast<float*>(k_cache), const_cast<float*>(v_cache),
                           reinterpret_cast<const long long*>(pos), out, H, hd, ctx, out_stride, out_offset, (const float*)nullptr,
                           (const float*)nullptr, (const float*)nullptr);
+}
+
+extern "C" int nb_prefill_attention(const float* qkv, int B, int T, int H, int hd, const float* cos2, const float* sin2, int pos0,
+                                    float* k_cache, float* v_cache, int ctx, float* out, int out_stride, int out_offset,
+                                    void* stream) {
+  if (!qkv || !cos2 || !sin2 || !k_cache || !v_cache || !out || B < 1 || T < 1 || H < 1 || hd < 4 || ctx < 1 || pos0 < 0 ||
+      out_stride < 1 || out_offset < 0)
+    return NB_ERR_ARG;
+  if (hd > 128 || hd % 4 != 0 || pos0 + T > ctx || out_offset + H * hd > out_stride) return NB_ERR_SHAPE;
+  if ((uintptr_t)qkv % 16 || (uintptr_t)k_cache % 16 || (uintptr_t)v_cache % 16 || (uintptr_t)out % 16 || out_stride % 4 ||
+      out_offset % 4)
+    return NB_ERR_ALIGN;
+  if (H > 65535 || B > 65535) return NB_ERR_SHAPE;
+  if (int rc = check_device()) return rc;
+  const int hdp = hd + 4;
+  const size_t smem = (size_t)((kPQ + 2 * kPK) * hdp + kPQ * (kPK + 1)) * sizeof(float);      // <= 44 KB
+  prefill_attention_kernel<<<dim3((T + kPQ - 1) / kPQ, H, B), kPThreads, smem, (cudaStream_t)stream>>>(
+      qkv, cos2, sin2, k_cache, v_cache, out, T, H, hd, ctx, pos0, out_stride, out_offset, 1.0f / sqrtf((float)hd));
+  return record_cuda_error(cudaGetLastError());
 }
 
 extern "C" int nb_silu_mul(const float* gu, int B, int F, float* hmid, void* stream) {

@@ -1109,7 +1109,7 @@ __global__ void __launch_bounds__(GW * 32, 1) group_kernel(const GroupPlan* __re
   constexpr int D = RING / (GW * F::kBytes) < 8 ? RING / (GW * F::kBytes) : 8;   // ring stages per warp
   constexpr int kThreads = GW * 32;
   static_assert(D >= 4, "the per-warp ring needs at least four stages");
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_next;
   __shared__ int s_tile0[kGroupMaxItems + 1];
   __shared__ int s_fifo[GW][kGroupFifo];
@@ -1302,7 +1302,7 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
   constexpr int D = kTileRing / (kGW * F::kBytes) < 8 ? kTileRing / (kGW * F::kBytes) : 8;
   constexpr int kThreads = kGW * 32;
   static_assert(D >= 4, "the per-warp ring needs at least four stages");
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float s16[32];
   __shared__ float s_scale;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

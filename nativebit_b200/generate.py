@@ -201,6 +201,17 @@ class PackedGPT(torch.nn.Module):
         x = self.embedding[idx].float()
         new_caches = []
         for i, blk in enumerate(self.blocks):
+            if kv_caches is not None and x.is_cuda and kv_caches[i][0].shape[0] == B:
+                # RoPE, cache write and causal attention in one launch (the rotary tables and the caches are fp32)
+                k_buf, v_buf, cache_len = kv_caches[i]
+                qkv = blk.qkv(rms_norm(x, blk.ln1, self.config.norm_eps)).float().contiguous()
+                cols = self.heads_local * self.config.head_dim
+                out = (x.new_empty if cols == self.o_cols else x.new_zeros)(B, T, self.o_cols)
+                ops.prefill_attention(qkv.view(B * T, -1), T, self.cos2, self.sin2, int(cache_len), k_buf, v_buf,
+                                      out.view(B * T, -1), self.o_col0 if cols != self.o_cols else 0)
+                new_caches.append((k_buf, v_buf, cache_len + T))
+                x = self._finish_block(x, blk, out)
+                continue
             if kv_caches is not None:
                 k_buf, v_buf, cache_len = kv_caches[i]
                 q, k, v = self._attn_inputs(x, blk, cache_len, T)

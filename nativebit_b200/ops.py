@@ -368,6 +368,23 @@ def decode_attention_rope(qkv, cos2, sin2, pos, k_cache, v_cache, out, out_offse
                                                    out.shape[1], out_offset, _stream()), "nb_decode_attention_rope")
 
 
+def prefill_attention(qkv: torch.Tensor, T: int, cos2, sin2, pos0: int, k_cache, v_cache, out: torch.Tensor,
+                      out_offset: int = 0) -> None:
+    """RoPE + cache write + causal attention of a T-token prompt chunk per sequence in one launch.
+    qkv (B*T, 3*H*hd) fp32 contiguous; caches (B, H, ctx, hd) fp32; out (B*T, >= out_offset + H*hd) fp32."""
+    b, h, ctx, hd = k_cache.shape
+    for t in (qkv, k_cache, v_cache, out, cos2, sin2):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise RuntimeError("prefill_attention needs contiguous fp32 tensors")
+    if qkv.numel() != b * T * 3 * h * hd:
+        raise RuntimeError(f"prefill_attention: qkv has {qkv.numel()} values, expected {b}*{T}*3*{h}*{hd}")
+    if cos2.shape[0] < pos0 + T or cos2.shape[-1] != hd:
+        raise RuntimeError("prefill_attention: the rotary tables do not cover the positions")
+    _lib.check(_lib.lib().nb_prefill_attention(qkv.data_ptr(), b, T, h, hd, cos2.data_ptr(), sin2.data_ptr(), pos0,
+                                               k_cache.data_ptr(), v_cache.data_ptr(), ctx, out.data_ptr(), out.shape[-1],
+                                               out_offset, _stream()), "nb_prefill_attention")
+
+
 def embed_rows(table: torch.Tensor, token: torch.Tensor, out: torch.Tensor) -> None:
     """out (B, C) fp32 = table[token] for a bf16 (V, C) table and int64 token (B,)."""
     if table.dtype != torch.bfloat16 or token.dtype != torch.int64 or out.dtype != torch.float32:

@@ -133,6 +133,44 @@ def test_decode_attention_against_torch(built_lib, B, H, hd, ctx):
         assert (out.double() - ref).abs().max() <= 2e-5 * ref.abs().max(), p_
 
 
+@pytest.mark.parametrize("B,T,H,hd,ctx,pos0,o_stride,o_off", [(1, 128, 32, 80, 1024, 0, 2560, 0), (2, 37, 4, 80, 256, 0, 320, 0),
+                                                                (1, 1, 3, 64, 64, 0, 192, 0), (3, 50, 2, 128, 200, 23, 384, 128),
+                                                                (1, 16, 4, 80, 64, 48, 320, 0), (2, 200, 5, 80, 512, 100, 400, 0)])
+def test_prefill_attention_against_torch(built_lib, B, T, H, hd, ctx, pos0, o_stride, o_off):
+    """RoPE + cache write + causal attention of a prompt chunk in one launch against the torch expressions of the
+    reference's cached path in fp64; prompts that are no multiple of the query tile, chunks that continue a cache,
+    an output wider than the heads (the padded out_proj input of an 8-way shard)."""
+    from nativebit_b200 import ops
+    from nativebit_b200 import generate as G
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(B * 1000 + T)
+    cos2, sin2 = G.precompute_rope(hd, ctx, 10000.0, dev)
+    qkv = torch.randn(B, T, 3 * H * hd, device=dev, generator=g)
+    k_cache = torch.randn(B, H, ctx, hd, device=dev, generator=g)      # below pos0: an earlier chunk's keys; above: stale values
+    v_cache = torch.randn(B, H, ctx, hd, device=dev, generator=g)
+    k0, v0 = k_cache.clone(), v_cache.clone()
+    out = torch.full((B * T, o_stride), 7.0, device=dev)
+    ops.prefill_attention(qkv.view(B * T, -1), T, cos2, sin2, pos0, k_cache, v_cache, out, o_off)
+    q, k, v = (t.reshape(B, T, H, hd).transpose(1, 2) for t in qkv.split(H * hd, dim=-1))
+    qr = G.apply_rope(q, cos2[pos0:pos0 + T], sin2[pos0:pos0 + T])
+    kr = G.apply_rope(k, cos2[pos0:pos0 + T], sin2[pos0:pos0 + T])
+    # the caches: rotated keys and the values at pos0 .. pos0 + T - 1, everything else untouched
+    assert torch.allclose(k_cache[:, :, pos0:pos0 + T], kr, rtol=0, atol=2e-6)
+    assert torch.equal(v_cache[:, :, pos0:pos0 + T], v)
+    for c, c0 in ((k_cache, k0), (v_cache, v0)):
+        assert torch.equal(c[:, :, :pos0], c0[:, :, :pos0]) and torch.equal(c[:, :, pos0 + T:], c0[:, :, pos0 + T:])
+    n = pos0 + T
+    kk = torch.cat((k0[:, :, :pos0], kr), dim=2).double()
+    vv = torch.cat((v0[:, :, :pos0], v), dim=2).double()
+    sc = torch.einsum("bhtd,bhjd->bhtj", qr.double(), kk) / hd ** 0.5
+    mask = torch.arange(n, device=dev)[None, :] <= (pos0 + torch.arange(T, device=dev))[:, None]
+    sc = sc.masked_fill(~mask, float("-inf"))
+    ref = torch.einsum("bhtj,bhjd->bhtd", torch.softmax(sc, -1), vv).transpose(1, 2).reshape(B * T, H * hd)
+    got = out[:, o_off:o_off + H * hd].double()
+    assert (got - ref).abs().max() <= 2e-5 * ref.abs().max()
+    assert bool((out[:, :o_off] == 7.0).all()) and bool((out[:, o_off + H * hd:] == 7.0).all())   # nothing outside the heads' columns
+
+
 def test_step_ends_match_torch(built_lib):
     """Embedding lookup and soft-cap + argmax kernels against the torch expressions of the reference's step."""
     from nativebit_b200 import ops
