@@ -154,6 +154,19 @@ class PackedGPT(torch.nn.Module):
             cos2, sin2 = self.cos2.index_select(0, pos0), self.sin2.index_select(0, pos0)
         return apply_rope(q, cos2, sin2), apply_rope(k, cos2, sin2), v
 
+    @staticmethod
+    def _add_norm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float) -> torch.Tensor:
+        """x += delta in place (delta may be None); returns RMSNorm(x) * weight: one kernel on the GPU."""
+        C = x.shape[-1]
+        if (delta is not None and x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and C <= 4096
+                and weight.dtype == torch.float32 and delta.dtype == torch.float32 and delta.is_contiguous()):
+            out = torch.empty_like(x)
+            ops.add_rmsnorm(x.view(-1, C), delta.view(-1, C), weight, eps, out.view(-1, C))
+            return out
+        if delta is not None:
+            x.add_(delta)
+        return rms_norm(x, weight, eps)
+
     def _finish_block(self, x, blk, attn_out):
         """attn_out (B, T, Hl*hd) -> residual adds of out_proj and the SwiGLU FFN."""
         if attn_out.shape[-1] != self.o_cols:  # pad to the whole codebook blocks covering this rank's columns
@@ -200,18 +213,27 @@ class PackedGPT(torch.nn.Module):
         B, T = idx.shape
         x = self.embedding[idx].float()
         new_caches = []
+        delta = None                                   # a residual update that the next norm kernel will add
         for i, blk in enumerate(self.blocks):
             if kv_caches is not None and x.is_cuda and kv_caches[i][0].shape[0] == B:
-                # RoPE, cache write and causal attention in one launch (the rotary tables and the caches are fp32)
+                # RoPE, cache write and causal attention in one launch (the rotary tables and the caches are fp32); the
+                # residual adds ride in the norm kernels, the last one of a block is still pending when the block ends
                 k_buf, v_buf, cache_len = kv_caches[i]
-                qkv = blk.qkv(rms_norm(x, blk.ln1, self.config.norm_eps)).float().contiguous()
+                eps = self.config.norm_eps
+                qkv = blk.qkv(self._add_norm(x, delta, blk.ln1, eps)).float().contiguous()
                 cols = self.heads_local * self.config.head_dim
                 out = (x.new_empty if cols == self.o_cols else x.new_zeros)(B, T, self.o_cols)
                 ops.prefill_attention(qkv.view(B * T, -1), T, self.cos2, self.sin2, int(cache_len), k_buf, v_buf,
                                       out.view(B * T, -1), self.o_col0 if cols != self.o_cols else 0)
                 new_caches.append((k_buf, v_buf, cache_len + T))
-                x = self._finish_block(x, blk, out)
+                d1 = self._all_reduce(blk.out_proj(out).float())
+                gu = blk.gate_up(self._add_norm(x, d1, blk.ln2, eps)).float().contiguous()
+                act = torch.empty(B, T, gu.shape[-1] // 2, dtype=torch.float32, device=gu.device)
+                ops.silu_mul(gu.view(B * T, -1), act.view(B * T, -1))
+                delta = self._all_reduce(blk.down(act).float())
                 continue
+            if delta is not None:
+                x, delta = x + delta, None
             if kv_caches is not None:
                 k_buf, v_buf, cache_len = kv_caches[i]
                 q, k, v = self._attn_inputs(x, blk, cache_len, T)
@@ -227,7 +249,11 @@ class PackedGPT(torch.nn.Module):
                 q, k, v = self._attn_inputs(x, blk, 0, T)
                 out = F.scaled_dot_product_attention(q, k, v, is_causal=True)
             x = self._finish_block(x, blk, out.transpose(1, 2).reshape(B, T, -1))
-        logits = self._logits(x[:, -1:, :].contiguous() if last_only else x)
+        if last_only:
+            x = x[:, -1:, :] if delta is None else x[:, -1:, :] + delta[:, -1:, :]
+        elif delta is not None:
+            x = x + delta
+        logits = self._logits(x.contiguous())
         return (logits, new_caches) if kv_caches is not None else logits
 
     # ------------------------------------------------------------------ construction
