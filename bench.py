@@ -453,6 +453,23 @@ def run_ours(args):
                   "algorithmic_bytes": kb,
                   "one_chain_us": ms_k1 * 1e3, "one_chain_GBps": kb / (ms_k1 * 1e-3) / 1e9, "one_chain_frac": kb / (ms_k1 * 1e-3) / 1e9 / peak,
                   "two_chains_us": ms_k * 1e3, "two_chains_GBps": kb / (ms_k * 1e-3) / 1e9, "two_chains_frac": kb / (ms_k * 1e-3) / 1e9 / peak}
+        if m == 1:
+            # the same chain on the decode step's kernel: one nb_gemv_stream launch per matrix over the stream-layout
+            # copies (programmatic dependent launches: a kernel's first weight requests overlap the drain of the one before)
+            yf = torch.empty(FFN, dtype=torch.float32, device=dev)
+            g3 = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream):
+                for lin in gate_up[:2]:
+                    ops.gemv_stream(ops.PRO_NONE, x, lin.stream_weight(), BITS, FFN, HIDDEN, yf)
+                with torch.cuda.graph(g3, stream=stream):
+                    for lin in gate_up:
+                        ops.gemv_stream(ops.PRO_NONE, x, lin.stream_weight(), BITS, FFN, HIDDEN, yf)
+                for _ in range(3):
+                    g3.replay()
+            ms_k3 = timed(g3.replay, reps) / (reps * len(gate_up))
+            single.update({"stream_layout_chain_kernel": "nb::tile_gemv_kernel<3,1> (nb_gemv_stream), one launch per matrix, one chain",
+                           "stream_layout_chain_us": ms_k3 * 1e3, "stream_layout_chain_GBps": kb / (ms_k3 * 1e-3) / 1e9,
+                           "stream_layout_chain_frac": kb / (ms_k3 * 1e-3) / 1e9 / peak})
         if use_group:
             # the persistent kernel on the two FFN shapes alone: 52 gate/up matrices, 26 down matrices per launch
             per = {}
