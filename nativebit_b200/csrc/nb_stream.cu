@@ -1484,6 +1484,221 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
   cp_async_wait<0>();
 }
 
+
+// ====================================================================================================
+// The same chained matvec for up to eight activation rows (a decode step of 2 .. 8 sequences)
+// ====================================================================================================
+// Y (m, N) = act(X) W^T with m <= 8 fp32 activation rows against ONE pass over the weights: activation row g rides in
+// column g of the m16n8k16 MMAs (the lanes of group g supply it), so eight rows cost the arithmetic of one — the
+// columns that tile_gemv_kernel feeds zeros.  Everything else is that kernel: teams of warps per row tile, per-warp
+// copy rings, one barrier per round, first weight requests before griddepcontrol.wait.  The staged rows take the
+// shared memory that the ring gives up (three stages per warp instead of five): a row is its two fp16 terms back to
+// back plus 16 bytes, so the eight lane groups read different banks.  For staging, the warps are dealt to the rows
+// (24 / m warps per row, each a contiguous part of it); the squares of a row are added per warp and then in warp
+// order, so every CTA scales a row by the same bits.
+constexpr int kRowsD = 3;
+constexpr int kRowsPartFloats = 2 * kGW * 8 * 16;           // [2][kGW][8 columns][16 rows]
+
+struct TileRowsParams {
+  const uint8_t* w;          // stream-layout weights
+  const float* x;            // (m, K) activations, or (m, 2K) rows [gate | up] with the SwiGLU prologue
+  const float* delta;        // prologue 1: (m, K) added to x before the norm (may be null)
+  const float* weight;       // prologue 1: RMSNorm weight (K)
+  float* x_out;              // prologue 1: receives x + delta (may be null; must not alias x)
+  float* y;                  // (m, N) outputs, fp32
+  int N, bpr, prologue, m;
+  float eps;
+  int wpt;                   // warps per team
+  int row_bytes, term_bytes; // a staged row, one fp16 term of it
+};
+
+__device__ __forceinline__ void stage4_row(uint8_t* row_s, int term_bytes, int i4, float u0, float u1, float u2, float u3) {
+  uint8_t* dst = row_s + (i4 >> 3) * kXSegBytes + (i4 & 7) * 8;
+  const uint32_t h01 = f32x2_to_f16x2_sat(u0, u1), h23 = f32x2_to_f16x2_sat(u2, u3);
+  *reinterpret_cast<uint2*>(dst) = make_uint2(h01, h23);
+  const float2 r01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+  const float2 r23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+  const uint32_t l01 = f32x2_to_f16x2_sat(fminf(fmaxf(u0, -65504.f), 65504.f) - r01.x, fminf(fmaxf(u1, -65504.f), 65504.f) - r01.y);
+  const uint32_t l23 = f32x2_to_f16x2_sat(fminf(fmaxf(u2, -65504.f), 65504.f) - r23.x, fminf(fmaxf(u3, -65504.f), 65504.f) - r23.y);
+  *reinterpret_cast<uint2*>(dst + term_bytes) = make_uint2(l01, l23);
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_rows_kernel(const TileRowsParams p) {
+  using F = UnitFmt<BITS>;
+  constexpr int D = kRowsD;
+  constexpr int kThreads = kGW * 32;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ float s_ss[kGW];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m = p.m;
+  uint8_t* ring = smem + warp * (D * F::kBytes);
+  uint8_t* x_s = smem + kGW * D * F::kBytes;
+  float* s_part = reinterpret_cast<float*>(x_s + m * p.row_bytes);
+  uint8_t* x_zero = reinterpret_cast<uint8_t*>(s_part + kRowsPartFloats);
+  const int bpr = p.bpr, K = bpr * kBlock;
+  const int wpt = p.wpt;
+  const int tpr = kGW / wpt;
+  const int team = warp / wpt, wi = warp - team * wpt;
+  const int u_lo = bpr * wi / wpt, u_hi = bpr * (wi + 1) / wpt;
+  const int n_tiles = (p.N + 15) >> 4;
+  const int per_round = (int)gridDim.x * tpr;
+  const int rounds = (n_tiles + per_round - 1) / per_round;
+  auto tile_at = [&](int r, int tm) { return r * per_round + tm * (int)gridDim.x + (int)blockIdx.x; };
+  auto tile_of = [&](int r) { return tile_at(r, team); };
+
+  int rq_round = 0, rq_u = u_lo, rq_stage = 0, use_stage = 0;
+  auto request_one = [&]() {
+    while (rq_round < rounds && (rq_u >= u_hi || tile_of(rq_round) >= n_tiles)) { ++rq_round; rq_u = u_lo; }
+    if (rq_round < rounds) {
+      const uint8_t* src = p.w + ((size_t)tile_of(rq_round) * bpr + rq_u) * F::kBytes;
+      uint8_t* dst = ring + rq_stage * F::kBytes;
+      constexpr int kChunks = F::kBytes / 16;
+#pragma unroll
+      for (int i = 0; i < (kChunks + 31) / 32; ++i)
+        if (i * 32 + 32 <= kChunks || lane + i * 32 < kChunks) cp_async16(dst + 16 * (lane + i * 32), src + 16 * (lane + i * 32));
+      ++rq_u;
+    }
+    if (++rq_stage == D) rq_stage = 0;
+    cp_async_commit();
+  };
+#pragma unroll 1
+  for (int i = 0; i < D - 2; ++i) request_one();
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- the activation rows (and the element-wise step in front of this linear)
+  {
+    const int wpr = kGW / m;                                // warps per row; 24 % m warps stay idle here
+    const int r = warp / wpr, q = warp - r * wpr;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float ss = 0.f;
+    if (r < m) {
+      const int n4 = K >> 2;
+      const int lo = n4 * q / wpr, hi = n4 * (q + 1) / wpr;
+      uint8_t* row_s = x_s + r * p.row_bytes;
+      if (p.prologue == 1) {
+        const float4* xr = reinterpret_cast<const float4*>(p.x) + (size_t)r * n4;
+        const float4* dr = p.delta ? reinterpret_cast<const float4*>(p.delta) + (size_t)r * n4 : nullptr;
+        const float4* w4 = reinterpret_cast<const float4*>(p.weight);
+        float4* xo = (blockIdx.x == 0 && p.x_out) ? reinterpret_cast<float4*>(p.x_out) + (size_t)r * n4 : nullptr;
+#pragma unroll 1
+        for (int i0 = lo + lane; i0 < hi; i0 += 128) {
+          float4 vx[4], vd[4], vw[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {                     // all loads first: one memory round trip per four
+            const int i4 = i0 + 32 * j;
+            const bool in = i4 < hi;
+            vx[j] = in ? __ldcg(xr + i4) : zero4;
+            vd[j] = (in && dr) ? __ldcg(dr + i4) : zero4;
+            vw[j] = in ? __ldg(w4 + i4) : zero4;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i4 = i0 + 32 * j;
+            if (i4 < hi) {
+              float4 v = vx[j];
+              v.x += vd[j].x; v.y += vd[j].y; v.z += vd[j].z; v.w += vd[j].w;
+              if (xo) xo[i4] = v;
+              ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+              stage4_row(row_s, p.term_bytes, i4, v.x * vw[j].x, v.y * vw[j].y, v.z * vw[j].z, v.w * vw[j].w);
+            }
+          }
+        }
+      } else if (p.prologue == 2) {
+        const float4* g4 = reinterpret_cast<const float4*>(p.x) + (size_t)r * 2 * n4;
+        const float4* u4 = g4 + n4;
+#pragma unroll 1
+        for (int i0 = lo + lane; i0 < hi; i0 += 128) {
+          float4 vg[4], vu[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i4 = i0 + 32 * j;
+            vg[j] = i4 < hi ? __ldcg(g4 + i4) : zero4;
+            vu[j] = i4 < hi ? __ldcg(u4 + i4) : zero4;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i4 = i0 + 32 * j;
+            const float4 g = vg[j], u = vu[j];
+            if (i4 < hi)
+              stage4_row(row_s, p.term_bytes, i4, g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y,
+                         g.z / (1.f + __expf(-g.z)) * u.z, g.w / (1.f + __expf(-g.w)) * u.w);
+          }
+        }
+      } else {
+        const float4* xr = reinterpret_cast<const float4*>(p.x) + (size_t)r * n4;
+#pragma unroll 1
+        for (int i0 = lo + lane; i0 < hi; i0 += 128) {
+          float4 vx[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) vx[j] = i0 + 32 * j < hi ? __ldcg(xr + i0 + 32 * j) : zero4;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (i0 + 32 * j < hi) stage4_row(row_s, p.term_bytes, i0 + 32 * j, vx[j].x, vx[j].y, vx[j].z, vx[j].w);
+        }
+      }
+    }
+    ss = warp_sum_f(ss);
+    if (lane == 0) s_ss[warp] = ss;
+    if (tid < 16) reinterpret_cast<uint32_t*>(x_zero)[tid] = 0u;      // for the MMA columns that carry no row
+    __syncthreads();
+  }
+
+  // ---- rounds: every team one row tile; a warp adds its units for all rows, the team's sums meet in shared memory
+  const int g = lane >> 2, t = lane & 3;
+  const bool have = g < m;
+  const uint8_t* xrow = x_s + g * p.row_bytes;
+  const int term = have ? p.term_bytes : 0;
+#pragma unroll 1
+  for (int r = 0; r < rounds; ++r) {
+    const int tile = tile_of(r);
+    float c[2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) c[h][e] = 0.f;
+    if (tile < n_tiles) {
+#pragma unroll 1
+      for (int u = u_lo; u < u_hi; ++u) {
+        request_one();
+        cp_async_wait<D - 2>();
+        __syncwarp();
+        const uint8_t* xseg = have ? xrow + (u * 4 + t) * kXSegBytes : x_zero;
+        unit_mma_x<BITS, 2>(ring + use_stage * F::kBytes, xseg, term, lane, c);
+        if (++use_stage == D) use_stage = 0;
+        __syncwarp();
+      }
+    }
+    // lane (g, t) holds weight rows g and g + 8 of columns 2t and 2t + 1 = activation rows 2t, 2t + 1
+    float* part = s_part + (r & 1) * (kGW * 128) + warp * 128;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      part[(2 * t + e) * 16 + g] = c[0][e] + c[1][e];
+      part[(2 * t + e) * 16 + g + 8] = c[0][2 + e] + c[1][2 + e];
+    }
+    __syncthreads();                                       // one barrier per round: the buffers alternate
+    const float* pr = s_part + (r & 1) * (kGW * 128);
+    const int wpr = kGW / m;
+    for (int idx = tid; idx < tpr * 16 * m; idx += kThreads) {
+      const int tm = idx / (16 * m), rem = idx - tm * 16 * m;
+      const int col = rem >> 4, row = rem & 15;
+      const int t_out = tile_at(r, tm);
+      float acc = 0.f;
+      for (int j = 0; j < wpt; ++j) acc += pr[(tm * wpt + j) * 128 + col * 16 + row];      // the team's warps in k order
+      float scale = 1.f;
+      if (p.prologue == 1) {
+        float tot = 0.f;
+        for (int q = 0; q < wpr; ++q) tot += s_ss[col * wpr + q];
+        scale = 1.0f / sqrtf(tot / (float)K + p.eps);
+      }
+      const int n = t_out * 16 + row;
+      if (t_out < n_tiles && n < p.N) p.y[(size_t)col * p.N + n] = acc * scale;
+    }
+  }
+  cp_async_wait<0>();
+}
+
 }  // namespace nb
 
 using namespace nb;
@@ -1805,6 +2020,75 @@ extern "C" int nb_gemv_stream(int prologue, const void* x, int x_dtype, const fl
   cfg.gridDim = dim3(nb_stream_ctas());
   cfg.blockDim = dim3(kGW * 32);
   cfg.dynamicSmemBytes = kTileSmem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  void* args[] = {&p};
+  return record_cuda_error(cudaLaunchKernelExC(&cfg, fn, args));
+}
+
+// shared memory of tile_gemv_rows_kernel for m rows of K activations (0: bad arguments)
+static size_t rows_smem_bytes(int bits, int K, int m) {
+  if ((bits != 2 && bits != 3 && bits != 4) || K < kBlock || K % kBlock != 0 || K / kBlock > kMaxKBlocks || m < 1 || m > 8) return 0;
+  const size_t unit = bits == 4 ? UnitFmt<4>::kBytes : UnitFmt<3>::kBytes;
+  const size_t term = (size_t)(K / kBlock) * 4 * kXSegBytes;
+  return (size_t)kGW * kRowsD * unit + (size_t)m * (2 * term + 16) + (size_t)kRowsPartFloats * 4 + 64;
+}
+constexpr size_t kRowsSmemLimit = 227 * 1024 - 256;         // per CTA, less the kernel's static shared memory
+
+extern "C" int nb_gemv_stream_max_rows(int bits, int K) {
+  int best = 0;
+  for (int m = 1; m <= 8; ++m) {
+    const size_t need = rows_smem_bytes(bits, K, m);
+    if (need != 0 && need <= kRowsSmemLimit) best = m;
+  }
+  return best;
+}
+
+extern "C" int nb_gemv_stream_rows(int prologue, const float* x, int M, const float* delta, const float* norm_weight, float eps,
+                                   float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, void* stream) {
+  if (!x || !w_stream || !y || N < 1 || M < 1) return NB_ERR_ARG;
+  if (prologue < 0 || prologue > 2) return NB_ERR_ARG;
+  if (bits != 2 && bits != 3 && bits != 4) return NB_ERR_SHAPE;
+  if (K < kBlock || K % kBlock != 0 || K / kBlock > kMaxKBlocks) return NB_ERR_SHAPE;
+  if (M > nb_gemv_stream_max_rows(bits, K)) return NB_ERR_SHAPE;
+  if (prologue == 1 && !norm_weight) return NB_ERR_ARG;
+  if ((uintptr_t)w_stream % 16 || (uintptr_t)x % 16 || (uintptr_t)delta % 16 || (uintptr_t)norm_weight % 16 || (uintptr_t)x_out % 16)
+    return NB_ERR_ALIGN;
+  if (x_out && x_out == x) return NB_ERR_ARG;
+  if (int rc = check_device()) return rc;
+  TileRowsParams p{};
+  p.w = w_stream; p.x = x; p.delta = delta; p.weight = norm_weight; p.x_out = x_out; p.y = y;
+  p.N = N; p.bpr = K / kBlock; p.prologue = prologue; p.m = M; p.eps = eps;
+  p.term_bytes = p.bpr * 4 * kXSegBytes;
+  p.row_bytes = 2 * p.term_bytes + 16;
+  {
+    const int G = nb_stream_ctas(), n_tiles = (N + 15) / 16;
+    double best = 1e30;
+    for (int wpt : {24, 12, 6, 3}) {
+      const int per_round = G * (kGW / wpt);
+      const int rounds = (n_tiles + per_round - 1) / per_round;
+      const double cost = rounds * ((p.bpr + wpt - 1) / wpt + 0.67);
+      if (cost < best) { best = cost; p.wpt = wpt; }
+    }
+  }
+  const void* fn = bits == 3 ? (const void*)tile_gemv_rows_kernel<3> : bits == 2 ? (const void*)tile_gemv_rows_kernel<2>
+                                                                                 : (const void*)tile_gemv_rows_kernel<4>;
+  const size_t smem = rows_smem_bytes(bits, K, M);
+  static size_t attr_bytes[64][5] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (attr_bytes[dev & 63][bits] < smem) {
+    if (cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRowsSmemLimit)) return record_cuda_error(e);
+    attr_bytes[dev & 63][bits] = kRowsSmemLimit;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nb_stream_ctas());
+  cfg.blockDim = dim3(kGW * 32);
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -342,6 +342,10 @@ class DecodeSession:
         fits = (blk0 is not None and model.config.block_size == 128 and model.config.bits in (2, 3, 4)
                 and all(l.in_features % 128 == 0 and l.in_features <= 7168 for l in (blk0.qkv, blk0.out_proj, blk0.gate_up, blk0.down)))
         self.tile_gemv = bool(fits and batch_size == 1 and fused) if tile_gemv is None else bool(tile_gemv and fits and batch_size == 1)
+        # 2 .. 8 sequences: the same kernel family with the rows in the MMA columns a single row leaves empty
+        # (nb_gemv_stream_rows): one pass over the weights for all rows, as many rows per launch as shared memory holds
+        self.tile_rows = bool(fits and 2 <= batch_size <= 8 and fused and tile_gemv is not False
+                              and getattr(model, "exchange", None) is None)
         # stream=True (one sequence on one GPU): the whole step is ONE launch of the persistent kernel
         # (stream.py).  The default is the chain of fused kernels, which measures faster: inside one launch
         # every operation pays a device-wide flag wait and the staging of its activations in full.
@@ -417,6 +421,10 @@ class DecodeSession:
                 ops.gemv_stream(ops.PRO_ADD_RMSNORM, xa, lin.stream_weight(1 if swiglu else 0), lin.bits, lin.out_features,
                                 lin.in_features, out, delta=delta, norm_weight=w, eps=eps, x_out=xb, swiglu=swiglu)
                 xa, xb = xb, xa
+            elif self.tile_rows:
+                ops.gemv_stream_rows(ops.PRO_ADD_RMSNORM, xa, lin.stream_weight(), lin.bits, lin.out_features, lin.in_features,
+                                     out, delta=delta, norm_weight=w, eps=eps, x_out=xb)
+                xa, xb = xb, xa
             elif fold:
                 ops.gemv_fused(ops.PRO_ADD_RMSNORM, xa, *args, out, delta=delta, norm_weight=w, eps=eps, x_out=xb)
                 xa, xb = xb, xa
@@ -434,6 +442,8 @@ class DecodeSession:
                 return None
             if self.tile_gemv:
                 ops.gemv_stream(prologue, x, lin.stream_weight(), lin.bits, lin.out_features, lin.in_features, out)
+            elif self.tile_rows:
+                ops.gemv_stream_rows(prologue, x, lin.stream_weight(), lin.bits, lin.out_features, lin.in_features, out)
             elif prologue == ops.PRO_SILU_MUL and fold:
                 ops.gemv_fused(prologue, x, *args, out)
             elif prologue == ops.PRO_SILU_MUL:

@@ -219,6 +219,45 @@ def gemv_stream(prologue: int, x: torch.Tensor, w_stream: torch.Tensor, bits: in
     return out
 
 
+_max_rows: dict = {}
+
+
+def gemv_stream_max_rows(bits: int, k: int) -> int:
+    """Activation rows one nb_gemv_stream_rows call takes for a matrix with k columns (8 at k = 2560, 3 at k = 6912)."""
+    key = (bits, k)
+    if key not in _max_rows:
+        _max_rows[key] = int(_lib.lib().nb_gemv_stream_max_rows(bits, k))
+    return _max_rows[key]
+
+
+def gemv_stream_rows(prologue: int, x: torch.Tensor, w_stream: torch.Tensor, bits: int, n: int, k: int, out: torch.Tensor,
+                     delta: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None, eps: float = 0.0,
+                     x_out: torch.Tensor | None = None) -> torch.Tensor:
+    """gemv_stream for a few fp32 activation rows in one pass over the weights (nb_gemv_stream_rows): out (m, n) fp32 =
+    act(x) W^T for x (m, k) — (m, 2k) with PRO_SILU_MUL.  More rows than gemv_stream_max_rows(bits, k) are split over
+    several launches here."""
+    _need_cuda(x, w_stream, out)
+    cols = 2 * k if prologue == PRO_SILU_MUL else k
+    if (x.dim() != 2 or x.shape[1] != cols or x.dtype != torch.float32 or not x.is_contiguous() or out.dtype != torch.float32
+            or out.shape != (x.shape[0], n) or not out.is_contiguous()):
+        raise RuntimeError(f"gemv_stream_rows needs contiguous fp32 x (m, {cols}) and out (m, {n})")
+    for t in (delta, x_out):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (x.shape[0], k) or not t.is_contiguous()):
+            raise RuntimeError(f"gemv_stream_rows: delta and x_out must be contiguous fp32 (m, {k})")
+    m, step = x.shape[0], gemv_stream_max_rows(bits, k)
+    if step < 1:
+        raise RuntimeError(f"gemv_stream_rows: no row of {k} activations fits ({bits} bits)")
+    with torch.cuda.device(x.device):
+        for r0 in range(0, m, step):
+            r1 = min(m, r0 + step)
+            _lib.check(_lib.lib().nb_gemv_stream_rows(prologue, x[r0:r1].data_ptr(), r1 - r0,
+                                                      0 if delta is None else delta[r0:r1].data_ptr(),
+                                                      0 if norm_weight is None else norm_weight.data_ptr(), float(eps),
+                                                      0 if x_out is None else x_out[r0:r1].data_ptr(), w_stream.data_ptr(), bits, n, k,
+                                                      out[r0:r1].data_ptr(), _stream()), "nb_gemv_stream_rows")
+    return out
+
+
 def gemv_tp(prologue: int, x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, bits: int, block_size: int,
             n: int, k: int, exchange, out: torch.Tensor | None = None, gather: bool = False, push: bool = False,
             norm_weight: torch.Tensor | None = None, eps: float = 0.0, x_out: torch.Tensor | None = None,

@@ -324,6 +324,80 @@ def test_decode_step_on_the_stream_layout_equals_the_workspace_kernels(built_lib
     assert torch.equal(toks_g, toks_e)
 
 
+@pytest.mark.parametrize("B", [2, 5, 8])
+def test_batched_decode_step_on_the_rows_kernel_equals_the_workspace_kernels(built_lib, B):
+    """A session of 2 .. 8 sequences with its packed linears on nb_gemv_stream_rows against the same session on
+    nb_gemv_fused: identical greedy tokens for different prompts per sequence, logits within summation-order
+    differences; graph replay equals the eager loop."""
+    from nativebit_b200 import generate as G
+    dev = _dev()
+    cfg = G.ModelConfig(vocab_size=512, n_layers=3, n_embd=512, n_head=4, ffn_hidden=1408, context_len=64)
+    model = G.PackedGPT.random_init(cfg, seed=5, device=dev)
+    prompt = torch.randint(0, cfg.vocab_size, (B, 7), generator=torch.Generator().manual_seed(B)).to(dev)
+    a = G.DecodeSession(model, B, use_graph=False)
+    b = G.DecodeSession(model, B, use_graph=False, tile_gemv=False)
+    assert a.tile_rows and not b.tile_rows
+    a.prefill(prompt); b.prefill(prompt)
+    for _ in range(10):
+        a.step(); b.step()
+        assert torch.equal(a.token, b.token)
+        assert (a.logits - b.logits).abs().max() <= 1e-4 * b.logits.abs().max()
+    toks_g = G.DecodeSession(model, B, use_graph=True).generate(prompt, 10)
+    toks_e = G.DecodeSession(model, B, use_graph=False).generate(prompt, 10)
+    assert torch.equal(toks_g, toks_e)
+
+
+@pytest.mark.parametrize("bits,n,k,m", [(3, 7680, 2560, 8), (3, 2560, 6912, 3), (3, 13824, 2560, 5), (3, 1000, 640, 2), (2, 2560, 2560, 7),
+                                        (4, 512, 1280, 4), (3, 320, 384, 8), (3, 40, 7168, 1), (3, 2560, 6912, 8)])
+def test_chain_gemv_rows(built_lib, bits, n, k, m):
+    """nb_gemv_stream_rows: a few fp32 activation rows in one pass over the weights (more rows than fit one launch are
+    split by the wrapper), plain / residual add + RMSNorm / SwiGLU in front; against the fp64 oracle row by row, twice
+    bit-identical, and nothing written outside the m rows."""
+    from nativebit_b200 import ops, stream as S
+    dev = _dev()
+    assert ops.gemv_stream_max_rows(3, 2560) == 8 and ops.gemv_stream_max_rows(3, 6912) == 3
+    packed, cb, _ = o.make_packed_linear(n, k, bits, seed=n % 97 + bits)
+    w = S.stream_pack(_cu(packed, dev), _cu(cb, dev), bits, n, k)
+    cbf = cb.astype(np.float32)
+    rng = np.random.default_rng(n + k + m)
+
+    def check(y, act, tol=2e-5):
+        ref = o.packed_linear_forward(act, packed, cbf, n, k, bits, acc_dtype=np.float64)
+        got = y.double().cpu().numpy()
+        for r in range(m):
+            assert np.abs(got[r] - ref[r]).max() <= tol * np.abs(ref[r]).max(), r
+
+    x = (rng.standard_normal((m, k)) * (1.0 + 1e-4 * np.arange(k))).astype(np.float32)
+    y = torch.full((m + 1, n), float("nan"), device=dev)
+    y2 = torch.full((m, n), float("nan"), device=dev)
+    ops.gemv_stream_rows(ops.PRO_NONE, _cu(x, dev), w, bits, n, k, y[:m])
+    ops.gemv_stream_rows(ops.PRO_NONE, _cu(x, dev), w, bits, n, k, y2)
+    torch.cuda.synchronize()
+    check(y[:m], x.astype(np.float64))
+    assert torch.equal(y[:m], y2) and bool(torch.isnan(y[m]).all())
+    # residual add + RMSNorm, every row with its own scale
+    h = (rng.standard_normal((m, k)) * (1.0 + np.arange(m))[:, None]).astype(np.float32)
+    d = rng.standard_normal((m, k)).astype(np.float32)
+    g = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    for delta in (d, None):
+        v = h.astype(np.float64) + (0 if delta is None else delta.astype(np.float64))
+        act = v / np.sqrt((v * v).mean(axis=1, keepdims=True) + 1e-6) * g
+        y = torch.full((m, n), float("nan"), device=dev)
+        x_out = torch.full((m, k), float("nan"), device=dev)
+        ops.gemv_stream_rows(ops.PRO_ADD_RMSNORM, _cu(h, dev), w, bits, n, k, y, delta=None if delta is None else _cu(delta, dev),
+                             norm_weight=_cu(g, dev), eps=1e-6, x_out=x_out)
+        torch.cuda.synchronize()
+        check(y, act)
+        assert np.array_equal(x_out.cpu().numpy(), (h + delta).astype(np.float32) if delta is not None else h)
+    # SwiGLU
+    gu = rng.standard_normal((m, 2 * k)).astype(np.float32)
+    gate, up = gu[:, :k].astype(np.float64), gu[:, k:].astype(np.float64)
+    y = torch.full((m, n), float("nan"), device=dev)
+    ops.gemv_stream_rows(ops.PRO_SILU_MUL, _cu(gu, dev), w, bits, n, k, y)
+    torch.cuda.synchronize()
+    check(y, gate / (1 + np.exp(-gate)) * up, tol=5e-5)                 # __expf in the activation
+
+
 @pytest.mark.parametrize("bits,f,k", [(3, 6912, 2560), (3, 704, 640), (2, 1408, 1280)])
 def test_chain_gemv_swiglu_epilogue(built_lib, bits, f, k):
     """A fused [gate | up] matrix packed with 8 gate and the 8 matching up channels per tile: the matvec's epilogue
