@@ -709,7 +709,7 @@ def run_ours(args):
     if args.serving or compact:
         from nativebit_b200 import generate as G
         serving = {"prompt_tokens": 512, "n_generate": 64, "tp": world,
-                   "linears": "up to 16 sequences: fused GEMV; more: the tensor-core kernel that dequantises inside (exact fp16 weights)"}
+                   "linears": "1 sequence: nb_gemv_stream; 2..8: nb_gemv_stream_rows (the rows in the MMA columns, one weight pass); 9..16: fused GEMV; more: the tensor-core kernel that dequantises inside (exact fp16 weights)"}
         for bits in (3, 2):
             cfg = G.ModelConfig(bits=bits)
             model = G.PackedGPT.random_init(cfg, seed=0, device=dev, tp_rank=rank, tp_size=world)
