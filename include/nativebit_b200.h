@@ -189,6 +189,14 @@ int nb_decode_attention_rope(const float* qkv, const float* cos2, const float* s
 int nb_embed_rows(const void* table_bf16, const int64_t* token, int B, int V, int C, float* out, void* stream);
 int nb_softcap_argmax(const void* logits, int logits_dtype, int B, int V, float cap, float* logits_out, int64_t* token,
                       int64_t* pos, void* stream);
+/* The tied LM head of ONE sequence with both ends of it in the same two launches (inference/generate_torch.py:155-160,
+ * :300-310): logits_out (V) fp32 = cap * tanh(dot(table[v], h) / cap) with h = rmsnorm(x + delta) * norm_weight (delta may
+ * be NULL; norm_weight NULL: h = x + delta), token[0] = index of the largest capped logit (lowest index among equals),
+ * *pos += 1 if pos != NULL.  table: bf16 (V, C), C a multiple of 256 up to 3072; products are exact in fp32.  scratch:
+ * nb_lm_head_scratch_bytes() bytes, 16-byte aligned (per-CTA arg-max candidates). */
+size_t nb_lm_head_scratch_bytes(void);
+int nb_lm_head(const float* x, const float* delta, const float* norm_weight, float eps, const void* table_bf16, int V, int C,
+               float cap, float* logits_out, int64_t* token, int64_t* pos, void* scratch, void* stream);
 
 /* ---- nb_gemv with the preceding element-wise step of the decoder folded into the staging of its
  * activations, so the step needs no separate launch for it (fp32 activations, M <= 8; everything

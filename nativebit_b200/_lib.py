@@ -44,6 +44,9 @@ _SIGNATURES = {
     "nb_decode_attention_rope": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int,
                                             _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p]),
     "nb_silu_mul": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
+    "nb_lm_head_scratch_bytes": (_c.c_size_t, []),
+    "nb_lm_head": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_float, _c.c_void_p, _c.c_int, _c.c_int, _c.c_float,
+                              _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p]),
     "nb_prefill_attention": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_int,
                                         _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p]),
     "nb_allreduce_buffer_bytes": (_c.c_size_t, [_c.c_int, _c.c_int]),

@@ -448,6 +448,164 @@ __global__ void __launch_bounds__(kPThreads) prefill_attention_kernel(
   }
 }
 
+// The tied LM head of one sequence as a matvec over the bf16 embedding table, with the final residual add + RMSNorm
+// in front and the soft-cap + arg-max behind it (inference/generate_torch.py:155-160 and :300-310): logits[v] =
+// cap * tanh(dot(table[v], norm(x + delta) * w) / cap).  HBM-bound (164 MB per token at V = 32000, C = 2560): CTA b
+// owns the table rows [V*b/G, V*(b+1)/G); a warp takes them two at a time through its own double buffer of 16-byte
+// asynchronous copies (the next pair is in flight while this one is multiplied: eight warps keep a pair each, 80 KB
+// per SM, on the way — plain loads were sunk to their uses by the compiler, four in flight per lane) and multiplies
+// them with the activations staged once in shared memory as fp32 (bf16 x fp32 products are exact in fp32).  The
+// norm's scale is one factor on the dot products.  Every CTA leaves its best (value, index) as a candidate;
+// lm_head_finish_kernel picks the token (largest capped logit, lowest index among equals) and advances the
+// position.  C = 256 * NC: a lane owns eight values of every 256.
+constexpr int kHeadThreads = 256;
+constexpr int kHeadWarps = kHeadThreads / 32;
+constexpr int kHeadMaxCtas = 1024;
+constexpr int kHeadMaxNC = 12;                               // C <= 3072: the double buffers of eight warps fit shared memory
+
+__device__ __forceinline__ void head_cp_async16(void* dst, const void* src) {   // 16 bytes global -> shared, past L1
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+__global__ void __launch_bounds__(kHeadThreads, 1) lm_head_kernel(const float* __restrict__ x, const float* __restrict__ delta,
+                                                                  const float* __restrict__ w, float eps,
+                                                                  const __nv_bfloat16* __restrict__ table, int V, int NC, float cap,
+                                                                  float* __restrict__ logits_out, float* __restrict__ cand_val,
+                                                                  int* __restrict__ cand_idx) {
+  extern __shared__ __align__(16) uint8_t head_smem[];
+  __shared__ float s_red[kHeadWarps];
+  __shared__ int s_ci[kHeadWarps];
+  __shared__ float s_scale;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int C = NC * 256, row_bytes = C * 2;
+  float* hs = reinterpret_cast<float*>(head_smem);                                   // C floats
+  uint8_t* ring = head_smem + (size_t)C * 4 + (size_t)warp * 4 * row_bytes;         // [2 pairs][2 rows][row_bytes]
+  const int G = gridDim.x, b = blockIdx.x;
+  const int row0 = (int)((long long)V * b / G), row1 = (int)((long long)V * (b + 1) / G);
+  // pair i of this warp: rows row0 + warp + 16 i and + 8 more
+  auto request = [&](int i) {
+    const int ra = row0 + warp + 2 * kHeadWarps * i;
+    uint8_t* dst = ring + (size_t)(i & 1) * 2 * row_bytes;
+#pragma unroll 1
+    for (int h = 0; h < 2; ++h) {
+      const int r = ra + h * kHeadWarps;
+      if (r < row1) {
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(table) + (size_t)r * row_bytes;
+        for (int j = 0; j < NC; ++j) head_cp_async16(dst + h * row_bytes + (j * 32 + lane) * 16, src + (j * 32 + lane) * 16);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  asm volatile("griddepcontrol.launch_dependents;");
+  request(0);                                                // the table does not depend on the launch before
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  float ss = 0.f;
+  for (int i4 = tid; i4 < C / 4; i4 += kHeadThreads) {
+    float4 v = __ldcg(reinterpret_cast<const float4*>(x) + i4);
+    if (delta) {
+      const float4 d = __ldcg(reinterpret_cast<const float4*>(delta) + i4);
+      v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+    }
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    if (w) {
+      const float4 g = __ldg(reinterpret_cast<const float4*>(w) + i4);
+      v.x *= g.x; v.y *= g.y; v.z *= g.z; v.w *= g.w;
+    }
+    reinterpret_cast<float4*>(hs)[i4] = v;
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) s_red[warp] = ss;
+  __syncthreads();
+  if (tid == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < kHeadWarps; ++i) tot += s_red[i];
+    s_scale = w ? 1.0f / sqrtf(tot / (float)C + eps) : 1.0f;
+  }
+  __syncthreads();
+  const float scale = s_scale;
+  float best = -FLT_MAX;
+  int best_i = 0x7fffffff;
+  const int n_pairs = (row1 - row0 - warp + 2 * kHeadWarps - 1) / (2 * kHeadWarps);   // <= 0: no row for this warp
+#pragma unroll 1
+  for (int i = 0; i < n_pairs; ++i) {
+    request(i + 1);                                          // (past the end: an empty group)
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncwarp();
+    const int ra = row0 + warp + 2 * kHeadWarps * i, rb = ra + kHeadWarps;
+    const uint8_t* pa = ring + (size_t)(i & 1) * 2 * row_bytes;
+    const uint8_t* pb = pa + row_bytes;
+    const bool have_b = rb < row1;
+    float acc_a = 0.f, acc_b = 0.f;
+#pragma unroll 2
+    for (int j = 0; j < NC; ++j) {
+      const float4 x0 = *reinterpret_cast<const float4*>(hs + (j * 32 + lane) * 8);
+      const float4 x1 = *reinterpret_cast<const float4*>(hs + (j * 32 + lane) * 8 + 4);
+      const uint4 ta = *reinterpret_cast<const uint4*>(pa + (j * 32 + lane) * 16);
+      const uint4 tb = have_b ? *reinterpret_cast<const uint4*>(pb + (j * 32 + lane) * 16) : make_uint4(0u, 0u, 0u, 0u);
+      const uint32_t wa[4] = {ta.x, ta.y, ta.z, ta.w}, wb[4] = {tb.x, tb.y, tb.z, tb.w};
+      const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {                          // a word holds elements 2e (low half) and 2e + 1
+        acc_a += __uint_as_float(wa[e] << 16) * xs[2 * e] + __uint_as_float(wa[e] & 0xffff0000u) * xs[2 * e + 1];
+        acc_b += __uint_as_float(wb[e] << 16) * xs[2 * e] + __uint_as_float(wb[e] & 0xffff0000u) * xs[2 * e + 1];
+      }
+    }
+    __syncwarp();                                            // every lane is done with this buffer before it is requested again
+    acc_a = warp_sum(acc_a);
+    acc_b = warp_sum(acc_b);
+    if (lane == 0) {
+      const float ya = cap * tanhf(acc_a * scale / cap);
+      logits_out[ra] = ya;
+      if (ya > best || (ya == best && ra < best_i)) { best = ya; best_i = ra; }
+      if (have_b) {
+        const float yb = cap * tanhf(acc_b * scale / cap);
+        logits_out[rb] = yb;
+        if (yb > best || (yb == best && rb < best_i)) { best = yb; best_i = rb; }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();                                           // s_red is reused
+  if (lane == 0) { s_red[warp] = best; s_ci[warp] = best_i; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int i = 1; i < kHeadWarps; ++i)
+      if (s_red[i] > best || (s_red[i] == best && s_ci[i] < best_i)) { best = s_red[i]; best_i = s_ci[i]; }
+    cand_val[b] = best;
+    cand_idx[b] = best_i;
+  }
+}
+
+__global__ void __launch_bounds__(256) lm_head_finish_kernel(const float* __restrict__ cand_val, const int* __restrict__ cand_idx, int G,
+                                                             long long* __restrict__ token, long long* __restrict__ pos) {
+  __shared__ float s_val[8];
+  __shared__ int s_idx[8];
+  pdl_enter();
+  const int tid = threadIdx.x;
+  float best = -FLT_MAX;
+  int best_i = 0x7fffffff;
+  for (int i = tid; i < G; i += 256) {
+    const float v = cand_val[i];
+    const int vi = cand_idx[i];
+    if (v > best || (v == best && vi < best_i)) { best = v; best_i = vi; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  if ((tid & 31) == 0) { s_val[tid >> 5] = best; s_idx[tid >> 5] = best_i; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int i = 1; i < 8; ++i)
+      if (s_val[i] > best || (s_val[i] == best && s_idx[i] < best_i)) { best = s_val[i]; best_i = s_idx[i]; }
+    token[0] = best_i == 0x7fffffff ? 0 : best_i;
+    if (pos) *pos += 1;
+  }
+}
+
+
 // h[b, i] = silu(gu[b, i]) * gu[b, F + i]
 __global__ void silu_mul_kernel(const float* __restrict__ gu, float* __restrict__ hmid, int F, int total) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -601,6 +759,35 @@ extern "C" int nb_prefill_attention(const float* qkv, int B, int T, int H, int h
   prefill_attention_kernel<<<dim3((T + kPQ - 1) / kPQ, H, B), kPThreads, smem, (cudaStream_t)stream>>>(
       qkv, cos2, sin2, k_cache, v_cache, out, T, H, hd, ctx, pos0, out_stride, out_offset, 1.0f / sqrtf((float)hd));
   return record_cuda_error(cudaGetLastError());
+}
+
+extern "C" size_t nb_lm_head_scratch_bytes(void) { return (size_t)kHeadMaxCtas * 8; }
+
+extern "C" int nb_lm_head(const float* x, const float* delta, const float* norm_weight, float eps, const void* table_bf16, int V, int C,
+                          float cap, float* logits_out, int64_t* token, int64_t* pos, void* scratch, void* stream) {
+  if (!x || !table_bf16 || !logits_out || !token || !scratch || V < 1 || C < 1 || !(cap > 0.f)) return NB_ERR_ARG;
+  if (C % 256 != 0 || C / 256 > kHeadMaxNC) return NB_ERR_SHAPE;
+  if ((uintptr_t)x % 16 || (uintptr_t)delta % 16 || (uintptr_t)norm_weight % 16 || (uintptr_t)table_bf16 % 16 || (uintptr_t)scratch % 16)
+    return NB_ERR_ALIGN;
+  if (int rc = check_device()) return rc;
+  const int G = std::min(std::min(sm_count(), kHeadMaxCtas), V);
+  float* cv = reinterpret_cast<float*>(scratch);
+  int* ci = reinterpret_cast<int*>(cv + kHeadMaxCtas);
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = (size_t)C * 4 + (size_t)kHeadWarps * 4 * C * 2;
+  static size_t attr_bytes[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (attr_bytes[dev & 63] < smem) {
+    const size_t most = (size_t)kHeadMaxNC * 256 * 4 + (size_t)kHeadWarps * 4 * kHeadMaxNC * 256 * 2;
+    if (cudaError_t e = cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most)) return record_cuda_error(e);
+    attr_bytes[dev & 63] = most;
+  }
+  if (int rc = launch_pdl(lm_head_kernel, dim3(G), dim3(kHeadThreads), smem, st, x, delta, norm_weight, eps,
+                          reinterpret_cast<const __nv_bfloat16*>(table_bf16), V, C / 256, cap, logits_out, cv, ci))
+    return rc;
+  return launch_pdl(lm_head_finish_kernel, dim3(1), dim3(256), 0, st, (const float*)cv, (const int*)ci, G,
+                    reinterpret_cast<long long*>(token), reinterpret_cast<long long*>(pos));
 }
 
 extern "C" int nb_silu_mul(const float* gu, int B, int F, float* hmid, void* stream) {

@@ -333,8 +333,9 @@ class DecodeSession:
     (inference/generate_torch.py:91-97)."""
 
     def __init__(self, model: PackedGPT, batch_size: int = 1, use_graph: bool = True, fused: bool = True,
-                 batch_gemm: bool = False, stream: bool | None = None, tile_gemv: bool | None = None):
+                 batch_gemm: bool = False, stream: bool | None = None, tile_gemv: bool | None = None, hand_head: bool = True):
         self.model, self.B = model, batch_size
+        self.hand_head = hand_head            # False: the LM head of a single sequence stays a library GEMM (comparison)
         self.fused = fused
         # one sequence: the packed linears of the step run on the kernel that reads the tile-major copy of the weights
         # (nb_gemv_stream: teams of warps per row tile, no workspace); tile_gemv=False keeps nb_gemv_fused
@@ -465,6 +466,11 @@ class DecodeSession:
         if pending:
             ops.exchange_gather(self.bd, xch, xch.status)
             delta = self.bd
+        if (self.B == 1 and self.hand_head and getattr(m, "head_ar", None) is None and m.tp_size == 1
+                and ops.lm_head_supported(m.embedding)):
+            # one sequence on one GPU: final add + norm, the tied head over the bf16 table, soft-cap and arg-max in two launches
+            ops.lm_head(xa, delta, m.ln_f, eps, m.embedding, cfg.logit_cap, self.logits, self.token, self.pos)
+            return
         ops.add_rmsnorm(xa, delta, m.ln_f, eps, self.bh)
         if getattr(m, "head_ar", None) is not None and self.B <= m.head_batch:
             if getattr(self, "blog_in", None) is None:

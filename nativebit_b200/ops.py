@@ -424,6 +424,37 @@ def prefill_attention(qkv: torch.Tensor, T: int, cos2, sin2, pos0: int, k_cache,
                                                out_offset, _stream()), "nb_prefill_attention")
 
 
+def lm_head_supported(table: torch.Tensor) -> bool:
+    return table.is_cuda and table.dtype == torch.bfloat16 and table.is_contiguous() and table.shape[1] % 256 == 0 and table.shape[1] <= 3072
+
+
+_head_scratch: dict = {}
+
+
+def lm_head(x: torch.Tensor, delta: torch.Tensor | None, norm_weight: torch.Tensor | None, eps: float, table: torch.Tensor, cap: float,
+            logits_out: torch.Tensor, token: torch.Tensor, pos: torch.Tensor | None = None) -> None:
+    """One sequence: logits_out (V) = cap * tanh(table @ (rmsnorm(x + delta) * norm_weight) / cap), token = arg-max,
+    pos += 1 (nb_lm_head: the bf16 table is read once, final norm, soft-cap and arg-max ride in the same two launches)."""
+    _need_cuda(x, table, logits_out)
+    v, c = table.shape
+    if not lm_head_supported(table) or x.numel() != c or x.dtype != torch.float32 or not x.is_contiguous():
+        raise RuntimeError("lm_head needs a contiguous bf16 (V, C) table with C a multiple of 256 up to 3072 and one fp32 row of C values")
+    if logits_out.dtype != torch.float32 or logits_out.numel() != v or not logits_out.is_contiguous() or token.dtype != torch.int64:
+        raise RuntimeError("lm_head needs a contiguous fp32 output of V values and an int64 token")
+    for t in (delta, norm_weight):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != c or not t.is_contiguous()):
+            raise RuntimeError("lm_head: delta and norm_weight must be contiguous fp32 vectors of C values")
+    key = (x.device.index, torch.cuda.current_stream(x.device).cuda_stream)
+    scratch = _head_scratch.get(key)
+    if scratch is None:
+        scratch = _head_scratch[key] = torch.empty(int(_lib.lib().nb_lm_head_scratch_bytes()), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().nb_lm_head(x.data_ptr(), 0 if delta is None else delta.data_ptr(),
+                                         0 if norm_weight is None else norm_weight.data_ptr(), float(eps), table.data_ptr(), v, c,
+                                         float(cap), logits_out.data_ptr(), token.data_ptr(), 0 if pos is None else pos.data_ptr(),
+                                         scratch.data_ptr(), _stream()), "nb_lm_head")
+
+
 def embed_rows(table: torch.Tensor, token: torch.Tensor, out: torch.Tensor) -> None:
     """out (B, C) fp32 = table[token] for a bf16 (V, C) table and int64 token (B,)."""
     if table.dtype != torch.bfloat16 or token.dtype != torch.int64 or out.dtype != torch.float32:

@@ -171,6 +171,35 @@ def test_prefill_attention_against_torch(built_lib, B, T, H, hd, ctx, pos0, o_st
     assert bool((out[:, :o_off] == 7.0).all()) and bool((out[:, o_off + H * hd:] == 7.0).all())   # nothing outside the heads' columns
 
 
+@pytest.mark.parametrize("V,C", [(32000, 2560), (515, 256), (1000, 3072), (40, 512)])
+def test_lm_head_kernel_against_torch(built_lib, V, C):
+    """Final add + RMSNorm, tied head over the bf16 table, soft-cap, arg-max and position increment in two launches,
+    against the torch expressions of the reference's step in fp64; equal rows: the lowest index wins."""
+    from nativebit_b200 import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(V + C)
+    table = (0.05 * torch.randn(V, C, device=dev, generator=g)).bfloat16()
+    table[V // 2] = table[3]                                        # two equal rows ...
+    x = torch.randn(1, C, device=dev, generator=g)
+    x = x + 10.0 * table[3].float() / table[3].float().norm()       # ... that carry the largest logit by a wide margin
+    delta = 0.1 * torch.randn(1, C, device=dev, generator=g)
+    w = 1.0 + 0.1 * torch.randn(C, device=dev, generator=g)
+    cap = 30.0
+    for d, wt in ((delta, w), (None, w), (None, None)):
+        logits = torch.full((1, V), float("nan"), device=dev)
+        tok = torch.full((1, 1), -1, dtype=torch.long, device=dev)
+        pos = torch.tensor([41], device=dev)
+        ops.lm_head(x, d, wt, 1e-6, table, cap, logits, tok, pos)
+        v = x.double() + (0 if d is None else d.double())
+        h = v if wt is None else v / torch.sqrt((v * v).mean() + 1e-6) * wt.double()
+        ref = cap * torch.tanh((h @ table.double().T) / cap)
+        assert (logits.double() - ref).abs().max() <= 2e-5 * ref.abs().max()
+        assert int(pos.item()) == 42
+        best = logits.max()
+        assert int(tok.item()) == int((logits[0] == best).nonzero()[0].item())       # lowest index among equals
+        assert int(tok.item()) == 3 and bool(logits[0, 3] == logits[0, V // 2])
+
+
 def test_step_ends_match_torch(built_lib):
     """Embedding lookup and soft-cap + argmax kernels against the torch expressions of the reference's step."""
     from nativebit_b200 import ops
