@@ -39,6 +39,33 @@ def test_argument_validation_needs_no_gpu(built_lib):
     assert l.nb_gemv(fake, 2, 1, odd, fake, 1, 3, 128, 16, 128, fake, 2, None, 0, None) == 2     # alignment
 
 
+def test_decode_entry_points_validate_without_a_gpu(built_lib):
+    """Row limits, scratch sizes and argument checks of the decode-step entry points are host arithmetic."""
+    from nativebit_b200 import _lib
+    l = _lib.lib()
+    fake = ctypes.c_void_p(4096)
+    odd = ctypes.c_void_p(4100)
+    # rows one launch of the multi-row matvec takes: what the staged rows leave of the shared memory
+    assert l.nb_gemv_stream_max_rows(3, 2560) == 8 and l.nb_gemv_stream_max_rows(2, 2560) == 8
+    assert l.nb_gemv_stream_max_rows(3, 6912) == 3 and l.nb_gemv_stream_max_rows(3, 128) == 8
+    assert l.nb_gemv_stream_max_rows(3, 100) == 0 and l.nb_gemv_stream_max_rows(5, 2560) == 0
+    assert l.nb_gemv_stream_rows(0, fake, 4, None, None, 0.0, None, fake, 3, 64, 6912, fake, None) == 3      # four rows of 6912
+    assert l.nb_gemv_stream_rows(1, fake, 2, None, None, 0.0, None, fake, 3, 64, 2560, fake, None) == 1      # norm without a weight
+    assert l.nb_gemv_stream_rows(0, odd, 2, None, None, 0.0, None, fake, 3, 64, 2560, fake, None) == 2
+    assert l.nb_gemv_stream(0, fake, 0, None, None, 0.0, None, fake, 3, 64, 7296, fake, 0, None) == 3        # K > 7168
+    # LM head
+    assert l.nb_lm_head_scratch_bytes() == 8192
+    assert l.nb_lm_head(fake, None, None, 0.0, fake, 32000, 2500, 30.0, fake, fake, None, fake, None) == 3    # C % 256
+    assert l.nb_lm_head(fake, None, None, 0.0, fake, 32000, 4096, 30.0, fake, fake, None, fake, None) == 3    # C > 3072
+    assert l.nb_lm_head(fake, None, None, 0.0, fake, 32000, 2560, 0.0, fake, fake, None, fake, None) == 1     # cap must be positive
+    # prompt attention
+    args = (fake, 1, 16, 4, 80, fake, fake, 0, fake, fake, 64, fake, 320, 0, None)
+    assert l.nb_prefill_attention(*args[:4], 130, *args[5:]) == 3                                            # head_dim > 128
+    assert l.nb_prefill_attention(*args[:7], 60, *args[8:]) == 3                                             # pos0 + T > ctx
+    assert l.nb_prefill_attention(*args[:12], 300, *args[13:]) == 3                                          # heads wider than the output row
+    assert l.nb_prefill_attention(None, *args[1:]) == 1
+
+
 def test_workspace_size_is_bounded(built_lib):
     from nativebit_b200 import _lib
     l = _lib.lib()
