@@ -1292,6 +1292,7 @@ struct TileGemvParams {
   int N, bpr, x_dtype, prologue;
   float eps;
   int wpt;                   // warps per team (24, 12, 6 or 3): chosen on the host
+  int wpt_rcp, tpr, rounds;  // 65536 / wpt + 1; 24 / wpt; rounds of the launch
   int swiglu;                // epilogue: rows 0..7 of a tile are gate channels, rows 8..15 the matching up channels
                              // (nb_stream_pack row_mode 1); y receives N / 2 values silu(gate) * up
 };
@@ -1312,13 +1313,15 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
   const int bpr = p.bpr, K = bpr * kBlock;
   // the warps of a CTA form teams of wpt warps; a team shares the k-blocks of one row tile.  Tiles go round the CTAs
   // first and the teams second, so that a last, partly filled round still has work on every SM.
-  const int wpt = p.wpt;
-  const int tpr = kGW / wpt;                              // row tiles per CTA per round
-  const int team = warp / wpt, wi = warp - team * wpt;
-  const int u_lo = bpr * wi / wpt, u_hi = bpr * (wi + 1) / wpt;        // this warp's units of its team's tile
+  // (quotients by the team size as multiply + shift with the host's reciprocal: exact for the few thousand at most
+  // that occur here, and a kernel this short feels five integer divisions at its start)
+  const int wpt = p.wpt, rcp = p.wpt_rcp;
+  const int tpr = p.tpr;                                  // row tiles per CTA per round
+  const int team = (warp * rcp) >> 16, wi = warp - team * wpt;
+  const int u_lo = (bpr * wi * rcp) >> 16, u_hi = (bpr * (wi + 1) * rcp) >> 16;   // this warp's units of its team's tile
   const int n_tiles = (p.N + 15) >> 4;
   const int per_round = (int)gridDim.x * tpr;
-  const int rounds = (n_tiles + per_round - 1) / per_round;
+  const int rounds = p.rounds;
   auto tile_at = [&](int r, int tm) { return r * per_round + tm * (int)gridDim.x + (int)blockIdx.x; };
   auto tile_of = [&](int r) { return tile_at(r, team); };
 
@@ -1509,6 +1512,7 @@ struct TileRowsParams {
   int N, bpr, prologue, m;
   float eps;
   int wpt;                   // warps per team
+  int wpt_rcp, tpr, rounds;  // 65536 / wpt + 1; 24 / wpt; rounds of the launch
   int row_bytes, term_bytes; // a staged row, one fp16 term of it
 };
 
@@ -1537,13 +1541,13 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_rows_kernel(const TileR
   float* s_part = reinterpret_cast<float*>(x_s + m * p.row_bytes);
   uint8_t* x_zero = reinterpret_cast<uint8_t*>(s_part + kRowsPartFloats);
   const int bpr = p.bpr, K = bpr * kBlock;
-  const int wpt = p.wpt;
-  const int tpr = kGW / wpt;
-  const int team = warp / wpt, wi = warp - team * wpt;
-  const int u_lo = bpr * wi / wpt, u_hi = bpr * (wi + 1) / wpt;
+  const int wpt = p.wpt, rcp = p.wpt_rcp;                 // quotients by the team size: multiply + shift, as above
+  const int tpr = p.tpr;
+  const int team = (warp * rcp) >> 16, wi = warp - team * wpt;
+  const int u_lo = (bpr * wi * rcp) >> 16, u_hi = (bpr * (wi + 1) * rcp) >> 16;
   const int n_tiles = (p.N + 15) >> 4;
   const int per_round = (int)gridDim.x * tpr;
-  const int rounds = (n_tiles + per_round - 1) / per_round;
+  const int rounds = p.rounds;
   auto tile_at = [&](int r, int tm) { return r * per_round + tm * (int)gridDim.x + (int)blockIdx.x; };
   auto tile_of = [&](int r) { return tile_at(r, team); };
 
@@ -2000,8 +2004,10 @@ extern "C" int nb_gemv_stream(int prologue, const void* x, int x_dtype, const fl
       const int per_round = G * (kGW / wpt);
       const int rounds = (n_tiles + per_round - 1) / per_round;
       const double cost = rounds * ((p.bpr + wpt - 1) / wpt + 0.67);
-      if (cost < best) { best = cost; p.wpt = wpt; }
+      if (cost < best) { best = cost; p.wpt = wpt; p.rounds = rounds; }
     }
+    p.tpr = kGW / p.wpt;
+    p.wpt_rcp = 65536 / p.wpt + 1;
   }
   const int xs = x_dtype == NB_F32 ? 2 : 1;
   const void* fn = nullptr;
@@ -2072,8 +2078,10 @@ extern "C" int nb_gemv_stream_rows(int prologue, const float* x, int M, const fl
       const int per_round = G * (kGW / wpt);
       const int rounds = (n_tiles + per_round - 1) / per_round;
       const double cost = rounds * ((p.bpr + wpt - 1) / wpt + 0.67);
-      if (cost < best) { best = cost; p.wpt = wpt; }
+      if (cost < best) { best = cost; p.wpt = wpt; p.rounds = rounds; }
     }
+    p.tpr = kGW / p.wpt;
+    p.wpt_rcp = 65536 / p.wpt + 1;
   }
   const void* fn = bits == 3 ? (const void*)tile_gemv_rows_kernel<3> : bits == 2 ? (const void*)tile_gemv_rows_kernel<2>
                                                                                  : (const void*)tile_gemv_rows_kernel<4>;
