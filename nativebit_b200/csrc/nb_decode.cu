@@ -451,17 +451,18 @@ __global__ void __launch_bounds__(kPThreads) prefill_attention_kernel(
 // The tied LM head of one sequence as a matvec over the bf16 embedding table, with the final residual add + RMSNorm
 // in front and the soft-cap + arg-max behind it (inference/generate_torch.py:155-160 and :300-310): logits[v] =
 // cap * tanh(dot(table[v], norm(x + delta) * w) / cap).  HBM-bound (164 MB per token at V = 32000, C = 2560): CTA b
-// owns the table rows [V*b/G, V*(b+1)/G); a warp takes them two at a time through its own double buffer of 16-byte
-// asynchronous copies (the next pair is in flight while this one is multiplied: eight warps keep a pair each, 80 KB
-// per SM, on the way — plain loads were sunk to their uses by the compiler, four in flight per lane) and multiplies
-// them with the activations staged once in shared memory as fp32 (bf16 x fp32 products are exact in fp32).  The
+// owns the table rows [V*b/G, V*(b+1)/G); a warp takes every tenth of them through its own ring of 16-byte
+// asynchronous copies (up to four slots of one row: three rows are in flight while one is multiplied, 150 KB per SM
+// on the way — plain loads were sunk to their uses by the compiler, four in flight per lane) and multiplies them
+// with the activations staged once in shared memory as fp32 (bf16 x fp32 products are exact in fp32).  The
 // norm's scale is one factor on the dot products.  Every CTA leaves its best (value, index) as a candidate;
 // lm_head_finish_kernel picks the token (largest capped logit, lowest index among equals) and advances the
 // position.  C = 256 * NC: a lane owns eight values of every 256.
-constexpr int kHeadThreads = 256;
-constexpr int kHeadWarps = kHeadThreads / 32;
+constexpr int kHeadWarps = 10;
+constexpr int kHeadThreads = kHeadWarps * 32;
 constexpr int kHeadMaxCtas = 1024;
-constexpr int kHeadMaxNC = 12;                               // C <= 3072: the double buffers of eight warps fit shared memory
+constexpr int kHeadMaxNC = 12;                               // C <= 3072
+constexpr size_t kHeadSmemBudget = 216 * 1024;               // activations + the warps' rings
 
 __device__ __forceinline__ void head_cp_async16(void* dst, const void* src) {   // 16 bytes global -> shared, past L1
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -469,9 +470,9 @@ __device__ __forceinline__ void head_cp_async16(void* dst, const void* src) {   
 
 __global__ void __launch_bounds__(kHeadThreads, 1) lm_head_kernel(const float* __restrict__ x, const float* __restrict__ delta,
                                                                   const float* __restrict__ w, float eps,
-                                                                  const __nv_bfloat16* __restrict__ table, int V, int NC, float cap,
-                                                                  float* __restrict__ logits_out, float* __restrict__ cand_val,
-                                                                  int* __restrict__ cand_idx) {
+                                                                  const __nv_bfloat16* __restrict__ table, int V, int NC, int slots,
+                                                                  float cap, float* __restrict__ logits_out,
+                                                                  float* __restrict__ cand_val, int* __restrict__ cand_idx) {
   extern __shared__ __align__(16) uint8_t head_smem[];
   __shared__ float s_red[kHeadWarps];
   __shared__ int s_ci[kHeadWarps];
@@ -479,25 +480,24 @@ __global__ void __launch_bounds__(kHeadThreads, 1) lm_head_kernel(const float* _
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int C = NC * 256, row_bytes = C * 2;
   float* hs = reinterpret_cast<float*>(head_smem);                                   // C floats
-  uint8_t* ring = head_smem + (size_t)C * 4 + (size_t)warp * 4 * row_bytes;         // [2 pairs][2 rows][row_bytes]
+  uint8_t* ring = head_smem + (size_t)C * 4 + (size_t)warp * slots * row_bytes;     // [slots][row_bytes]
   const int G = gridDim.x, b = blockIdx.x;
   const int row0 = (int)((long long)V * b / G), row1 = (int)((long long)V * (b + 1) / G);
-  // pair i of this warp: rows row0 + warp + 16 i and + 8 more
-  auto request = [&](int i) {
-    const int ra = row0 + warp + 2 * kHeadWarps * i;
-    uint8_t* dst = ring + (size_t)(i & 1) * 2 * row_bytes;
-#pragma unroll 1
-    for (int h = 0; h < 2; ++h) {
-      const int r = ra + h * kHeadWarps;
-      if (r < row1) {
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(table) + (size_t)r * row_bytes;
-        for (int j = 0; j < NC; ++j) head_cp_async16(dst + h * row_bytes + (j * 32 + lane) * 16, src + (j * 32 + lane) * 16);
-      }
+  // row i of this warp: row0 + warp + 10 i, copied into ring slot i % slots
+  int rq = 0, rq_slot = 0;
+  auto request = [&]() {
+    const int r = row0 + warp + kHeadWarps * rq;
+    if (r < row1) {
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(table) + (size_t)r * row_bytes;
+      uint8_t* dst = ring + (size_t)rq_slot * row_bytes;
+      for (int j = 0; j < NC; ++j) head_cp_async16(dst + (j * 32 + lane) * 16, src + (j * 32 + lane) * 16);
     }
+    ++rq;
+    if (++rq_slot == slots) rq_slot = 0;
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   asm volatile("griddepcontrol.launch_dependents;");
-  request(0);                                                // the table does not depend on the launch before
+  for (int i = 0; i < slots - 1; ++i) request();             // the table does not depend on the launch before
   asm volatile("griddepcontrol.wait;" ::: "memory");
   float ss = 0.f;
   for (int i4 = tid; i4 < C / 4; i4 += kHeadThreads) {
@@ -525,43 +525,34 @@ __global__ void __launch_bounds__(kHeadThreads, 1) lm_head_kernel(const float* _
   const float scale = s_scale;
   float best = -FLT_MAX;
   int best_i = 0x7fffffff;
-  const int n_pairs = (row1 - row0 - warp + 2 * kHeadWarps - 1) / (2 * kHeadWarps);   // <= 0: no row for this warp
+  int use_slot = 0;
 #pragma unroll 1
-  for (int i = 0; i < n_pairs; ++i) {
-    request(i + 1);                                          // (past the end: an empty group)
-    asm volatile("cp.async.wait_group 1;" ::: "memory");
+  for (int r = row0 + warp; r < row1; r += kHeadWarps) {
+    request();                                               // (past the end: an empty group)
+    if (slots == 4) asm volatile("cp.async.wait_group 3;" ::: "memory");
+    else if (slots == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
+    else asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncwarp();
-    const int ra = row0 + warp + 2 * kHeadWarps * i, rb = ra + kHeadWarps;
-    const uint8_t* pa = ring + (size_t)(i & 1) * 2 * row_bytes;
-    const uint8_t* pb = pa + row_bytes;
-    const bool have_b = rb < row1;
-    float acc_a = 0.f, acc_b = 0.f;
+    const uint8_t* pr = ring + (size_t)use_slot * row_bytes;
+    float acc = 0.f;
 #pragma unroll 2
     for (int j = 0; j < NC; ++j) {
       const float4 x0 = *reinterpret_cast<const float4*>(hs + (j * 32 + lane) * 8);
       const float4 x1 = *reinterpret_cast<const float4*>(hs + (j * 32 + lane) * 8 + 4);
-      const uint4 ta = *reinterpret_cast<const uint4*>(pa + (j * 32 + lane) * 16);
-      const uint4 tb = have_b ? *reinterpret_cast<const uint4*>(pb + (j * 32 + lane) * 16) : make_uint4(0u, 0u, 0u, 0u);
-      const uint32_t wa[4] = {ta.x, ta.y, ta.z, ta.w}, wb[4] = {tb.x, tb.y, tb.z, tb.w};
-      const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {                          // a word holds elements 2e (low half) and 2e + 1
-        acc_a += __uint_as_float(wa[e] << 16) * xs[2 * e] + __uint_as_float(wa[e] & 0xffff0000u) * xs[2 * e + 1];
-        acc_b += __uint_as_float(wb[e] << 16) * xs[2 * e] + __uint_as_float(wb[e] & 0xffff0000u) * xs[2 * e + 1];
-      }
+      const uint4 t = *reinterpret_cast<const uint4*>(pr + (j * 32 + lane) * 16);
+      // a word holds elements 2e (low half) and 2e + 1
+      acc += __uint_as_float(t.x << 16) * x0.x + __uint_as_float(t.x & 0xffff0000u) * x0.y;
+      acc += __uint_as_float(t.y << 16) * x0.z + __uint_as_float(t.y & 0xffff0000u) * x0.w;
+      acc += __uint_as_float(t.z << 16) * x1.x + __uint_as_float(t.z & 0xffff0000u) * x1.y;
+      acc += __uint_as_float(t.w << 16) * x1.z + __uint_as_float(t.w & 0xffff0000u) * x1.w;
     }
-    __syncwarp();                                            // every lane is done with this buffer before it is requested again
-    acc_a = warp_sum(acc_a);
-    acc_b = warp_sum(acc_b);
+    if (++use_slot == slots) use_slot = 0;
+    __syncwarp();                                            // every lane is done with this slot before it is requested again
+    acc = warp_sum(acc);
     if (lane == 0) {
-      const float ya = cap * tanhf(acc_a * scale / cap);
-      logits_out[ra] = ya;
-      if (ya > best || (ya == best && ra < best_i)) { best = ya; best_i = ra; }
-      if (have_b) {
-        const float yb = cap * tanhf(acc_b * scale / cap);
-        logits_out[rb] = yb;
-        if (yb > best || (yb == best && rb < best_i)) { best = yb; best_i = rb; }
-      }
+      const float y = cap * tanhf(acc * scale / cap);
+      logits_out[r] = y;
+      if (y > best || (y == best && r < best_i)) { best = y; best_i = r; }
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -774,17 +765,20 @@ extern "C" int nb_lm_head(const float* x, const float* delta, const float* norm_
   float* cv = reinterpret_cast<float*>(scratch);
   int* ci = reinterpret_cast<int*>(cv + kHeadMaxCtas);
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = (size_t)C * 4 + (size_t)kHeadWarps * 4 * C * 2;
-  static size_t attr_bytes[64] = {};
+  // ring slots per warp: as many rows in flight as the shared memory holds (4 at C = 2560, 3 at C = 3072)
+  const size_t ring_row = (size_t)kHeadWarps * C * 2;
+  const int slots = (int)std::min<size_t>(4, (kHeadSmemBudget - (size_t)C * 4) / ring_row);
+  if (slots < 2) return NB_ERR_SHAPE;
+  const size_t smem = (size_t)C * 4 + (size_t)slots * ring_row;
+  static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (attr_bytes[dev & 63] < smem) {
-    const size_t most = (size_t)kHeadMaxNC * 256 * 4 + (size_t)kHeadWarps * 4 * kHeadMaxNC * 256 * 2;
-    if (cudaError_t e = cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most)) return record_cuda_error(e);
-    attr_bytes[dev & 63] = most;
+  if (!attr_done[dev & 63]) {
+    if (cudaError_t e = cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kHeadSmemBudget)) return record_cuda_error(e);
+    attr_done[dev & 63] = true;
   }
   if (int rc = launch_pdl(lm_head_kernel, dim3(G), dim3(kHeadThreads), smem, st, x, delta, norm_weight, eps,
-                          reinterpret_cast<const __nv_bfloat16*>(table_bf16), V, C / 256, cap, logits_out, cv, ci))
+                          reinterpret_cast<const __nv_bfloat16*>(table_bf16), V, C / 256, slots, cap, logits_out, cv, ci))
     return rc;
   return launch_pdl(lm_head_finish_kernel, dim3(1), dim3(256), 0, st, (const float*)cv, (const int*)ci, G,
                     reinterpret_cast<long long*>(token), reinterpret_cast<long long*>(pos));
