@@ -235,13 +235,22 @@ def run_ours(args):
         layers.append(mods)
         if full:
             full_layers[l] = full
-    x = synthetic.synthetic_activation(m, HIDDEN, 1, dev)
+    # the step's inputs live in one device buffer and its outputs in another, so that the end-to-end leg moves each
+    # with a single copy
     h_full = synthetic.synthetic_activation(m, FFN, 2, dev)
-    h = h_full[:, ch0:ch0 + ch_n].contiguous()
-    y_gate = torch.empty(LAYERS, m, ch_n, dtype=torch.bfloat16, device=dev)
-    y_up = torch.empty_like(y_gate)
+    io_in = torch.empty(m * HIDDEN + m * ch_n, dtype=torch.bfloat16, device=dev)
+    x = io_in[:m * HIDDEN].view(m, HIDDEN)
+    h = io_in[m * HIDDEN:].view(m, ch_n)
+    x.copy_(synthetic.synthetic_activation(m, HIDDEN, 1, dev))
+    h.copy_(h_full[:, ch0:ch0 + ch_n])
     # with more than one rank the partial down outputs are summed in fp32
-    y_down = torch.empty(LAYERS, m, HIDDEN, dtype=torch.bfloat16 if world == 1 else torch.float32, device=dev)
+    down_dtype = torch.bfloat16 if world == 1 else torch.float32
+    gu_bytes = LAYERS * m * ch_n * 2
+    down_bytes = LAYERS * m * HIDDEN * (2 if world == 1 else 4)
+    io_out = torch.empty(2 * gu_bytes + down_bytes, dtype=torch.uint8, device=dev)
+    y_gate = io_out[:gu_bytes].view(torch.bfloat16).view(LAYERS, m, ch_n)
+    y_up = io_out[gu_bytes:2 * gu_bytes].view(torch.bfloat16).view(LAYERS, m, ch_n)
+    y_down = io_out[2 * gu_bytes:].view(down_dtype).view(LAYERS, m, HIDDEN)
     ws = ops.workspace(dev, 8 << 20)
     oneshot = None
     if world > 1 and args.allreduce in ("oneshot", "fused"):
@@ -386,14 +395,11 @@ def run_ours(args):
         full_layers.clear()
 
     # ---- end to end through the public API with host buffers: inputs from pinned host memory, results back to it
-    x_host = x.cpu().pin_memory()
-    h_host = h.cpu().pin_memory()
-    out_host = torch.empty(LAYERS, m, HIDDEN, dtype=y_down.dtype).pin_memory()
-    gu_host = torch.empty(2, LAYERS, m, ch_n, dtype=torch.bfloat16).pin_memory()
+    in_host = io_in.cpu().pin_memory()
+    out_host = torch.empty(io_out.numel(), dtype=torch.uint8).pin_memory()
 
     def e2e_step():
-        x.copy_(x_host, non_blocking=True)
-        h.copy_(h_host, non_blocking=True)
+        io_in.copy_(in_host, non_blocking=True)
         if use_group:
             group_step()
         else:
@@ -403,9 +409,7 @@ def run_ours(args):
                 y_down[l] = mods["down"](h).to(y_down.dtype)
                 if world > 1:
                     all_reduce(y_down[l])
-        gu_host[0].copy_(y_gate, non_blocking=True)
-        gu_host[1].copy_(y_up, non_blocking=True)
-        out_host.copy_(y_down, non_blocking=True)
+        out_host.copy_(io_out, non_blocking=True)
         torch.cuda.current_stream().synchronize()          # the caller reads the results of every step
 
     with torch.cuda.stream(stream):
@@ -414,8 +418,8 @@ def run_ours(args):
     e2e_steps = max(1, min(args.steps, 20))
     ms_e2e = statistics.median(timed_blocks(e2e_step, e2e_steps, 5)) / e2e_steps
     e2e_value = step_bytes / (ms_e2e * 1e-3) / 1e9
-    h2d = x_host.numel() * 2 + h_host.numel() * 2
-    d2h = out_host.numel() * out_host.element_size() + gu_host.numel() * 2
+    h2d = in_host.numel() * 2
+    d2h = out_host.numel()
 
     # ---- roofline of the dominant kernel and the per-kernel figures (1 GPU only)
     roofline, extra = None, {}
