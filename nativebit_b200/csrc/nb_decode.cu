@@ -98,7 +98,8 @@ __global__ void rope_kv_kernel(const float* __restrict__ qkv, const float* __res
                                const long long* __restrict__ pos_ptr, float* __restrict__ k_cache, float* __restrict__ v_cache,
                                float* __restrict__ q_out, int H, int hd, int ctx) {
   const int h = blockIdx.x, b = blockIdx.y;
-  pdl_enter();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;");      // after the wait: the attention kernel behind reads the cache early
   const long long pos = *pos_ptr;
   if (pos < 0 || pos >= ctx) return;
   const float* base = qkv + (size_t)b * 3 * H * hd;
@@ -143,7 +144,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(
   cg::cluster_group cluster = cg::this_cluster();
   const int S = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  pdl_enter();
+  asm volatile("griddepcontrol.launch_dependents;");
+  // The position was written at the end of the step before, and the cache rows below it in earlier steps: neither
+  // depends on the launch before this one, so this CTA's first keys and values are requested BEFORE the dependency
+  // wait and arrive while the qkv matvec drains.  Only the row this step writes (position pos) is fetched after it.
   long long pos = *pos_ptr;
   if (pos < 0) return;  // the same for every CTA of the cluster
   if (pos >= ctx) pos = ctx - 1;
@@ -158,6 +162,25 @@ __global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(
   const size_t head = ((size_t)b * H + h);
   float* kb = k_cache + head * ctx * hd;
   float* vb = v_cache + head * ctx * hd;
+  const int kq = lane >> 2, t = lane & 3;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 kfirst[8], vfirst[8];  // keys and values of iteration 0
+  {
+    const int jl = warp * 8 + kq;
+    const bool ld = jl < cnt && k0 + jl != (int)pos;
+    const float4* krow = reinterpret_cast<const float4*>(kb + (size_t)(k0 + jl) * hd);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) kfirst[i] = (ld && t + 4 * i < hd4) ? krow[t + 4 * i] : zero4;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int ju = warp * 8 + u;
+      vfirst[u] = (ju < cnt && k0 + ju != (int)pos && lane < hd4) ? *reinterpret_cast<const float4*>(vb + (size_t)(k0 + ju) * hd + 4 * lane)
+                                                                   : zero4;
+    }
+  }
+  float c_pre = 0.f, s_pre = 0.f;  // this thread's entry of the rotary tables (head_dim <= 128 < threads per CTA)
+  if (qkv && tid < hd) { c_pre = cos2[pos * hd + tid]; s_pre = sin2[pos * hd + tid]; }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (qkv) {
     const float* base = qkv + (size_t)b * 3 * H * hd;
     const float* qh = base + h * hd;
@@ -165,7 +188,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(
     const float* vh = base + 2 * H * hd + h * hd;
     const bool owner = pos >= k0 && pos < k0 + cnt;
     for (int i = tid; i < hd; i += blockDim.x) {
-      const float c = cos2[pos * hd + i], s = sin2[pos * hd + i];
+      const float c = c_pre, s = s_pre;
       const int j = i ^ 1;
       const float sign = (i & 1) ? 1.f : -1.f;   // rot = (-x2, x1) on interleaved pairs
       qs[i] = (qh[i] * c + sign * qh[j] * s) * rsqrtf((float)hd);
@@ -180,14 +203,19 @@ __global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(
   __syncthreads();  // also orders the cache row written above before the reads below (same CTA)
 
   const int iters = (cnt + kAttnKeysPerIter - 1) / kAttnKeysPerIter;
-  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  float4 vfirst[8];  // values of iteration 0, in flight while the scores are computed
+  {  // the row written in this step (by this CTA above, or by the launch before): now it can be read
+    const int jl = warp * 8 + kq;
+    if (jl < cnt && k0 + jl == (int)pos) {
+      const float4* krow = reinterpret_cast<const float4*>(kb + (size_t)pos * hd);
 #pragma unroll
-  for (int u = 0; u < 8; ++u) {
-    const int jl = warp * 8 + u;
-    vfirst[u] = (jl < cnt && lane < hd4) ? *reinterpret_cast<const float4*>(vb + (size_t)(k0 + jl) * hd + 4 * lane) : zero4;
+      for (int i = 0; i < 8; ++i) kfirst[i] = (t + 4 * i < hd4) ? krow[t + 4 * i] : zero4;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int ju = warp * 8 + u;
+      if (ju < cnt && k0 + ju == (int)pos && lane < hd4) vfirst[u] = *reinterpret_cast<const float4*>(vb + (size_t)pos * hd + 4 * lane);
+    }
   }
-  const int kq = lane >> 2, t = lane & 3;
   float mx = -FLT_MAX;
   for (int it = 0; it < iters; ++it) {
     const int jl = (it * kAttnWarps + warp) * 8 + kq;
@@ -196,7 +224,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) decode_attention_kernel(
       const float4* krow = reinterpret_cast<const float4*>(kb + (size_t)(k0 + jl) * hd);
       float4 kv[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) kv[i] = (t + 4 * i < hd4) ? krow[t + 4 * i] : zero4;
+      for (int i = 0; i < 8; ++i) kv[i] = it == 0 ? kfirst[i] : ((t + 4 * i < hd4) ? krow[t + 4 * i] : zero4);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         if (t + 4 * i < hd4) {

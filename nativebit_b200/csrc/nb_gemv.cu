@@ -279,7 +279,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
             __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.codebook) + (row * p.bpr + kb0) * cb_blk) + j);
     }
   }
-  asm volatile("griddepcontrol.launch_dependents;");
   NB_TRACE_MARK(1);
 
   if (tid < kBlock) {
@@ -287,6 +286,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 2) gemv_kernel(const GemvParam
     dst_off[pos] = (uint16_t)((slot >> 2) * (XR * 4) + (slot & 3));
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // dependents are released only now: a launch behind this one may read, before its own wait, what was written two
+  // or more launches back (the attention kernel prefetches cached keys and values that way)
+  asm volatile("griddepcontrol.launch_dependents;");
   NB_TRACE_MARK(2);
   if (PUSH) {
     // peer pointers and the sequence number of this push: requested now, used after the units, so

@@ -1344,27 +1344,34 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
   };
 #pragma unroll 1
   for (int i = 0; i < D - 2; ++i) request_one();
-  asm volatile("griddepcontrol.launch_dependents;");
+  // the RMSNorm weight does not depend on the launch before either: a third of the bytes this CTA stages
+  constexpr int kIt = (kMaxKBlocks * kBlock / 4 + kThreads - 1) / kThreads;      // K <= 7168: at most three float4 per thread
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 vw[kIt];
+#pragma unroll
+  for (int j = 0; j < kIt; ++j) {
+    const int i4 = tid + j * kThreads;
+    vw[j] = (p.prologue == 1 && i4 < K / 4) ? __ldg(reinterpret_cast<const float4*>(p.weight) + i4) : zero4;
+  }
+  // (the dependents are released only after this kernel's own dependency is met: a launch behind this one may then
+  // read, before ITS wait, anything written two or more launches back — the attention kernel does, see nb_decode.cu)
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;");
 
   // ---- the activations (and the element-wise step in front of this linear)
   if (p.prologue == 1) {
     const float4* xr = reinterpret_cast<const float4*>(p.x);
     const float4* dr = reinterpret_cast<const float4*>(p.delta);
-    const float4* w4 = reinterpret_cast<const float4*>(p.weight);
     const bool writer = blockIdx.x == 0 && p.x_out != nullptr;
     float ss = 0.f;
-    // K <= 7168: at most three float4 per thread; all loads are issued before the first use (one memory round trip)
-    constexpr int kIt = (kMaxKBlocks * kBlock / 4 + kThreads - 1) / kThreads;
-    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 vx[kIt], vd[kIt], vw[kIt];
+    // all loads are issued before the first use (one memory round trip)
+    float4 vx[kIt], vd[kIt];
 #pragma unroll
     for (int j = 0; j < kIt; ++j) {
       const int i4 = tid + j * kThreads;
       const bool in = i4 < K / 4;
       vx[j] = in ? __ldcg(xr + i4) : zero4;
       vd[j] = (in && dr) ? __ldcg(dr + i4) : zero4;
-      vw[j] = in ? __ldg(w4 + i4) : zero4;
     }
 #pragma unroll
     for (int j = 0; j < kIt; ++j) {
@@ -1388,8 +1395,6 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
   } else if (p.prologue == 2) {
     const float4* g4 = reinterpret_cast<const float4*>(p.x);
     const float4* u4 = g4 + K / 4;
-    constexpr int kIt = (kMaxKBlocks * kBlock / 4 + kThreads - 1) / kThreads;
-    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 vg[kIt], vu[kIt];
 #pragma unroll
     for (int j = 0; j < kIt; ++j) {      // all loads first: one memory round trip
@@ -1568,8 +1573,10 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_rows_kernel(const TileR
   };
 #pragma unroll 1
   for (int i = 0; i < D - 2; ++i) request_one();
-  asm volatile("griddepcontrol.launch_dependents;");
+  // (the dependents are released only after this kernel's own dependency is met: a launch behind this one may then
+  // read, before ITS wait, anything written two or more launches back — the attention kernel does, see nb_decode.cu)
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;");
 
   // ---- the activation rows (and the element-wise step in front of this linear)
   {
