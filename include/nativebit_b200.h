@@ -390,8 +390,11 @@ int nb_group_run(const void* plan_device, const void* plan_host, void* stream);
  * act = silu(gate) * up.  One CTA per SM; the k-blocks of a 16-row tile are shared by a team of warps of one CTA, so
  * there is no workspace and nothing to wait for but the launch's own copies; weights are requested before the
  * launch waits for the one before it (programmatic dependent launch).  K % 128 == 0, K <= 7168; 16-byte aligned
- * pointers.  swiglu != 0: W is a fused [gate | up] matrix packed with nb_stream_pack row_mode 1 (N % 16 == 0) and y
- * receives the N / 2 values silu(gate_c) * up_c (the SwiGLU of generate_torch.py:116-117 in the epilogue).
+ * pointers.  swiglu is a set of flags.  Bit 0: W is a fused [gate | up] matrix packed with nb_stream_pack row_mode 1
+ * (N % 16 == 0) and y receives the N / 2 values silu(gate_c) * up_c (the SwiGLU of generate_torch.py:116-117 in the
+ * epilogue).  Bit 1: fp32 activations enter the tensor cores rounded to ONE fp16 term (11 significant bits) instead of
+ * two (22 bits): half the tensor-core instructions, an error of a few 1e-4 of max |y| per matvec — measured 4e-3 of
+ * max |logit| at the end of the 26-layer decoder, above its 2e-3 gate, so it is off in this package's decode session.
  * Bit-identical from run to run. */
 int nb_gemv_stream(int prologue, const void* x, int x_dtype, const float* delta, const float* norm_weight, float eps,
                    float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, int swiglu, void* stream);

@@ -1381,7 +1381,7 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
         v.x += vd[j].x; v.y += vd[j].y; v.z += vd[j].z; v.w += vd[j].w;
         if (writer) reinterpret_cast<float4*>(p.x_out)[i4] = v;
         ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        stage4<2>(x_s, i4, v.x * vw[j].x, v.y * vw[j].y, v.z * vw[j].z, v.w * vw[j].w);
+        stage4<XS>(x_s, i4, v.x * vw[j].x, v.y * vw[j].y, v.z * vw[j].z, v.w * vw[j].w);
       }
     }
     ss = warp_sum_f(ss);                                   // the warps' sums, then in warp order: the same bits in every CTA
@@ -1407,7 +1407,7 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
       const int i4 = tid + j * kThreads;
       const float4 g = vg[j], u = vu[j];
       if (i4 < K / 4)
-        stage4<2>(x_s, i4, g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y, g.z / (1.f + __expf(-g.z)) * u.z,
+        stage4<XS>(x_s, i4, g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y, g.z / (1.f + __expf(-g.z)) * u.z,
                   g.w / (1.f + __expf(-g.w)) * u.w);
     }
     if (tid == 0) s_scale = 1.f;
@@ -1991,7 +1991,8 @@ extern "C" int nb_gemv_stream(int prologue, const void* x, int x_dtype, const fl
                               float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, int swiglu, void* stream) {
   if (!x || !w_stream || !y || N < 1) return NB_ERR_ARG;
   if (prologue < 0 || prologue > 2) return NB_ERR_ARG;
-  if (swiglu && N % 16 != 0) return NB_ERR_SHAPE;
+  if (swiglu < 0 || swiglu > 3) return NB_ERR_ARG;
+  if ((swiglu & 1) && N % 16 != 0) return NB_ERR_SHAPE;
   if (bits != 2 && bits != 3 && bits != 4) return NB_ERR_SHAPE;
   if (K < kBlock || K % kBlock != 0 || K / kBlock > kMaxKBlocks) return NB_ERR_SHAPE;
   if (prologue == 1 && !norm_weight) return NB_ERR_ARG;
@@ -2003,7 +2004,7 @@ extern "C" int nb_gemv_stream(int prologue, const void* x, int x_dtype, const fl
   if (int rc = check_device()) return rc;
   TileGemvParams p{};
   p.w = w_stream; p.x = x; p.delta = delta; p.weight = norm_weight; p.x_out = x_out; p.y = y;
-  p.N = N; p.bpr = K / kBlock; p.x_dtype = x_dtype; p.prologue = prologue; p.eps = eps; p.swiglu = swiglu ? 1 : 0;
+  p.N = N; p.bpr = K / kBlock; p.x_dtype = x_dtype; p.prologue = prologue; p.eps = eps; p.swiglu = (swiglu & 1) ? 1 : 0;
   {  // team size: rounds x (units per warp + the round's barrier and sum, about two thirds of a unit)
     const int G = nb_stream_ctas(), n_tiles = (N + 15) / 16;
     double best = 1e30;
@@ -2016,7 +2017,7 @@ extern "C" int nb_gemv_stream(int prologue, const void* x, int x_dtype, const fl
     p.tpr = kGW / p.wpt;
     p.wpt_rcp = 65536 / p.wpt + 1;
   }
-  const int xs = x_dtype == NB_F32 ? 2 : 1;
+  const int xs = (x_dtype == NB_F32 && !(swiglu & 2)) ? 2 : 1;      // flag 2: fp32 activations rounded to ONE fp16 term
   const void* fn = nullptr;
   if (bits == 3) fn = xs == 2 ? (const void*)tile_gemv_kernel<3, 2> : (const void*)tile_gemv_kernel<3, 1>;
   else if (bits == 2) fn = xs == 2 ? (const void*)tile_gemv_kernel<2, 2> : (const void*)tile_gemv_kernel<2, 1>;
