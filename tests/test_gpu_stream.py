@@ -291,6 +291,12 @@ def test_chain_gemv_over_the_stream_layout(built_lib, bits, n, k):
                         norm_weight=_cu(g, dev), eps=1e-6, x_out=x_out)
         torch.cuda.synchronize()
         check(y, act)
+        # the one-term option: activations rounded to fp16 once (11 bits), the same sums otherwise
+        y1 = torch.full((n,), float("nan"), device=dev)
+        ops.gemv_stream(ops.PRO_ADD_RMSNORM, _cu(h, dev), w, bits, n, k, y1, delta=None if delta is None else _cu(delta, dev),
+                        norm_weight=_cu(g, dev), eps=1e-6, single_term=True)
+        ref1 = o.packed_linear_forward(act.astype(np.float16).astype(np.float64).reshape(1, k), packed, cbf, n, k, bits, acc_dtype=np.float64)[0]
+        assert np.abs(y1.double().cpu().numpy() - ref1).max() <= 1e-4 * np.abs(ref1).max()
         assert np.array_equal(x_out.cpu().numpy(), (h + delta).astype(np.float32) if delta is not None else h)
     # SwiGLU
     gu = rng.standard_normal(2 * k).astype(np.float32)
