@@ -402,10 +402,11 @@ int nb_gemv_stream(int prologue, const void* x, int x_dtype, const float* delta,
  * inference/generate_torch.py:307-311 with a batch): ONE pass over the weights, the rows ride in the columns of the
  * tensor-core instructions that a single row leaves empty.  x (M, K) — (M, 2K) rows [gate | up] with NB_PRO_SILU_MUL —,
  * delta and x_out (M, K), y (M, N) fp32, all row-major and 16-byte aligned.  The row limit is what the staged rows
- * leave of the shared memory (8 rows at K = 2560, 3 at K = 6912); a caller with more rows splits them over calls. */
+ * leave of the shared memory (8 rows at K = 2560, 3 at K = 6912); a caller with more rows splits them over calls.
+ * swiglu = 1: the SwiGLU epilogue of nb_gemv_stream (row_mode 1 copy of [gate | up]), y is (M, N / 2). */
 int nb_gemv_stream_max_rows(int bits, int K);
 int nb_gemv_stream_rows(int prologue, const float* x, int M, const float* delta, const float* norm_weight, float eps,
-                        float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, void* stream);
+                        float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, int swiglu, void* stream);
 
 /* Launch geometry nb_gemv will use for a shape on the current device (no launch; works without
  * a GPU, assuming 148 SMs): out6 = {grid.x, grid.y (k partitions), threads per CTA, dynamic

@@ -82,7 +82,7 @@ _SIGNATURES = {
                                   _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p]),
     "nb_gemv_stream_max_rows": (_c.c_int, [_c.c_int, _c.c_int]),
     "nb_gemv_stream_rows": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_float, _c.c_void_p, _c.c_void_p,
-                                       _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
+                                       _c.c_int, _c.c_int, _c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p]),
     "nb_group_plan_bytes": (_c.c_size_t, [_c.c_void_p, _c.c_int]),
     "nb_group_max_items": (_c.c_int, []),
     "nb_group_build": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p, _c.c_size_t]),

@@ -1519,6 +1519,8 @@ struct TileRowsParams {
   int wpt;                   // warps per team
   int wpt_rcp, tpr, rounds;  // 65536 / wpt + 1; 24 / wpt; rounds of the launch
   int row_bytes, term_bytes; // a staged row, one fp16 term of it
+  int swiglu;                // epilogue: rows 0..7 of a tile are gate channels, rows 8..15 the matching up channels
+                             // (nb_stream_pack row_mode 1); y is (m, N / 2) = silu(gate) * up
 };
 
 __device__ __forceinline__ void stage4_row(uint8_t* row_s, int term_bytes, int i4, float u0, float u1, float u2, float u3) {
@@ -1691,6 +1693,28 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_rows_kernel(const TileR
     __syncthreads();                                       // one barrier per round: the buffers alternate
     const float* pr = s_part + (r & 1) * (kGW * 128);
     const int wpr = kGW / m;
+    if (p.swiglu) {
+      for (int idx = tid; idx < tpr * 8 * m; idx += kThreads) {
+        const int tm = idx / (8 * m), rem = idx - tm * 8 * m;
+        const int col = rem >> 3, ch = rem & 7;
+        const int t_out = tile_at(r, tm);
+        float gate = 0.f, up = 0.f;
+        for (int j = 0; j < wpt; ++j) {                                          // the team's warps in k order
+          gate += pr[(tm * wpt + j) * 128 + col * 16 + ch];
+          up += pr[(tm * wpt + j) * 128 + col * 16 + 8 + ch];
+        }
+        float scale = 1.f;
+        if (p.prologue == 1) {
+          float tot = 0.f;
+          for (int q = 0; q < wpr; ++q) tot += s_ss[col * wpr + q];
+          scale = 1.0f / sqrtf(tot / (float)K + p.eps);
+        }
+        gate *= scale; up *= scale;
+        const int c_out = t_out * 8 + ch;
+        if (t_out < n_tiles && c_out < (p.N >> 1)) p.y[(size_t)col * (p.N >> 1) + c_out] = gate / (1.f + __expf(-gate)) * up;
+      }
+      continue;
+    }
     for (int idx = tid; idx < tpr * 16 * m; idx += kThreads) {
       const int tm = idx / (16 * m), rem = idx - tm * 16 * m;
       const int col = rem >> 4, row = rem & 15;
@@ -2063,9 +2087,10 @@ extern "C" int nb_gemv_stream_max_rows(int bits, int K) {
 }
 
 extern "C" int nb_gemv_stream_rows(int prologue, const float* x, int M, const float* delta, const float* norm_weight, float eps,
-                                   float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, void* stream) {
+                                   float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, int swiglu, void* stream) {
   if (!x || !w_stream || !y || N < 1 || M < 1) return NB_ERR_ARG;
-  if (prologue < 0 || prologue > 2) return NB_ERR_ARG;
+  if (prologue < 0 || prologue > 2 || swiglu < 0 || swiglu > 1) return NB_ERR_ARG;
+  if (swiglu && N % 16 != 0) return NB_ERR_SHAPE;
   if (bits != 2 && bits != 3 && bits != 4) return NB_ERR_SHAPE;
   if (K < kBlock || K % kBlock != 0 || K / kBlock > kMaxKBlocks) return NB_ERR_SHAPE;
   if (M > nb_gemv_stream_max_rows(bits, K)) return NB_ERR_SHAPE;
@@ -2076,7 +2101,7 @@ extern "C" int nb_gemv_stream_rows(int prologue, const float* x, int M, const fl
   if (int rc = check_device()) return rc;
   TileRowsParams p{};
   p.w = w_stream; p.x = x; p.delta = delta; p.weight = norm_weight; p.x_out = x_out; p.y = y;
-  p.N = N; p.bpr = K / kBlock; p.prologue = prologue; p.m = M; p.eps = eps;
+  p.N = N; p.bpr = K / kBlock; p.prologue = prologue; p.m = M; p.eps = eps; p.swiglu = swiglu;
   p.term_bytes = p.bpr * 4 * kXSegBytes;
   p.row_bytes = 2 * p.term_bytes + 16;
   {

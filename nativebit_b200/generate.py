@@ -428,8 +428,8 @@ class DecodeSession:
                                 single_term=self.single_term)
                 xa, xb = xb, xa
             elif self.tile_rows:
-                ops.gemv_stream_rows(ops.PRO_ADD_RMSNORM, xa, lin.stream_weight(), lin.bits, lin.out_features, lin.in_features,
-                                     out, delta=delta, norm_weight=w, eps=eps, x_out=xb)
+                ops.gemv_stream_rows(ops.PRO_ADD_RMSNORM, xa, lin.stream_weight(1 if swiglu else 0), lin.bits, lin.out_features,
+                                     lin.in_features, out, delta=delta, norm_weight=w, eps=eps, x_out=xb, swiglu=swiglu)
                 xa, xb = xb, xa
             elif fold:
                 ops.gemv_fused(ops.PRO_ADD_RMSNORM, xa, *args, out, delta=delta, norm_weight=w, eps=eps, x_out=xb)
@@ -467,8 +467,8 @@ class DecodeSession:
             delta = row_parallel(blk.out_proj, ops.PRO_NONE, self.batt, self.bo)
             # SwiGLU in gate_up's epilogue (nb_gemv_stream's swiglu flag over a row_mode-1 copy): the 2F intermediate is
             # never written and down stages half the bytes (0.897 -> 0.875 ms per token)
-            if self.tile_gemv and self.swiglu_epilogue and xch is None:
-                norm_linear(blk.gate_up, delta, blk.ln2, self.bhm[0], swiglu=True)
+            if (self.tile_gemv or self.tile_rows) and self.swiglu_epilogue and xch is None:
+                norm_linear(blk.gate_up, delta, blk.ln2, self.bhm[0] if self.tile_gemv else self.bhm, swiglu=True)
                 delta = row_parallel(blk.down, ops.PRO_NONE, self.bhm, self.bd)
                 continue
             norm_linear(blk.gate_up, delta, blk.ln2, self.bgu)

@@ -236,15 +236,16 @@ def gemv_stream_max_rows(bits: int, k: int) -> int:
 
 def gemv_stream_rows(prologue: int, x: torch.Tensor, w_stream: torch.Tensor, bits: int, n: int, k: int, out: torch.Tensor,
                      delta: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None, eps: float = 0.0,
-                     x_out: torch.Tensor | None = None) -> torch.Tensor:
+                     x_out: torch.Tensor | None = None, swiglu: bool = False) -> torch.Tensor:
     """gemv_stream for a few fp32 activation rows in one pass over the weights (nb_gemv_stream_rows): out (m, n) fp32 =
     act(x) W^T for x (m, k) — (m, 2k) with PRO_SILU_MUL.  More rows than gemv_stream_max_rows(bits, k) are split over
-    several launches here."""
+    several launches here.  swiglu: W is a [gate | up] matrix packed with row_mode 1 and out is (m, n / 2)."""
     _need_cuda(x, w_stream, out)
     cols = 2 * k if prologue == PRO_SILU_MUL else k
+    n_out = n // 2 if swiglu else n
     if (x.dim() != 2 or x.shape[1] != cols or x.dtype != torch.float32 or not x.is_contiguous() or out.dtype != torch.float32
-            or out.shape != (x.shape[0], n) or not out.is_contiguous()):
-        raise RuntimeError(f"gemv_stream_rows needs contiguous fp32 x (m, {cols}) and out (m, {n})")
+            or out.shape != (x.shape[0], n_out) or not out.is_contiguous()):
+        raise RuntimeError(f"gemv_stream_rows needs contiguous fp32 x (m, {cols}) and out (m, {n_out})")
     for t in (delta, x_out):
         if t is not None and (t.dtype != torch.float32 or t.shape != (x.shape[0], k) or not t.is_contiguous()):
             raise RuntimeError(f"gemv_stream_rows: delta and x_out must be contiguous fp32 (m, {k})")
@@ -258,7 +259,7 @@ def gemv_stream_rows(prologue: int, x: torch.Tensor, w_stream: torch.Tensor, bit
                                                       0 if delta is None else delta[r0:r1].data_ptr(),
                                                       0 if norm_weight is None else norm_weight.data_ptr(), float(eps),
                                                       0 if x_out is None else x_out[r0:r1].data_ptr(), w_stream.data_ptr(), bits, n, k,
-                                                      out[r0:r1].data_ptr(), _stream()), "nb_gemv_stream_rows")
+                                                      out[r0:r1].data_ptr(), 1 if swiglu else 0, _stream()), "nb_gemv_stream_rows")
     return out
 
 

@@ -49,9 +49,9 @@ def test_decode_entry_points_validate_without_a_gpu(built_lib):
     assert l.nb_gemv_stream_max_rows(3, 2560) == 8 and l.nb_gemv_stream_max_rows(2, 2560) == 8
     assert l.nb_gemv_stream_max_rows(3, 6912) == 3 and l.nb_gemv_stream_max_rows(3, 128) == 8
     assert l.nb_gemv_stream_max_rows(3, 100) == 0 and l.nb_gemv_stream_max_rows(5, 2560) == 0
-    assert l.nb_gemv_stream_rows(0, fake, 4, None, None, 0.0, None, fake, 3, 64, 6912, fake, None) == 3      # four rows of 6912
-    assert l.nb_gemv_stream_rows(1, fake, 2, None, None, 0.0, None, fake, 3, 64, 2560, fake, None) == 1      # norm without a weight
-    assert l.nb_gemv_stream_rows(0, odd, 2, None, None, 0.0, None, fake, 3, 64, 2560, fake, None) == 2
+    assert l.nb_gemv_stream_rows(0, fake, 4, None, None, 0.0, None, fake, 3, 64, 6912, fake, 0, None) == 3      # four rows of 6912
+    assert l.nb_gemv_stream_rows(1, fake, 2, None, None, 0.0, None, fake, 3, 64, 2560, fake, 0, None) == 1      # norm without a weight
+    assert l.nb_gemv_stream_rows(0, odd, 2, None, None, 0.0, None, fake, 3, 64, 2560, fake, 0, None) == 2
     assert l.nb_gemv_stream(0, fake, 0, None, None, 0.0, None, fake, 3, 64, 7296, fake, 0, None) == 3        # K > 7168
     # LM head
     assert l.nb_lm_head_scratch_bytes() == 8192

@@ -429,3 +429,18 @@ def test_chain_gemv_swiglu_epilogue(built_lib, bits, f, k):
                     x_out=torch.empty(k, device=dev), swiglu=True)
     torch.cuda.synchronize()
     assert np.abs(y.double().cpu().numpy() - ref).max() <= 5e-5 * np.abs(ref).max()
+    # the same epilogue for five rows in one pass over the weights
+    m = 5
+    hm = rng.standard_normal((m, k)).astype(np.float32)
+    dm = rng.standard_normal((m, k)).astype(np.float32)
+    vm = hm.astype(np.float64) + dm.astype(np.float64)
+    actm = vm / np.sqrt((vm * vm).mean(axis=1, keepdims=True) + 1e-6) * g
+    gum = o.packed_linear_forward(actm, packed, cb.astype(np.float32), n, k, bits, acc_dtype=np.float64)
+    refm = gum[:, :f] / (1 + np.exp(-gum[:, :f])) * gum[:, f:]
+    ym = torch.full((m, f), float("nan"), device=dev)
+    ops.gemv_stream_rows(ops.PRO_ADD_RMSNORM, _cu(hm, dev), w, bits, n, k, ym, delta=_cu(dm, dev), norm_weight=_cu(g, dev), eps=1e-6,
+                         x_out=torch.empty(m, k, device=dev), swiglu=True)
+    torch.cuda.synchronize()
+    got = ym.double().cpu().numpy()
+    for r in range(m):
+        assert np.abs(got[r] - refm[r]).max() <= 5e-5 * np.abs(refm[r]).max(), r
