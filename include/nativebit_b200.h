@@ -163,7 +163,8 @@ int nb_gemm_bf16(const void* x, const void* w, int M, int N, int K, void* y, int
  *   Launched with programmatic stream serialization, the attention kernels read *pos, the rotary entries and the
  *   cache rows below *pos BEFORE their dependency wait: these must have been written at least two launches earlier
  *   (a decode loop writes them in the step before), and the launch directly before must not release its dependents
- *   ahead of its own dependency wait (no kernel of this library does; a launch without the attribute never does).
+ *   ahead of its own dependency wait (the matvec, norm, rope and glue kernels of this library release after it; a
+ *   launch without the attribute never releases early).
  * nb_silu_mul: hmid (B, F) = silu(gu[:, :F]) * gu[:, F:]. */
 int nb_add_rmsnorm(float* x, const float* delta, const float* w, float eps, float* out, int B, int C, void* stream);
 int nb_rope_kv_write(const float* qkv, int B, int H, int hd, const float* cos2, const float* sin2, const int64_t* pos,

@@ -19,11 +19,12 @@ namespace nb {
 namespace cg = cooperative_groups;
 
 // Every kernel of the decode chain is launched with programmatic stream serialization: it may be
-// scheduled while its predecessor still runs, lets its own successor do the same, and waits for
-// the predecessor's results before it touches memory.
+// scheduled while its predecessor still runs and waits for the predecessor's results before it
+// touches memory.  It releases its own successor only AFTER that wait: a successor may then read,
+// ahead of its own wait, anything written two or more launches back (the attention kernel does).
 __device__ __forceinline__ void pdl_enter() {
-  asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;");
 }
 
 template <typename... KArgs, typename... Args>
@@ -98,8 +99,7 @@ __global__ void rope_kv_kernel(const float* __restrict__ qkv, const float* __res
                                const long long* __restrict__ pos_ptr, float* __restrict__ k_cache, float* __restrict__ v_cache,
                                float* __restrict__ q_out, int H, int hd, int ctx) {
   const int h = blockIdx.x, b = blockIdx.y;
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;");      // after the wait: the attention kernel behind reads the cache early
+  pdl_enter();                                             // releases after the wait: the attention kernel behind reads the cache early
   const long long pos = *pos_ptr;
   if (pos < 0 || pos >= ctx) return;
   const float* base = qkv + (size_t)b * 3 * H * hd;

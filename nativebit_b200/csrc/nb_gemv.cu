@@ -923,8 +923,8 @@ constexpr uint32_t kXchgSpinLimit = 1u << 23;  // several seconds: a probe is an
 // Sum over the ranks of the vectors pushed last -> out (count floats); grid of a few CTAs, each waits itself.
 __global__ void __launch_bounds__(256) exchange_gather_kernel(float* __restrict__ out, int count, const uint8_t* self, int world,
                                                               int max_count, uint32_t spin_limit, int* status) {
-  asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;");
   const int tid = threadIdx.x;
   const uint32_t seq = __ldcg(xchg_seq(self, world, max_count));
   const int set = seq & 1;
