@@ -400,7 +400,8 @@ int nb_group_run(const void* plan_device, const void* plan_host, void* stream);
  * epilogue).  Bit 1: fp32 activations enter the tensor cores rounded to ONE fp16 term (11 significant bits) instead of
  * two (22 bits): half the tensor-core instructions, an error of a few 1e-4 of max |y| per matvec — measured 4e-3 of
  * max |logit| at the end of the 26-layer decoder, above its 2e-3 gate, so it is off in this package's decode session.
- * Bit-identical from run to run. */
+ * Bit 2 (not with bit 0): y += W . act(x) — the residual update of a decoder block (generate_torch.py:114, :117) inside the
+ * matvec that produces it; every output is read and written by the same thread.  Bit-identical from run to run. */
 int nb_gemv_stream(int prologue, const void* x, int x_dtype, const float* delta, const float* norm_weight, float eps,
                    float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, int swiglu, void* stream);
 /* nb_gemv_stream for M = 1 .. nb_gemv_stream_max_rows(bits, K) fp32 activation rows (a decode step of a few sequences,

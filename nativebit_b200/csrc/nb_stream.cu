@@ -1295,6 +1295,7 @@ struct TileGemvParams {
   int wpt_rcp, tpr, rounds;  // 65536 / wpt + 1; 24 / wpt; rounds of the launch
   int swiglu;                // epilogue: rows 0..7 of a tile are gate channels, rows 8..15 the matching up channels
                              // (nb_stream_pack row_mode 1); y receives N / 2 values silu(gate) * up
+  int accumulate;            // y += W act(x): the residual update of a block in the matvec that produces it
 };
 
 template <int BITS, int XS>
@@ -1444,6 +1445,12 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
 #pragma unroll 1
   for (int r = 0; r < rounds; ++r) {
     const int tile = tile_of(r);
+    // accumulate flag: the output's old value (the residual stream) is requested now and added behind the round's barrier
+    float res = 0.f;
+    if (p.accumulate && tid < tpr * 16) {
+      const int n_res = tile_at(r, tid >> 4) * 16 + (tid & 15);
+      if (n_res < p.N) res = __ldcg(p.y + n_res);
+    }
     float c[2][4];
 #pragma unroll
     for (int h = 0; h < 2; ++h)
@@ -1486,7 +1493,7 @@ __global__ void __launch_bounds__(kGW * 32, 1) tile_gemv_kernel(const TileGemvPa
       float acc = 0.f;
       for (int j = 0; j < wpt; ++j) acc += part[(tm * wpt + j) * 16 + row];     // the team's warps in k order
       const int n = t_out * 16 + row;
-      if (t_out < n_tiles && n < p.N) p.y[n] = acc * scale;
+      if (t_out < n_tiles && n < p.N) p.y[n] = acc * scale + res;
     }
   }
   cp_async_wait<0>();
@@ -2015,7 +2022,7 @@ extern "C" int nb_gemv_stream(int prologue, const void* x, int x_dtype, const fl
                               float* x_out, const uint8_t* w_stream, int bits, int N, int K, float* y, int swiglu, void* stream) {
   if (!x || !w_stream || !y || N < 1) return NB_ERR_ARG;
   if (prologue < 0 || prologue > 2) return NB_ERR_ARG;
-  if (swiglu < 0 || swiglu > 3) return NB_ERR_ARG;
+  if (swiglu < 0 || swiglu > 7 || ((swiglu & 1) && (swiglu & 4))) return NB_ERR_ARG;
   if ((swiglu & 1) && N % 16 != 0) return NB_ERR_SHAPE;
   if (bits != 2 && bits != 3 && bits != 4) return NB_ERR_SHAPE;
   if (K < kBlock || K % kBlock != 0 || K / kBlock > kMaxKBlocks) return NB_ERR_SHAPE;
@@ -2029,6 +2036,7 @@ extern "C" int nb_gemv_stream(int prologue, const void* x, int x_dtype, const fl
   TileGemvParams p{};
   p.w = w_stream; p.x = x; p.delta = delta; p.weight = norm_weight; p.x_out = x_out; p.y = y;
   p.N = N; p.bpr = K / kBlock; p.x_dtype = x_dtype; p.prologue = prologue; p.eps = eps; p.swiglu = (swiglu & 1) ? 1 : 0;
+  p.accumulate = (swiglu & 4) ? 1 : 0;
   {  // team size: rounds x (units per warp + the round's barrier and sum, about two thirds of a unit)
     const int G = nb_stream_ctas(), n_tiles = (N + 15) / 16;
     double best = 1e30;

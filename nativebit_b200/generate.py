@@ -336,6 +336,8 @@ class DecodeSession:
                  batch_gemm: bool = False, stream: bool | None = None, tile_gemv: bool | None = None, hand_head: bool = True):
         self.model, self.B = model, batch_size
         self.hand_head = hand_head            # False: the LM head of a single sequence stays a library GEMM (comparison)
+        self.residual_in_matvec = False       # True: out_proj and down add into the residual stream themselves (flag 4 of
+                                              # nb_gemv_stream) instead of the next norm prologue: bit-identical, measured neutral
         self.single_term = False              # True: activations enter the matvecs as one fp16 term: 7 % faster, but 4e-3 of
                                               # max |logit| away from the two-term step at 26 layers (the gate is 2e-3)
         self.swiglu_epilogue = True           # SwiGLU in gate_up's epilogue: down stages F values instead of 2F (costs a
@@ -414,6 +416,8 @@ class DecodeSession:
             xa.copy_(m.embedding[self.token[:, 0]])
         delta = None
         pending = False                                           # a pushed vector waits to be gathered
+        # one sequence on one rank: out_proj and down add their result to the residual stream themselves
+        inplace = self.tile_gemv and m.tp_size == 1 and xch is None and self.residual_in_matvec
 
         def norm_linear(lin, delta, w, out, swiglu=False):
             nonlocal xa, xb, pending
@@ -422,6 +426,9 @@ class DecodeSession:
                 ops.gemv_tp(ops.PRO_ADD_RMSNORM, xa, *args, xch, out=out, gather=True, norm_weight=w, eps=eps, x_out=xb)
                 xa, xb = xb, xa
                 pending = False
+            elif self.tile_gemv and inplace:                      # the residual stream was updated by the matvec before
+                ops.gemv_stream(ops.PRO_ADD_RMSNORM, xa, lin.stream_weight(1 if swiglu else 0), lin.bits, lin.out_features,
+                                lin.in_features, out, norm_weight=w, eps=eps, swiglu=swiglu, single_term=self.single_term)
             elif self.tile_gemv:
                 ops.gemv_stream(ops.PRO_ADD_RMSNORM, xa, lin.stream_weight(1 if swiglu else 0), lin.bits, lin.out_features,
                                 lin.in_features, out, delta=delta, norm_weight=w, eps=eps, x_out=xb, swiglu=swiglu,
@@ -445,6 +452,10 @@ class DecodeSession:
             if xch is not None:
                 ops.gemv_tp(prologue, x, *args, xch, push=True)
                 pending = True
+                return None
+            if self.tile_gemv and inplace:                        # x += W act(...): no delta vector, no add in the next norm
+                ops.gemv_stream(prologue, x, lin.stream_weight(), lin.bits, lin.out_features, lin.in_features, xa,
+                                single_term=self.single_term, accumulate=True)
                 return None
             if self.tile_gemv:
                 ops.gemv_stream(prologue, x, lin.stream_weight(), lin.bits, lin.out_features, lin.in_features, out,

@@ -200,13 +200,14 @@ def gemv_fused(prologue: int, x: torch.Tensor, packed: torch.Tensor, codebook: t
 
 def gemv_stream(prologue: int, x: torch.Tensor, w_stream: torch.Tensor, bits: int, n: int, k: int, out: torch.Tensor,
                 delta: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None, eps: float = 0.0,
-                x_out: torch.Tensor | None = None, swiglu: bool = False, single_term: bool = False) -> torch.Tensor:
+                x_out: torch.Tensor | None = None, swiglu: bool = False, single_term: bool = False,
+                accumulate: bool = False) -> torch.Tensor:
     """One packed matvec of a dependent chain over the stream-layout copy of the weights (nb_gemv_stream): out (n) fp32
     = W . act(x), act as in gemv_fused (PRO_NONE: x of any float type; PRO_ADD_RMSNORM / PRO_SILU_MUL: fp32).
     swiglu: W is a [gate | up] matrix packed with row_mode 1 and out receives the n / 2 values silu(gate) * up.
     single_term: fp32 activations enter the tensor cores rounded to one fp16 value (11 significant bits) instead of as
     two fp16 terms (22 bits): half the MMAs, an error of a few 1e-4 of max |y| per matvec (4e-3 of max |logit| through the
-    26-layer decoder)."""
+    26-layer decoder).  accumulate: out += W act(x) (the residual update of a block; not together with swiglu)."""
     _need_cuda(x, w_stream, out)
     cols = 2 * k if prologue == PRO_SILU_MUL else k
     n_out = n // 2 if swiglu else n
@@ -218,7 +219,7 @@ def gemv_stream(prologue: int, x: torch.Tensor, w_stream: torch.Tensor, bits: in
         _lib.check(_lib.lib().nb_gemv_stream(prologue, x.data_ptr(), _DTYPE[x.dtype], 0 if delta is None else delta.data_ptr(),
                                              0 if norm_weight is None else norm_weight.data_ptr(), float(eps),
                                              0 if x_out is None else x_out.data_ptr(), w_stream.data_ptr(), bits, n, k,
-                                             out.data_ptr(), (1 if swiglu else 0) | (2 if single_term else 0), _stream()),
+                                             out.data_ptr(), (1 if swiglu else 0) | (2 if single_term else 0) | (4 if accumulate else 0), _stream()),
                    "nb_gemv_stream")
     return out
 

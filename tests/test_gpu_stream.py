@@ -278,6 +278,15 @@ def test_chain_gemv_over_the_stream_layout(built_lib, bits, n, k):
         torch.cuda.synchronize()
         check(y, xt.double().cpu().numpy())
         assert torch.equal(y, y2)
+    # y += W x: the residual update inside the matvec
+    x32 = rng.standard_normal(k).astype(np.float32)
+    y0 = rng.standard_normal(n).astype(np.float32)
+    yacc = _cu(y0, dev).clone()
+    ops.gemv_stream(ops.PRO_NONE, _cu(x32, dev), w, bits, n, k, yacc, accumulate=True)
+    yplain = torch.empty(n, device=dev)
+    ops.gemv_stream(ops.PRO_NONE, _cu(x32, dev), w, bits, n, k, yplain)
+    torch.cuda.synchronize()
+    assert torch.equal(yacc, yplain + _cu(y0, dev))
     # residual add + RMSNorm
     h = rng.standard_normal(k).astype(np.float32)
     d = rng.standard_normal(k).astype(np.float32)
